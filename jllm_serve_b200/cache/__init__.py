@@ -1,0 +1,3 @@
+"""The cache manager: page pools, block tables, layer groups and state slots."""
+from .pages import PageBookkeepingError, PagePool, PoolExhausted, StateSlotPool
+from .manager import RELEASED, CacheManager, CacheNeed, FixedState, PagedKeysValues

@@ -1,0 +1,154 @@
+"""Builds the kernel library from the .cu files beside this file, in-tree, with nvcc for sm_100a.
+
+The library is compiled at the first call that needs it and again whenever a source, a
+header or a flag changes (a hash of all of them is kept beside the library). Each .cu
+file becomes one object, compiled in parallel; a line is printed when each finishes, so a
+first call in a fresh checkout shows progress. Nothing is written outside the build
+folder: `csrc/_build/` by default, or `$JLLM_B200_BUILD_DIR`, or a folder under the
+system's temporary directory if the tree is read-only.
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+CSRC = Path(__file__).resolve().parent
+LIB_NAME = "libjllm_b200.so"
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
+              "--expt-relaxed-constexpr"]
+_lock = threading.Lock()
+
+
+class BuildError(RuntimeError):
+    pass
+
+
+def find_nvcc() -> str:
+    for cand in (os.environ.get("JLLM_B200_NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and Path(cand).is_file():
+            return cand
+    raise BuildError("nvcc not found (looked at $JLLM_B200_NVCC, PATH and /usr/local/cuda/bin): "
+                     "the CUDA kernels cannot be built, and there is no other path")
+
+
+def sources() -> list:
+    return sorted(CSRC.glob("*.cu"))
+
+
+def _headers() -> list:
+    return sorted(list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")))
+
+
+def _fingerprint(nvcc: str) -> str:
+    h = hashlib.sha256()
+    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
+    h.update(nvcc.encode())
+    for p in sources() + _headers():
+        h.update(p.name.encode())
+        h.update(p.read_bytes())
+    return h.hexdigest()
+
+
+def build_dir() -> Path:
+    env = os.environ.get("JLLM_B200_BUILD_DIR")
+    if env:
+        d = Path(env)
+    else:
+        d = CSRC / "_build"
+    try:
+        d.mkdir(parents=True, exist_ok=True)
+        probe = d / f".write_probe_{os.getpid()}"
+        probe.write_text("")
+        probe.unlink()
+        return d
+    except OSError:
+        d = Path(tempfile.gettempdir()) / f"jllm_b200_build_{os.getuid()}"
+        d.mkdir(parents=True, exist_ok=True)
+        return d
+
+
+def _say(msg: str) -> None:
+    print(f"[jllm-b200 build] {msg}", file=sys.stderr, flush=True)
+
+
+def _compile_one(nvcc: str, src: Path, obj: Path, verbose: bool) -> str:
+    cmd = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+    if verbose:
+        cmd.insert(1, "-Xptxas")
+        cmd.insert(2, "-v")
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise BuildError(f"nvcc failed on {src.name}:\n{proc.stdout}\n{proc.stderr}")
+    return proc.stderr
+
+
+def ensure_built(force: bool = False, verbose: bool = False) -> Path:
+    """Returns the path of an up-to-date library, compiling it first if need be."""
+    with _lock:
+        nvcc = None
+        out_dir = build_dir()
+        lib, stamp = out_dir / LIB_NAME, out_dir / "stamp.json"
+        try:
+            nvcc = find_nvcc()
+        except BuildError:
+            if lib.is_file() and not force:
+                return lib  # a prebuilt library travels with the tree; without nvcc it cannot be checked
+            raise
+        want = _fingerprint(nvcc)
+        if not force and lib.is_file() and stamp.is_file():
+            try:
+                if json.loads(stamp.read_text()).get("fingerprint") == want:
+                    return lib
+            except (json.JSONDecodeError, OSError):
+                pass
+        srcs = sources()
+        _say(f"compiling {len(srcs)} CUDA files for sm_100a into {out_dir} (first call, or a source changed)")
+        t0 = time.time()
+        done = []
+        stop = threading.Event()
+
+        def heartbeat():
+            while not stop.wait(10.0):
+                _say(f"... still compiling, {len(done)}/{len(srcs)} files done after {time.time() - t0:.0f} s")
+
+        hb = threading.Thread(target=heartbeat, daemon=True)
+        hb.start()
+        logs = {}
+        try:
+            with ThreadPoolExecutor(max_workers=min(len(srcs), os.cpu_count() or 4)) as pool:
+                futures = {}
+                for s in srcs:
+                    obj = out_dir / (s.stem + ".o")
+                    futures[pool.submit(_compile_one, nvcc, s, obj, verbose)] = s
+                for fut, s in futures.items():
+                    logs[s.name] = fut.result()
+                    done.append(s)
+                    _say(f"compiled {s.name} ({len(done)}/{len(srcs)}, {time.time() - t0:.0f} s)")
+            tmp = out_dir / (LIB_NAME + f".tmp{os.getpid()}")
+            link = [nvcc, *ARCH_FLAGS, "-shared", "-o", str(tmp)] + [str(out_dir / (s.stem + ".o")) for s in srcs]
+            proc = subprocess.run(link, capture_output=True, text=True)
+            if proc.returncode != 0:
+                raise BuildError(f"linking {LIB_NAME} failed:\n{proc.stdout}\n{proc.stderr}")
+            os.replace(tmp, lib)
+            stamp.write_text(json.dumps({"fingerprint": want, "seconds": round(time.time() - t0, 1)}))
+        finally:
+            stop.set()
+        _say(f"built {lib.name} in {time.time() - t0:.0f} s")
+        if verbose:
+            for name, log in logs.items():
+                print(f"---- {name}\n{log}", file=sys.stderr)
+        return lib
+
+
+if __name__ == "__main__":
+    print(ensure_built(force="--force" in sys.argv, verbose="-v" in sys.argv))

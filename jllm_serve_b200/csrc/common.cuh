@@ -1,0 +1,96 @@
+// Shared pieces of the sm_100a kernels: element types, error reporting, block reductions.
+//
+// Every exported launcher returns 0 on success and a non-zero code otherwise; the text of the
+// last error of the calling thread is read with jllm_last_error(). Launchers never allocate:
+// the caller passes inputs, outputs and (where a kernel needs it) scratch memory.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+#define JLLM_EXPORT extern "C" __attribute__((visibility("default")))
+
+enum JllmDtype : int { JLLM_F32 = 0, JLLM_BF16 = 1 };
+
+enum JllmError : int {
+    JLLM_OK = 0,
+    JLLM_BAD_ARGUMENT = 1,   // a size or option the kernels refuse
+    JLLM_CUDA_ERROR = 2,     // a CUDA call failed
+    JLLM_UNSUPPORTED = 3,    // a combination that is not built
+};
+
+int jllm_fail(int code, const char* fmt, ...);
+int jllm_check_launch(const char* what);
+
+#define JLLM_REQUIRE(cond, ...)                                   \
+    do {                                                          \
+        if (!(cond)) return jllm_fail(JLLM_BAD_ARGUMENT, __VA_ARGS__); \
+    } while (0)
+
+// ---- element access: everything is computed in float -------------------------------------------------
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// A vector (gain, bias) whose stored type is known only at run time.
+struct VecRef {
+    const void* p;
+    int dtype;
+    __device__ __forceinline__ float operator[](int i) const {
+        return dtype == JLLM_F32 ? static_cast<const float*>(p)[i]
+                                 : __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+    }
+};
+
+// ---- reductions with a fixed order: the result of a row never depends on what else is in the batch ----
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result. `scratch` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < warps ? scratch[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < warps ? scratch[lane] : -INFINITY;
+        t = warp_max(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}

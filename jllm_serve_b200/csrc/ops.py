@@ -1,0 +1,156 @@
+"""Python face of the kernel library: loads it (building it first if need be) and wraps each launcher.
+
+The launchers are plain C functions taking device pointers, sizes and a stream; tensors are
+torch tensors used as typed device memory only. There is no other implementation behind
+these functions: without the library or without a B200 they raise.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_double, c_float, c_int, c_void_p
+
+import torch
+
+from .build import ensure_built
+
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_lib = None
+_device_ok = False
+
+
+def library():
+    global _lib
+    if _lib is None:
+        path = ensure_built()
+        lib = ctypes.CDLL(str(path))
+        lib.jllm_last_error.restype = c_char_p
+        for name in dir(_Signatures):
+            if name.startswith("jllm_"):
+                fn = getattr(lib, name)
+                fn.argtypes = getattr(_Signatures, name)
+                fn.restype = c_int
+        _lib = lib
+    return _lib
+
+
+def require_device() -> None:
+    """Raises unless a B200 is current and the library can run on it."""
+    global _device_ok
+    if _device_ok:
+        return
+    if not torch.cuda.is_available():
+        raise KernelError("no CUDA device: this engine runs on a B200 (sm_100a) only, it has no CPU path")
+    _call("jllm_check_device")
+    _device_ok = True
+
+
+def _call(name, *args):
+    lib = library()
+    code = getattr(lib, name)(*args)
+    if code != 0:
+        raise KernelError(f"{name} failed ({code}): {lib.jllm_last_error().decode(errors='replace')}")
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t):
+    return 0 if t is None else t.data_ptr()
+
+
+class _Signatures:
+    P, I, F = c_void_p, c_int, c_float
+    jllm_check_device = []
+    jllm_embed_rows = [P, P, I, P, I, I, I, P]
+    jllm_rmsnorm = [P, P, I, P, I, P, I, I, F, P]
+    jllm_swiglu = [P, P, I, I, I, P]
+    jllm_qk_norm_rope_store = [P, I, P, P, I, I, F, P, P, I, P, P, P, P, I, I, I, I, I, I, I, P]
+    jllm_gemm_plain = [P, I, I, P, I, P, I, P, I, I, I, I, I, I, P]
+    jllm_attention_plain = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P]
+    jllm_argmax = [P, I, I, I, P, P]
+    jllm_sample = [P, I, I, I, P, P, P, P, P, P, P]
+
+
+# ---------------------------------------------------------------------------------------------------------
+
+def embed_rows(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = table[ids[r]] as float32; ids int32 [rows]."""
+    assert ids.dtype == torch.int32 and out.dtype == torch.float32 and table.dim() == 2
+    _call("jllm_embed_rows", ids.data_ptr(), table.data_ptr(), _DT[table.dtype], out.data_ptr(), ids.numel(),
+          table.shape[1], table.shape[0], _stream())
+
+
+def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor, row_index: torch.Tensor | None = None,
+            rows: int | None = None) -> None:
+    """out[r] = rmsnorm(x[row_index[r] or r]) * gain; x float32 [*, dim]; out float32 or bfloat16."""
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()
+    n = (row_index.numel() if row_index is not None else x.shape[0]) if rows is None else rows
+    _call("jllm_rmsnorm", x.data_ptr(), gain.data_ptr(), _DT[gain.dtype], out.data_ptr(), _DT[out.dtype],
+          _p(row_index), n, x.shape[-1], float(eps), _stream())
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r, j] = silu(gate_up[r, j]) * gate_up[r, hidden + j]."""
+    assert gate_up.dtype == out.dtype and gate_up.is_contiguous() and out.is_contiguous()
+    _call("jllm_swiglu", gate_up.data_ptr(), out.data_ptr(), _DT[out.dtype], out.shape[0], out.shape[1], _stream())
+
+
+def qk_norm_rope_store(qkv, q_gain, k_gain, eps, cos, sin, rotary_dim, positions, slots, k_cache, v_cache,
+                       heads, kv_heads, head_dim, page_size, write_kv=True) -> None:
+    """In place on the queries of qkv [rows, stride]; keys and values go to the cache rows `slots`."""
+    use_norm = q_gain is not None
+    _call("jllm_qk_norm_rope_store", qkv.data_ptr(), _DT[qkv.dtype], _p(q_gain), _p(k_gain),
+          _DT[q_gain.dtype] if use_norm else F32, int(use_norm), float(eps), _p(cos), _p(sin), int(rotary_dim),
+          positions.data_ptr(), _p(slots), _p(k_cache), _p(v_cache), int(write_kv), qkv.shape[0], qkv.stride(0),
+          heads, kv_heads, head_dim, page_size, _stream())
+
+
+def gemm_plain(a, w, out, bias=None, accumulate=False) -> None:
+    """out (+)= a @ w.T (+ bias) on the CUDA cores with float32 accumulation in ascending k."""
+    assert a.dtype == w.dtype and a.stride(-1) == 1 and w.stride(-1) == 1 and out.stride(-1) == 1
+    _call("jllm_gemm_plain", a.data_ptr(), _DT[a.dtype], a.stride(0), w.data_ptr(), w.stride(0), _p(bias),
+          _DT[bias.dtype] if bias is not None else F32, out.data_ptr(), _DT[out.dtype], out.stride(0),
+          int(accumulate), a.shape[0], w.shape[0], a.shape[1], _stream())
+
+
+def attention_plain(q, q_stride, k_cache, v_cache, out, row_seg, row_pos, block_tables, rows, heads, kv_heads,
+                    head_dim, page_size, window, scale) -> None:
+    _call("jllm_attention_plain", q.data_ptr(), q_stride, k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+          out.stride(0), row_seg.data_ptr(), row_pos.data_ptr(), block_tables.data_ptr(), block_tables.stride(0),
+          rows, heads, kv_heads, head_dim, page_size, int(window), float(scale), _DT[q.dtype], _stream())
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor, vocab: int | None = None) -> None:
+    assert logits.dtype == torch.float32 and out.dtype == torch.int32
+    _call("jllm_argmax", logits.data_ptr(), logits.stride(0), logits.shape[0], vocab or logits.shape[1],
+          out.data_ptr(), _stream())
+
+
+def sample(logits, temperature, top_k, top_p, min_p, uniform, out, vocab: int | None = None) -> None:
+    assert logits.dtype == torch.float32 and uniform.dtype == torch.float64 and out.dtype == torch.int32
+    _call("jllm_sample", logits.data_ptr(), logits.stride(0), logits.shape[0], vocab or logits.shape[1],
+          temperature.data_ptr(), top_k.data_ptr(), top_p.data_ptr(), min_p.data_ptr(), uniform.data_ptr(),
+          out.data_ptr(), _stream())
+
+
+def gemm_bf16_fits(a, w, out) -> bool:
+    """Whether the tensor-core kernels take this product; otherwise the CUDA-core kernel runs it."""
+    return False
+
+
+def gemm_bf16(a, w, out, bias=None, accumulate=False) -> None:
+    raise KernelError("the tensor-core matrix product is not built for this shape")
+
+
+def attention(q, k_cache, v_cache, out, batch, group, heads, kv_heads, head_dim, page_size, window, scale) -> None:
+    """Causal attention of every row of the batch over its own request's cached keys and values."""
+    attention_plain(q, q.stride(0), k_cache, v_cache, out, batch.row_seg, batch.positions, batch.block_tables[group],
+                    batch.rows, heads, kv_heads, head_dim, page_size, window, scale)

@@ -1,0 +1,180 @@
+// Row-wise kernels: embedding gather, RMSNorm, SwiGLU, and the fused per-head q/k RMSNorm +
+// rotary position encoding + write of keys and values into the paged cache.
+//
+// All arithmetic is 32-bit float whatever the storage type; each row's result depends on that row
+// alone (fixed reduction order), so it is the same in any batch.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------------------------
+// x[r, :] = table[ids[r], :]  (float residual stream from a float or bfloat16 table)
+// ---------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_rows_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ x,
+                                  int dim, int vocab) {
+    const int r = blockIdx.x;
+    int id = ids[r];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // ids are validated on the host; never read out of bounds
+    const T* src = table + (size_t)id * dim;
+    float* dst = x + (size_t)r * dim;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) dst[i] = to_float(src[i]);
+}
+
+JLLM_EXPORT int jllm_embed_rows(const int* ids, const void* table, int table_dtype, float* x, int rows, int dim,
+                                int vocab, cudaStream_t stream) {
+    JLLM_REQUIRE(rows >= 0 && dim > 0 && vocab > 0, "embed_rows: rows=%d dim=%d vocab=%d", rows, dim, vocab);
+    if (rows == 0) return JLLM_OK;
+    if (table_dtype == JLLM_F32)
+        embed_rows_kernel<float><<<rows, 256, 0, stream>>>(ids, (const float*)table, x, dim, vocab);
+    else
+        embed_rows_kernel<__nv_bfloat16><<<rows, 256, 0, stream>>>(ids, (const __nv_bfloat16*)table, x, dim, vocab);
+    return jllm_check_launch("embed_rows");
+}
+
+// ---------------------------------------------------------------------------------------------------
+// RMSNorm: out[r] = (x[src(r)] * (1 / sqrt(mean(x^2) + eps))) * gain, src(r) = row_index ? row_index[r] : r
+// The scale is taken in double from a float mean, as the reference does.
+// ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float rms_scale(float sum_squares, int n, float eps) {
+    const float mean = sum_squares / (float)n + eps;
+    return (float)(1.0 / sqrt((double)mean));
+}
+
+template <typename Tout>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, VecRef gain, Tout* __restrict__ out,
+                               const int* __restrict__ row_index, int dim, float eps) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const float* src = x + (size_t)(row_index ? row_index[r] : r) * dim;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float v = src[i];
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float s = rms_scale(ss, dim, eps);
+    Tout* dst = out + (size_t)r * dim;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) dst[i] = from_float<Tout>(__fmul_rn(__fmul_rn(src[i], s), gain[i]));
+}
+
+JLLM_EXPORT int jllm_rmsnorm(const float* x, const void* gain, int gain_dtype, void* out, int out_dtype,
+                             const int* row_index, int rows, int dim, float eps, cudaStream_t stream) {
+    JLLM_REQUIRE(rows >= 0 && dim > 0, "rmsnorm: rows=%d dim=%d", rows, dim);
+    if (rows == 0) return JLLM_OK;
+    const VecRef g{gain, gain_dtype};
+    const int threads = dim >= 2048 ? 512 : 256;
+    if (out_dtype == JLLM_F32)
+        rmsnorm_kernel<float><<<rows, threads, 0, stream>>>(x, g, (float*)out, row_index, dim, eps);
+    else
+        rmsnorm_kernel<__nv_bfloat16><<<rows, threads, 0, stream>>>(x, g, (__nv_bfloat16*)out, row_index, dim, eps);
+    return jllm_check_launch("rmsnorm");
+}
+
+// ---------------------------------------------------------------------------------------------------
+// SwiGLU: h[r, j] = silu(gate_up[r, j]) * gate_up[r, hidden + j],  silu(g) = g / (1 + exp(-g))
+// ---------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ h, int hidden, size_t total) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / hidden, j = i - r * hidden;
+        const float g = to_float(gate_up[r * 2 * hidden + j]);
+        const float u = to_float(gate_up[r * 2 * hidden + hidden + j]);
+        h[i] = from_float<T>(__fmul_rn(g / (1.f + expf(-g)), u));
+    }
+}
+
+JLLM_EXPORT int jllm_swiglu(const void* gate_up, void* h, int dtype, int rows, int hidden, cudaStream_t stream) {
+    JLLM_REQUIRE(rows >= 0 && hidden > 0, "swiglu: rows=%d hidden=%d", rows, hidden);
+    if (rows == 0) return JLLM_OK;
+    const size_t total = (size_t)rows * hidden;
+    const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+    if (dtype == JLLM_F32)
+        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)h, hidden, total);
+    else
+        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)h, hidden, total);
+    return jllm_check_launch("swiglu");
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Per (row, head): optional RMSNorm over the head, rotate-half RoPE over the first rotary_dim values,
+// then queries go back in place and keys / values go into the paged cache.
+//
+// qkv is [rows, row_stride] with queries, keys, values side by side ((heads + 2 kv_heads) * head_dim values;
+// heads * head_dim when the run reads another run's cache and writes no keys or values). The cache of one layer run is
+// K[pages, kv_heads, page_size, head_dim] and V alike; row r is written at slot[r] = page * page_size + offset.
+// cos/sin are [positions, rotary_dim / 2] float tables (angles made in double on the host).
+// ---------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, VecRef q_gain, VecRef k_gain, int use_norm, float eps,
+                                          const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                          int rotary_dim, const int* __restrict__ positions,
+                                          const int* __restrict__ slots, T* __restrict__ k_cache,
+                                          T* __restrict__ v_cache, int heads, int kv_heads, int head_dim,
+                                          int page_size, int row_stride) {
+    extern __shared__ float vec[];  // head_dim floats + 33 scratch
+    float* scratch = vec + head_dim;
+    const int r = blockIdx.x, h = blockIdx.y;
+    T* src = qkv + (size_t)r * row_stride + (size_t)h * head_dim;
+    const bool is_q = h < heads, is_k = !is_q && h < heads + kv_heads;
+    for (int i = threadIdx.x; i < head_dim; i += blockDim.x) vec[i] = to_float(src[i]);
+    __syncthreads();
+    if (is_q || is_k) {
+        if (use_norm) {
+            float ss = 0.f;
+            for (int i = threadIdx.x; i < head_dim; i += blockDim.x) ss = fmaf(vec[i], vec[i], ss);
+            ss = block_sum(ss, scratch);
+            const float s = rms_scale(ss, head_dim, eps);
+            const VecRef g = is_q ? q_gain : k_gain;
+            for (int i = threadIdx.x; i < head_dim; i += blockDim.x) vec[i] = __fmul_rn(__fmul_rn(vec[i], s), g[i]);
+            __syncthreads();
+        }
+        if (rotary_dim > 0) {
+            const int half = rotary_dim >> 1;
+            const float* c = cos_t + (size_t)positions[r] * half;
+            const float* s = sin_t + (size_t)positions[r] * half;
+            for (int i = threadIdx.x; i < half; i += blockDim.x) {
+                const float a = vec[i], b = vec[i + half];
+                vec[i] = __fsub_rn(__fmul_rn(a, c[i]), __fmul_rn(b, s[i]));
+                vec[i + half] = __fadd_rn(__fmul_rn(b, c[i]), __fmul_rn(a, s[i]));
+            }
+            __syncthreads();
+        }
+    }
+    if (is_q) {
+        for (int i = threadIdx.x; i < head_dim; i += blockDim.x) src[i] = from_float<T>(vec[i]);
+    } else {
+        const int kvh = is_k ? h - heads : h - heads - kv_heads;
+        const int slot = slots[r];
+        const size_t page = slot / page_size, off = slot % page_size;
+        T* dst = (is_k ? k_cache : v_cache) + ((page * kv_heads + kvh) * page_size + off) * head_dim;
+        for (int i = threadIdx.x; i < head_dim; i += blockDim.x) dst[i] = from_float<T>(vec[i]);
+    }
+}
+
+JLLM_EXPORT int jllm_qk_norm_rope_store(void* qkv, int dtype, const void* q_gain, const void* k_gain, int gain_dtype,
+                                        int use_norm, float eps, const float* cos_t, const float* sin_t,
+                                        int rotary_dim, const int* positions, const int* slots, void* k_cache,
+                                        void* v_cache, int write_kv, int rows, int row_stride, int heads, int kv_heads,
+                                        int head_dim, int page_size, cudaStream_t stream) {
+    JLLM_REQUIRE(rows >= 0 && heads > 0 && kv_heads > 0 && head_dim > 0 && page_size > 0,
+                 "qk_norm_rope_store: rows=%d heads=%d kv_heads=%d head_dim=%d page_size=%d", rows, heads, kv_heads,
+                 head_dim, page_size);
+    JLLM_REQUIRE(rotary_dim >= 0 && rotary_dim % 2 == 0 && rotary_dim <= head_dim,
+                 "qk_norm_rope_store: rotary_dim=%d must be even and at most head_dim=%d", rotary_dim, head_dim);
+    JLLM_REQUIRE(row_stride >= (write_kv ? heads + 2 * kv_heads : heads) * head_dim,
+                 "qk_norm_rope_store: row_stride=%d is too small", row_stride);
+    JLLM_REQUIRE(head_dim <= 8192, "qk_norm_rope_store: head_dim=%d is above 8192", head_dim);
+    if (rows == 0) return JLLM_OK;
+    const dim3 grid(rows, write_kv ? heads + 2 * kv_heads : heads);
+    const int threads = head_dim <= 64 ? 32 : (head_dim <= 128 ? 64 : 128);
+    const size_t smem = (head_dim + 33) * sizeof(float);
+    const VecRef qg{q_gain, gain_dtype}, kg{k_gain, gain_dtype};
+    if (dtype == JLLM_F32)
+        qk_norm_rope_store_kernel<float><<<grid, threads, smem, stream>>>(
+            (float*)qkv, qg, kg, use_norm, eps, cos_t, sin_t, rotary_dim, positions, slots, (float*)k_cache,
+            (float*)v_cache, heads, kv_heads, head_dim, page_size, row_stride);
+    else
+        qk_norm_rope_store_kernel<__nv_bfloat16><<<grid, threads, smem, stream>>>(
+            (__nv_bfloat16*)qkv, qg, kg, use_norm, eps, cos_t, sin_t, rotary_dim, positions, slots,
+            (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, heads, kv_heads, head_dim, page_size, row_stride);
+    return jllm_check_launch("qk_norm_rope_store");
+}

@@ -1,0 +1,40 @@
+// Error reporting of the kernel library, and what the host asks about the device.
+#include "common.cuh"
+
+#include <cstring>
+
+namespace {
+thread_local char g_error[1024] = "";
+}
+
+int jllm_fail(int code, const char* fmt, ...) {
+    va_list args;
+    va_start(args, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, args);
+    va_end(args);
+    return code;
+}
+
+int jllm_check_launch(const char* what) {
+    const cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) return JLLM_OK;
+    return jllm_fail(JLLM_CUDA_ERROR, "%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
+}
+
+JLLM_EXPORT const char* jllm_last_error() { return g_error; }
+
+// The library is built for one architecture only. Returns 0 if the current device can run it.
+JLLM_EXPORT int jllm_check_device() {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return jllm_fail(JLLM_CUDA_ERROR, "no CUDA device: %s", cudaGetErrorString(e));
+    cudaDeviceProp prop;
+    e = cudaGetDeviceProperties(&prop, dev);
+    if (e != cudaSuccess) return jllm_fail(JLLM_CUDA_ERROR, "cudaGetDeviceProperties: %s", cudaGetErrorString(e));
+    if (prop.major != 10)
+        return jllm_fail(JLLM_UNSUPPORTED, "the kernels are built for sm_100a (B200); device %d is %s, sm_%d%d", dev,
+                         prop.name, prop.major, prop.minor);
+    return JLLM_OK;
+}
+
+JLLM_EXPORT int jllm_abi_version() { return 1; }

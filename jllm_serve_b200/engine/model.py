@@ -1,0 +1,97 @@
+"""The generic decoder: embedding, the scheduled layer runs, final norm and head, built from parts.
+
+The model is what a registry entry builds from a `Decoder` spec. It knows the order of
+layer runs (data: `spec.schedule`), hands every run the cache it reads or writes, and
+computes logits only for the rows that were asked for, as the reference does
+(src/main/java/org/robomiri/jllm/cpu/CpuBackend.java:895-928,980-985). The head is the
+embedding when `tie_word_embeddings` is set, else `lm_head.weight`, which must then exist
+(model/ModelWeights.java:37).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..config.specs import Decoder
+from ..csrc import ops
+from ..parts import Linear, RunCache, Runtime, part_class
+from ..weights.loader import TensorWant
+
+
+class DecoderModel:
+    def __init__(self, spec: Decoder, tensors: Dict[str, torch.Tensor], runtime: Runtime):
+        self.spec, self.rt = spec, runtime
+        core, names = spec.core, spec.names
+        tensors = dict(tensors)
+        self.embedding = tensors.pop(names.embedding)
+        head = self.embedding if core.tied else tensors.pop(names.head)
+        self.head = Linear(head)
+        self.position_encodings = [part_class("position", "rotary")(t, runtime.max_positions, runtime.device)
+                                   for t in spec.rope_tables]
+        self.blocks = []
+        for l, layer in enumerate(spec.layers):
+            cls = part_class("block", layer.arrangement)
+            self.blocks.append(cls(layer, core.dim, tensors, names.layer.format(l), runtime, self.position_encodings))
+        self.final_norm = part_class("norm", spec.final_norm.kind)(spec.final_norm, core.dim, tensors,
+                                                                   names.final_norm, runtime)
+        self.vocab, self.dim = core.vocab, core.dim
+
+    @classmethod
+    def wants(cls, spec: Decoder) -> Dict[str, TensorWant]:
+        core, names = spec.core, spec.names
+        out = {names.embedding: TensorWant((core.vocab, core.dim))}
+        if not core.tied:
+            out[names.head] = TensorWant((core.vocab, core.dim))
+        for l, layer in enumerate(spec.layers):
+            out.update(part_class("block", layer.arrangement).wants(layer, core.dim, names.layer.format(l)))
+        out.update(part_class("norm", spec.final_norm.kind).wants(spec.final_norm, core.dim, names.final_norm))
+        return out
+
+    def cache_needs(self) -> List[Optional[object]]:
+        """One entry per scheduled run: what it keeps between steps (None if it reads another run's cache)."""
+        needs = []
+        for run in self.spec.schedule:
+            mixer = self.spec.layers[run.layer].mixer
+            needs.append(None if run.cache_of is not None else part_class("mixer", mixer.kind).cache_need(mixer))
+        return needs
+
+    def _run_cache(self, cache, i: int) -> RunCache:
+        run = self.spec.schedule[i]
+        owner = i if run.cache_of is None else run.cache_of
+        kind, group = cache.group_of_run.get(owner, (None, -1))
+        if kind == "paged":
+            k, v = cache.keys_values(owner)
+            return RunCache(owner, run.cache_of is None, group, k, v)
+        if kind == "fixed":
+            return RunCache(owner, run.cache_of is None, -1, state=cache.state(owner))
+        return RunCache(owner, run.cache_of is None)
+
+    def forward(self, batch, cache, logits_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Runs the batch's rows through every scheduled layer; returns float32 logits [wanted rows, vocab]."""
+        rows = batch.rows
+        x = self.rt.buffer("residual", self.dim, torch.float32)[:rows]
+        ops.embed_rows(batch.token_ids, self.embedding, x)
+        for pe in self.position_encodings:
+            pe.on_embedding(x, batch)
+        for i, run in enumerate(self.spec.schedule):
+            self.blocks[run.layer].forward(x, batch, self._run_cache(cache, i))
+        n = batch.num_wanted
+        if logits_out is None:
+            logits_out = torch.empty((n, self.vocab), dtype=torch.float32, device=self.rt.device)
+        if n == 0:
+            return logits_out[:0]
+        hb = self.rt.buffer("head_in", self.dim)[:n]
+        self.final_norm.forward(x, hb, row_index=batch.logit_rows, rows=n)
+        self.head.forward(hb, logits_out[:n])
+        return logits_out[:n]
+
+
+def build_model(entry, spec, tensors, runtime):
+    """What the registry's entry builds: its own builder, else the generic decoder."""
+    return (entry.build or DecoderModel)(spec, tensors, runtime)
+
+
+def model_wants(entry, spec) -> Dict[str, TensorWant]:
+    builder = entry.build or DecoderModel
+    return builder.wants(spec)

@@ -1,0 +1,184 @@
+"""The step function: a batch of (request, its next tokens) in, logits at the wanted places out.
+
+`ModelRunner` ties the model, the cache manager and the batch tables together. One call of
+`step` runs exactly the tokens it is given, as one batch, on top of what earlier steps left
+in the cache; prompt portions and single decoded tokens ride together (the reference's
+`forwardMixed`, src/main/java/org/robomiri/jllm/cpu/CpuBackend.java:821-930). Generation,
+trace replay, the benchmark and the tests all go through this one function.
+"""
+from __future__ import annotations
+
+import json
+from pathlib import Path
+from typing import Hashable, List, Optional, Sequence
+
+import torch
+
+from ..cache import CacheManager, PoolExhausted
+from ..config.registry import architecture_entry, load_config, parse_config
+from ..csrc import ops
+from ..parts import Runtime
+from ..weights import TensorSource, convert_checked, load_checked, random_tensors
+from .batch import BatchBuilder, Segment, StepBatch
+from .model import build_model, model_wants
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+
+
+def _as_dtype(dtype) -> torch.dtype:
+    if isinstance(dtype, torch.dtype):
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"dtype {dtype} is not built (bfloat16 or float32)")
+        return dtype
+    if dtype not in DTYPES:
+        raise ValueError(f"dtype {dtype!r} is not built (bfloat16 or float32)")
+    return DTYPES[dtype]
+
+
+class ModelRunner:
+    def __init__(self, model_dir=None, *, config: Optional[dict] = None, seed: Optional[int] = None,
+                 dtype="bfloat16", device="cuda:0", page_size: int = 16, num_pages: Optional[int] = None,
+                 max_tokens: Optional[int] = None, max_batch_tokens: int = 2048, max_requests: int = 64,
+                 ctx: Optional[int] = None, schedule=None, poison_freed_pages: bool = False):
+        """Either `model_dir` (config.json + model.safetensors) or `config` + `seed` (random weights made on
+        the device). The pool holds `num_pages` pages per group, or enough for `max_tokens` cached tokens."""
+        ops.require_device()
+        self.device = torch.device(device)
+        torch.cuda.set_device(self.device)
+        self.dtype = _as_dtype(dtype)
+        if model_dir is not None:
+            spec, raw = load_config(model_dir)
+        elif config is not None:
+            spec, raw = parse_config(config), config
+        else:
+            raise ValueError("a model folder, or a config and a seed, is needed")
+        if schedule is not None:
+            spec = spec.with_schedule(schedule)
+        self.spec, self.config = spec, raw
+        entry = architecture_entry(raw["model_type"])
+        self.ctx = int(ctx or spec.core.max_positions)
+        self.page_size = int(page_size)
+        self.max_rows = int(max_batch_tokens)
+        self.max_requests = int(max_requests)
+        rt = Runtime(self.device, self.dtype, self.ctx, self.max_rows, self.page_size)
+        wants = model_wants(entry, spec)
+        self.notes: List[str] = []
+        if model_dir is not None:
+            tensors = load_checked(TensorSource(model_dir), wants, self.dtype, self.device, self.notes)
+        else:
+            made = random_tensors(wants, 0 if seed is None else seed, self.device, torch.bfloat16)
+            tensors = convert_checked(made, wants, self.dtype, self.device)
+            del made
+        self.model = build_model(entry, spec, tensors, rt)
+        del tensors
+        self.runtime = rt
+        self.vocab = spec.core.vocab
+        if num_pages is None:
+            tokens = max_tokens if max_tokens is not None else self.ctx * min(self.max_requests, 4)
+            num_pages = max(1, -(-int(tokens) // self.page_size))
+        self.poison = poison_freed_pages
+        self.cache = CacheManager(self.model.cache_needs(), self.page_size, int(num_pages), self.max_requests,
+                                  allocate=self._allocate)
+        max_blocks = -(-self.ctx // self.page_size)
+        self.builder = BatchBuilder(self.device, self.max_rows, self.max_requests, max_blocks, len(self.cache.paged),
+                                    self.page_size)
+        self.steps = 0
+
+    def _allocate(self, shape, kind):
+        if kind == "kv":
+            t = torch.empty(shape, dtype=self.dtype, device=self.device)
+            t.fill_(float("nan")) if self.poison else t.zero_()
+            return t
+        return torch.zeros(shape, dtype=getattr(torch, kind), device=self.device)
+
+    # ---- the step -----------------------------------------------------------------------------------------
+    def step(self, segments: Sequence[Segment], logits_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Runs the segments as one batch; returns float32 logits [wanted places, vocab] on the device, in
+        the order of the segments and of each segment's `want`."""
+        segments = list(segments)
+        if sum(len(s.tokens) for s in segments) > self.max_rows:
+            return self._step_in_parts(segments, logits_out)
+        return self._step_once(segments, logits_out)
+
+    def _step_in_parts(self, segments, logits_out):
+        """More rows than one batch holds: the same tokens as several batches, one after the other. The
+        logits come back in the order that was asked for."""
+        wanted = sum(len(s.want) for s in segments)
+        out = logits_out[:wanted] if logits_out is not None else \
+            torch.empty((wanted, self.vocab), dtype=torch.float32, device=self.device)
+        parts, room, order = [[]], self.max_rows, [[]]
+        k = 0
+        for seg in segments:
+            places = {}
+            for w in seg.want:
+                places.setdefault(w, []).append(k)
+                k += 1
+            lo = 0
+            while lo < len(seg.tokens):
+                if room == 0:
+                    parts.append([])
+                    order.append([])
+                    room = self.max_rows
+                n = min(room, len(seg.tokens) - lo)
+                want = [w - lo for w in sorted(places) if lo <= w < lo + n for _ in places[w]]
+                order[-1].extend(i for w in sorted(places) if lo <= w < lo + n for i in places[w])
+                parts[-1].append(Segment(seg.request, seg.tokens[lo:lo + n], seg.start + lo, want))
+                lo += n
+                room -= n
+        for part, idx in zip(parts, order):
+            logits = self._step_once(part, None)
+            if idx:
+                out[torch.tensor(idx, device=self.device)] = logits
+        return out
+
+    def _step_once(self, segments, logits_out):
+        opened, reserved = [], []
+        try:
+            for seg in segments:
+                if seg.start + len(seg.tokens) > self.ctx:
+                    raise ValueError(f"request {seg.request!r}: position {seg.start + len(seg.tokens)} is beyond "
+                                     f"the context of {self.ctx}")
+                if not self.cache.is_open(seg.request):
+                    self.cache.open(seg.request)
+                    opened.append(seg.request)
+                self.cache.reserve(seg.request, seg.start, len(seg.tokens))
+                reserved.append(seg.request)
+            batch = self.builder.build(segments, self.cache, self.vocab)
+        except Exception:
+            for r in reserved:
+                self.cache.trim(r)
+            for r in opened:
+                self.cache.close(r)
+            raise
+        logits = self.model.forward(batch, self.cache, logits_out)
+        for seg in segments:
+            released = self.cache.commit(seg.request, seg.start + len(seg.tokens))
+            if self.poison:
+                self._poison(released)
+        self.steps += 1
+        self.last_batch = batch
+        return logits
+
+    def finish(self, request: Hashable) -> None:
+        """The request is over: everything it holds is given back."""
+        if not self.cache.is_open(request):
+            return
+        if self.poison:
+            rc = self.cache.requests[request]
+            held = [(g, p) for g in range(len(self.cache.paged)) for p in rc.tables[g] if p >= 0]
+            self.cache.close(request)
+            self._poison(held)
+        else:
+            self.cache.close(request)
+
+    def _poison(self, pages) -> None:
+        """Testing aid: a page that was given back is filled with NaN, so a kernel that reads a page its
+        request does not hold (or a row that was never written) shows in the logits."""
+        for g, page in pages:
+            self.cache.paged[g].storage[:, :, page].fill_(float("nan"))
+
+    def describe(self) -> str:
+        core = self.spec.core
+        return (f"{core.description} | dtype={str(self.dtype).replace('torch.', '')} ctx={self.ctx} "
+                f"page={self.page_size} pages={self.cache.num_pages} groups={len(self.cache.paged)} "
+                f"max_batch_tokens={self.max_rows}")

@@ -1,0 +1,143 @@
+"""The engine against the plain implementation under every way of cutting the work (GPU)."""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from tests import traces
+from tests.helpers import compare_with_plain, model_folder, replay, requests_for
+from tests.tiny import CONFIGS
+
+pytestmark = pytest.mark.gpu
+
+ROOT = Path(__file__).resolve().parent.parent
+LENGTHS = {"A": (5, 17, 33, 70), "B": (1, 7, 64, 129), "C": (3, 50, 97, 130)}
+PAGE = {"A": 4, "B": 8, "C": 16}
+
+
+def make_runner(name, dtype, steps=None, **kw):
+    from jllm_serve_b200.engine import ModelRunner
+    page = kw.pop("page_size", PAGE[name])
+    tokens = traces.peak_tokens(steps, 64) if steps is not None else 1024
+    return ModelRunner(model_folder(name), dtype=dtype, page_size=page, num_pages=-(-tokens // page),
+                       max_batch_tokens=kw.pop("max_batch_tokens", 512), max_requests=8, ctx=512,
+                       poison_freed_pages=True, **kw)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_whole_requests(name, dtype):
+    reqs = requests_for(name, LENGTHS[name])
+    steps = traces.whole(reqs)
+    got = replay(make_runner(name, dtype, steps), steps)
+    compare_with_plain(got, model_folder(name), reqs, dtype, what=f"{name} whole")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_last_32_tokens_one_by_one(name, dtype):
+    reqs = requests_for(name, LENGTHS[name])
+    steps = traces.prompt_then_decode(reqs, 32)
+    got = replay(make_runner(name, dtype, steps), steps)
+    compare_with_plain(got, model_folder(name), reqs, dtype, what=f"{name} decode tail")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_portions_of_changing_size(name, dtype):
+    reqs = requests_for(name, LENGTHS[name])
+    steps = traces.changing_portions(reqs)
+    got = replay(make_runner(name, dtype, steps), steps)
+    compare_with_plain(got, model_folder(name), reqs, dtype, what=f"{name} portions")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_mixed_batches_with_pages_used_again(name, dtype):
+    reqs = requests_for(name, LENGTHS[name] + (41, 90, 12), seed=23)
+    steps = traces.mixed(reqs, max_live=4)
+    runner = make_runner(name, dtype, steps)
+    got = replay(runner, steps)
+    compare_with_plain(got, model_folder(name), reqs, dtype, what=f"{name} mixed")
+    assert all(g.pool.reuses > 0 for g in runner.cache.paged), "the pool was so large that no page was used again"
+    assert all(g.pool.num_free == g.pool.num_pages for g in runner.cache.paged), "pages were not all given back"
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_float32_cuts_agree_bit_for_bit(name):
+    """In float32 every row's arithmetic is independent of the batch it rides in, so all ways of cutting
+    give the same bits on one device."""
+    reqs = requests_for(name, LENGTHS[name])
+    base = replay(make_runner(name, "float32"), traces.whole(reqs))
+    for cut in (traces.prompt_then_decode(reqs), traces.changing_portions(reqs), traces.mixed(reqs)):
+        got = replay(make_runner(name, "float32"), cut)
+        for key, row in base.items():
+            assert torch.equal(row, got[key]), f"{name}: row {key} differs between cuts"
+
+
+def test_long_decoding():
+    """300 tokens one by one after a short prompt: every page edge and the window's edge are crossed."""
+    for name, dtype in (("B", "float32"), ("C", "float32"), ("C", "bfloat16")):
+        reqs = requests_for(name, (330,), seed=5)
+        steps = traces.prompt_then_decode(reqs, 300)
+        got = replay(make_runner(name, dtype, steps), steps)
+        compare_with_plain(got, model_folder(name), reqs, dtype, what=f"{name} long decode")
+
+
+def test_first_tokens_of_a_sequence():
+    for name in ("A", "B", "C"):
+        for dtype in ("float32", "bfloat16"):
+            reqs = requests_for(name, (1, 2, 3), seed=31)
+            steps = [{"step": 0, "entries": [{"id": r, "tokens": t, "want": list(range(len(t)))}
+                                             for r, t in reqs.items()], "end": list(reqs)}]
+            got = replay(make_runner(name, dtype, steps), steps)
+            compare_with_plain(got, model_folder(name), reqs, dtype, what=f"{name} first tokens")
+
+
+def test_step_larger_than_a_batch_is_split():
+    reqs = requests_for("B", (129, 64), seed=3)
+    steps = [{"step": 0, "entries": [{"id": r, "tokens": t, "want": list(range(len(t)))[::-1]}
+                                     for r, t in reqs.items()], "end": list(reqs)}]
+    runner = make_runner("B", "float32", steps, max_batch_tokens=50)
+    rows = runner.step([__import__("jllm_serve_b200").engine.Segment(e["id"], e["tokens"], 0, e["want"])
+                        for e in steps[0]["entries"]]).cpu()
+    from tests.helpers import plain_logits
+    r = 0
+    for rid, toks in reqs.items():
+        want = plain_logits(model_folder("B"), tuple(toks))
+        for p in reversed(range(len(toks))):
+            assert float((rows[r] - want[p]).abs().max()) < 2e-5 * float(want.abs().max())
+            r += 1
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(dtype, tmp_path):
+    """bin/trace_run as a user runs it: JSON lines in, <step>.f32 files and `done` lines out."""
+    name = "B"
+    reqs = requests_for(name, (40, 70, 9, 33, 64), seed=17)
+    steps = traces.mixed(reqs, max_live=4, portion=20)
+    out = tmp_path / "logits"
+    text = "\n".join(json.dumps(s) for s in steps) + "\n"
+    proc = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(model_folder(name)),
+                           "--dtype", dtype, "--out", str(out), "--max-tokens", str(traces.peak_tokens(steps, 64)),
+                           "--poison"], input=text, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == [f"done {s['step']}" for s in steps]
+    vocab = CONFIGS[name]["vocab_size"]
+
+    def rows(st):
+        n = sum(len(e["want"]) for e in st["entries"])
+        if n == 0:
+            assert not (out / f"{st['step']}.f32").exists()
+            return None
+        a = np.fromfile(out / f"{st['step']}.f32", dtype="<f4")
+        assert a.size == n * vocab
+        return torch.from_numpy(a.reshape(n, vocab).copy())
+
+    got = traces.collect(steps, rows)
+    compare_with_plain(got, model_folder(name), reqs, dtype, what="trace_run")

@@ -1,0 +1,37 @@
+"""The tiny configurations of the test suite: they differ in every size and option."""
+import json
+import tempfile
+from pathlib import Path
+
+import torch
+
+# A: tied head, head_dim 16, group 2, H * hd == D, theta 1e4, eps 1e-6, no window
+TINY_A = dict(model_type="qwen3", architectures=["Qwen3ForCausalLM"], hidden_size=64, num_hidden_layers=2,
+              num_attention_heads=4, num_key_value_heads=2, head_dim=16, intermediate_size=128, vocab_size=256,
+              rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=True, attention_bias=False,
+              use_sliding_window=False, max_position_embeddings=128, hidden_act="silu")
+# B: untied head, head_dim 32, group 4, H * hd = 256 != D = 96, F = 200, V = 1000, theta 1e6, eps 1e-5
+TINY_B = dict(model_type="qwen3", architectures=["Qwen3ForCausalLM"], hidden_size=96, num_hidden_layers=3,
+              num_attention_heads=8, num_key_value_heads=2, head_dim=32, intermediate_size=200, vocab_size=1000,
+              rope_theta=1000000.0, rms_norm_eps=1e-5, tie_word_embeddings=False, attention_bias=False,
+              use_sliding_window=False, max_position_embeddings=512, hidden_act="silu")
+# C: a window from layer 1 on, biases, head_dim 48 (no power of two), group 3, partial rotary, linear rope scaling
+TINY_C = dict(model_type="qwen3", architectures=["Qwen3ForCausalLM"], hidden_size=72, num_hidden_layers=4,
+              num_attention_heads=6, num_key_value_heads=2, head_dim=48, intermediate_size=176, vocab_size=517,
+              rope_theta=50000.0, rms_norm_eps=3e-6, tie_word_embeddings=False, attention_bias=True,
+              use_sliding_window=True, sliding_window=40, max_window_layers=1, max_position_embeddings=1024,
+              partial_rotary_factor=0.5, rope_scaling={"rope_type": "linear", "factor": 2.0}, hidden_act="silu")
+
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+
+
+def make_model_folder(config: dict, seed: int, where=None, vector_dtype=None) -> Path:
+    """A temporary model folder with random weights; never inside the repository."""
+    from jllm_serve_b200.weights import write_model_folder
+    d = Path(where or tempfile.mkdtemp(prefix="jllm_tiny_"))
+    return write_model_folder(config, seed, d, torch.bfloat16, vector_dtype)
+
+
+def random_tokens(n: int, vocab: int, seed: int) -> list:
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()

@@ -1,0 +1,111 @@
+"""Trace scripts: the same requests cut into steps in different ways.
+
+A trace is a list of steps {"step", "entries": [{"id", "tokens", "want"}], "end": [...]}, the
+format `bin/trace_run` reads. Every entry asks for the logits of all its tokens, so each way
+of cutting yields logits for every (request, position) and all can be compared with the
+plain implementation's whole-sequence logits.
+"""
+from __future__ import annotations
+
+import math
+
+
+def whole(requests: dict) -> list:
+    """Each request alone and whole: one step per request."""
+    steps = []
+    for i, (rid, toks) in enumerate(requests.items()):
+        steps.append({"step": i, "entries": [{"id": rid, "tokens": toks, "want": list(range(len(toks)))}],
+                      "end": [rid]})
+    return steps
+
+
+def prompt_then_decode(requests: dict, tail: int = 32) -> list:
+    """Most of it in one step, the last `tail` tokens one by one."""
+    steps = []
+    for rid, toks in requests.items():
+        head = max(1, len(toks) - tail)
+        steps.append({"step": len(steps), "entries": [{"id": rid, "tokens": toks[:head],
+                                                        "want": list(range(head))}], "end": []})
+        for p in range(head, len(toks)):
+            steps.append({"step": len(steps), "entries": [{"id": rid, "tokens": toks[p:p + 1], "want": [0]}],
+                          "end": [rid] if p == len(toks) - 1 else []})
+        if head == len(toks):
+            steps[-1]["end"] = [rid]
+    return steps
+
+
+def changing_portions(requests: dict, sizes=(7, 2, 33, 3, 16, 2, 64, 5)) -> list:
+    """Each request alone, in portions of changing size, down to two tokens."""
+    steps = []
+    for rid, toks in requests.items():
+        lo, k = 0, 0
+        while lo < len(toks):
+            n = min(sizes[k % len(sizes)], len(toks) - lo)
+            steps.append({"step": len(steps), "entries": [{"id": rid, "tokens": toks[lo:lo + n],
+                                                            "want": list(range(n))}],
+                          "end": [rid] if lo + n == len(toks) else []})
+            lo += n
+            k += 1
+    return steps
+
+
+def mixed(requests: dict, max_live: int = 4, portion: int = 24, prefill_share: float = 0.6) -> list:
+    """Up to `max_live` requests at a time: each is fed in portions until `prefill_share` of it is in,
+    then one token per step (as if decoded), while the others' portions ride in the same batch. A
+    request that ends frees its pages, and the next one waiting takes them."""
+    waiting = list(requests.items())
+    live = {}   # rid -> [tokens, fed, prefill_end]
+    steps = []
+    turn = 0
+    while waiting or live:
+        while waiting and len(live) < max_live:
+            rid, toks = waiting.pop(0)
+            live[rid] = [toks, 0, max(1, min(len(toks), math.ceil(len(toks) * prefill_share)))]
+        entries, ended = [], []
+        for j, (rid, st) in enumerate(list(live.items())):
+            toks, fed, pre = st
+            if fed < pre:
+                if (turn + j) % 3 == 2 and len(live) > 1:
+                    continue  # this request sits a step out and goes on later
+                n = min(portion - 5 * (j % 3), pre - fed)
+                n = max(2, n) if pre - fed >= 2 else pre - fed
+            else:
+                n = 1
+            entries.append({"id": rid, "tokens": toks[fed:fed + n], "want": list(range(n))})
+            st[1] = fed + n
+            if st[1] == len(toks):
+                ended.append(rid)
+        for rid in ended:
+            del live[rid]
+        steps.append({"step": len(steps), "entries": entries, "end": ended})
+        turn += 1
+    return steps
+
+
+def peak_tokens(steps: list, round_to: int = 64) -> int:
+    """The most tokens live requests hold at any time, each request's count rounded up to `round_to`."""
+    held, peak = {}, 0
+    for st in steps:
+        for e in st["entries"]:
+            held[e["id"]] = held.get(e["id"], 0) + len(e["tokens"])
+        peak = max(peak, sum(-(-n // round_to) * round_to for n in held.values()))
+        for rid in st["end"]:
+            held.pop(rid, None)
+    return peak
+
+
+def collect(steps: list, logits_of_step) -> dict:
+    """{(request, position): logits row} from a replay; `logits_of_step(step)` gives [wanted, vocab] or None."""
+    out, fed = {}, {}
+    for st in steps:
+        rows = logits_of_step(st)
+        r = 0
+        for e in st["entries"]:
+            base = fed.get(e["id"], 0)
+            for w in e["want"]:
+                out[(e["id"], base + w)] = rows[r]
+                r += 1
+            fed[e["id"]] = base + len(e["tokens"])
+        for rid in st["end"]:
+            fed.pop(rid, None)
+    return out
