@@ -223,11 +223,12 @@ class CacheManager:
         if length >= rc.length:
             return
         keep = -(-length // self.page_size)
-        for gi, g in enumerate(self.paged):
+        for gi, g in enumerate(self.paged):    # first look, then touch: a refused rewind changes nothing
             if g.need.window > 0 and self._first_needed_page(g, rc.length) > self._first_needed_page(g, length):
                 if any(p == RELEASED for p in rc.tables[gi][self._first_needed_page(g, length):keep]):
                     raise ValueError(f"request {request!r}: a windowed group has released pages that a rewind "
                                      f"to {length} needs; recompute from the start")
+        for gi, g in enumerate(self.paged):
             table = rc.tables[gi]
             while len(table) > keep:
                 page = table.pop()

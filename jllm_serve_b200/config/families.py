@@ -55,6 +55,10 @@ def parse_qwen3(values: dict) -> Decoder:
     heads = c.positive("num_attention_heads")
     kv_heads = c.integer("num_key_value_heads", heads)
     head_dim = c.integer("head_dim", dim // heads)
+    if head_dim <= 0:
+        raise ConfigError(f"head_dim must be positive, got {head_dim}")
+    if kv_heads <= 0 or heads % kv_heads:
+        raise ConfigError(f"num_key_value_heads={kv_heads} must be positive and divide num_attention_heads={heads}")
     if c.has("num_experts") and c.integer("num_experts") > 0:
         raise ConfigError("num_experts > 0: expert feed-forwards belong to another architecture (qwen3_moe), not built")
     hidden = c.integer("intermediate_size", 0)

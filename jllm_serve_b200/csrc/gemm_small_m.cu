@@ -1,0 +1,181 @@
+// out[m, n] (+)= sum_k a[m, k] * w[n, k] (+ bias[n]) for a few rows (m <= 64): the decode-step product.
+//
+// With so few rows the product is a stream of the weight matrix: every weight is read once from HBM
+// and used for all rows, so the kernel is built around the weight loads. The roles of the tensor-core
+// operands are swapped: 16 (or 32) weight rows are the M side of mma.sync.m16n8k16 and 8 tokens are
+// its N side, so no tensor-core rows are wasted on padding tokens. Each thread loads 16 contiguous
+// bytes of a weight row straight from global memory into the registers of the A fragment; the k index
+// inside one 32-wide chunk is permuted (thread t owns k = 8t .. 8t+7), and the activation fragment is
+// loaded with the same permutation, which a sum over k does not notice. The 8 warps of a block take
+// interleaved 32-wide chunks of K (so the block reads 512 contiguous bytes of every row at a time),
+// and their partial sums are added in shared memory in a fixed order: results are deterministic.
+//
+// Requirements (else the caller uses the CUDA-core kernel): bfloat16 inputs, K a multiple of 8,
+// 16-byte aligned rows (lda, ldw multiples of 8; aligned base pointers), 1 <= M <= 64.
+#include "common.cuh"
+
+namespace {
+
+constexpr int WARPS = 8;
+constexpr int KCHUNK = 32;
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 load_16(const __nv_bfloat16* p) {
+    return __ldg(reinterpret_cast<const uint4*>(p));
+}
+
+// streaming load of weights: read once, do not keep in L1
+__device__ __forceinline__ uint4 load_16_stream(const __nv_bfloat16* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+template <int NT, int RT, int UNROLL, typename Tout>
+__global__ void __launch_bounds__(WARPS * 32)
+gemm_small_m_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w, int ldw,
+                    VecRef bias, int has_bias, Tout* __restrict__ out, int ldo, int accumulate, int M, int N, int K) {
+    extern __shared__ float red[];  // [WARPS][RT * 16][NT * 8]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int n0 = blockIdx.x * (16 * RT);
+    float acc[RT][NT][4];
+#pragma unroll
+    for (int r = 0; r < RT; ++r)
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[r][j][i] = 0.f;
+
+    const __nv_bfloat16* wrow[RT][2];
+    bool wok[RT][2];
+#pragma unroll
+    for (int r = 0; r < RT; ++r)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int n = n0 + r * 16 + h * 8 + g;
+            wok[r][h] = n < N;
+            wrow[r][h] = w + (size_t)(wok[r][h] ? n : 0) * ldw;
+        }
+    const __nv_bfloat16* arow[NT];
+    bool aok[NT];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        const int m = j * 8 + g;
+        aok[j] = m < M;
+        arow[j] = a + (size_t)(aok[j] ? m : 0) * lda;
+    }
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    const int chunks = (K + KCHUNK - 1) / KCHUNK;
+    for (int c0 = warp; c0 < chunks; c0 += WARPS * UNROLL) {
+        uint4 wv[UNROLL][RT][2];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int k = (c0 + u * WARPS) * KCHUNK + 8 * t;
+            const bool kin = (c0 + u * WARPS) < chunks && k < K;
+#pragma unroll
+            for (int r = 0; r < RT; ++r)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) wv[u][r][h] = (kin && wok[r][h]) ? load_16_stream(wrow[r][h] + k) : zero;
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int k = (c0 + u * WARPS) * KCHUNK + 8 * t;
+            const bool kin = (c0 + u * WARPS) < chunks && k < K;
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                const uint4 xv = (kin && aok[j]) ? load_16(arow[j] + k) : zero;
+#pragma unroll
+                for (int r = 0; r < RT; ++r) {
+                    mma_bf16_16816(acc[r][j], wv[u][r][0].x, wv[u][r][1].x, wv[u][r][0].y, wv[u][r][1].y, xv.x, xv.y);
+                    mma_bf16_16816(acc[r][j], wv[u][r][0].z, wv[u][r][1].z, wv[u][r][0].w, wv[u][r][1].w, xv.z, xv.w);
+                }
+            }
+        }
+    }
+    // partial sums of the 8 warps -> shared memory, laid out [warp][token][row] so the final pass writes
+    // consecutive output features from consecutive threads
+    constexpr int ROWS = RT * 16, TOK = NT * 8;
+    float* mine = red + (size_t)warp * ROWS * TOK;
+#pragma unroll
+    for (int r = 0; r < RT; ++r)
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            const int row = r * 16 + g, tok = j * 8 + 2 * t;
+            mine[(tok + 0) * ROWS + row] = acc[r][j][0];
+            mine[(tok + 1) * ROWS + row] = acc[r][j][1];
+            mine[(tok + 0) * ROWS + row + 8] = acc[r][j][2];
+            mine[(tok + 1) * ROWS + row + 8] = acc[r][j][3];
+        }
+    __syncthreads();
+    for (int e = threadIdx.x; e < ROWS * TOK; e += WARPS * 32) {
+        const int tok = e / ROWS, row = e % ROWS;
+        const int n = n0 + row;
+        if (tok >= M || n >= N) continue;
+        float v = 0.f;
+#pragma unroll
+        for (int wi = 0; wi < WARPS; ++wi) v += red[(size_t)wi * ROWS * TOK + e];
+        if (has_bias) v += bias[n];
+        Tout* dst = out + (size_t)tok * ldo + n;
+        if (accumulate) v += to_float(*dst);
+        *dst = from_float<Tout>(v);
+    }
+}
+
+template <int NT, int RT, int UNROLL>
+int launch(const void* a, int lda, const void* w, int ldw, VecRef bias, int has_bias, void* out, int out_dtype, int ldo,
+           int accumulate, int M, int N, int K, cudaStream_t stream) {
+    const int grid = (N + 16 * RT - 1) / (16 * RT);
+    const size_t smem = (size_t)WARPS * RT * 16 * NT * 8 * sizeof(float);
+    if (out_dtype == JLLM_F32) {
+        auto kern = gemm_small_m_kernel<NT, RT, UNROLL, float>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        kern<<<grid, WARPS * 32, smem, stream>>>((const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)w, ldw, bias,
+                                                 has_bias, (float*)out, ldo, accumulate, M, N, K);
+    } else {
+        auto kern = gemm_small_m_kernel<NT, RT, UNROLL, __nv_bfloat16>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        kern<<<grid, WARPS * 32, smem, stream>>>((const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)w, ldw, bias,
+                                                 has_bias, (__nv_bfloat16*)out, ldo, accumulate, M, N, K);
+    }
+    return jllm_check_launch("gemm_small_m");
+}
+
+}  // namespace
+
+// Returns 1 if jllm_gemm_small_m takes this product.
+JLLM_EXPORT int jllm_gemm_small_m_fits(const void* a, int lda, const void* w, int ldw, int M, int N, int K) {
+    return M >= 1 && M <= 64 && N >= 1 && K >= 8 && K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 &&
+           ((uintptr_t)a % 16) == 0 && ((uintptr_t)w % 16) == 0;
+}
+
+JLLM_EXPORT int jllm_gemm_small_m(const void* a, int lda, const void* w, int ldw, const void* bias, int bias_dtype,
+                                  void* out, int out_dtype, int ldo, int accumulate, int M, int N, int K,
+                                  int tuning, cudaStream_t stream) {
+    JLLM_REQUIRE(jllm_gemm_small_m_fits(a, lda, w, ldw, M, N, K),
+                 "gemm_small_m: needs 1 <= M <= 64, K %% 8 == 0 and 16-byte aligned rows (M=%d N=%d K=%d lda=%d ldw=%d)",
+                 M, N, K, lda, ldw);
+    JLLM_REQUIRE(ldo >= N, "gemm_small_m: ldo=%d < N=%d", ldo, N);
+    const VecRef b{bias, bias_dtype};
+    const int hb = bias != nullptr;
+    // 32 rows per block halve the activation reads but need N large enough to keep every SM busy
+    bool wide = N >= 64 * 148;
+    int deep = 0;
+    if (tuning > 0) { wide = (tuning & 1) != 0; deep = (tuning >> 1) & 1; }
+#define JLLM_GO(NT, RT, UN) return launch<NT, RT, UN>(a, lda, w, ldw, b, hb, out, out_dtype, ldo, accumulate, M, N, K, stream)
+    if (M <= 8) { if (wide) { if (deep) JLLM_GO(1, 2, 8); JLLM_GO(1, 2, 4); } if (deep) JLLM_GO(1, 1, 8); JLLM_GO(1, 1, 4); }
+    if (M <= 16) { if (wide) JLLM_GO(2, 2, 4); if (deep) JLLM_GO(2, 1, 8); JLLM_GO(2, 1, 4); }
+    if (M <= 32) { if (wide) JLLM_GO(4, 2, 2); JLLM_GO(4, 1, 4); }
+    if (wide) JLLM_GO(8, 2, 2);
+    JLLM_GO(8, 1, 2);
+#undef JLLM_GO
+}

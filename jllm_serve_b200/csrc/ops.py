@@ -74,7 +74,9 @@ class _Signatures:
     jllm_swiglu = [P, P, I, I, I, P]
     jllm_qk_norm_rope_store = [P, I, P, P, I, I, F, P, P, I, P, P, P, P, I, I, I, I, I, I, I, P]
     jllm_gemm_plain = [P, I, I, P, I, P, I, P, I, I, I, I, I, I, P]
+    jllm_gemm_small_m = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, P]
     jllm_attention_plain = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P]
+    jllm_attention_decode = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
     jllm_argmax = [P, I, I, I, P, P]
     jllm_sample = [P, I, I, I, P, P, P, P, P, P, P]
 
@@ -141,16 +143,69 @@ def sample(logits, temperature, top_k, top_p, min_p, uniform, out, vocab: int | 
           out.data_ptr(), _stream())
 
 
+def _small_m_fits(a, w) -> bool:
+    M, K = a.shape
+    return (1 <= M <= 64 and K >= 8 and K % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
 def gemm_bf16_fits(a, w, out) -> bool:
     """Whether the tensor-core kernels take this product; otherwise the CUDA-core kernel runs it."""
-    return False
+    return a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and _small_m_fits(a, w)
 
 
 def gemm_bf16(a, w, out, bias=None, accumulate=False) -> None:
+    """out (+)= a @ w.T (+ bias) on the tensor cores: bfloat16 operands, float32 accumulation."""
+    if _small_m_fits(a, w):
+        return gemm_small_m(a, w, out, bias, accumulate)
     raise KernelError("the tensor-core matrix product is not built for this shape")
 
 
-def attention(q, k_cache, v_cache, out, batch, group, heads, kv_heads, head_dim, page_size, window, scale) -> None:
+def gemm_small_m(a, w, out, bias=None, accumulate=False, tuning: int = 0) -> None:
+    """The decode-step product (at most 64 rows): a weight stream through mma.sync with swapped operands."""
+    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.stride(-1) == 1
+    _call("jllm_gemm_small_m", a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), _p(bias),
+          _DT[bias.dtype] if bias is not None else F32, out.data_ptr(), _DT[out.dtype], out.stride(0),
+          int(accumulate), a.shape[0], w.shape[0], a.shape[1], int(tuning), _stream())
+
+
+def attention_decode_fits(dtype, heads, kv_heads, head_dim) -> bool:
+    return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256 and heads // kv_heads <= 16
+
+
+def attention_decode_scratch_floats(rows, heads, head_dim, splits) -> int:
+    return 0 if splits <= 1 else rows * heads * splits * (head_dim + 2)
+
+
+def attention_decode(q, k_cache, v_cache, out, row_seg, row_pos, block_tables, rows, heads, kv_heads, head_dim,
+                     page_size, window, scale, splits=1, scratch=None) -> None:
+    """One query position per row; the key range of a row may be split over `splits` blocks (needs scratch)."""
+    if splits > 1:
+        assert scratch is not None and scratch.dtype == torch.float32 and \
+            scratch.numel() >= attention_decode_scratch_floats(rows, heads, head_dim, splits)
+    _call("jllm_attention_decode", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+          out.stride(0), row_seg.data_ptr(), row_pos.data_ptr(), block_tables.data_ptr(), block_tables.stride(0),
+          rows, heads, kv_heads, head_dim, page_size, int(window), float(scale), int(splits), _p(scratch), _stream())
+
+
+def attention(q, k_cache, v_cache, out, batch, group, heads, kv_heads, head_dim, page_size, window, scale,
+              scratch=None) -> None:
     """Causal attention of every row of the batch over its own request's cached keys and values."""
+    if batch.decode_only and attention_decode_fits(q.dtype, heads, kv_heads, head_dim):
+        splits = decode_splits(batch.rows, kv_heads, batch.max_kv_len if window <= 0 else min(window, batch.max_kv_len),
+                               heads, head_dim, scratch)
+        return attention_decode(q, k_cache, v_cache, out, batch.row_seg, batch.positions, batch.block_tables[group],
+                                batch.rows, heads, kv_heads, head_dim, page_size, window, scale, splits, scratch)
     attention_plain(q, q.stride(0), k_cache, v_cache, out, batch.row_seg, batch.positions, batch.block_tables[group],
                     batch.rows, heads, kv_heads, head_dim, page_size, window, scale)
+
+
+def decode_splits(rows, kv_heads, max_keys, heads, head_dim, scratch, target_blocks: int = 2 * 148) -> int:
+    """How many blocks share one row's keys: enough to fill the GPU, each with at least 256 keys."""
+    want = -(-target_blocks // max(1, rows * kv_heads))
+    splits = max(1, min(want, max_keys // 256, 32))
+    if scratch is None:
+        return 1
+    while splits > 1 and attention_decode_scratch_floats(rows, heads, head_dim, splits) > scratch.numel():
+        splits -= 1
+    return splits

@@ -2,3 +2,5 @@
 from .batch import BatchBuilder, Segment, StepBatch
 from .model import DecoderModel, build_model, model_wants
 from .runner import ModelRunner
+from .scheduler import Item, Pick, PlannedSegment, Request, Scheduler, plan_pass
+from .engine import Engine, Result, Stats

@@ -1,0 +1,144 @@
+"""The Python entry point: load a model, generate for a list of prompts.
+
+The reference's programmatic surface is `ModelLoader.load(...)` + `Engine.generate(prompt,
+SamplingParams, sink, cancelled) -> Result(text, tokens, finishReason, Stats)`
+(src/main/java/org/robomiri/jllm/ModelLoader.java:159-210, engine/Engine.java:43-78,368-376).
+Here prompts are token ids (the engine carries no tokenizer) and many prompts are generated
+together by the scheduler: `Engine(model_dir, ...).generate(prompts, params) -> [Result]`.
+`add_request` / `run_until_done` drive the same loop by hand; `step` is the raw step
+function.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Hashable, List, Optional, Sequence, Union
+
+import torch
+
+from ..sampling import RequestRng, Sampler, SamplingParams
+from .batch import Segment
+from .runner import ModelRunner
+from .scheduler import Request, Scheduler
+
+
+@dataclass
+class Stats:
+    """As the reference's Engine.Stats (engine/Engine.java:43-57): counts and the two phases' times."""
+    prompt_tokens: int = 0
+    cached_tokens: int = 0
+    generated: int = 0
+    prefill_ms: float = 0.0
+    decode_ms: float = 0.0
+    preemptions: int = 0
+
+    @property
+    def tok_per_sec(self) -> float:
+        return self.generated / (self.decode_ms / 1000.0) if self.decode_ms > 0 else 0.0
+
+    def line(self) -> str:
+        """The reference's stats line (Main.java:384-389)."""
+        return (f"{self.prompt_tokens} prompt tok ({self.cached_tokens} cached), prefill {self.prefill_ms:.0f} ms, "
+                f"{self.generated} generated in {self.decode_ms:.0f} ms = {self.tok_per_sec:.1f} tok/s")
+
+
+@dataclass
+class Result:
+    tokens: List[int]
+    finish_reason: str
+    stats: Stats = field(default_factory=Stats)
+
+
+class Engine:
+    def __init__(self, model_dir=None, *, config: Optional[dict] = None, seed: Optional[int] = None,
+                 dtype="bfloat16", device="cuda:0", ctx: Optional[int] = None, page_size: int = 16,
+                 num_pages: Optional[int] = None, max_tokens_cached: Optional[int] = None,
+                 max_batch_tokens: int = 2048, chunk: int = 512, min_chunk: int = 16, max_running: int = 64,
+                 sample_vocab: Optional[int] = None, cuda_graphs: bool = True):
+        self.runner = ModelRunner(model_dir, config=config, seed=seed, dtype=dtype, device=device,
+                                  page_size=page_size, num_pages=num_pages, max_tokens=max_tokens_cached,
+                                  max_batch_tokens=max_batch_tokens, max_requests=max_running, ctx=ctx,
+                                  cuda_graphs=cuda_graphs)
+        core = self.runner.spec.core
+        self.scheduler = Scheduler(self.runner.cache, self.runner.ctx, max_batch_tokens, chunk, min_chunk, max_running,
+                                   eos_ids=core.eos)
+        self.sampler = Sampler(self.runner.device, max_running, core.vocab, sample_vocab)
+        self._rngs = {}
+        self._times = {}
+        self._ids = 0
+
+    # ---- requests ------------------------------------------------------------------------------------------
+    def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
+                    request_id: Optional[Hashable] = None) -> Hashable:
+        params = params or SamplingParams()
+        rid = request_id if request_id is not None else f"req-{self._ids}"
+        self._ids += 1
+        prompt = [int(t) for t in prompt]
+        vocab = self.runner.vocab
+        if any(t < 0 or t >= vocab for t in prompt):
+            raise ValueError(f"request {rid!r}: token id outside [0, {vocab})")
+        self.scheduler.add(Request(rid, prompt, params))
+        self._rngs[rid] = RequestRng(params.seed)
+        self._times[rid] = {"start": time.perf_counter(), "first": None, "end": None}
+        return rid
+
+    def step_once(self) -> List[Request]:
+        """One scheduler step: plan, run, sample, complete. Returns the requests that finished."""
+        plan = self.scheduler.plan()
+        if not plan:
+            return []
+        segments = [Segment(p.request.id, p.tokens, p.start, [len(p.tokens) - 1] if p.wants_logits else [])
+                    for p in plan]
+        logits = self.runner.step(segments)
+        wanting = [p.request for p in plan if p.wants_logits]
+        sampled = self.sampler.sample(logits, [r.params for r in wanting],
+                                      [0.0 if r.params.greedy else self._rngs[r.id].next() for r in wanting])
+        now = time.perf_counter()
+        for r in wanting:
+            if self._times[r.id]["first"] is None:
+                self._times[r.id]["first"] = now
+        done = self.scheduler.complete(plan, sampled)
+        for r in done:
+            self._times[r.id]["end"] = now
+        return done
+
+    def run_until_done(self) -> List[Request]:
+        finished = []
+        while self.scheduler.has_work():
+            finished.extend(self.step_once())
+        return finished
+
+    def result_of(self, rid: Hashable) -> Result:
+        r = self.scheduler.finished[rid]
+        t = self._times[rid]
+        end = t["end"] or time.perf_counter()
+        first = t["first"] or end
+        return Result(list(r.output), r.finish_reason,
+                      Stats(len(r.prompt), 0, len(r.output), (first - t["start"]) * 1e3, (end - first) * 1e3,
+                            r.preemptions))
+
+    def generate(self, prompts: Sequence[Sequence[int]],
+                 params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> List[Result]:
+        """Generates for every prompt (token ids); one SamplingParams for all, or one per prompt."""
+        if params is None or isinstance(params, SamplingParams):
+            params = [params or SamplingParams()] * len(prompts)
+        if len(params) != len(prompts):
+            raise ValueError(f"{len(prompts)} prompts but {len(params)} sampling parameters")
+        ids = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
+        self.run_until_done()
+        out = [self.result_of(i) for i in ids]
+        for i in ids:
+            self.scheduler.finished.pop(i, None)
+            self._rngs.pop(i, None)
+            self._times.pop(i, None)
+        return out
+
+    def step(self, segments: Sequence[Segment]) -> torch.Tensor:
+        """The raw step function: logits [wanted places, vocab] for a batch of (request, its next tokens)."""
+        return self.runner.step(segments)
+
+    def finish(self, request: Hashable) -> None:
+        self.runner.finish(request)
+
+    def describe(self) -> str:
+        return self.runner.describe()

@@ -39,7 +39,8 @@ class ModelRunner:
     def __init__(self, model_dir=None, *, config: Optional[dict] = None, seed: Optional[int] = None,
                  dtype="bfloat16", device="cuda:0", page_size: int = 16, num_pages: Optional[int] = None,
                  max_tokens: Optional[int] = None, max_batch_tokens: int = 2048, max_requests: int = 64,
-                 ctx: Optional[int] = None, schedule=None, poison_freed_pages: bool = False):
+                 ctx: Optional[int] = None, schedule=None, poison_freed_pages: bool = False,
+                 cuda_graphs: bool = True):
         """Either `model_dir` (config.json + model.safetensors) or `config` + `seed` (random weights made on
         the device). The pool holds `num_pages` pages per group, or enough for `max_tokens` cached tokens."""
         ops.require_device()
@@ -83,6 +84,7 @@ class ModelRunner:
         self.builder = BatchBuilder(self.device, self.max_rows, self.max_requests, max_blocks, len(self.cache.paged),
                                     self.page_size)
         self.steps = 0
+        self.use_graphs = bool(cuda_graphs)
 
     def _allocate(self, shape, kind):
         if kind == "kv":

@@ -1,0 +1,259 @@
+"""The scheduler: admits requests, forms each step's batch under a token budget, finishes and frees.
+
+The pass-forming rule is the reference's (docs/25-scheduler.md;
+src/main/java/org/robomiri/jllm/engine/PassPlanner.java:74-112): every decoding request
+rides along with its one token, in order of arrival, while it fits the budget; then ONE
+prompt portion, the head of the prefill line, takes what is left, trimmed to the room, but
+only if that is at least `min_chunk` rows (or all the portion needs); if nothing fits, the
+oldest item goes alone, so a pass is never empty. A prompt that has run a portion goes to
+the back of the prefill line, so prompts alternate (docs/25:133-134).
+
+Admission is first come, first served (the reference's classes, aging and sessions,
+engine/Admission.java:217-285, are not built): a waiting request starts when fewer than
+`max_running` run and the pages of its first portion are free.
+
+When pages run out. A step's pages are reserved before it runs. If the pool cannot cover
+a step, the most recently admitted running request is preempted: its pages go back, it
+returns to the FRONT of the waiting line with everything it has generated so far as part
+of its prompt, and is recomputed later (the reference pauses the newest background request
+and recomputes what could not be kept: engine/Admission.java:288-301, engine/Engine.java:
+657-666). The oldest request is never preempted, so it always finishes; a request that
+cannot fit in the empty pool ends with the reason "kv_exhausted".
+
+The scheduler is host logic only: it asks the cache manager for pages and tells the caller
+which segments to run; it never touches a tensor.
+"""
+from __future__ import annotations
+
+import itertools
+from dataclasses import dataclass, field
+from typing import Callable, Dict, Hashable, List, Optional, Sequence
+
+from ..cache import PoolExhausted
+from ..sampling.params import SamplingParams
+
+WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+
+
+@dataclass
+class Request:
+    id: Hashable
+    prompt: List[int]
+    params: SamplingParams
+    output: List[int] = field(default_factory=list)
+    state: str = WAITING
+    computed: int = 0                      # tokens whose keys and values are in the cache
+    finish_reason: Optional[str] = None
+    arrival: int = 0
+    admitted: int = -1                     # order of (re)admission, for choosing whom to preempt
+    preemptions: int = 0
+    max_new: int = 0                       # max_tokens clamped to the context
+
+    @property
+    def tokens(self) -> List[int]:
+        return self.prompt + self.output
+
+    @property
+    def remaining(self) -> int:
+        return len(self.prompt) + len(self.output) - self.computed
+
+
+@dataclass(frozen=True)
+class Item:
+    """One piece of pending work for the pass planner."""
+    ref: object
+    kind: str                              # "rider" (a decoding request's rows, all wanted) or "chunk"
+    rows: int
+    enqueued: int
+
+
+@dataclass(frozen=True)
+class Pick:
+    ref: object
+    kind: str
+    rows: int
+
+
+def plan_pass(pending: Sequence[Item], budget: int, min_chunk: int) -> List[Pick]:
+    """The picks of the next pass: the chunk (if any) first, then the riders by arrival.
+
+    Riders that do not fit are left for the next pass, never trimmed; the chunk is the head of the
+    `pending` chunks in the order given, trimmed to the room left, and waits if the room is smaller
+    than min(min_chunk, its rows)."""
+    if budget < 1:
+        raise ValueError("a pass needs a budget of at least one row")
+    riders = sorted((i for i in pending if i.kind != "chunk"), key=lambda i: i.enqueued)
+    chunks = [i for i in pending if i.kind == "chunk"]
+    used, rider_picks = 0, []
+    for r in riders:
+        if used + r.rows <= budget:
+            rider_picks.append(Pick(r.ref, r.kind, r.rows))
+            used += r.rows
+    out: List[Pick] = []
+    if chunks:
+        c = chunks[0]
+        rows = min(c.rows, budget - used)
+        if rows >= min(min_chunk, c.rows) and rows > 0:
+            out.append(Pick(c.ref, "chunk", rows))
+    out.extend(rider_picks)
+    if not out and pending:
+        first = min(pending, key=lambda i: i.enqueued)
+        out.append(Pick(first.ref, first.kind, min(first.rows, budget) if first.kind == "chunk" else first.rows))
+    return out
+
+
+@dataclass
+class PlannedSegment:
+    request: Request
+    start: int
+    tokens: List[int]
+    wants_logits: bool
+
+
+class Scheduler:
+    def __init__(self, cache, ctx: int, max_batch_tokens: int, chunk: int = 512, min_chunk: int = 16,
+                 max_running: int = 64, eos_ids: Sequence[int] = ()):
+        self.cache, self.ctx = cache, ctx
+        self.budget, self.chunk, self.min_chunk, self.max_running = max_batch_tokens, chunk, min_chunk, max_running
+        self.eos = set(eos_ids)
+        self.waiting: List[Request] = []
+        self.running: List[Request] = []
+        self.prefill_line: List[Request] = []
+        self.finished: Dict[Hashable, Request] = {}
+        self._clock = itertools.count()
+        self._admissions = itertools.count()
+        self.preemptions = 0
+        self.on_finish: Optional[Callable[[Request], None]] = None
+
+    # ---- requests in -------------------------------------------------------------------------------------
+    def add(self, request: Request) -> None:
+        n = len(request.prompt)
+        if n < 1:
+            raise ValueError(f"request {request.id!r}: the prompt is empty")
+        if n >= self.ctx:
+            raise ValueError(f"request {request.id!r}: a prompt of {n} tokens does not fit the context of {self.ctx}")
+        request.arrival = next(self._clock)
+        request.max_new = min(request.params.max_tokens, self.ctx - n)
+        request.state = WAITING
+        self.waiting.append(request)
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # ---- one step ------------------------------------------------------------------------------------------
+    def _admit(self) -> None:
+        while self.waiting and len(self.running) < self.max_running:
+            r = self.waiting[0]
+            first = min(r.remaining, self.chunk, self.budget)
+            if not self._fits_now(r, first + 1):
+                if not self.running:
+                    # alone in an empty pool and still no room: it can never run
+                    self.waiting.pop(0)
+                    self._finish(r, "kv_exhausted")
+                    continue
+                break
+            self.waiting.pop(0)
+            r.state, r.admitted = RUNNING, next(self._admissions)
+            self.running.append(r)
+            self.cache.open(r.id)
+            if r.remaining > 1:
+                self.prefill_line.append(r)
+
+    def _fits_now(self, r: Request, rows: int) -> bool:
+        rows = min(rows, self.ctx - r.computed)
+        if self.cache.is_open(r.id):
+            return self.cache.can_reserve(r.id, r.computed, rows)
+        missing = -(-(r.computed + rows) // self.cache.page_size)
+        return all(missing <= free for free in self.cache.free_pages())
+
+    def plan(self) -> List[PlannedSegment]:
+        """Admits, picks the step's segments and reserves their pages (preempting if the pool is short)."""
+        self._admit()
+        while True:
+            items = []
+            for r in sorted(self.running, key=lambda q: q.arrival):
+                if r.remaining == 1:
+                    items.append(Item(r, "rider", 1, r.arrival))
+            for r in self.prefill_line:
+                items.append(Item(r, "chunk", min(r.remaining, self.chunk), r.arrival))
+            if not items:
+                return []
+            picks = plan_pass(items, self.budget, self.min_chunk)
+            reserved: List[Request] = []
+            try:
+                for p in picks:
+                    r = p.ref
+                    self.cache.reserve(r.id, r.computed, p.rows)
+                    reserved.append(r)
+            except PoolExhausted:
+                for r in reserved:
+                    self.cache.trim(r.id)
+                if not self._preempt_one():
+                    # a single running request that cannot grow: it ends here
+                    r = self.running[0]
+                    self._release(r)
+                    self._finish(r, "kv_exhausted")
+                    if not self.has_work():
+                        return []
+                    self._admit()
+                continue
+            segments = []
+            for p in picks:
+                r = p.ref
+                toks = r.tokens[r.computed:r.computed + p.rows]
+                segments.append(PlannedSegment(r, r.computed, toks, r.computed + p.rows == len(r.prompt) + len(r.output)))
+                if p.kind == "chunk":
+                    self.prefill_line.remove(r)
+                    if r.remaining - p.rows > 1:
+                        self.prefill_line.append(r)   # to the back: prompts alternate
+            return segments
+
+    def _preempt_one(self) -> bool:
+        """The most recently admitted running request gives everything back and waits again, in front."""
+        if len(self.running) <= 1:
+            return False
+        victim = max(self.running, key=lambda q: q.admitted)
+        self._release(victim)
+        victim.state, victim.computed = WAITING, 0
+        victim.preemptions += 1
+        self.preemptions += 1
+        self.waiting.insert(0, victim)
+        return True
+
+    def _release(self, r: Request) -> None:
+        if r in self.running:
+            self.running.remove(r)
+        if r in self.prefill_line:
+            self.prefill_line.remove(r)
+        if self.cache.is_open(r.id):
+            self.cache.close(r.id)
+
+    def _finish(self, r: Request, reason: str) -> None:
+        r.state, r.finish_reason = FINISHED, reason
+        self.finished[r.id] = r
+        if self.on_finish:
+            self.on_finish(r)
+
+    def complete(self, segments: Sequence[PlannedSegment], sampled: Sequence[int]) -> List[Request]:
+        """After the step ran: lengths are committed, the sampled tokens (one per segment that wanted
+        logits, in order) are appended, and requests that are done are finished and freed."""
+        done = []
+        it = iter(sampled)
+        for seg in segments:
+            r = seg.request
+            r.computed = seg.start + len(seg.tokens)
+            self.cache.commit(r.id, r.computed)
+            if not seg.wants_logits:
+                continue
+            tok = next(it)
+            stops = self.eos | set(r.params.stop_token_ids)
+            if tok in stops and not r.params.ignore_eos:
+                reason = "stop"            # the stop token is not part of the output
+            else:
+                r.output.append(tok)
+                reason = "length" if len(r.output) >= r.max_new or len(r.prompt) + len(r.output) >= self.ctx else None
+            if reason:
+                self._release(r)
+                self._finish(r, reason)
+                done.append(r)
+        return done

@@ -75,8 +75,9 @@ class GqaAttention(Mixer):
                                batch.slots[cache.group] if cache.writes else None, cache.keys, cache.values,
                                s.heads, s.kv_heads, s.head_dim, self.rt.page_size, write_kv=cache.writes)
         att = self.rt.buffer("attention_out", self.q_width)[:rows]
+        scratch = self.rt.buffer("attention_scratch", 2 << 20, torch.float32, rows=1)[0]
         ops.attention(qkv, cache.keys, cache.values, att, batch, cache.group, s.heads, s.kv_heads, s.head_dim,
-                      self.rt.page_size, s.window, s.scale)
+                      self.rt.page_size, s.window, s.scale, scratch)
         self.out.forward(att, x, accumulate=True)
 
 

@@ -15,6 +15,7 @@ from __future__ import annotations
 import json
 import mmap
 import struct
+import warnings
 from pathlib import Path
 from typing import Dict, Iterable, Tuple
 
@@ -99,7 +100,9 @@ class SafetensorsFile:
         if hi == lo:
             return torch.empty(shape, dtype=dtype)
         count = (hi - lo) // _DTYPES[_NAMES[dtype]][1]
-        return torch.frombuffer(self._map, dtype=dtype, count=count, offset=lo).reshape(shape)
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore", UserWarning)   # the map is read-only; the tensors are only ever read
+            return torch.frombuffer(self._map, dtype=dtype, count=count, offset=lo).reshape(shape)
 
 
 class TensorSource:

@@ -1,0 +1,152 @@
+"""The cache manager without a model: no page lost, held twice or freed twice, under random orders."""
+import random
+
+import pytest
+
+from jllm_serve_b200.cache import (RELEASED, CacheManager, FixedState, PageBookkeepingError, PagedKeysValues, PagePool,
+                                   PoolExhausted, StateSlotPool)
+
+
+def test_block_table_arithmetic():
+    # docs/24-paged-kv-cache.md:63-68 of the reference: p = 37, B = 16, table [7, 12, 3] -> page 3, row 5
+    table, page_size, p = [7, 12, 3], 16, 37
+    assert (table[p // page_size], p % page_size) == (3, 5)
+
+
+def test_pool_alloc_free_reuse():
+    pool = PagePool(3)
+    a, b, c = pool.alloc("x"), pool.alloc("x"), pool.alloc("y")
+    assert sorted([a, b, c]) == [0, 1, 2] and pool.num_free == 0
+    with pytest.raises(PoolExhausted):
+        pool.alloc("z")
+    pool.free(b, "x")
+    assert pool.alloc("z") == b and pool.reuses == 1          # the page freed last is used again first
+    with pytest.raises(PageBookkeepingError):
+        pool.free(a, "y")                                      # not the holder
+    pool.free(a, "x")
+    with pytest.raises(PageBookkeepingError):
+        pool.free(a, "x")                                      # freed twice
+    pool.check()
+
+
+def test_one_long_request_takes_ceil_pages():
+    # the reference's KvPoolTest: a conversation of 4100 tokens takes ceil(4100 / 16) blocks
+    m = CacheManager([PagedKeysValues(2, 16)] * 3, 16, 300, 4)
+    m.open("a")
+    m.reserve("a", 0, 4100)
+    m.commit("a", 4100)
+    assert len(m.table("a", 0)) == 257 and m.free_pages() == [300 - 257]
+    m.truncate("a", 33)                                        # pages wholly past 33 go back
+    assert len(m.table("a", 0)) == 3 and m.length("a") == 33
+    m.close("a")
+    assert m.free_pages() == [300]                             # everything is released afterwards
+    m.check()
+
+
+def test_groups_by_need_and_tables_per_group():
+    needs = [PagedKeysValues(2, 16), PagedKeysValues(2, 16, window=8), None, PagedKeysValues(2, 16),
+             FixedState((4, 3)), PagedKeysValues(2, 16, window=8)]
+    made = []
+    m = CacheManager(needs, 4, 10, 2, allocate=lambda shape, kind: made.append((shape, kind)) or ("mem", shape))
+    assert [g.runs for g in m.paged] == [[0, 3], [1, 5]] and [g.runs for g in m.fixed] == [[4]]
+    assert ((2, 2, 10, 2, 4, 16), "kv") in made and ((1, 2, 4, 3), "float32") in made
+    assert m.paged_group_of(3) == 0 and m.paged_group_of(5) == 1
+    with pytest.raises(KeyError):
+        m.paged_group_of(2)
+
+
+def test_window_group_gives_pages_back_as_the_window_passes():
+    m = CacheManager([PagedKeysValues(1, 8), PagedKeysValues(1, 8, window=6)], 4, 8, 2)
+    m.open("a")
+    m.reserve("a", 0, 20)
+    released = m.commit("a", 20)
+    # the next query (position 20) sees keys >= 15: pages 0..2 (positions 0..11) are passed; page 3 holds 12..15
+    assert [p for g, p in released if g == 1] == m.table("a", 0)[:3] or len(released) == 3
+    assert m.table("a", 1)[:3] == [RELEASED] * 3 and m.table("a", 1)[3] != RELEASED
+    assert m.free_pages() == [8 - 5, 8 - 2]
+    for pos in range(20, 31):                                  # decoding: the window group stays at <= 3 pages
+        m.reserve("a", pos, 1)
+        m.commit("a", pos + 1)
+        assert sum(p != RELEASED for p in m.table("a", 1)) <= 3
+        m.check()
+    m.close("a")
+    assert m.free_pages() == [8, 8]
+
+
+def test_reserve_takes_all_or_nothing():
+    m = CacheManager([PagedKeysValues(1, 8), PagedKeysValues(1, 8, window=6)], 4, 4, 3)
+    m.open("a")
+    m.open("b")
+    m.reserve("a", 0, 9)          # 3 pages in both groups
+    with pytest.raises(PoolExhausted):
+        m.reserve("b", 0, 8)      # needs 2, one is free
+    assert m.table("b", 0) == [] and m.table("b", 1) == [] and m.free_pages() == [1, 1]
+    assert not m.can_reserve("b", 0, 8) and m.can_reserve("b", 0, 4)
+    assert m.pages_missing("a", 9, 3) == [0, 0] and m.pages_missing("a", 9, 4) == [1, 1]
+    m.check()
+
+
+def test_state_slots():
+    s = StateSlotPool(2)
+    a, b = s.alloc("x"), s.alloc("y")
+    with pytest.raises(PoolExhausted):
+        s.alloc("z")
+    s.free(a, "x")
+    with pytest.raises(PageBookkeepingError):
+        s.free(a, "x")
+    assert s.alloc("z") == a
+    s.check()
+    m = CacheManager([FixedState((3,))], 4, 1, 2)
+    m.open("p")
+    m.open("q")
+    assert {m.state_slot("p"), m.state_slot("q")} == {0, 1}
+    with pytest.raises(PoolExhausted):
+        m.open("r")
+    m.close("p")
+    m.open("r")
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_orders_keep_the_books(seed):
+    """Requests open, grow by portions and single tokens, rewind, and end in random order; after every
+    operation every page is either free once or in exactly one table once."""
+    rng = random.Random(seed)
+    page = rng.choice([1, 4, 16])
+    m = CacheManager([PagedKeysValues(2, 16), PagedKeysValues(2, 16, window=rng.choice([5, 40])), None], page, 40, 5)
+    live, next_id = {}, 0
+    for _ in range(600):
+        op = rng.random()
+        if op < 0.15 and len(live) < 5:
+            rid = f"r{next_id}"
+            next_id += 1
+            m.open(rid)
+            live[rid] = 0
+        elif op < 0.75 and live:
+            rid = rng.choice(list(live))
+            n = rng.choice([1, 1, 1, 2, 7, 33])
+            try:
+                m.reserve(rid, live[rid], n)
+                live[rid] += n
+                m.commit(rid, live[rid])
+            except PoolExhausted:
+                assert not m.can_reserve(rid, live[rid], n)
+        elif op < 0.8 and live:
+            rid = rng.choice(list(live))
+            keep = rng.randrange(live[rid] + 1)
+            try:
+                m.truncate(rid, keep)
+                live[rid] = min(live[rid], keep)
+            except ValueError:
+                pass                                           # a windowed group cannot rewind behind its window
+        elif live:
+            rid = rng.choice(list(live))
+            m.close(rid)
+            del live[rid]
+        m.check()
+        for rid, n in live.items():
+            assert m.length(rid) == n
+            assert len(m.table(rid, 0)) >= -(-n // page)
+    for rid in list(live):
+        m.close(rid)
+    m.check()
+    assert m.free_pages() == [40, 40] and m.slots.num_free == 5

@@ -1,0 +1,281 @@
+"""Each kernel alone against a plain float32 reference of the same operation, at sizes the engine's
+tiny models do not use (GPU)."""
+import math
+
+import pytest
+import torch
+
+from tests.plain import qwen3_plain as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from jllm_serve_b200.csrc import ops as o
+    o.require_device()
+    return o
+
+
+def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator().manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed_rows(ops, dtype):
+    table = rnd(517, 72, dtype=dtype)
+    ids = torch.tensor([0, 516, 3, 3, 100], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 72, device=DEV)
+    ops.embed_rows(ids, table, out)
+    assert torch.equal(out, table.float()[ids.long()])
+
+
+@pytest.mark.parametrize("dim", [72, 1000, 4096, 5120])
+@pytest.mark.parametrize("gain_dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm(ops, dim, gain_dtype):
+    x, gain = rnd(7, dim, scale=3.0), (1 + 0.1 * rnd(dim)).to(gain_dtype)
+    want = P.rmsnorm(x.cpu(), gain.float().cpu(), 1e-5)
+    out = torch.empty(7, dim, device=DEV)
+    ops.rmsnorm(x, gain, 1e-5, out)
+    assert torch.allclose(out.cpu(), want, rtol=2e-6, atol=1e-6)
+    out16 = torch.empty(7, dim, dtype=torch.bfloat16, device=DEV)
+    ops.rmsnorm(x, gain, 1e-5, out16)
+    assert torch.allclose(out16.float().cpu(), want, rtol=2 ** -8, atol=1e-6)
+    idx = torch.tensor([6, 0, 6], dtype=torch.int32, device=DEV)          # gathered rows (the head's input)
+    sel = torch.empty(3, dim, device=DEV)
+    ops.rmsnorm(x, gain, 1e-5, sel, row_index=idx)
+    assert torch.equal(sel, out[idx.long()])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu(ops, dtype):
+    gu = rnd(5, 2 * 200, dtype=dtype, scale=2.0)
+    out = torch.empty(5, 200, dtype=dtype, device=DEV)
+    ops.swiglu(gu, out)
+    g, u = gu.float().cpu()[:, :200], gu.float().cpu()[:, 200:]
+    want = P.silu(g) * u
+    tol = 1e-6 if dtype == torch.float32 else 2 ** -8
+    assert torch.allclose(out.float().cpu(), want, rtol=tol, atol=1e-6)
+
+
+def gemm_want(a, w, bias=None, base=None):
+    y = a.double().cpu() @ w.double().cpu().t()
+    if bias is not None:
+        y = y + bias.double().cpu()
+    if base is not None:
+        y = y + base.double().cpu()
+    return y.float()
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (3, 130, 72), (65, 64, 129), (200, 517, 96)])
+def test_gemm_plain_float32(ops, M, N, K):
+    a, w, bias = rnd(M, K), rnd(N, K, seed=1), rnd(N, seed=2)
+    out = torch.empty(M, N, device=DEV)
+    ops.gemm_plain(a, w, out, bias)
+    assert torch.allclose(out.cpu(), gemm_want(a, w, bias), rtol=1e-5, atol=1e-5)
+    base = rnd(M, N, seed=3)
+    acc = base.clone()
+    ops.gemm_plain(a, w, acc, None, accumulate=True)
+    assert torch.allclose(acc.cpu(), gemm_want(a, w, None, base), rtol=1e-5, atol=1e-5)
+    # a row's result does not depend on the rows beside it: bit for bit
+    one = torch.empty(1, N, device=DEV)
+    ops.gemm_plain(a[M // 2:M // 2 + 1], w, one, bias)
+    assert torch.equal(one[0], out[M // 2])
+
+
+def test_gemm_plain_strided_and_bfloat16(ops):
+    big = rnd(9, 300, dtype=torch.bfloat16)
+    a, w = big[:, 100:172], rnd(50, 72, dtype=torch.bfloat16, seed=4)      # a view with a row stride of 300
+    out = torch.zeros(9, 80, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_plain(a, w, out[:, :50])
+    assert torch.allclose(out[:, :50].float().cpu(), gemm_want(a, w), rtol=2 ** -7, atol=1e-3)
+    assert float(out[:, 50:].abs().max()) == 0
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 9, 16, 31, 33, 64])
+@pytest.mark.parametrize("N,K", [(40, 64), (517, 72), (6144, 4096), (4736, 1000)])
+def test_gemm_small_m(ops, M, N, K):
+    a, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=1, scale=0.05)
+    bias = rnd(N, dtype=torch.bfloat16, seed=2)
+    want = gemm_want(a, w, bias)
+    out = torch.empty(M, N, device=DEV)
+    ops.gemm_small_m(a, w, out, bias)
+    tol = 1e-4 * math.sqrt(K)
+    assert torch.allclose(out.cpu(), want, rtol=1e-4, atol=tol * 0.05)
+    base = rnd(M, N, seed=3)
+    acc = base.clone()
+    ops.gemm_small_m(a, w, acc, None, accumulate=True)
+    assert torch.allclose(acc.cpu(), gemm_want(a, w, None, base), rtol=1e-4, atol=tol * 0.05)
+    out16 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_small_m(a, w, out16)
+    assert torch.allclose(out16.float().cpu(), gemm_want(a, w), rtol=2 ** -7, atol=2e-3)
+
+
+def test_gemm_small_m_refuses_what_it_cannot_do(ops):
+    a, w = rnd(3, 12, dtype=torch.bfloat16), rnd(8, 12, dtype=torch.bfloat16)
+    with pytest.raises(ops.KernelError, match="K % 8"):
+        ops.gemm_small_m(a, w, torch.empty(3, 8, device=DEV))
+    assert not ops.gemm_bf16_fits(a, w, None)
+
+
+# ---- q/k norm + RoPE + cache write, and attention over a shuffled, poisoned pool --------------------------------
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,Hkv,hd,rot,norm", [(6, 2, 48, 24, True), (4, 4, 16, 16, False), (8, 1, 128, 128, True),
+                                                (2, 2, 80, 0, True)])
+def test_qk_norm_rope_store(ops, dtype, H, Hkv, hd, rot, norm):
+    R, page, pages, eps = 11, 4, 9, 1e-5
+    width = (H + 2 * Hkv) * hd
+    qkv = rnd(R, width, dtype=dtype)
+    qg, kg = (1 + 0.1 * rnd(hd)).to(dtype), (1 + 0.1 * rnd(hd, seed=1)).to(dtype)
+    positions = torch.tensor([5, 6, 7, 0, 1, 2, 3, 30, 31, 32, 33], dtype=torch.int32)
+    slots = torch.randperm(pages * page)[:R].to(torch.int32)
+    cos, sin = P.rope_table(range(40), rot, 50000.0) if rot else (None, None)
+    kc = torch.full((pages, Hkv, page, hd), float("nan"), dtype=dtype, device=DEV)
+    vc = torch.full_like(kc, float("nan"))
+    x = qkv.float().cpu().reshape(R, H + 2 * Hkv, hd)
+    q, k, v = x[:, :H], x[:, H:H + Hkv], x[:, H + Hkv:]
+    if norm:
+        q, k = P.rmsnorm(q, qg.float().cpu(), eps), P.rmsnorm(k, kg.float().cpu(), eps)
+    if rot:
+        q, k = P.apply_rope(q, cos[positions.long()], sin[positions.long()]), \
+            P.apply_rope(k, cos[positions.long()], sin[positions.long()])
+    work = qkv.clone()
+    ops.qk_norm_rope_store(work, qg if norm else None, kg if norm else None, eps,
+                           cos.to(DEV) if rot else None, sin.to(DEV) if rot else None, rot, positions.to(DEV),
+                           slots.to(DEV), kc, vc, H, Hkv, hd, page)
+    tol = dict(rtol=1e-5, atol=1e-6) if dtype == torch.float32 else dict(rtol=2 ** -7, atol=1e-3)
+    got = work.float().cpu().reshape(R, H + 2 * Hkv, hd)
+    assert torch.allclose(got[:, :H], q, **tol)
+    assert torch.equal(got[:, H:], x[:, H:])                       # keys and values in the buffer are left alone
+    for r in range(R):
+        pg, off = int(slots[r]) // page, int(slots[r]) % page
+        assert torch.allclose(kc[pg, :, off].float().cpu(), k[r], **tol)
+        assert torch.allclose(vc[pg, :, off].float().cpu(), v[r].to(dtype).float(), **tol)
+    written = torch.zeros(pages * page, dtype=torch.bool)
+    written[slots.long()] = True
+    rest = kc.float().cpu().permute(0, 2, 1, 3).reshape(pages * page, -1)[~written]
+    assert torch.isnan(rest).all()                                   # nothing else was touched
+
+
+def attention_case(ops, dtype, H, Hkv, hd, page, lens, window, scale, make_far_key=False):
+    """Several requests of `lens` cached positions each; the last `q_len` positions of each are the step's rows."""
+    torch.manual_seed(H * 1000 + hd + page)
+    nseq = len(lens)
+    q_lens = [min(l, 1 + 3 * i) for i, l in enumerate(lens)]
+    pages_needed = sum(-(-l // page) for l in lens)
+    pool = pages_needed + 5
+    perm = torch.randperm(pool).tolist()
+    kc = torch.full((pool, Hkv, page, hd), float("nan"), dtype=dtype, device=DEV)
+    vc = torch.full_like(kc, float("nan"))
+    max_blocks = max(-(-l // page) for l in lens) + 2
+    tables = torch.full((nseq, max_blocks), -1, dtype=torch.int32)
+    rows_q, row_seg, row_pos, wants = [], [], [], []
+    for s, L in enumerate(lens):
+        k, v, q = torch.randn(L, Hkv, hd), torch.randn(L, Hkv, hd), torch.randn(L, H, hd)
+        if make_far_key:
+            # one early key that the last query matches strongly: a fault that drops or misplaces far keys shows
+            far = 1 if L > 3 else 0
+            k[far, :, :] = 0
+            k[far, :, 0] = 6.0 / scale / max(1.0, hd ** 0.5)
+            q[L - 1, :, :] *= 0.05
+            q[L - 1, :, 0] = hd ** 0.5
+            v[far] = 7.0
+        k, v, q = k.to(dtype).float(), v.to(dtype).float(), q.to(dtype).float()
+        for b in range(-(-L // page)):
+            pg = perm.pop()
+            tables[s, b] = pg
+            n = min(page, L - b * page)
+            kc[pg, :, :n] = k[b * page:b * page + n].transpose(0, 1).to(dtype).to(DEV)
+            vc[pg, :, :n] = v[b * page:b * page + n].transpose(0, 1).to(dtype).to(DEV)
+        want = P.causal_gqa_attention(q, k, v, scale, window).reshape(L, H * hd)
+        for p in range(L - q_lens[s], L):
+            rows_q.append(q[p].reshape(-1))
+            row_seg.append(s)
+            row_pos.append(p)
+            wants.append(want[p])
+    qd = torch.stack(rows_q).to(dtype).to(DEV)
+    out = torch.empty_like(qd)
+    return qd, kc, vc, out, torch.tensor(row_seg, dtype=torch.int32, device=DEV), \
+        torch.tensor(row_pos, dtype=torch.int32, device=DEV), tables.to(DEV), torch.stack(wants), q_lens
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,Hkv,hd,page,window", [(6, 2, 48, 16, 0), (4, 4, 16, 4, 0), (8, 1, 128, 16, 0),
+                                                   (6, 3, 80, 8, 21), (4, 2, 256, 16, 0), (2, 1, 32, 1, 7)])
+def test_attention_plain(ops, dtype, H, Hkv, hd, page, window):
+    lens, scale = [1, 17, 64, 131, 300], 1.0 / math.sqrt(hd)
+    for far in (False, True):
+        q, kc, vc, out, rseg, rpos, tables, want, _ = attention_case(ops, dtype, H, Hkv, hd, page, lens, window, scale,
+                                                                      far)
+        ops.attention_plain(q, q.stride(0), kc, vc, out, rseg, rpos, tables, q.shape[0], H, Hkv, hd, page, window, scale)
+        tol = dict(rtol=1e-4, atol=2e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+        assert torch.isfinite(out).all()
+        assert torch.allclose(out.float().cpu(), want, **tol), float((out.float().cpu() - want).abs().max())
+
+
+@pytest.mark.parametrize("splits", [1, 3, 8])
+@pytest.mark.parametrize("H,Hkv,hd,page,window", [(6, 2, 48, 16, 0), (4, 4, 16, 4, 0), (32, 8, 128, 16, 0),
+                                                   (6, 3, 80, 8, 21), (16, 1, 256, 16, 0), (2, 1, 32, 1, 7),
+                                                   (8, 2, 64, 16, 100)])
+def test_attention_decode(ops, H, Hkv, hd, page, window, splits):
+    """One query per request: rows of the decode kernel against the plain attention, also split over blocks."""
+    lens, scale = [1, 17, 64, 131, 300, 1000], 1.0 / math.sqrt(hd)
+    for far in (False, True):
+        q, kc, vc, out, rseg, rpos, tables, want, q_lens = attention_case(ops, torch.bfloat16, H, Hkv, hd, page, lens,
+                                                                          window, scale, far)
+        # keep the last row of every request only: one query position per row
+        last = torch.tensor([sum(q_lens[:i + 1]) - 1 for i in range(len(lens))], device=DEV)
+        q1, rseg1, rpos1, want1 = q[last].contiguous(), rseg[last].contiguous(), rpos[last].contiguous(), want[last.cpu()]
+        out1 = torch.full_like(q1, float("nan"))
+        scratch = torch.full((ops.attention_decode_scratch_floats(len(lens), H, hd, splits) + 1,), float("nan"),
+                             device=DEV)
+        ops.attention_decode(q1, kc, vc, out1, rseg1, rpos1, tables, len(lens), H, Hkv, hd, page, window, scale, splits,
+                             scratch)
+        assert torch.isfinite(out1).all()
+        assert torch.allclose(out1.float().cpu(), want1, rtol=2e-2, atol=2e-2), float((out1.float().cpu() - want1).abs().max())
+
+
+# ---- choosing tokens -----------------------------------------------------------------------------------------
+
+def test_argmax_lowest_index_among_equals(ops):
+    logits = rnd(4, 151936)
+    logits[1, 70000] = logits[1, 150000] = 50.0
+    logits[2, 0] = 60.0
+    logits[3, 151935] = 60.0
+    out = torch.empty(4, dtype=torch.int32, device=DEV)
+    ops.argmax(logits, out)
+    assert out.tolist() == [P.argmax_lowest(logits[0].cpu()), 70000, 0, 151935]
+    ops.argmax(logits, out, vocab=151000)                    # padding rows of the head are never chosen
+    assert out.tolist()[3] == P.argmax_lowest(logits[3, :151000].cpu())
+
+
+@pytest.mark.parametrize("T,k,p,mp", [(0.8, 0, 1.0, 0.0), (1.0, 20, 0.95, 0.0), (0.6, 0, 0.9, 0.0), (1.3, 0, 1.0, 0.05),
+                                      (0.7, 5, 1.0, 0.3), (1.0, 2000, 0.5, 0.0), (0.9, 3, 0.5, 0.9)])
+def test_sample_follows_the_plain_walk(ops, T, k, p, mp):
+    V, rows = 1000, 24
+    logits = rnd(rows, V, scale=2.5, seed=int(T * 10) + k)
+    logits[:, 17] = logits[:, 400]                              # equal logits: the lower index comes first
+    g = torch.Generator().manual_seed(5)
+    u = torch.rand(rows, generator=g, dtype=torch.float64)
+    u[0], u[1] = 0.0, 0.999999
+    f = lambda v, dt: torch.full((rows,), v, dtype=dt, device=DEV)
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops.sample(logits, f(T, torch.float32), f(k, torch.int32), f(p, torch.float32), f(mp, torch.float32), u.to(DEV), out)
+    for r in range(rows):
+        idx, w = P.sampling_weights(logits[r].cpu(), T, k, p, mp)
+        assert out[r].item() == P.draw(idx, w, float(u[r])), (r, float(u[r]))
+
+
+def test_sample_rows_have_their_own_parameters(ops):
+    logits = rnd(3, 517, scale=3.0)
+    out = torch.empty(3, dtype=torch.int32, device=DEV)
+    t = torch.tensor([0.0, 1.0, 1.0], device=DEV)
+    k = torch.tensor([0, 1, 4], dtype=torch.int32, device=DEV)
+    ops.sample(logits, t, k, torch.ones(3, device=DEV), torch.zeros(3, device=DEV),
+               torch.tensor([0.3, 0.3, 0.99999], dtype=torch.float64, device=DEV), out)
+    top4 = torch.topk(logits[2], 4).indices.tolist()
+    assert out[0].item() == int(logits[0].argmax()) and out[1].item() == int(logits[1].argmax())
+    assert out[2].item() == top4[3]

@@ -1,0 +1,191 @@
+"""The scheduler's decisions without a model: pass forming, admission, finishing, preemption (CPU)."""
+import random
+
+import pytest
+
+from jllm_serve_b200.cache import CacheManager, PagedKeysValues
+from jllm_serve_b200.cli import Settings, SettingsError, main
+from jllm_serve_b200.engine.scheduler import Item, Request, Scheduler, plan_pass
+from jllm_serve_b200.sampling import SamplingParams
+
+
+def names(picks):
+    return [f"{p.ref}:{p.rows}" for p in picks]
+
+
+def worked_example():
+    # the reference's worked pass (docs/25-scheduler.md:140-159; SchedulerPolicyTest.java:60-108): decoding
+    # slots D1..D6, a 5-row verification run V1, and two prompts of 256 rows each waiting to be prefilled
+    return [Item("D1", "rider", 1, 0), Item("P-A", "chunk", 256, 1), Item("V1", "rider", 5, 2),
+            Item("D2", "rider", 1, 3), Item("D3", "rider", 1, 4), Item("D4", "rider", 1, 5), Item("D5", "rider", 1, 6),
+            Item("D6", "rider", 1, 7), Item("P-B", "chunk", 256, 8)]
+
+
+def test_riders_first_then_one_chunk():
+    picks = plan_pass(worked_example(), 288, 16)
+    assert names(picks) == ["P-A:256", "D1:1", "V1:5", "D2:1", "D3:1", "D4:1", "D5:1", "D6:1"]
+    assert sum(p.rows for p in picks) == 267
+
+
+def test_chunk_is_trimmed_to_the_room_riders_never():
+    picks = plan_pass(worked_example(), 100, 16)
+    assert names(picks)[0] == "P-A:89" and sum(p.rows for p in picks) == 100
+
+
+def test_chunk_waits_when_the_leftover_is_too_small():
+    picks = plan_pass(worked_example(), 20, 16)                 # 9 rows left < min_chunk
+    assert all(p.kind == "rider" for p in picks) and sum(p.rows for p in picks) == 11
+
+
+def test_small_chunk_runs_whole_and_nothing_stalls():
+    assert names(plan_pass([Item("P", "chunk", 7, 0), Item("D", "rider", 1, 1)], 64, 16)) == ["P:7", "D:1"]
+    # a run larger than the budget still goes, alone
+    assert names(plan_pass([Item("V", "rider", 9, 0)], 4, 16)) == ["V:9"]
+    assert names(plan_pass([Item("P", "chunk", 500, 0)], 64, 16)) == ["P:64"]
+    assert plan_pass([], 64, 16) == []
+
+
+# ---- the scheduler over a real cache manager, with a fake model -------------------------------------------
+
+def make(pages=64, page_size=4, budget=32, chunk=16, max_running=4, ctx=256, eos=()):
+    cache = CacheManager([PagedKeysValues(1, 8)], page_size, pages, max_running)
+    return Scheduler(cache, ctx, budget, chunk, min_chunk=4, max_running=max_running, eos_ids=eos), cache
+
+
+def drive(s, cache, token_of=lambda r: 7, limit=10000):
+    """Runs the loop with a fake model; returns the list of steps as [(request id, start, rows, wants)]."""
+    steps = []
+    while s.has_work():
+        plan = s.plan()
+        if not plan:
+            break
+        steps.append([(p.request.id, p.start, len(p.tokens), p.wants_logits) for p in plan])
+        s.complete(plan, [token_of(p.request) for p in plan if p.wants_logits])
+        cache.check()
+        assert len(steps) < limit
+    return steps
+
+
+def test_prompt_is_cut_into_portions_and_decoding_rides_along():
+    s, cache = make()
+    s.add(Request("a", list(range(40)), SamplingParams.greedy_params(3)))
+    s.add(Request("b", list(range(5)), SamplingParams.greedy_params(6)))
+    steps = drive(s, cache)
+    assert steps[0] == [("a", 0, 16, False)]
+    assert steps[1] == [("b", 0, 5, True)]                       # prompts alternate: a went to the back of the line
+    assert steps[2] == [("a", 16, 16, False), ("b", 5, 1, True)]  # b decodes beside a's next portion
+    assert steps[3] == [("a", 32, 8, True), ("b", 6, 1, True)]
+    assert all(rows <= 32 for st in steps for rows in [sum(x[2] for x in st)])
+    assert s.finished["a"].output == [7, 7, 7] and s.finished["a"].finish_reason == "length"
+    assert len(s.finished["b"].output) == 6
+    assert cache.free_pages() == [64] and not cache.requests
+
+
+def test_stop_token_ends_without_being_emitted():
+    s, cache = make(eos=(9,))
+    seq = iter([4, 5, 9, 1, 1])
+    s.add(Request("a", [1, 2, 3], SamplingParams.greedy_params(10)))
+    drive(s, cache, token_of=lambda r: next(seq))
+    assert s.finished["a"].output == [4, 5] and s.finished["a"].finish_reason == "stop"
+    s.add(Request("b", [1, 2, 3], SamplingParams.greedy_params(4, ignore_eos=True)))
+    drive(s, cache, token_of=lambda r: 9)
+    assert s.finished["b"].output == [9, 9, 9, 9] and s.finished["b"].finish_reason == "length"
+
+
+def test_context_limits():
+    s, cache = make(ctx=16)
+    with pytest.raises(ValueError, match="does not fit the context"):
+        s.add(Request("big", list(range(16)), SamplingParams.greedy_params(4)))
+    with pytest.raises(ValueError, match="empty"):
+        s.add(Request("none", [], SamplingParams.greedy_params(4)))
+    s.add(Request("a", list(range(12)), SamplingParams.greedy_params(100)))
+    drive(s, cache)
+    assert len(s.finished["a"].output) == 4 and s.finished["a"].finish_reason == "length"   # clamped to ctx - prompt
+
+
+def test_max_running_and_first_come_first_served():
+    s, cache = make(max_running=2)
+    for i in range(4):
+        s.add(Request(f"r{i}", [1, 2, 3], SamplingParams.greedy_params(2)))
+    steps = drive(s, cache)
+    first_seen = []
+    for st in steps:
+        for rid, *_ in st:
+            if rid not in first_seen:
+                first_seen.append(rid)
+        assert len({rid for rid, *_ in st}) <= 2
+    assert first_seen == ["r0", "r1", "r2", "r3"]
+
+
+def test_preempts_the_newest_when_pages_run_out_and_recomputes():
+    # 6 pages of 4 positions: two requests of 8 + up to 8 new tokens cannot both stay
+    s, cache = make(pages=6, page_size=4, budget=32, chunk=16, max_running=2)
+    s.add(Request("old", list(range(8)), SamplingParams.greedy_params(8)))
+    s.add(Request("new", list(range(8)), SamplingParams.greedy_params(8)))
+    steps = drive(s, cache)
+    assert s.preemptions >= 1 and s.finished["new"].preemptions >= 1 and s.finished["old"].preemptions == 0
+    assert len(s.finished["old"].output) == 8 and len(s.finished["new"].output) == 8
+    # after its preemption `new` is prefilled again from position 0 with what it had generated so far
+    restarts = [x for st in steps for x in st if x[0] == "new" and x[1] == 0]
+    assert len(restarts) >= 2 and restarts[-1][2] > 8
+    assert cache.free_pages() == [6]
+
+
+def test_request_that_can_never_fit_ends_with_kv_exhausted():
+    s, cache = make(pages=2, page_size=4)
+    s.add(Request("huge", list(range(20)), SamplingParams.greedy_params(4)))
+    s.add(Request("ok", [1, 2], SamplingParams.greedy_params(2)))
+    drive(s, cache)
+    assert s.finished["huge"].finish_reason == "kv_exhausted" and s.finished["huge"].output == []
+    assert s.finished["ok"].finish_reason == "length"
+    s2, cache2 = make(pages=3, page_size=4)
+    s2.add(Request("grows", list(range(10)), SamplingParams.greedy_params(50)))
+    drive(s2, cache2)
+    assert s2.finished["grows"].finish_reason == "kv_exhausted" and len(s2.finished["grows"].output) == 3
+    assert cache2.free_pages() == [3]
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_random_load_always_finishes(seed):
+    rng = random.Random(seed)
+    s, cache = make(pages=24, page_size=4, budget=24, chunk=12, max_running=4, ctx=128)
+    want = {}
+    for i in range(12):
+        n, m = rng.randrange(1, 40), rng.randrange(1, 20)
+        s.add(Request(f"r{i}", [rng.randrange(50) for _ in range(n)], SamplingParams.greedy_params(m)))
+        want[f"r{i}"] = m
+    drive(s, cache, token_of=lambda r: len(r.output))
+    assert set(s.finished) == set(want)
+    for rid, m in want.items():
+        assert s.finished[rid].output == list(range(m))              # preemption loses no token and repeats none
+    assert cache.free_pages() == [24]
+
+
+# ---- settings and command line ------------------------------------------------------------------------------
+
+def test_settings_layers_aliases_and_errors(tmp_path):
+    f = tmp_path / "my.properties"
+    f.write_text("# comment\nsampling.top-k = 5\nbackend.ctx=300\n")
+    s = Settings.load(["--config", str(f), "--temp", "0", "--sampling.top-p=0.5", "--ignore-eos"]).validate()
+    assert s.get("sampling.top-k") == "5" and s.sources["sampling.top-k"] == str(f)
+    assert s.sampling().temperature == 0 and s.sampling().top_p == 0.5 and s.sampling().ignore_eos
+    assert s.sources["sampling.temperature"] == "flag" and s.sources["backend.batch"] == "default"
+    assert "backend.ctx = 300" in s.describe()
+    with pytest.raises(SettingsError, match="unknown option --nope"):
+        Settings.load(["--nope", "1"])
+    with pytest.raises(SettingsError, match="top_p"):
+        Settings.load(["--top-p", "0"]).validate()
+    f.write_text("sampling.topk=5\n")
+    with pytest.raises(SettingsError, match="unknown setting"):
+        Settings.load(["--config", str(f)])
+    assert main(["run", "--nope"]) == 2 and main(["frobnicate"]) == 2 and main(["config"]) == 0
+
+
+def test_sampling_params_validation():
+    for bad in (dict(temperature=-0.1), dict(top_k=-1), dict(top_p=0.0), dict(top_p=1.5), dict(min_p=2.0),
+                dict(temperature=float("nan")), dict(max_tokens=0)):
+        with pytest.raises(ValueError):
+            SamplingParams(**bad)
+    d = SamplingParams()
+    assert (d.temperature, d.top_k, d.top_p, d.min_p, d.seed, d.max_tokens) == (0.6, 20, 0.95, 0.0, -1, 1024)
+    assert SamplingParams(temperature=0).greedy and SamplingParams(top_k=1).greedy and not d.greedy
