@@ -1,0 +1,273 @@
+"""Decode and prefill throughput of the Qwen3-8B shape with random weights on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one decode step of a batch of 8 requests whose contexts end at 4,096 tokens. `value` is
+decoded tokens per second timed on the device with CUDA events around exactly K steps (each step:
+the batch tables copied to the device, the captured decode graph replayed, argmax on the device);
+`e2e` is the same through the public entry point (`Engine.add_request` / `Engine.step_once`): host
+token lists in, sampled tokens read back on the host every step, prompts prefilled by the engine
+itself. `prefill` times one 2,048-token prompt; `roofline` compares the bytes a decode step has to
+read (every weight once plus the cache of the live requests) with the measured copy bandwidth;
+`points` holds decode at batch 1 and 64. Peaks come from MEASURED_PEAKS.json when it exists.
+
+The engine runs on one GPU; for --gpus above 1 the program says so and exits with 2.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+QWEN3_8B = dict(model_type="qwen3", architectures=["Qwen3ForCausalLM"], hidden_size=4096, num_hidden_layers=36,
+                num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288,
+                vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                attention_bias=False, use_sliding_window=False, max_position_embeddings=40960, hidden_act="silu")
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+PAGE = 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        try:
+            raw = json.loads(path.read_text())
+            out = {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]), "source": "measured"}
+            if "bf16_tflops_sustained" in raw:
+                out["bf16_tflops_sustained"] = float(raw["bf16_tflops_sustained"])
+            return out
+        except (KeyError, ValueError, TypeError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while a timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "--id=0", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = [int(r[0]) for r in self.rows if r and r[0].isdigit()]
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 6 for n, v in zip(names, r[2:6]) if v.lower() == "active"})
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def model_numbers(cfg: dict, layers: int) -> dict:
+    D, H, Hkv, hd, F, V = (cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"],
+                           cfg["intermediate_size"], cfg["vocab_size"])
+    per_layer = D * (H + 2 * Hkv) * hd + H * hd * D + 3 * D * F
+    return {"layer_params": per_layer, "head_params": V * D, "weight_bytes": 2 * (per_layer * layers + V * D),
+            "kv_bytes_per_token": 2 * layers * Hkv * hd * 2,
+            "attn_flops_per_layer": lambda T: 4 * (T * (T + 1) // 2) * H * hd}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"],
+                    help="run fewer layers than the configuration has (named in the record)")
+    ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-points", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "beniaminp/jllm-serve is a Java 26 program with an Apple "
+                          "Metal GPU path (no Python package, no CUDA code): pip cannot install it and no JDK is present"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not built")
+        return 2
+    args.warmup = max(3, args.warmup)
+
+    import torch
+
+    from jllm_serve_b200.csrc import ops
+    from jllm_serve_b200.engine import Engine, Segment
+    from jllm_serve_b200.sampling import SamplingParams
+
+    cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
+    nums = model_numbers(cfg, args.layers)
+    pk = peaks()
+    dev = torch.device("cuda:0")
+    biggest = 64 if not args.skip_points else args.batch
+    pool_tokens = biggest * CONTEXT + 2 * PREFILL_TOKENS
+    t0 = time.time()
+    engine = Engine(config=cfg, seed=0, dtype="bfloat16", ctx=CONTEXT, page_size=PAGE, num_pages=pool_tokens // PAGE,
+                    max_batch_tokens=PREFILL_TOKENS + 64, chunk=PREFILL_TOKENS, max_running=biggest)
+    runner = engine.runner
+    print(f"bench: {runner.describe()} (built in {time.time() - t0:.0f} s)", file=sys.stderr, flush=True)
+    for g in runner.cache.paged:      # any cached values do for timing; zeros would be kinder to the memory system
+        g.storage.normal_()
+    out_tok = torch.empty(64, dtype=torch.int32, device=dev)
+
+    def events():
+        return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def decode_device_timed(batch: int, steps: int, warmup: int):
+        """`batch` requests whose contexts END at CONTEXT after warmup + steps decoded tokens; the cache content
+        is synthetic. Returns (ms per step, mean context during the timed steps, kernels launched)."""
+        ids = [f"d{batch}-{i}" for i in range(batch)]
+        start = CONTEXT - warmup - steps
+        for i in ids:
+            runner.cache.open(i)
+            runner.cache.reserve(i, 0, start)
+            runner.cache.commit(i, start)
+
+        def one_step():
+            segs = [Segment(i, [1 + k], runner.cache.length(i), [0]) for k, i in enumerate(ids)]
+            logits = runner.step(segs)
+            ops.argmax(logits, out_tok[:batch])
+
+        for _ in range(warmup):
+            one_step()
+        torch.cuda.synchronize()
+        before = ops.launch_count
+        s, e = events()
+        s.record()
+        for _ in range(steps):
+            one_step()
+        e.record()
+        torch.cuda.synchronize()
+        ms = s.elapsed_time(e) / steps
+        launched = ops.launch_count - before
+        for i in ids:
+            runner.finish(i)
+        return ms, CONTEXT - steps / 2.0, launched
+
+    def decode_bytes(batch: int, context: float) -> float:
+        return nums["weight_bytes"] + batch * context * nums["kv_bytes_per_token"]
+
+    # ---- the headline: decode at the default batch, clocks sampled meanwhile -------------------------------
+    clocks = ClockSampler()
+    clocks.start()
+    ms_step, mean_ctx, launches = decode_device_timed(args.batch, args.steps, args.warmup)
+    clock_record = clocks.stop()
+    value = args.batch * 1000.0 / ms_step
+    achieved = decode_bytes(args.batch, mean_ctx) / (ms_step * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / pk["hbm_gbs"], 4), "peak_source": pk["source"]}
+
+    # ---- prefill of one 2,048-token prompt ---------------------------------------------------------------------
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, cfg["vocab_size"], (PREFILL_TOKENS,), generator=g).tolist()
+
+    def prefill_once(tag):
+        s, e = events()
+        s.record()
+        runner.step([Segment(tag, prompt, 0, [PREFILL_TOKENS - 1])])
+        e.record()
+        torch.cuda.synchronize()
+        runner.finish(tag)
+        return s.elapsed_time(e)
+
+    times = [prefill_once(f"p{i}") for i in range(5)]
+    pre_ms = statistics.median(times[2:])
+    flops = 2.0 * nums["layer_params"] * args.layers * PREFILL_TOKENS + nums["attn_flops_per_layer"](PREFILL_TOKENS) \
+        * args.layers + 2.0 * nums["head_params"]
+    prefill = {"value": round(PREFILL_TOKENS / pre_ms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
+               "frac": round(flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "tflops": round(flops / pre_ms / 1e9, 1)}
+
+    # ---- decode at batch 1 and 64 --------------------------------------------------------------------------------
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            ms_b, _, _ = decode_device_timed(b, max(8, args.steps // 2), 3)
+            points[f"decode_b{b}"] = round(b * 1000.0 / ms_b, 1)
+
+    # ---- end to end through the public entry point --------------------------------------------------------------
+    e2e = None
+    if not args.skip_e2e:
+        e2e = end_to_end(engine, args.batch, args.steps, args.warmup, cfg["vocab_size"])
+
+    record = {
+        "metric": "decode tok/s @ batch 8, context 4096 (Qwen3-8B shape, bf16, random weights)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic token ids, random-init weights N(0, 0.02); device-timed cache content synthetic",
+        "config": {"model": "Qwen3-8B shape", "layers": args.layers, "layers_of_config": QWEN3_8B["num_hidden_layers"],
+                   "hidden": 4096, "heads": 32, "kv_heads": 8, "head_dim": 128, "intermediate": 12288,
+                   "vocab": 151936, "global_batch": args.batch, "seq_len": CONTEXT, "page_size": PAGE,
+                   "parallelism": "single GPU", "l2": "inputs larger than L2 (weights 15 GB per step)",
+                   "cuda_graphs": runner.use_graphs},
+        "clocks": clock_record, "e2e": e2e, "gpu_launches": launches, "prefill": prefill, "roofline": roofline,
+        "points": points,
+    }
+    print(json.dumps(record))
+    return 0
+
+
+def end_to_end(engine, batch: int, steps: int, warmup: int, vocab: int):
+    """Decode tokens per second through Engine.add_request / Engine.step_once: every step copies its batch
+    tables from pinned host memory to the device and reads the sampled tokens back to the host."""
+    import torch
+
+    from jllm_serve_b200.sampling import SamplingParams
+    new_tokens = warmup + steps + 1
+    prompt_len = CONTEXT - new_tokens
+    g = torch.Generator().manual_seed(2)
+    params = SamplingParams.greedy_params(max_tokens=new_tokens, ignore_eos=True)
+    ids = [engine.add_request(torch.randint(0, vocab, (prompt_len,), generator=g).tolist(), params)
+           for _ in range(batch)]
+    sched = engine.scheduler
+    while any(r.remaining > 1 or not r.output for r in sched.running + sched.waiting):
+        engine.step_once()                       # prefill (untimed): until every request is decoding
+    for _ in range(warmup - 1):
+        engine.step_once()
+    torch.cuda.synchronize()
+    h2d = engine.runner.builder.bytes_per_step(batch)
+    t0 = time.perf_counter()
+    done = 0
+    for _ in range(steps):
+        engine.step_once()
+        done += batch
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    engine.run_until_done()
+    for i in ids:
+        engine.scheduler.finished.pop(i, None)
+    return {"value": round(done / dt, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * batch,
+            "ms_per_step": round(dt / steps * 1e3, 4)}
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -51,8 +51,13 @@ def require_device() -> None:
     _device_ok = True
 
 
+launch_count = 0   # kernels of this library launched (or captured into a graph) by this process
+
+
 def _call(name, *args):
+    global launch_count
     lib = library()
+    launch_count += 1
     code = getattr(lib, name)(*args)
     if code != 0:
         raise KernelError(f"{name} failed ({code}): {lib.jllm_last_error().decode(errors='replace')}")
@@ -183,6 +188,8 @@ def attention_decode(q, k_cache, v_cache, out, row_seg, row_pos, block_tables, r
     if splits > 1:
         assert scratch is not None and scratch.dtype == torch.float32 and \
             scratch.numel() >= attention_decode_scratch_floats(rows, heads, head_dim, splits)
+    global launch_count
+    launch_count += 1 if splits > 1 else 0     # the combine kernel
     _call("jllm_attention_decode", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
           out.stride(0), row_seg.data_ptr(), row_pos.data_ptr(), block_tables.data_ptr(), block_tables.stride(0),
           rows, heads, kv_heads, head_dim, page_size, int(window), float(scale), int(splits), _p(scratch), _stream())
@@ -192,18 +199,19 @@ def attention(q, k_cache, v_cache, out, batch, group, heads, kv_heads, head_dim,
               scratch=None) -> None:
     """Causal attention of every row of the batch over its own request's cached keys and values."""
     if batch.decode_only and attention_decode_fits(q.dtype, heads, kv_heads, head_dim):
-        splits = decode_splits(batch.rows, kv_heads, batch.max_kv_len if window <= 0 else min(window, batch.max_kv_len),
-                               heads, head_dim, scratch)
+        bucket = batch.kv_bucket if window <= 0 else max(1, min(batch.kv_bucket, window // 256))
+        splits = decode_splits(batch.rows, kv_heads, bucket, heads, head_dim, scratch)
         return attention_decode(q, k_cache, v_cache, out, batch.row_seg, batch.positions, batch.block_tables[group],
                                 batch.rows, heads, kv_heads, head_dim, page_size, window, scale, splits, scratch)
     attention_plain(q, q.stride(0), k_cache, v_cache, out, batch.row_seg, batch.positions, batch.block_tables[group],
                     batch.rows, heads, kv_heads, head_dim, page_size, window, scale)
 
 
-def decode_splits(rows, kv_heads, max_keys, heads, head_dim, scratch, target_blocks: int = 2 * 148) -> int:
-    """How many blocks share one row's keys: enough to fill the GPU, each with at least 256 keys."""
+def decode_splits(rows, kv_heads, kv_bucket, heads, head_dim, scratch, target_blocks: int = 2 * 148) -> int:
+    """How many blocks share one row's keys: enough to fill the GPU, each with at least 256 keys
+    (`kv_bucket` = the longest request's keys in units of 256)."""
     want = -(-target_blocks // max(1, rows * kv_heads))
-    splits = max(1, min(want, max_keys // 256, 32))
+    splits = max(1, min(want, kv_bucket, 32))
     if scratch is None:
         return 1
     while splits > 1 and attention_decode_scratch_floats(rows, heads, head_dim, splits) > scratch.numel():

@@ -44,6 +44,7 @@ class StepBatch:
     num_wanted: int
     max_q_len: int
     max_kv_len: int
+    kv_bucket: int = 1                     # max_kv_len in units of 256 keys, capped: picks the decode split
     host_seg_start: List[int] = field(default_factory=list)
     host_state_slots: List[int] = field(default_factory=list)
 
@@ -73,6 +74,10 @@ class BatchBuilder:
         self._copied = torch.cuda.Event() if torch.cuda.is_available() else None
         self._np_small = self._host_small.numpy()
         self._np_tables = self._host_tables.numpy().reshape(max(1, G), S, max_blocks)
+
+    def bytes_per_step(self, segments: int) -> int:
+        """Bytes a step with `segments` segments copies from pinned host memory to the device."""
+        return 4 * (self._dev_small.numel() + self.groups * segments * self.max_blocks)
 
     def _row_view(self, buf, i):
         R = self.max_rows
@@ -154,4 +159,5 @@ class BatchBuilder:
             state_slots=self._seg_view(d, 3)[:S],
             block_tables=[dt[g, :S] for g in range(self.groups)],
             num_wanted=n_want, max_q_len=max_q, max_kv_len=max_kv,
+            kv_bucket=max(1, min(32, max_kv // 256, -(-296 // rows))),
             host_seg_start=[int(v) for v in sstart[:S]], host_state_slots=[int(v) for v in sslot[:S]])

@@ -85,6 +85,9 @@ class ModelRunner:
                                     self.page_size)
         self.steps = 0
         self.use_graphs = bool(cuda_graphs)
+        self.graph_safe = all(getattr(b.mixer, "graph_safe", True) and getattr(b.feed_forward, "graph_safe", True)
+                              for b in getattr(self.model, "blocks", []))
+        self._graphs, self._graph_seen, self._static_logits, self._graph_kernels = {}, set(), None, {}
 
     def _allocate(self, shape, kind):
         if kind == "kv":
@@ -152,7 +155,7 @@ class ModelRunner:
             for r in opened:
                 self.cache.close(r)
             raise
-        logits = self.model.forward(batch, self.cache, logits_out)
+        logits = self._run_model(batch, logits_out)
         for seg in segments:
             released = self.cache.commit(seg.request, seg.start + len(seg.tokens))
             if self.poison:
@@ -160,6 +163,41 @@ class ModelRunner:
         self.steps += 1
         self.last_batch = batch
         return logits
+
+    def _run_model(self, batch: StepBatch, logits_out):
+        """Decode-only batches are replayed from a captured CUDA graph: a step is some hundreds of short
+        kernels, and launching them one by one from the host costs more than running them (the reference
+        met the same wall and answered with decode replay, docs/08-metal-backend.md:1354 there). A graph is
+        captured the second time a shape is seen (the first run warms every buffer up) and is keyed by what
+        the launches bake in: rows, wanted rows and the split of the attention's key range. All device
+        addresses a step uses are fixed (batch tables, scratch buffers, the cache), so replaying is exact.
+        The returned logits live in a buffer that the next replay overwrites."""
+        if not (self.use_graphs and self.graph_safe and batch.decode_only):
+            return self.model.forward(batch, self.cache, logits_out)
+        key = (batch.rows, batch.num_wanted, batch.kv_bucket)
+        graph = self._graphs.get(key)
+        if graph is None:
+            if key not in self._graph_seen:
+                self._graph_seen.add(key)
+                return self.model.forward(batch, self.cache, logits_out)
+            if self._static_logits is None:
+                self._static_logits = torch.empty((self.max_requests, self.vocab), dtype=torch.float32,
+                                                  device=self.device)
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launch_count
+            with torch.cuda.graph(graph):
+                self.model.forward(batch, self.cache, self._static_logits)
+            self._graphs[key] = graph
+            self._graph_kernels[key] = ops.launch_count - before
+            ops.launch_count = before
+        graph.replay()
+        ops.launch_count += self._graph_kernels[key]
+        out = self._static_logits[:batch.num_wanted]
+        if logits_out is not None:
+            logits_out[:batch.num_wanted].copy_(out)
+            return logits_out[:batch.num_wanted]
+        return out
 
     def finish(self, request: Hashable) -> None:
         """The request is over: everything it holds is given back."""

@@ -65,6 +65,10 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # False for a part whose forward decides on the host from values that change between steps of the same
+    # shape (it cannot be captured once and replayed); decode steps then run launch by launch
+    graph_safe = True
+
     @classmethod
     def cache_need(cls, spec):
         """A `cache.CacheNeed` (or None): what a run of this mixer keeps between steps."""
@@ -75,6 +79,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    graph_safe = True
+
     def forward(self, xb, x, batch) -> None:
         raise NotImplementedError
 
