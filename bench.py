@@ -109,6 +109,7 @@ def main() -> int:
                     help="run fewer layers than the configuration has (named in the record)")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--skip-prefill", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "beniaminp/jllm-serve is a Java 26 program with an Apple "
@@ -200,7 +201,7 @@ def main() -> int:
         runner.finish(tag)
         return s.elapsed_time(e)
 
-    times = [prefill_once(f"p{i}") for i in range(5)]
+    times = [prefill_once(f"p{i}") for i in range(5)] if not args.skip_prefill else [float("nan")] * 5
     pre_ms = statistics.median(times[2:])
     flops = 2.0 * nums["layer_params"] * args.layers * PREFILL_TOKENS + nums["attn_flops_per_layer"](PREFILL_TOKENS) \
         * args.layers + 2.0 * nums["head_params"]

@@ -1,0 +1,445 @@
+// out[m, n] (+)= sum_k a[m, k] * w[n, k] (+ bias[n]) on the 5th-generation tensor cores (tcgen05), bfloat16.
+//
+// The prefill product. A persistent kernel, one block per SM, walks 128 x 256 output tiles:
+//   * warp 0 (one lane) is the TMA producer: for every 64-wide k block it waits for a free stage and
+//     issues two tiled bulk copies (a 128 x 64 tile of A, a 256 x 64 tile of W) into 128-byte-swizzled
+//     shared memory, completing on the stage's "full" mbarrier (no cluster multicast anywhere);
+//   * warp 1 (one lane) issues the MMAs: 4 x tcgen05.mma (M 128, N 256, K 16) per k block, operands
+//     described by shared-memory descriptors, the float32 accumulator in tensor memory (TMEM);
+//     tcgen05.commit frees the stage, and after the last k block signals "accumulator full";
+//   * warps 2-5 are the epilogue: each reads its 32 TMEM lanes (= 32 rows of the tile) with
+//     tcgen05.ld, adds bias / the float32 residual, and stores float32 or bfloat16.
+// TMEM holds two accumulators (2 x 256 columns), so the epilogue of one tile overlaps the main loop of
+// the next. Tiles are visited with m fastest, so the blocks running together share W tiles in L2.
+//
+// Edges need no special code in the main loop: TMA fills out-of-range rows and k with zeros, and the
+// epilogue stores only what lies inside [M, N]. Every mbarrier wait is bounded: if one runs out, the
+// kernel raises an error word that the host reads, all roles leave their loops, and TMEM is freed.
+//
+// Requirements (else the caller uses another kernel): bfloat16, K a multiple of 8, row strides
+// multiples of 8 elements, 16-byte aligned base pointers.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int THREADS = 192;           // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
+constexpr int TMEM_COLS = 512;
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+
+// ---- PTX wrappers ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false if the phase did not complete within the limit or another role gave up already.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                 uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+        "%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile in shared memory, rows of 64 bfloat16 = 128 bytes, 128-byte swizzle, rows packed:
+// 8-row groups are 1024 bytes apart (stride byte offset); the leading byte offset is unused for swizzled
+// K-major layouts. Bits: start address >> 4 at [0,14), LBO >> 4 at [16,30), SBO >> 4 at [32,46),
+// descriptor version 1 at [46,48), layout type 2 (SWIZZLE_128B) at [61,64).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor of kind::f16: float32 accumulate (1 at [4,6)), A and B bfloat16 (1 at [7,10) and
+// [10,13)), both K-major (0 at 15 and 16), N >> 3 at [17,23), M >> 4 at [24,29).
+constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+template <typename Tout>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, VecRef bias,
+                    int has_bias, Tout* __restrict__ out, int ldo, int accumulate, int M, int N, int K,
+                    int* __restrict__ error_word) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzled tiles want 1024-byte alignment
+    uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bars = base + STAGES * STAGE_BYTES;
+    // barriers: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]; then the TMEM base and the abort flag
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+    auto acc_full_bar = [&](int b) { return bars + 8u * (2 * STAGES + b); };
+    auto acc_empty_bar = [&](int b) { return bars + 8u * (2 * STAGES + 2 + b); };
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(aligned + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 4));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN, tiles = tiles_m * tiles_n;
+    const int k_blocks = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full_bar(b), 1);
+            mbar_init(acc_empty_bar(b), 4);   // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 2) {   // one warp allocates all 512 TMEM columns (one block per SM: nobody else wants any)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_base_slot)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_base_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t parity = ((it / STAGES) & 1u) ^ 1u;
+                    if (!mbar_wait(empty_bar(s), parity, abort_flag)) { ok = false; break; }
+                    const uint32_t dst = base + s * STAGE_BYTES;
+                    mbar_expect_tx(full_bar(s), STAGE_BYTES);
+                    tma_load_2d(dst, &map_a, kb * BK, m0, full_bar(s));
+                    tma_load_2d(dst + A_BYTES, &map_w, kb * BK, n0, full_bar(s));
+                }
+            }
+            if (!ok) { *abort_flag = 1; atomicExch(error_word, 1); }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            uint32_t it = 0, local_tile = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local_tile) {
+                const uint32_t buf = local_tile & 1u;
+                if (!mbar_wait(acc_empty_bar(buf), ((local_tile >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+                tcgen05_fence_after();
+                const uint32_t tmem_d = tmem_base + buf * BN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(full_bar(s), (it / STAGES) & 1u, abort_flag)) { ok = false; break; }
+                    tcgen05_fence_after();
+                    const uint32_t a_addr = base + s * STAGE_BYTES, b_addr = a_addr + A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        // 16 bfloat16 = 32 bytes further along k inside the 128-byte swizzled rows
+                        tcgen05_mma_bf16(tmem_d, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), IDESC,
+                                         (kb | k) != 0);
+                    }
+                    tcgen05_commit(empty_bar(s));   // arrives when the MMAs above have read the stage
+                }
+                if (ok) tcgen05_commit(acc_full_bar(buf));
+            }
+            if (!ok) { *abort_flag = 1; atomicExch(error_word, 2); }
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5, TMEM lanes 32 * (warp % 4) ----------------
+        const int quad = warp & 3;
+        uint32_t local_tile = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local_tile) {
+            const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+            const uint32_t buf = local_tile & 1u;
+            if (!mbar_wait(acc_full_bar(buf), (local_tile >> 1) & 1u, abort_flag)) { ok = false; break; }
+            tcgen05_fence_after();
+            const int row = m0 + quad * 32 + lane;
+            const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(taddr + c0, v);
+                tmem_ld_wait();
+                if (row < M) {
+                    const int n_base = n0 + c0;
+                    Tout* dst = out + (size_t)row * ldo + n_base;
+                    if (n_base + 32 <= N) {
+                        if constexpr (sizeof(Tout) == 4) {
+                            float4* d4 = reinterpret_cast<float4*>(dst);
+                            const bool vec = (((uintptr_t)dst) & 15u) == 0;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                float4 r;
+                                r.x = __uint_as_float(v[4 * j + 0]);
+                                r.y = __uint_as_float(v[4 * j + 1]);
+                                r.z = __uint_as_float(v[4 * j + 2]);
+                                r.w = __uint_as_float(v[4 * j + 3]);
+                                if (has_bias) {
+                                    r.x += bias[n_base + 4 * j + 0];
+                                    r.y += bias[n_base + 4 * j + 1];
+                                    r.z += bias[n_base + 4 * j + 2];
+                                    r.w += bias[n_base + 4 * j + 3];
+                                }
+                                if (vec) {
+                                    if (accumulate) {
+                                        const float4 o = d4[j];
+                                        r.x += o.x; r.y += o.y; r.z += o.z; r.w += o.w;
+                                    }
+                                    d4[j] = r;
+                                } else {
+                                    float* d = reinterpret_cast<float*>(dst) + 4 * j;
+                                    if (accumulate) { r.x += d[0]; r.y += d[1]; r.z += d[2]; r.w += d[3]; }
+                                    d[0] = r.x; d[1] = r.y; d[2] = r.z; d[3] = r.w;
+                                }
+                            }
+                        } else {
+                            const bool vec = (((uintptr_t)dst) & 15u) == 0;
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                uint32_t p[4];
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    float lo = __uint_as_float(v[8 * j + 2 * e]), hi = __uint_as_float(v[8 * j + 2 * e + 1]);
+                                    if (has_bias) { lo += bias[n_base + 8 * j + 2 * e]; hi += bias[n_base + 8 * j + 2 * e + 1]; }
+                                    if (accumulate) { lo += to_float(dst[8 * j + 2 * e]); hi += to_float(dst[8 * j + 2 * e + 1]); }
+                                    __nv_bfloat162 b2 = __floats2bfloat162_rn(lo, hi);
+                                    p[e] = *reinterpret_cast<uint32_t*>(&b2);
+                                }
+                                if (vec) {
+                                    reinterpret_cast<uint4*>(dst)[j] = make_uint4(p[0], p[1], p[2], p[3]);
+                                } else {
+#pragma unroll
+                                    for (int e = 0; e < 4; ++e) {
+                                        __nv_bfloat162 b2 = *reinterpret_cast<__nv_bfloat162*>(&p[e]);
+                                        dst[8 * j + 2 * e] = b2.x;
+                                        dst[8 * j + 2 * e + 1] = b2.y;
+                                    }
+                                }
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if (n_base + j < N) {
+                                float r = __uint_as_float(v[j]);
+                                if (has_bias) r += bias[n_base + j];
+                                if (accumulate) r += to_float(dst[j]);
+                                dst[j] = from_float<Tout>(r);
+                            }
+                        }
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+        }
+        if (!ok && lane == 0) { *abort_flag = 1; atomicExch(error_word, 3); }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 2) {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---- host side: tensor maps (cached) and the launch ---------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr;
+    long long rows, cols, ld;
+    int box_rows;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = std::hash<const void*>()(k.ptr);
+        h = h * 1000003u ^ std::hash<long long>()(k.rows * 131 + k.cols);
+        return h * 1000003u ^ std::hash<long long>()(k.ld * 7 + k.box_rows);
+    }
+};
+
+// A [rows, cols] bfloat16 matrix with row stride ld, read in boxes of box_rows x 64 with the 128-byte swizzle.
+int tensor_map_for(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    const MapKey key{ptr, rows, cols, ld, box_rows};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = it->second;
+        return JLLM_OK;
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return jllm_fail(JLLM_CUDA_ERROR, "gemm_tcgen05: the driver does not offer cuTensorMapEncodeTiled");
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    CUtensorMap map;
+    const CUresult r = fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return jllm_fail(JLLM_CUDA_ERROR, "gemm_tcgen05: cuTensorMapEncodeTiled failed (%d) for [%lld, %lld] ld %lld",
+                         (int)r, rows, cols, ld);
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, map);
+    *out = map;
+    return JLLM_OK;
+}
+
+// The error word lives in device memory that belongs to the library (no allocation): its address is looked
+// up once per device.
+__device__ int g_gemm_error_word = 0;
+
+int* error_word_for_device() {
+    static int* words[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!words[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_gemm_error_word) != cudaSuccess) return nullptr;
+        words[dev] = static_cast<int*>(p);
+    }
+    return words[dev];
+}
+
+}  // namespace
+
+JLLM_EXPORT int jllm_gemm_tcgen05_fits(const void* a, int lda, const void* w, int ldw, int M, int N, int K) {
+    return M >= 1 && N >= 1 && K >= 8 && K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && ((uintptr_t)a % 16) == 0 &&
+           ((uintptr_t)w % 16) == 0;
+}
+
+// Reads and clears the error word that a kernel whose wait ran out has raised (0 = none). Synchronises the device.
+JLLM_EXPORT int jllm_gemm_tcgen05_error() {
+    int* word = error_word_for_device();
+    if (!word) return -1;
+    int v = 0;
+    if (cudaMemcpy(&v, word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (v) cudaMemset(word, 0, sizeof(int));
+    return v;
+}
+
+JLLM_EXPORT int jllm_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, const void* bias, int bias_dtype,
+                                  void* out, int out_dtype, int ldo, int accumulate, int M, int N, int K, int max_blocks,
+                                  cudaStream_t stream) {
+    JLLM_REQUIRE(jllm_gemm_tcgen05_fits(a, lda, w, ldw, M, N, K),
+                 "gemm_tcgen05: needs K %% 8 == 0 and 16-byte aligned rows (M=%d N=%d K=%d lda=%d ldw=%d)", M, N, K, lda,
+                 ldw);
+    JLLM_REQUIRE(ldo >= N, "gemm_tcgen05: ldo=%d < N=%d", ldo, N);
+    CUtensorMap map_a, map_w;
+    int rc = tensor_map_for(a, M, K, lda, BM, &map_a);
+    if (rc != JLLM_OK) return rc;
+    rc = tensor_map_for(w, N, K, ldw, BN, &map_w);
+    if (rc != JLLM_OK) return rc;
+    int* error_word = error_word_for_device();
+    if (!error_word) return jllm_fail(JLLM_CUDA_ERROR, "gemm_tcgen05: no error word");
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    int grid = tiles < sms ? tiles : sms;
+    if (max_blocks > 0 && grid > max_blocks) grid = max_blocks;
+    const VecRef b{bias, bias_dtype};
+    if (out_dtype == JLLM_F32) {
+        auto kern = gemm_tcgen05_kernel<float>;
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        kern<<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_w, b, bias != nullptr, (float*)out, ldo, accumulate, M, N, K,
+                                                    error_word);
+    } else {
+        auto kern = gemm_tcgen05_kernel<__nv_bfloat16>;
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        kern<<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_w, b, bias != nullptr, (__nv_bfloat16*)out, ldo, accumulate, M,
+                                                    N, K, error_word);
+    }
+    return jllm_check_launch("gemm_tcgen05");
+}

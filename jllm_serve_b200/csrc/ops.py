@@ -80,6 +80,8 @@ class _Signatures:
     jllm_qk_norm_rope_store = [P, I, P, P, I, I, F, P, P, I, P, P, P, P, I, I, I, I, I, I, I, P]
     jllm_gemm_plain = [P, I, I, P, I, P, I, P, I, I, I, I, I, I, P]
     jllm_gemm_small_m = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, P]
+    jllm_gemm_tcgen05 = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, P]
+    jllm_gemm_tcgen05_error = []
     jllm_attention_plain = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P]
     jllm_attention_decode = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
     jllm_argmax = [P, I, I, I, P, P]
@@ -154,16 +156,40 @@ def _small_m_fits(a, w) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
+def _tcgen05_fits(a, w) -> bool:
+    M, K = a.shape
+    return (M >= 1 and K >= 8 and K % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
 def gemm_bf16_fits(a, w, out) -> bool:
     """Whether the tensor-core kernels take this product; otherwise the CUDA-core kernel runs it."""
-    return a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and _small_m_fits(a, w)
+    return a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and _tcgen05_fits(a, w)
+
+
+SMALL_M_ROWS = 32   # up to here the weight-streaming kernel wins; above, the tcgen05 tiles
 
 
 def gemm_bf16(a, w, out, bias=None, accumulate=False) -> None:
     """out (+)= a @ w.T (+ bias) on the tensor cores: bfloat16 operands, float32 accumulation."""
-    if _small_m_fits(a, w):
+    if a.shape[0] <= SMALL_M_ROWS and _small_m_fits(a, w):
         return gemm_small_m(a, w, out, bias, accumulate)
+    if _tcgen05_fits(a, w):
+        return gemm_tcgen05(a, w, out, bias, accumulate)
     raise KernelError("the tensor-core matrix product is not built for this shape")
+
+
+def gemm_tcgen05(a, w, out, bias=None, accumulate=False, max_blocks: int = 0) -> None:
+    """The prefill product: TMA-fed tcgen05.mma tiles of 128 x 256 with the accumulator in tensor memory."""
+    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.stride(-1) == 1
+    _call("jllm_gemm_tcgen05", a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), _p(bias),
+          _DT[bias.dtype] if bias is not None else F32, out.data_ptr(), _DT[out.dtype], out.stride(0),
+          int(accumulate), a.shape[0], w.shape[0], a.shape[1], int(max_blocks), _stream())
+
+
+def gemm_tcgen05_error() -> int:
+    """0, or the code a tcgen05 kernel raised because one of its bounded waits ran out (synchronises)."""
+    return library().jllm_gemm_tcgen05_error()
 
 
 def gemm_small_m(a, w, out, bias=None, accumulate=False, tuning: int = 0) -> None:

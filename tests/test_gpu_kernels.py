@@ -113,6 +113,27 @@ def test_gemm_small_m(ops, M, N, K):
     assert torch.allclose(out16.float().cpu(), gemm_want(a, w), rtol=2 ** -7, atol=2e-3)
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (1, 8, 8), (100, 517, 72), (300, 1000, 200), (2048, 6144, 4096),
+                                   (257, 4096, 12288), (64, 300, 4096), (129, 257, 136)])
+def test_gemm_tcgen05(ops, M, N, K):
+    a, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=1, scale=0.05)
+    bias = rnd(N, dtype=torch.bfloat16, seed=2)
+    want = gemm_want(a, w, bias)
+    out = torch.full((M, N), float("nan"), device=DEV)
+    ops.gemm_tcgen05(a, w, out, bias)
+    assert ops.gemm_tcgen05_error() == 0
+    tol = 1e-4 * math.sqrt(K) * 0.05
+    assert torch.allclose(out.cpu(), want, rtol=1e-4, atol=tol), float((out.cpu() - want).abs().max())
+    base = rnd(M, N, seed=3)
+    acc = base.clone()
+    ops.gemm_tcgen05(a, w, acc, None, accumulate=True, max_blocks=3)    # few blocks: every block walks many tiles
+    assert torch.allclose(acc.cpu(), gemm_want(a, w, None, base), rtol=1e-4, atol=tol)
+    out16 = torch.zeros(M, N + 8, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tcgen05(a, w, out16[:, :N])
+    assert torch.allclose(out16[:, :N].float().cpu(), gemm_want(a, w), rtol=2 ** -7, atol=2e-3)
+    assert float(out16[:, N:].abs().max()) == 0 and ops.gemm_tcgen05_error() == 0
+
+
 def test_gemm_small_m_refuses_what_it_cannot_do(ops):
     a, w = rnd(3, 12, dtype=torch.bfloat16), rnd(8, 12, dtype=torch.bfloat16)
     with pytest.raises(ops.KernelError, match="K % 8"):
