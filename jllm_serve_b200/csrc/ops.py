@@ -84,6 +84,7 @@ class _Signatures:
     jllm_gemm_tcgen05_error = []
     jllm_attention_plain = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P]
     jllm_attention_decode = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
+    jllm_attention_prefill = [P, I, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P]
     jllm_argmax = [P, I, I, I, P, P]
     jllm_sample = [P, I, I, I, P, P, P, P, P, P, P]
 
@@ -229,8 +230,25 @@ def attention(q, k_cache, v_cache, out, batch, group, heads, kv_heads, head_dim,
         splits = decode_splits(batch.rows, kv_heads, bucket, heads, head_dim, scratch)
         return attention_decode(q, k_cache, v_cache, out, batch.row_seg, batch.positions, batch.block_tables[group],
                                 batch.rows, heads, kv_heads, head_dim, page_size, window, scale, splits, scratch)
+    if q.dtype == torch.bfloat16 and attention_prefill_fits(head_dim):
+        return attention_prefill(q, k_cache, v_cache, out, batch.seg_start, batch.seg_len, batch.seg_kv_len,
+                                 batch.block_tables[group], batch.rows, heads, kv_heads, head_dim, page_size, window,
+                                 scale)
     attention_plain(q, q.stride(0), k_cache, v_cache, out, batch.row_seg, batch.positions, batch.block_tables[group],
                     batch.rows, heads, kv_heads, head_dim, page_size, window, scale)
+
+
+def attention_prefill_fits(head_dim) -> bool:
+    return head_dim in (64, 128, 256)
+
+
+def attention_prefill(q, k_cache, v_cache, out, seg_start, seg_len, seg_kv_len, block_tables, rows, heads, kv_heads,
+                      head_dim, page_size, window, scale) -> None:
+    """Flash attention of prompt portions: segments of consecutive rows, each over its own request's pages."""
+    _call("jllm_attention_prefill", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+          out.stride(0), seg_start.data_ptr(), seg_len.data_ptr(), seg_kv_len.data_ptr(), block_tables.data_ptr(),
+          block_tables.stride(0), seg_start.numel(), rows, heads, kv_heads, head_dim, page_size, int(window),
+          float(scale), _stream())
 
 
 def decode_splits(rows, kv_heads, kv_bucket, heads, head_dim, scratch, target_blocks: int = 2 * 148) -> int:

@@ -181,11 +181,11 @@ def test_qk_norm_rope_store(ops, dtype, H, Hkv, hd, rot, norm):
     assert torch.isnan(rest).all()                                   # nothing else was touched
 
 
-def attention_case(ops, dtype, H, Hkv, hd, page, lens, window, scale, make_far_key=False):
+def attention_case(ops, dtype, H, Hkv, hd, page, lens, window, scale, make_far_key=False, q_lens=None):
     """Several requests of `lens` cached positions each; the last `q_len` positions of each are the step's rows."""
     torch.manual_seed(H * 1000 + hd + page)
     nseq = len(lens)
-    q_lens = [min(l, 1 + 3 * i) for i, l in enumerate(lens)]
+    q_lens = q_lens or [min(l, 1 + 3 * i) for i, l in enumerate(lens)]
     pages_needed = sum(-(-l // page) for l in lens)
     pool = pages_needed + 5
     perm = torch.randperm(pool).tolist()
@@ -235,6 +235,24 @@ def test_attention_plain(ops, dtype, H, Hkv, hd, page, window):
         tol = dict(rtol=1e-4, atol=2e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
         assert torch.isfinite(out).all()
         assert torch.allclose(out.float().cpu(), want, **tol), float((out.float().cpu() - want).abs().max())
+
+
+@pytest.mark.parametrize("H,Hkv,hd,page,window", [(6, 2, 64, 16, 0), (4, 4, 128, 4, 0), (32, 8, 128, 16, 0),
+                                                   (6, 3, 64, 8, 21), (4, 1, 256, 16, 0), (2, 1, 64, 1, 7),
+                                                   (8, 2, 128, 16, 100)])
+def test_attention_prefill(ops, H, Hkv, hd, page, window):
+    """Portions of prompts (and single rows) of several requests in one launch, starting anywhere in a page."""
+    lens, q_lens, scale = [1, 17, 64, 131, 300, 1000, 77], [1, 17, 30, 131, 200, 65, 1], 1.0 / math.sqrt(hd)
+    for far in (False, True):
+        q, kc, vc, out, rseg, rpos, tables, want, q_lens = attention_case(ops, torch.bfloat16, H, Hkv, hd, page, lens,
+                                                                          window, scale, far, q_lens)
+        out.fill_(float("nan"))
+        starts = [sum(q_lens[:i]) for i in range(len(lens))]
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+        ops.attention_prefill(q, kc, vc, out, i32(starts), i32(q_lens), i32(lens), tables, q.shape[0], H, Hkv, hd, page,
+                              window, scale)
+        assert torch.isfinite(out).all()
+        assert torch.allclose(out.float().cpu(), want, rtol=2e-2, atol=2e-2), float((out.float().cpu() - want).abs().max())
 
 
 @pytest.mark.parametrize("splits", [1, 3, 8])

@@ -22,7 +22,14 @@ TINY_C = dict(model_type="qwen3", architectures=["Qwen3ForCausalLM"], hidden_siz
               use_sliding_window=True, sliding_window=40, max_window_layers=1, max_position_embeddings=1024,
               partial_rotary_factor=0.5, rope_scaling={"rope_type": "linear", "factor": 2.0}, hidden_act="silu")
 
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# D: head_dim 64 (the size the tensor-core prefill attention takes), a window on every layer but the first two
+TINY_D = dict(model_type="qwen3", architectures=["Qwen3ForCausalLM"], hidden_size=136, num_hidden_layers=3,
+              num_attention_heads=6, num_key_value_heads=3, head_dim=64, intermediate_size=264, vocab_size=333,
+              rope_theta=20000.0, rms_norm_eps=2e-6, tie_word_embeddings=True, attention_bias=False,
+              use_sliding_window=True, sliding_window=70, max_window_layers=2, max_position_embeddings=2048,
+              hidden_act="silu")
+
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 
 
 def make_model_folder(config: dict, seed: int, where=None, vector_dtype=None) -> Path:
