@@ -307,3 +307,65 @@ JLLM_EXPORT int jllm_attention_decode(const void* q, int q_stride, const void* k
                                                                    heads, head_dim, splits);
     return jllm_check_launch("attention_combine");
 }
+
+// ---------------------------------------------------------------------------------------------------
+// The same attention with the split scratch inside the library: see attention_decode_static.h.
+// ---------------------------------------------------------------------------------------------------
+#include "attention_decode_static.h"
+
+namespace {
+
+// Partial (output, max, sum) of the key-range splits. The memory belongs to the library image: every GPU
+// that loads the library holds these 8 MiB until the process exits. In host code this name is only a
+// stand-in for the symbol (not a device address); the address comes from cudaGetSymbolAddress below.
+static __device__ __align__(256) float g_decode_static_scratch[JLLM_ATTENTION_DECODE_STATIC_FLOATS];
+
+constexpr int MAX_DEVICES = 64;
+float* g_static_scratch_ptr[MAX_DEVICES] = {};
+
+// Once per device, with that device current: look the array's device address up.
+int static_scratch_for_current_device(float** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return jllm_fail(JLLM_CUDA_ERROR, "attention_decode_static: cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= MAX_DEVICES)
+        return jllm_fail(JLLM_UNSUPPORTED, "attention_decode_static: device %d is beyond the %d devices it keeps track of",
+                         dev, MAX_DEVICES);
+    if (g_static_scratch_ptr[dev] == nullptr) {
+        float* ptr = nullptr;
+        e = cudaGetSymbolAddress((void**)&ptr, g_decode_static_scratch);
+        if (e != cudaSuccess || ptr == nullptr)
+            return jllm_fail(JLLM_CUDA_ERROR, "attention_decode_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        g_static_scratch_ptr[dev] = ptr;
+    }
+    *out = g_static_scratch_ptr[dev];
+    return JLLM_OK;
+}
+
+}  // namespace
+
+JLLM_EXPORT long long jllm_attention_decode_static_capacity() { return JLLM_ATTENTION_DECODE_STATIC_FLOATS; }
+
+JLLM_EXPORT int jllm_attention_decode_static(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                                             void* out, int out_stride, const int* row_seg, const int* row_pos,
+                                             const int* block_tables, int table_stride, int rows, int heads,
+                                             int kv_heads, int head_dim, int page_size, int window, float scale,
+                                             int splits, cudaStream_t stream) {
+    JLLM_REQUIRE(rows >= 0 && heads > 0 && head_dim > 0 && splits >= 1, "attention_decode_static: rows=%d heads=%d "
+                 "head_dim=%d splits=%d", rows, heads, head_dim, splits);
+    const long long need = jllm_attention_decode_scratch_floats(rows, heads, head_dim, splits);
+    if (need > (long long)JLLM_ATTENTION_DECODE_STATIC_FLOATS)
+        return jllm_fail(JLLM_BAD_ARGUMENT,
+                         "attention_decode_static: %d rows x %d heads x %d splits x (head_dim %d + 2) = %lld floats of "
+                         "scratch, the built-in array holds %lld; use fewer splits or rows, or jllm_attention_decode "
+                         "with scratch of your own", rows, heads, splits, head_dim, need,
+                         (long long)JLLM_ATTENTION_DECODE_STATIC_FLOATS);
+    float* scratch = nullptr;
+    const int rc = static_scratch_for_current_device(&scratch);
+    if (rc != JLLM_OK) return rc;
+    // Nothing in the array has to start at zero: every (row, head, split) slot that the combine step reads
+    // is written by the block of that split in the same call, also when the split holds no keys.
+    return jllm_attention_decode(q, q_stride, k_cache, v_cache, out, out_stride, row_seg, row_pos, block_tables,
+                                 table_stride, rows, heads, kv_heads, head_dim, page_size, window, scale, splits,
+                                 scratch, stream);
+}
