@@ -1,0 +1,138 @@
+"""Generation through the public entry point and the command line (GPU)."""
+import json
+import random
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+from tests.helpers import TOL, model_folder, plain_logits
+from tests.plain import qwen3_plain as P
+from tests.tiny import CONFIGS, make_model_folder, random_tokens
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def engine_for(name, dtype, **kw):
+    from jllm_serve_b200.engine import Engine
+    args = dict(dtype=dtype, page_size=8, max_tokens_cached=2048, max_batch_tokens=64, chunk=32, min_chunk=4,
+                max_running=4, ctx=512)
+    args.update(kw)
+    return Engine(model_folder(name), **args)
+
+
+def prompts_for(name, lengths, seed=3):
+    return [random_tokens(n, CONFIGS[name]["vocab_size"], seed + i) for i, n in enumerate(lengths)]
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_generation_float32_equals_plain(name):
+    from jllm_serve_b200.sampling import SamplingParams
+    cfg, w = P.load_plain(model_folder(name))
+    prompts = prompts_for(name, (5, 17, 33))
+    got = engine_for(name, "float32").generate(prompts, SamplingParams.greedy_params(16, ignore_eos=True))
+    for p, r in zip(prompts, got):
+        assert r.tokens == P.greedy_generate(cfg, w, p, 16) and r.finish_reason == "length"
+        assert r.stats.prompt_tokens == len(p) and r.stats.generated == 16
+
+
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_greedy_generation_bfloat16_follows_plain(name):
+    """Every token the bfloat16 engine picks is (within bfloat16's tolerance) a best token of the plain float32
+    logits for the same prefix; the prefix is the engine's own, so one near-tie cannot derail the comparison."""
+    from jllm_serve_b200.sampling import SamplingParams
+    prompts = prompts_for(name, (9, 40, 70))
+    got = engine_for(name, "bfloat16").generate(prompts, SamplingParams.greedy_params(12, ignore_eos=True))
+    for p, r in zip(prompts, got):
+        assert len(r.tokens) == 12
+        logits = plain_logits(model_folder(name), tuple(p + r.tokens[:-1]))
+        for i, t in enumerate(r.tokens):
+            row = logits[len(p) - 1 + i]
+            assert float(row.max() - row[t]) <= TOL["bfloat16"] * float(logits.abs().max()), (i, t)
+
+
+def test_scheduled_together_equals_alone_with_preemption():
+    """Six requests through portions of 32 under a budget of 48 rows and a pool so small that the scheduler must
+    preempt and recompute: the tokens are those of each request generated alone."""
+    from jllm_serve_b200.sampling import SamplingParams
+    name = "B"
+    prompts = prompts_for(name, (70, 1, 33, 64, 129, 20), seed=9)
+    params = SamplingParams.greedy_params(24, ignore_eos=True)
+    alone = [engine_for(name, "float32").generate([p], params)[0].tokens for p in prompts[:3]]
+    tight = engine_for(name, "float32", max_tokens_cached=224, max_batch_tokens=48)
+    got = tight.generate(prompts, params)
+    cfg, w = P.load_plain(model_folder(name))
+    for i, (p, r) in enumerate(zip(prompts, got)):
+        want = alone[i] if i < 3 else P.greedy_generate(cfg, w, p, 24)
+        assert r.tokens == want, f"request {i}"
+    assert tight.scheduler.preemptions > 0, "the pool was large enough: the test did not exercise preemption"
+    assert tight.runner.cache.free_pages() == [28] and not tight.runner.cache.requests
+
+
+def test_temperature_sampling_is_seeded_and_matches_the_plain_walk():
+    from jllm_serve_b200.sampling import SamplingParams
+    name = "B"
+    prompts = prompts_for(name, (1, 7, 64, 129), seed=21)
+    params = [SamplingParams(temperature=0.8, top_k=0, top_p=1.0, seed=100 + i, max_tokens=24, ignore_eos=True)
+              for i in range(4)]
+    together = engine_for(name, "float32").generate(prompts, params)
+    again = engine_for(name, "float32", chunk=16, max_batch_tokens=40).generate(prompts[::-1], params[::-1])[::-1]
+    for a, b in zip(together, again):
+        assert a.tokens == b.tokens                      # the seed decides, not the batch or the cut
+    # the plain walk with the same uniform numbers
+    for p, sp, r in zip(prompts, params, together):
+        rng, toks = random.Random(sp.seed), list(p)
+        for t in r.tokens:
+            logits = plain_logits(model_folder(name), tuple(toks))[-1]
+            idx, w = P.sampling_weights(logits, sp.temperature, sp.top_k, sp.top_p, sp.min_p)
+            assert t == P.draw(idx, w, rng.random())
+            toks.append(t)
+    other = engine_for(name, "float32").generate(prompts[2:3], SamplingParams(temperature=0.8, top_k=20, top_p=0.9,
+                                                                              seed=5, max_tokens=24, ignore_eos=True))
+    assert other[0].tokens != together[2].tokens
+
+
+def test_stop_token_and_context_limit(tmp_path):
+    from jllm_serve_b200.engine import Engine
+    from jllm_serve_b200.sampling import SamplingParams
+    base = CONFIGS["A"]
+    prompt = random_tokens(11, base["vocab_size"], 77)
+    free = Engine(make_model_folder(base, 7, tmp_path / "free"), dtype="float32", ctx=64, max_batch_tokens=32, chunk=16,
+                  max_running=2, page_size=4, max_tokens_cached=256)
+    tokens = free.generate([prompt], SamplingParams.greedy_params(10))[0].tokens
+    stop_at = tokens[4]
+    first = tokens.index(stop_at)
+    stopping = Engine(make_model_folder(dict(base, eos_token_id=[stop_at, 255]), 7, tmp_path / "stop"), dtype="float32",
+                      ctx=64, max_batch_tokens=32, chunk=16, max_running=2, page_size=4, max_tokens_cached=256)
+    r = stopping.generate([prompt], SamplingParams.greedy_params(10))[0]
+    assert r.finish_reason == "stop" and r.tokens == tokens[:first]          # the stop token is not emitted
+    r = stopping.generate([prompt], SamplingParams.greedy_params(10, ignore_eos=True))[0]
+    assert r.finish_reason == "length" and r.tokens == tokens
+    r = free.generate([prompt], SamplingParams.greedy_params(1000))[0]
+    assert r.finish_reason == "length" and len(r.tokens) == 64 - 11            # clamped to the context
+    with pytest.raises(ValueError, match="does not fit the context"):
+        free.generate([list(range(64))], SamplingParams.greedy_params(4))
+    with pytest.raises(ValueError, match="token id outside"):
+        free.generate([[1, 2, 256]], SamplingParams.greedy_params(4))
+
+
+def test_command_line_run_and_bench(tmp_path):
+    folder = model_folder("A")
+    prompt = random_tokens(9, 256, 5)
+    cmd = [sys.executable, str(ROOT / "bin" / "jllm"), "run", "--model", str(folder), "--dtype", "fp32", "--temp", "0",
+           "--max-tokens", "6", "--ctx", "64", "--ignore-eos", "--tokens", ",".join(map(str, prompt))]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    cfg, w = P.load_plain(folder)
+    assert [int(t) for t in proc.stdout.strip().split(",")] == P.greedy_generate(cfg, w, prompt, 6)
+    assert "9 prompt tok (0 cached)" in proc.stderr and "6 generated" in proc.stderr
+    cfg_file = tmp_path / "config.json"
+    cfg_file.write_text(json.dumps(CONFIGS["B"]))
+    proc = subprocess.run([sys.executable, str(ROOT / "bin" / "jllm"), "bench", "--random-weights", "3", "--model-config",
+                           str(cfg_file), "--ctx", "256", "--bench.prompt-tokens", "50", "--bench.max-tokens", "8",
+                           "--bench.rounds", "2"], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.startswith("prefill 50 tok in") and "decode 8 tok in" in proc.stdout

@@ -1,0 +1,261 @@
+"""Each part of a layer alone against its plain counterpart, the layer schedule as data, and a toy
+architecture with a stateful mixer that is defined here and registered from outside the package (GPU)."""
+import math
+from dataclasses import dataclass, field
+
+import pytest
+import torch
+
+from tests import traces
+from tests.helpers import TOL, compare_with_plain, model_folder, replay, requests_for
+from tests.plain import qwen3_plain as P
+from tests.tiny import CONFIGS, make_model_folder, random_tokens
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+
+
+def runtime(dtype, max_rows=256, page=4, ctx=256):
+    from jllm_serve_b200.csrc import ops
+    from jllm_serve_b200.parts import Runtime
+    ops.require_device()
+    return Runtime(DEV, dtype, ctx, max_rows, page)
+
+
+def weights_for(cls, spec, dim, prefix, dtype, seed=0):
+    from jllm_serve_b200.weights import random_tensors
+    wants = cls.wants(spec, dim, prefix)
+    cpu = random_tensors(wants, seed, "cpu", torch.bfloat16)
+    return {k: v.float() for k, v in cpu.items()}, {k: v.to(DEV, dtype if wants[k].role == "matrix" else v.dtype)
+                                                    for k, v in cpu.items()}
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_part(dtype):
+    from jllm_serve_b200.config import NormSpec
+    from jllm_serve_b200.parts import RmsNorm
+    cpu, dev = weights_for(RmsNorm, NormSpec("rmsnorm", 3e-5), 200, "n.", dtype)
+    norm = RmsNorm(NormSpec("rmsnorm", 3e-5), 200, dev, "n.", runtime(dtype))
+    x = torch.randn(9, 200, device=DEV) * 4
+    out = torch.empty(9, 200, dtype=dtype, device=DEV)
+    norm.forward(x, out)
+    want = P.rmsnorm(x.cpu(), cpu["n.weight"], 3e-5)
+    assert torch.allclose(out.float().cpu(), want, rtol=1e-5 if dtype == torch.float32 else 2 ** -7, atol=1e-5)
+
+
+@pytest.mark.parametrize("scaling", [None, {"rope_type": "linear", "factor": 4.0},
+                                     {"rope_type": "yarn", "factor": 8.0, "original_max_position_embeddings": 64}])
+def test_rotary_table_part(scaling):
+    from jllm_serve_b200.config import parse_config
+    from jllm_serve_b200.parts import RotaryTable
+    cfg = dict(CONFIGS["B"], partial_rotary_factor=0.75)
+    if scaling:
+        cfg["rope_scaling"] = scaling
+    spec = parse_config(cfg).rope_tables[0]
+    table = RotaryTable(spec, 300, DEV)
+    cos, sin = P.rope_table(range(300), 24, 1e6, scaling, 512)
+    assert table.rotary_dim == 24 and torch.equal(table.cos.cpu(), cos) and torch.equal(table.sin.cpu(), sin)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows", [1, 40, 130])
+def test_feed_forward_part(dtype, rows):
+    from jllm_serve_b200.config import DenseGluSpec
+    from jllm_serve_b200.parts import DenseGlu
+    spec, dim = DenseGluSpec(hidden=152), 80
+    cpu, dev = weights_for(DenseGlu, spec, dim, "f.", dtype)
+    ffn = DenseGlu(spec, dim, dev, "f.", runtime(dtype))
+    xb = (torch.randn(rows, dim) * 2).to(dtype)
+    x = torch.randn(rows, dim)
+    xd = x.to(DEV)
+    ffn.forward(xb.to(DEV), xd, None)
+    want = x + P.swiglu_feed_forward(xb.float(), cpu["f.gate_proj.weight"], cpu["f.up_proj.weight"],
+                                     cpu["f.down_proj.weight"])
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert torch.allclose(xd.cpu(), want, rtol=tol, atol=tol * float(want.abs().max()))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window, bias, hd", [(0, False, 32), (11, True, 48), (0, True, 64)])
+def test_attention_part_and_block(dtype, window, bias, hd):
+    """The mixer alone and then the whole pre-norm block, on two requests fed in two steps each (a portion,
+    then the rest), over a real cache manager and batch builder."""
+    from jllm_serve_b200.cache import CacheManager
+    from jllm_serve_b200.config import DenseGluSpec, GqaAttentionSpec, LayerSpec, NormSpec, RopeTableSpec
+    from jllm_serve_b200.engine.batch import BatchBuilder, Segment
+    from jllm_serve_b200.parts import PreNormBlock, RotaryTable, RunCache
+    dim, H, Hkv, page = 72, 6, 2, 4
+    aspec = GqaAttentionSpec(heads=H, kv_heads=Hkv, head_dim=hd, window=window, rope_table=0, qk_norm=True,
+                             qk_norm_eps=2e-6, bias=bias, out_bias=bias, scale=1 / math.sqrt(hd))
+    lspec = LayerSpec(aspec, DenseGluSpec(hidden=100), NormSpec("rmsnorm", 2e-6))
+    rt = runtime(dtype, page=page)
+    cpu, dev = weights_for(PreNormBlock, lspec, dim, "L.", dtype)
+    rope = RotaryTable(RopeTableSpec(hd, 5000.0), 256, DEV)
+    block = PreNormBlock(lspec, dim, dict(dev), "L.", rt, [rope])
+
+    def allocate(shape, kind):
+        return torch.full(shape, float("nan"), dtype=dtype, device=DEV)
+
+    cache = CacheManager([block.mixer.cache_need(aspec)], page, 64, 4, allocate=allocate)
+    builder = BatchBuilder(DEV, 256, 4, 64, 1, page)
+    lens = {"a": 37, "b": 21}
+    xs = {r: torch.randn(n, dim) for r, n in lens.items()}
+    got = {r: [] for r in lens}
+    for lo_hi in ((0, 0.6), (0.6, 1.0)):
+        segs, rows = [], []
+        for r, n in lens.items():
+            lo, hi = int(n * lo_hi[0]), int(n * lo_hi[1])
+            if not cache.is_open(r):
+                cache.open(r)
+            cache.reserve(r, lo, hi - lo)
+            segs.append(Segment(r, [0] * (hi - lo), lo))
+            rows.append(xs[r][lo:hi])
+        batch = builder.build(segs, cache, 10)
+        x = torch.cat(rows).to(DEV)
+        k, v = cache.keys_values(0)
+        block.forward(x, batch, RunCache(0, True, 0, k, v))
+        at = 0
+        for s in segs:
+            got[s.request].append(x[at:at + len(s.tokens)].cpu())
+            at += len(s.tokens)
+            cache.commit(s.request, s.start + len(s.tokens))
+    cfg = P.PlainConfig(dict(hidden_size=dim, num_hidden_layers=1, vocab_size=10, num_attention_heads=H,
+                             num_key_value_heads=Hkv, head_dim=hd, intermediate_size=100, rms_norm_eps=2e-6,
+                             rope_theta=5000.0, attention_bias=bias))
+    w = {"model.layers.0." + k[2:]: v for k, v in cpu.items()}
+    for r, n in lens.items():
+        x = xs[r]
+        cos, sin = P.rope_table(range(n), hd, 5000.0)
+        xb = P.rmsnorm(x, w["model.layers.0.input_layernorm.weight"], 2e-6)
+        y, _ = P.attention_block(xb, w, "model.layers.0.self_attn.", cfg, window, cos, sin)
+        x = x + y
+        xb = P.rmsnorm(x, w["model.layers.0.post_attention_layernorm.weight"], 2e-6)
+        want = x + P.swiglu_feed_forward(xb, w["model.layers.0.mlp.gate_proj.weight"], w["model.layers.0.mlp.up_proj.weight"],
+                                         w["model.layers.0.mlp.down_proj.weight"])
+        out = torch.cat(got[r])
+        tol = 2e-5 if dtype == torch.float32 else 3e-2
+        assert torch.isfinite(out).all()
+        assert float((out - want).abs().max()) <= tol * float(want.abs().max()), r
+
+
+# ---- the order of layers is data ---------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_schedule_names_a_layer_twice_and_reads_another_runs_cache(dtype):
+    from jllm_serve_b200.engine import ModelRunner
+    schedule = ((0, None), (1, None), (1, None), (0, 0), (1, 2))   # layer 1 twice with caches of its own; two readers
+    reqs = requests_for("B", (1, 40, 77), seed=4)
+    for steps in (traces.whole(reqs), traces.prompt_then_decode(reqs, 20), traces.mixed(reqs, max_live=3, portion=13)):
+        runner = ModelRunner(model_folder("B"), dtype=dtype, page_size=8, num_pages=40, max_batch_tokens=128,
+                             max_requests=4, ctx=256, schedule=schedule, poison_freed_pages=True)
+        assert len(runner.cache.paged) == 1 and runner.cache.paged[0].runs == [0, 1, 2]
+        got = replay(runner, steps)
+        compare_with_plain(got, model_folder("B"), reqs, dtype, schedule=schedule, what="schedule")
+
+
+# ---- a toy architecture with a stateful mixer, defined and registered here -------------------------------------
+
+def toy_pieces():
+    """Defines and registers the toy parts; returns (config dict, plain forward)."""
+    from jllm_serve_b200.cache import FixedState
+    from jllm_serve_b200.config import (Core, Decoder, DenseGluSpec, GqaAttentionSpec, LayerSpec, MixerSpec, NormSpec,
+                                        RopeTableSpec, register_architecture)
+    from jllm_serve_b200.parts import Mixer, register_mixer
+    from jllm_serve_b200.weights import TensorWant
+
+    @dataclass(frozen=True)
+    class RunningMeanSpec(MixerSpec):
+        kind: str = field(default="toy_running_mean", init=False)
+        width: int = 0
+
+    class RunningMean(Mixer):
+        """y_t = W mean(xb_0 .. xb_t): its state per request is the running sum and the count so far."""
+        graph_safe = False    # walks the batch's segments on the host
+
+        def __init__(self, spec, dim, tensors, prefix, runtime):
+            self.dim = dim
+            self.w = tensors.pop(prefix + "mix.weight").float()
+
+        @classmethod
+        def wants(cls, spec, dim, prefix):
+            return {prefix + "mix.weight": TensorWant((dim, dim))}
+
+        @classmethod
+        def cache_need(cls, spec):
+            return FixedState((spec.width + 1,), "float32")
+
+        def forward(self, xb, x, batch, cache):
+            for seg, start, slot in zip(batch.segments, batch.host_seg_start, batch.host_state_slots):
+                n = len(seg.tokens)
+                state = cache.state[slot]
+                if seg.start == 0:
+                    state.zero_()
+                rows = xb[start:start + n].float()
+                sums = state[:self.dim] + torch.cumsum(rows, dim=0)
+                counts = state[self.dim] + torch.arange(1, n + 1, device=rows.device, dtype=torch.float32)
+                x[start:start + n] += (sums / counts[:, None]) @ self.w.t()
+                state[:self.dim] = sums[-1]
+                state[self.dim] = counts[-1]
+
+    register_mixer("toy_running_mean", RunningMean, replace=True)
+
+    def parse(values):
+        dim, layers = values["width"], values["depth"]
+        norm = NormSpec("rmsnorm", values["eps"])
+        attn = GqaAttentionSpec(heads=4, kv_heads=2, head_dim=16, rope_table=0, qk_norm=True, qk_norm_eps=values["eps"],
+                                scale=0.25)
+        specs = tuple(LayerSpec(attn if l % 2 else RunningMeanSpec(width=dim), DenseGluSpec(hidden=values["ffn"]), norm)
+                      for l in range(layers))
+        core = Core("ToyForCausalLM", "toy_mean", dim, layers, values["vocab"], values["eps"], True, -1, (), 512, "toy")
+        return Decoder(core, specs, (RopeTableSpec(16, 10000.0),), norm)
+
+    register_architecture("toy_mean", parse, replace=True)
+    config = dict(model_type="toy_mean", width=48, depth=3, ffn=72, vocab=97, eps=1e-5)
+
+    def plain_forward(w, tokens):
+        T = len(tokens)
+        x = P.embedding(w["model.embed_tokens.weight"], tokens)
+        cos, sin = P.rope_table(range(T), 16, 10000.0)
+        cfg = P.PlainConfig(dict(hidden_size=48, num_hidden_layers=3, vocab_size=97, num_attention_heads=4,
+                                 num_key_value_heads=2, head_dim=16, intermediate_size=72, rms_norm_eps=1e-5))
+        for l in range(3):
+            p = f"model.layers.{l}."
+            xb = P.rmsnorm(x, w[p + "input_layernorm.weight"], 1e-5)
+            if l % 2:
+                y, _ = P.attention_block(xb, w, p + "self_attn.", cfg, 0, cos, sin)
+            else:
+                mean = torch.cumsum(xb, dim=0) / torch.arange(1, T + 1, dtype=xb.dtype)[:, None]
+                y = mean @ w[p + "self_attn.mix.weight"].t()
+            x = x + y
+            xb = P.rmsnorm(x, w[p + "post_attention_layernorm.weight"], 1e-5)
+            x = x + P.swiglu_feed_forward(xb, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
+                                          w[p + "mlp.down_proj.weight"])
+        return P.linear(P.rmsnorm(x, w["model.norm.weight"], 1e-5), w["model.embed_tokens.weight"])
+
+    return config, plain_forward
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_mixer_with_state_registers_builds_and_steps(dtype, tmp_path):
+    from jllm_serve_b200.config import unregister_architecture
+    from jllm_serve_b200.engine import ModelRunner
+    config, plain_forward = toy_pieces()
+    try:
+        folder = make_model_folder(config, 3, tmp_path / "toy")
+        w = {k: v.float() for k, v in P.read_safetensors(folder / "model.safetensors").items()}
+        reqs = {f"r{i}": random_tokens(n, 97, 50 + i) for i, n in enumerate((1, 30, 61, 18, 45))}
+        for steps in (traces.whole(reqs), traces.prompt_then_decode(reqs, 16), traces.changing_portions(reqs),
+                      traces.mixed(reqs, max_live=3, portion=11)):
+            runner = ModelRunner(folder, dtype=dtype, page_size=4, num_pages=60, max_batch_tokens=128, max_requests=3,
+                                 ctx=128, poison_freed_pages=True)
+            assert len(runner.cache.fixed) == 1 and runner.cache.fixed[0].runs == [0, 2] and not runner.graph_safe
+            got = replay(runner, steps)
+            scale = 0.0
+            for rid, toks in reqs.items():
+                want = plain_forward(w, toks)
+                scale = max(scale, float(want.abs().max()))
+                for p in range(len(toks)):
+                    assert float((got[(rid, p)] - want[p]).abs().max()) <= TOL[dtype] * scale, (rid, p)
+            assert runner.cache.slots.num_free == 3
+    finally:
+        unregister_architecture("toy_mean")
