@@ -110,6 +110,7 @@ def main() -> int:
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true")
+    ap.add_argument("--prefill-only", action="store_true", help="profiling aid: time the prefill alone and print it")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "beniaminp/jllm-serve is a Java 26 program with an Apple "
@@ -177,6 +178,19 @@ def main() -> int:
 
     def decode_bytes(batch: int, context: float) -> float:
         return nums["weight_bytes"] + batch * context * nums["kv_bytes_per_token"]
+
+    if args.prefill_only:
+        g = torch.Generator().manual_seed(1)
+        prompt = torch.randint(0, cfg["vocab_size"], (PREFILL_TOKENS,), generator=g).tolist()
+        for i in range(max(1, args.steps)):
+            s, e = events()
+            s.record()
+            runner.step([Segment(f"p{i}", prompt, 0, [PREFILL_TOKENS - 1])])
+            e.record()
+            torch.cuda.synchronize()
+            runner.finish(f"p{i}")
+            print(json.dumps({"prefill_ms": round(s.elapsed_time(e), 3)}))
+        return 0
 
     # ---- the headline: decode at the default batch, clocks sampled meanwhile -------------------------------
     clocks = ClockSampler()

@@ -243,26 +243,38 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          __nv_bfloat16* __restrict__ out, int out_stride, int heads, int head_dim,
                                          int splits) {
+    constexpr int MAX_SPLITS = 32;
+    __shared__ float weight[MAX_SPLITS];
+    __shared__ float inv_total;
     const int r = blockIdx.x, head = blockIdx.y;
     const size_t slot0 = ((size_t)r * heads + head) * splits;
-    float M = -INFINITY;
-    for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(slot0 + s) * 2]);
-    float L = 0.f;
-    for (int s = 0; s < splits; ++s) {
-        const float ms = part_ml[(slot0 + s) * 2];
-        L += ms == -INFINITY ? 0.f : part_ml[(slot0 + s) * 2 + 1] * exp2f(ms - M);
+    if (threadIdx.x < 32) {
+        // one lane per split: all (max, sum) pairs are fetched at once; the sums over splits go in split order
+        const int s = threadIdx.x;
+        const float ms = s < splits ? part_ml[(slot0 + s) * 2] : -INFINITY;
+        const float ls = s < splits ? part_ml[(slot0 + s) * 2 + 1] : 0.f;
+        float M = ms;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        const float w = ms == -INFINITY ? 0.f : exp2f(ms - M);
+        weight[s] = w;
+        float L = 0.f;
+        for (int i = 0; i < splits; ++i) L += __shfl_sync(0xffffffffu, ls * w, i);
+        if (s == 0) inv_total = 1.f / L;
     }
+    __syncthreads();
+    const float inv = inv_total;
     for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
         float acc = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const float ms = part_ml[(slot0 + s) * 2];
-            if (ms != -INFINITY) acc += part_o[(slot0 + s) * head_dim + d] * exp2f(ms - M);
-        }
-        out[(size_t)r * out_stride + (size_t)head * head_dim + d] = __float2bfloat16_rn(acc / L);
+#pragma unroll 8
+        for (int s = 0; s < splits; ++s) acc += part_o[(slot0 + s) * head_dim + d] * weight[s];
+        out[(size_t)r * out_stride + (size_t)head * head_dim + d] = __float2bfloat16_rn(acc * inv);
     }
 }
 
 }  // namespace
+
+#include "attention_decode_staged.cuh"
 
 // Floats of scratch the split path needs: (head_dim + 2) per (row, head, split).
 JLLM_EXPORT long long jllm_attention_decode_scratch_floats(int rows, int heads, int head_dim, int splits) {
@@ -281,7 +293,7 @@ JLLM_EXPORT int jllm_attention_decode(const void* q, int q_stride, const void* k
     JLLM_REQUIRE(q_stride % 8 == 0 && ((uintptr_t)q % 16) == 0 && ((uintptr_t)k_cache % 16) == 0 &&
                      ((uintptr_t)v_cache % 16) == 0,
                  "attention_decode: q, K and V must be 16-byte aligned (q_stride=%d)", q_stride);
-    JLLM_REQUIRE(splits >= 1 && splits <= 65535 && kv_heads <= 65535, "attention_decode: splits=%d", splits);
+    JLLM_REQUIRE(splits >= 1 && splits <= 32 && kv_heads <= 65535, "attention_decode: splits=%d must be in [1, 32]", splits);
     JLLM_REQUIRE(splits == 1 || scratch != nullptr, "attention_decode: %d splits need scratch memory", splits);
     if (rows == 0) return JLLM_OK;
     const dim3 grid(rows, kv_heads, splits);
@@ -290,6 +302,19 @@ JLLM_EXPORT int jllm_attention_decode(const void* q, int q_stride, const void* k
     float* part_ml = scratch ? scratch + (size_t)rows * heads * splits * head_dim : nullptr;
     const float scale_log2 = scale * LOG2E;
     const int hdc = (head_dim + 63) / 64;
+    if (head_dim == 64 || head_dim == 128 || head_dim == 256) {
+        // the common head sizes stream the cache through a shared-memory ring (attention_decode_staged.cuh)
+#define JLLM_STAGED(HD)                                                                                             \
+    staged::launch<HD>(q, q_stride, k_cache, v_cache, out, out_stride, row_seg, row_pos, block_tables, table_stride, \
+                       rows, heads, kv_heads, page_size, window, scale_log2, splits, part_o, part_ml, stream)
+        if (head_dim == 64) JLLM_STAGED(64); else if (head_dim == 128) JLLM_STAGED(128); else JLLM_STAGED(256);
+#undef JLLM_STAGED
+        int rc2 = jllm_check_launch("attention_decode_staged");
+        if (rc2 != JLLM_OK || splits == 1) return rc2;
+        attention_combine_kernel<<<dim3(rows, heads), 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, out_stride,
+                                                                       heads, head_dim, splits);
+        return jllm_check_launch("attention_combine");
+    }
 #define JLLM_LAUNCH(HDC)                                                                                            \
     {                                                                                                               \
         auto kern = attention_decode_kernel<HDC>;                                                                   \

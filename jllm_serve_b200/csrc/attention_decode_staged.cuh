@@ -1,0 +1,241 @@
+// Decode attention for head sizes 64, 128 and 256: the same block layout and split scheme as the direct
+// kernel of attention_decode.cu, but keys and values travel through shared memory in a ring of stages.
+//
+// A decode step is a stream of the cache: what matters is how many bytes each SM has in flight. Here the
+// 128 threads of a block gather a tile of 64 keys and 64 values (from up to 64 / page_size pages) into
+// XOR-swizzled shared memory with cp.async, three tiles deep, so about two tiles (64 KB at head size 128)
+// are always on their way while the tensor cores work on a third. Warp w owns keys [16 w, 16 w + 16) of
+// every tile: S = Q K^T and O += P V with mma.sync.m16n8k16 from ldmatrix fragments, the G query heads
+// of the kv head being the 16 rows of the M side (rows beyond G are zero). Each warp keeps its own online
+// softmax state; the four are merged at the end exactly as in the direct kernel, and the per-split
+// partials go to the same scratch layout and combine kernel.
+#pragma once
+
+namespace staged {
+
+constexpr int WARPS = 4, THREADS = 128, TILE = 64, STAGES = 3;
+
+__device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldsm4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm4t(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void cp16(uint32_t dst, const void* src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void wait_group() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+template <int HD>
+__device__ __forceinline__ uint32_t off(int r, int c) { return (uint32_t)((r * (HD / 8) + (c ^ (r & 7))) * 16); }
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS)
+attention_decode_staged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
+                               const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
+                               __nv_bfloat16* __restrict__ out, int out_stride, const int* __restrict__ row_seg,
+                               const int* __restrict__ row_pos, const int* __restrict__ block_tables, int table_stride,
+                               int heads, int kv_heads, int page_size, int window, float scale_log2, int splits,
+                               float* __restrict__ part_o, float* __restrict__ part_ml) {
+    constexpr int CHUNKS = HD / 8, TILE_BYTES = TILE * HD * 2, STAGE_BYTES = 2 * TILE_BYTES;
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    const uint32_t s_q = (uint32_t)__cvta_generic_to_shared(smem_raw);
+    const uint32_t s_kv = s_q + 16 * HD * 2;
+    const int r = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int G = heads / kv_heads;
+    const int P = row_pos[r];
+    const int first = window > 0 ? max(0, P + 1 - window) : 0;
+    const int tiles_total = (P + 1 - first + TILE - 1) / TILE;
+    const int tiles_per_split = (tiles_total + splits - 1) / splits;
+    const int tile_lo = split * tiles_per_split, tile_hi = min(tiles_total, tile_lo + tiles_per_split);
+    const int n_tiles = max(0, tile_hi - tile_lo);
+    const int* table = block_tables + (size_t)row_seg[r] * table_stride;
+    const size_t page_stride = (size_t)kv_heads * page_size * HD;
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
+
+    // Q: the G heads of this kv head as rows 0 .. G-1 of a 16-row tile (the rest zero)
+    for (int i = threadIdx.x; i < 16 * CHUNKS; i += THREADS) {
+        const int row = i / CHUNKS, c = i % CHUNKS;
+        const __nv_bfloat16* src = q + (size_t)r * q_stride + (size_t)(kvh * G + min(row, G - 1)) * HD + c * 8;
+        cp16(s_q + off<HD>(row, c), src, row < G ? 16 : 0);
+    }
+    auto load_tile = [&](int i) {   // tile i of this block's range into stage i % STAGES
+        if (i < n_tiles) {
+            const uint32_t dk = s_kv + (i % STAGES) * STAGE_BYTES, dv = dk + TILE_BYTES;
+            const int key0 = first + (tile_lo + i) * TILE;
+            // consecutive threads take consecutive 16-byte chunks of a row (coalesced reads, conflict-free
+            // writes); a power-of-two page size turns the page lookup into a shift and a mask
+            for (int j = threadIdx.x; j < TILE * CHUNKS; j += THREADS) {
+                const int row = j / CHUNKS, c = j % CHUNKS;
+                const int key = key0 + row;
+                const bool ok = key <= P;
+                size_t o = 0;
+                if (ok) {
+                    const int pg = page_shift >= 0 ? key >> page_shift : key / page_size;
+                    const int in_page = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
+                    o = (size_t)table[pg] * page_stride + ((size_t)kvh * page_size + in_page) * HD + c * 8;
+                }
+                cp16(dk + off<HD>(row, c), k_cache + o, ok ? 16 : 0);
+                cp16(dv + off<HD>(row, c), v_cache + o, ok ? 16 : 0);
+            }
+        }
+        commit();   // an empty group keeps the group count in step with the tile count
+    };
+    load_tile(0);           // group 0 also carries Q
+#pragma unroll
+    for (int i = 1; i < STAGES - 1; ++i) load_tile(i);
+
+    uint32_t qf[HD / 16][4];
+    float o[HD / 8][4];
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[j][i] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    for (int i = 0; i < n_tiles; ++i) {
+        wait_group<STAGES - 2>();   // tile i has landed (the groups of later tiles may still be in flight)
+        __syncthreads();            // ... for every thread's part of it; and everyone is done with tile i - 1
+        load_tile(i + STAGES - 1);  // refills the stage that tile i - 1 used
+        if (i == 0) {
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks) ldsm4(qf[ks], s_q + off<HD>(lane & 15, ks * 2 + (lane >> 4)));
+        }
+        const uint32_t sk = s_kv + (i % STAGES) * STAGE_BYTES, sv = sk + TILE_BYTES;
+        const int key0 = first + (tile_lo + i) * TILE + warp * 16;
+        if (key0 > P) continue;     // this warp's 16 keys of the last tile are all past the end (warp-uniform)
+        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+            uint32_t kf[4];
+            ldsm4(kf, sk + off<HD>(warp * 16 + (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1)));
+            mma(s[0], qf[ks], kf[0], kf[1]);
+            mma(s[1], qf[ks], kf[2], kf[3]);
+        }
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int tile = 0; tile < 2; ++tile)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = key0 + tile * 8 + 2 * t + (e & 1);
+                s[tile][e] = key <= P ? s[tile][e] * scale_log2 : -INFINITY;
+                mx[e >> 1] = fmaxf(mx[e >> 1], s[tile][e]);
+            }
+        float corr[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+            const float m_new = fmaxf(m[h], mx[h]);   // finite: key0 <= P, so the warp sees at least one key
+            corr[h] = exp2f(m[h] - m_new);
+            m[h] = m_new;
+            l[h] *= corr[h];
+        }
+        uint32_t pf[4];
+#pragma unroll
+        for (int tile = 0; tile < 2; ++tile) {
+            const float p0 = exp2f(s[tile][0] - m[0]), p1 = exp2f(s[tile][1] - m[0]);
+            const float p2 = exp2f(s[tile][2] - m[1]), p3 = exp2f(s[tile][3] - m[1]);
+            l[0] += p0 + p1;
+            l[1] += p2 + p3;
+            __nv_bfloat162 a = __floats2bfloat162_rn(p0, p1), b = __floats2bfloat162_rn(p2, p3);
+            pf[tile * 2 + 0] = *reinterpret_cast<uint32_t*>(&a);
+            pf[tile * 2 + 1] = *reinterpret_cast<uint32_t*>(&b);
+        }
+#pragma unroll
+        for (int jp = 0; jp < HD / 16; ++jp) {
+            uint32_t vf[4];
+            ldsm4t(vf, sv + off<HD>(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, jp * 2 + (lane >> 4)));
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                o[2 * jp + e][0] *= corr[0];
+                o[2 * jp + e][1] *= corr[0];
+                o[2 * jp + e][2] *= corr[1];
+                o[2 * jp + e][3] *= corr[1];
+            }
+            mma(o[2 * jp], pf, vf[0], vf[1]);
+            mma(o[2 * jp + 1], pf, vf[2], vf[3]);
+        }
+    }
+    wait_group<0>();
+    __syncthreads();                // the stages are free: they become the merge area
+    // ---- merge the four warps (as the direct kernel does) ----
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+    float* so = reinterpret_cast<float*>(smem_raw + 16 * HD * 2);   // [WARPS][16][HD]
+    float* sml = so + WARPS * 16 * HD;                               // [WARPS][16][2]
+    if (t == 0) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            sml[(warp * 16 + g + 8 * h) * 2 + 0] = m[h];
+            sml[(warp * 16 + g + 8 * h) * 2 + 1] = l[h];
+        }
+    }
+    __syncthreads();
+    float scale_w[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float mm = -INFINITY;
+        for (int w = 0; w < WARPS; ++w) mm = fmaxf(mm, sml[(w * 16 + g + 8 * h) * 2]);
+        scale_w[h] = m[h] == -INFINITY ? 0.f : exp2f(m[h] - mm);
+    }
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            so[((size_t)warp * 16 + g + 8 * (e >> 1)) * HD + j * 8 + 2 * t + (e & 1)] = o[j][e] * scale_w[e >> 1];
+    __syncthreads();
+    for (int e = threadIdx.x; e < G * HD; e += THREADS) {
+        const int row = e / HD, d = e % HD;
+        float acc = 0.f, mm = -INFINITY, ll = 0.f;
+        for (int w = 0; w < WARPS; ++w) acc += so[((size_t)w * 16 + row) * HD + d];
+        for (int w = 0; w < WARPS; ++w) mm = fmaxf(mm, sml[(w * 16 + row) * 2]);
+        for (int w = 0; w < WARPS; ++w) {
+            const float mw = sml[(w * 16 + row) * 2];
+            ll += mw == -INFINITY ? 0.f : sml[(w * 16 + row) * 2 + 1] * exp2f(mw - mm);
+        }
+        const int head = kvh * G + row;
+        if (splits == 1) {
+            out[(size_t)r * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc / ll);
+        } else {
+            const size_t slot = ((size_t)r * heads + head) * splits + split;
+            part_o[slot * HD + d] = acc;
+            if (d == 0) {
+                part_ml[slot * 2 + 0] = mm;
+                part_ml[slot * 2 + 1] = ll;
+            }
+        }
+    }
+}
+
+template <int HD>
+void launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out, int out_stride,
+            const int* row_seg, const int* row_pos, const int* block_tables, int table_stride, int rows, int heads,
+            int kv_heads, int page_size, int window, float scale_log2, int splits, float* part_o, float* part_ml,
+            cudaStream_t stream) {
+    const size_t stage_bytes = (size_t)STAGES * 2 * TILE * HD * 2;
+    const size_t merge_bytes = ((size_t)WARPS * 16 * HD + WARPS * 16 * 2) * sizeof(float);
+    const size_t smem = 16 * HD * 2 + (stage_bytes > merge_bytes ? stage_bytes : merge_bytes);
+    auto kern = attention_decode_staged_kernel<HD>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    kern<<<dim3(rows, kv_heads, splits), THREADS, smem, stream>>>(
+        (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
+        (__nv_bfloat16*)out, out_stride, row_seg, row_pos, block_tables, table_stride, heads, kv_heads, page_size,
+        window, scale_log2, splits, part_o, part_ml);
+}
+
+}  // namespace staged

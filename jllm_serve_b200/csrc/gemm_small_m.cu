@@ -87,17 +87,26 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfl
 #pragma unroll
                 for (int h = 0; h < 2; ++h) wv[u][r][h] = (kin && wok[r][h]) ? load_16_stream(wrow[r][h] + k) : zero;
         }
+        // the activations of these chunks: issued before any of the weights is waited for, so that their
+        // (L2) latency overlaps the weights' (HBM) latency instead of following it
+        uint4 xv[UNROLL][NT];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             const int k = (c0 + u * WARPS) * KCHUNK + 8 * t;
             const bool kin = (c0 + u * WARPS) < chunks && k < K;
 #pragma unroll
+            for (int j = 0; j < NT; ++j) xv[u][j] = (kin && aok[j]) ? load_16(arow[j] + k) : zero;
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+#pragma unroll
             for (int j = 0; j < NT; ++j) {
-                const uint4 xv = (kin && aok[j]) ? load_16(arow[j] + k) : zero;
 #pragma unroll
                 for (int r = 0; r < RT; ++r) {
-                    mma_bf16_16816(acc[r][j], wv[u][r][0].x, wv[u][r][1].x, wv[u][r][0].y, wv[u][r][1].y, xv.x, xv.y);
-                    mma_bf16_16816(acc[r][j], wv[u][r][0].z, wv[u][r][1].z, wv[u][r][0].w, wv[u][r][1].w, xv.z, xv.w);
+                    mma_bf16_16816(acc[r][j], wv[u][r][0].x, wv[u][r][1].x, wv[u][r][0].y, wv[u][r][1].y, xv[u][j].x,
+                                   xv[u][j].y);
+                    mma_bf16_16816(acc[r][j], wv[u][r][0].z, wv[u][r][1].z, wv[u][r][0].w, wv[u][r][1].w, xv[u][j].z,
+                                   xv[u][j].w);
                 }
             }
         }

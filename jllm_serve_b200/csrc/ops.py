@@ -251,11 +251,12 @@ def attention_prefill(q, k_cache, v_cache, out, seg_start, seg_len, seg_kv_len, 
           float(scale), _stream())
 
 
-def decode_splits(rows, kv_heads, kv_bucket, heads, head_dim, scratch, target_blocks: int = 2 * 148) -> int:
-    """How many blocks share one row's keys: enough to fill the GPU, each with at least 256 keys
-    (`kv_bucket` = the longest request's keys in units of 256)."""
-    want = -(-target_blocks // max(1, rows * kv_heads))
-    splits = max(1, min(want, kv_bucket, 32))
+def decode_splits(rows, kv_heads, kv_bucket, heads, head_dim, scratch, resident_blocks: int = 2 * 148) -> int:
+    """How many blocks share one row's keys: as many as fit on the GPU at once (two blocks per SM; one block
+    more than that would cost a whole second wave), each with at least 128 keys (`kv_bucket` = the longest
+    request's keys in units of 256)."""
+    want = resident_blocks // max(1, rows * kv_heads)
+    splits = max(1, min(want, 2 * kv_bucket, 32))
     if scratch is None:
         return 1
     while splits > 1 and attention_decode_scratch_floats(rows, heads, head_dim, splits) > scratch.numel():
