@@ -55,6 +55,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     const int r = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int G = heads / kv_heads;
+    pdl_wait();
+    pdl_trigger();
     const int P = row_pos[r];
     const int first = window > 0 ? max(0, P + 1 - window) : 0;
     const int n_keys = P + 1 - first;
@@ -246,6 +248,8 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
     constexpr int MAX_SPLITS = 32;
     __shared__ float weight[MAX_SPLITS];
     __shared__ float inv_total;
+    pdl_wait();
+    pdl_trigger();
     const int r = blockIdx.x, head = blockIdx.y;
     const size_t slot0 = ((size_t)r * heads + head) * splits;
     if (threadIdx.x < 32) {
@@ -311,8 +315,8 @@ JLLM_EXPORT int jllm_attention_decode(const void* q, int q_stride, const void* k
 #undef JLLM_STAGED
         int rc2 = jllm_check_launch("attention_decode_staged");
         if (rc2 != JLLM_OK || splits == 1) return rc2;
-        attention_combine_kernel<<<dim3(rows, heads), 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, out_stride,
-                                                                       heads, head_dim, splits);
+        jllm_launch(attention_combine_kernel, dim3(rows, heads), dim3(128), 0, stream, true, (const float*)part_o,
+                    (const float*)part_ml, (__nv_bfloat16*)out, out_stride, heads, head_dim, splits);
         return jllm_check_launch("attention_combine");
     }
 #define JLLM_LAUNCH(HDC)                                                                                            \

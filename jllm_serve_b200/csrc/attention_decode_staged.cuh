@@ -54,6 +54,8 @@ attention_decode_staged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
     const int r = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int G = heads / kv_heads;
+    pdl_wait();      // the newest key and value of every row were written by the kernel before this one
+    pdl_trigger();
     const int P = row_pos[r];
     const int first = window > 0 ? max(0, P + 1 - window) : 0;
     const int tiles_total = (P + 1 - first + TILE - 1) / TILE;
@@ -232,7 +234,7 @@ void launch(const void* q, int q_stride, const void* k_cache, const void* v_cach
     const size_t smem = 16 * HD * 2 + (stage_bytes > merge_bytes ? stage_bytes : merge_bytes);
     auto kern = attention_decode_staged_kernel<HD>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    kern<<<dim3(rows, kv_heads, splits), THREADS, smem, stream>>>(
+    jllm_launch(kern, dim3(rows, kv_heads, splits), dim3(THREADS), smem, stream, true,
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
         (__nv_bfloat16*)out, out_stride, row_seg, row_pos, block_tables, table_stride, heads, kv_heads, page_size,
         window, scale_log2, splits, part_o, part_ml);

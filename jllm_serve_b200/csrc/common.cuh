@@ -31,6 +31,36 @@ int jllm_check_launch(const char* what);
         if (!(cond)) return jllm_fail(JLLM_BAD_ARGUMENT, __VA_ARGS__); \
     } while (0)
 
+// ---- programmatic dependent launch ---------------------------------------------------------------------
+// A decode step is a chain of some hundreds of short kernels. Launched the ordinary way each one starts
+// only when its predecessor has drained, and its own ramp-up (block scheduling, first loads) is dead time.
+// With programmatic dependent launch the next kernel's blocks become resident while the predecessor still
+// runs: they may do work that does not depend on it (a matrix product fetches its first weights), then
+// wait with pdl_wait() until the predecessor has completed and its writes are visible. Every kernel calls
+// pdl_wait() before it reads anything a predecessor wrote or writes anything a predecessor may read, and
+// only then pdl_trigger(), so at most one successor is resident early. Without the launch attribute both
+// calls return at once.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool jllm_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t jllm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                               bool dependent, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (dependent && jllm_pdl_enabled()) ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ---- element access: everything is computed in float -------------------------------------------------
 
 __device__ __forceinline__ float to_float(float v) { return v; }

@@ -76,8 +76,8 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfl
     }
     const uint4 zero = make_uint4(0, 0, 0, 0);
     const int chunks = (K + KCHUNK - 1) / KCHUNK;
-    for (int c0 = warp; c0 < chunks; c0 += WARPS * UNROLL) {
-        uint4 wv[UNROLL][RT][2];
+    uint4 wv[UNROLL][RT][2];
+    auto load_weights = [&](int c0) {
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             const int k = (c0 + u * WARPS) * KCHUNK + 8 * t;
@@ -87,6 +87,14 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfl
 #pragma unroll
                 for (int h = 0; h < 2; ++h) wv[u][r][h] = (kin && wok[r][h]) ? load_16_stream(wrow[r][h] + k) : zero;
         }
+    };
+    // The weights do not depend on the kernel before this one: the first batch is requested while that kernel
+    // is still running. (Pulling the block's whole slice into L2 ahead of time with a bulk prefetch was tried
+    // and made the step slower: it competes with the running kernel's own stream.)
+    load_weights(warp);
+    pdl_wait();
+    pdl_trigger();
+    for (int c0 = warp; c0 < chunks; c0 += WARPS * UNROLL) {
         // the activations of these chunks: issued before any of the weights is waited for, so that their
         // (L2) latency overlaps the weights' (HBM) latency instead of following it
         uint4 xv[UNROLL][NT];
@@ -110,6 +118,7 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfl
                 }
             }
         }
+        if (c0 + WARPS * UNROLL < chunks) load_weights(c0 + WARPS * UNROLL);
     }
     // partial sums of the 8 warps -> shared memory, laid out [warp][token][row] so the final pass writes
     // consecutive output features from consecutive threads
@@ -148,13 +157,13 @@ int launch(const void* a, int lda, const void* w, int ldw, VecRef bias, int has_
     if (out_dtype == JLLM_F32) {
         auto kern = gemm_small_m_kernel<NT, RT, UNROLL, float>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        kern<<<grid, WARPS * 32, smem, stream>>>((const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)w, ldw, bias,
-                                                 has_bias, (float*)out, ldo, accumulate, M, N, K);
+        jllm_launch(kern, dim3(grid), dim3(WARPS * 32), smem, stream, true, (const __nv_bfloat16*)a, lda,
+                    (const __nv_bfloat16*)w, ldw, bias, has_bias, (float*)out, ldo, accumulate, M, N, K);
     } else {
         auto kern = gemm_small_m_kernel<NT, RT, UNROLL, __nv_bfloat16>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        kern<<<grid, WARPS * 32, smem, stream>>>((const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)w, ldw, bias,
-                                                 has_bias, (__nv_bfloat16*)out, ldo, accumulate, M, N, K);
+        jllm_launch(kern, dim3(grid), dim3(WARPS * 32), smem, stream, true, (const __nv_bfloat16*)a, lda,
+                    (const __nv_bfloat16*)w, ldw, bias, has_bias, (__nv_bfloat16*)out, ldo, accumulate, M, N, K);
     }
     return jllm_check_launch("gemm_small_m");
 }
@@ -176,8 +185,9 @@ JLLM_EXPORT int jllm_gemm_small_m(const void* a, int lda, const void* w, int ldw
     JLLM_REQUIRE(ldo >= N, "gemm_small_m: ldo=%d < N=%d", ldo, N);
     const VecRef b{bias, bias_dtype};
     const int hb = bias != nullptr;
-    // 32 rows per block halve the activation reads but need N large enough to keep every SM busy
-    bool wide = N >= 64 * 148;
+    // 32 rows per block halve the activation reads and measured faster for every layer shape of an 8B
+    // model; tuning (experiments): bit 0 = 32 rows, bit 1 = deeper unroll, value 8 = 16 rows
+    bool wide = N >= 64 * 32;
     int deep = 0;
     if (tuning > 0) { wide = (tuning & 1) != 0; deep = (tuning >> 1) & 1; }
 #define JLLM_GO(NT, RT, UN) return launch<NT, RT, UN>(a, lda, w, ldw, b, hb, out, out_dtype, ldo, accumulate, M, N, K, stream)

@@ -160,6 +160,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_base_slot;
+    pdl_wait();       // barriers and tensor memory were set up while the kernel before this one was finishing
+    pdl_trigger();
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -433,13 +435,13 @@ JLLM_EXPORT int jllm_gemm_tcgen05(const void* a, int lda, const void* w, int ldw
     if (out_dtype == JLLM_F32) {
         auto kern = gemm_tcgen05_kernel<float>;
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
-        kern<<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_w, b, bias != nullptr, (float*)out, ldo, accumulate, M, N, K,
-                                                    error_word);
+        jllm_launch(kern, dim3(grid), dim3(THREADS), SMEM_BYTES, stream, true, map_a, map_w, b, (int)(bias != nullptr),
+                    (float*)out, ldo, accumulate, M, N, K, error_word);
     } else {
         auto kern = gemm_tcgen05_kernel<__nv_bfloat16>;
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
-        kern<<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_w, b, bias != nullptr, (__nv_bfloat16*)out, ldo, accumulate, M,
-                                                    N, K, error_word);
+        jllm_launch(kern, dim3(grid), dim3(THREADS), SMEM_BYTES, stream, true, map_a, map_w, b, (int)(bias != nullptr),
+                    (__nv_bfloat16*)out, ldo, accumulate, M, N, K, error_word);
     }
     return jllm_check_launch("gemm_tcgen05");
 }

@@ -63,6 +63,11 @@ def _call(name, *args):
         raise KernelError(f"{name} failed ({code}): {lib.jllm_last_error().decode(errors='replace')}")
 
 
+def set_dependent_launch(on: bool) -> None:
+    """Programmatic dependent launch of the step's kernels on (default) or off."""
+    library().jllm_set_pdl(int(on))
+
+
 def _stream():
     return torch.cuda.current_stream().cuda_stream
 
@@ -74,6 +79,7 @@ def _p(t):
 class _Signatures:
     P, I, F = c_void_p, c_int, c_float
     jllm_check_device = []
+    jllm_set_pdl = [I]
     jllm_embed_rows = [P, P, I, P, I, I, I, P]
     jllm_rmsnorm = [P, P, I, P, I, P, I, I, F, P]
     jllm_swiglu = [P, P, I, I, I, P]
@@ -193,8 +199,12 @@ def gemm_tcgen05_error() -> int:
     return library().jllm_gemm_tcgen05_error()
 
 
+_SMALL_M_TUNING = int(__import__("os").environ.get("JLLM_B200_SMALL_M_TUNING", "0"))   # experiments only
+
+
 def gemm_small_m(a, w, out, bias=None, accumulate=False, tuning: int = 0) -> None:
     """The decode-step product (at most 64 rows): a weight stream through mma.sync with swapped operands."""
+    tuning = tuning or _SMALL_M_TUNING
     assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.stride(-1) == 1
     _call("jllm_gemm_small_m", a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), _p(bias),
           _DT[bias.dtype] if bias is not None else F32, out.data_ptr(), _DT[out.dtype], out.stride(0),

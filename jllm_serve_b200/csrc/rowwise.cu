@@ -43,6 +43,8 @@ template <typename Tout>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, VecRef gain, Tout* __restrict__ out,
                                const int* __restrict__ row_index, int dim, float eps) {
     __shared__ float scratch[33];
+    pdl_wait();
+    pdl_trigger();
     const int r = blockIdx.x;
     const float* src = x + (size_t)(row_index ? row_index[r] : r) * dim;
     float ss = 0.f;
@@ -63,9 +65,10 @@ JLLM_EXPORT int jllm_rmsnorm(const float* x, const void* gain, int gain_dtype, v
     const VecRef g{gain, gain_dtype};
     const int threads = dim >= 2048 ? 512 : 256;
     if (out_dtype == JLLM_F32)
-        rmsnorm_kernel<float><<<rows, threads, 0, stream>>>(x, g, (float*)out, row_index, dim, eps);
+        jllm_launch(rmsnorm_kernel<float>, dim3(rows), dim3(threads), 0, stream, true, x, g, (float*)out, row_index, dim, eps);
     else
-        rmsnorm_kernel<__nv_bfloat16><<<rows, threads, 0, stream>>>(x, g, (__nv_bfloat16*)out, row_index, dim, eps);
+        jllm_launch(rmsnorm_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, stream, true, x, g, (__nv_bfloat16*)out,
+                    row_index, dim, eps);
     return jllm_check_launch("rmsnorm");
 }
 
@@ -74,6 +77,8 @@ JLLM_EXPORT int jllm_rmsnorm(const float* x, const void* gain, int gain_dtype, v
 // ---------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ h, int hidden, size_t total) {
+    pdl_wait();
+    pdl_trigger();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t r = i / hidden, j = i - r * hidden;
         const float g = to_float(gate_up[r * 2 * hidden + j]);
@@ -88,9 +93,11 @@ JLLM_EXPORT int jllm_swiglu(const void* gate_up, void* h, int dtype, int rows, i
     const size_t total = (size_t)rows * hidden;
     const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
     if (dtype == JLLM_F32)
-        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)h, hidden, total);
+        jllm_launch(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, stream, true, (const float*)gate_up, (float*)h, hidden,
+                    total);
     else
-        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)h, hidden, total);
+        jllm_launch(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, true, (const __nv_bfloat16*)gate_up,
+                    (__nv_bfloat16*)h, hidden, total);
     return jllm_check_launch("swiglu");
 }
 
@@ -112,6 +119,8 @@ __global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, VecRef q_gain, Ve
                                           int page_size, int row_stride) {
     extern __shared__ float vec[];  // head_dim floats + 33 scratch
     float* scratch = vec + head_dim;
+    pdl_wait();
+    pdl_trigger();
     const int r = blockIdx.x, h = blockIdx.y;
     T* src = qkv + (size_t)r * row_stride + (size_t)h * head_dim;
     const bool is_q = h < heads, is_k = !is_q && h < heads + kv_heads;
@@ -169,11 +178,11 @@ JLLM_EXPORT int jllm_qk_norm_rope_store(void* qkv, int dtype, const void* q_gain
     const size_t smem = (head_dim + 33) * sizeof(float);
     const VecRef qg{q_gain, gain_dtype}, kg{k_gain, gain_dtype};
     if (dtype == JLLM_F32)
-        qk_norm_rope_store_kernel<float><<<grid, threads, smem, stream>>>(
+        jllm_launch(qk_norm_rope_store_kernel<float>, grid, dim3(threads), smem, stream, true,
             (float*)qkv, qg, kg, use_norm, eps, cos_t, sin_t, rotary_dim, positions, slots, (float*)k_cache,
             (float*)v_cache, heads, kv_heads, head_dim, page_size, row_stride);
     else
-        qk_norm_rope_store_kernel<__nv_bfloat16><<<grid, threads, smem, stream>>>(
+        jllm_launch(qk_norm_rope_store_kernel<__nv_bfloat16>, grid, dim3(threads), smem, stream, true,
             (__nv_bfloat16*)qkv, qg, kg, use_norm, eps, cos_t, sin_t, rotary_dim, positions, slots,
             (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, heads, kv_heads, head_dim, page_size, row_stride);
     return jllm_check_launch("qk_norm_rope_store");

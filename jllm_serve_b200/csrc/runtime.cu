@@ -1,6 +1,7 @@
 // Error reporting of the kernel library, and what the host asks about the device.
 #include "common.cuh"
 
+#include <cstdlib>
 #include <cstring>
 
 namespace {
@@ -20,6 +21,21 @@ int jllm_check_launch(const char* what) {
     if (e == cudaSuccess) return JLLM_OK;
     return jllm_fail(JLLM_CUDA_ERROR, "%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
 }
+
+namespace {
+int g_pdl = -1;
+}
+
+bool jllm_pdl_enabled() {
+    if (g_pdl < 0) {
+        const char* e = getenv("JLLM_B200_PDL");
+        g_pdl = (e && e[0] == '0') ? 0 : 1;
+    }
+    return g_pdl == 1;
+}
+
+// 1 = kernels of a step are launched as programmatic dependents of their predecessors (default), 0 = plainly.
+JLLM_EXPORT void jllm_set_pdl(int on) { g_pdl = on ? 1 : 0; }
 
 JLLM_EXPORT const char* jllm_last_error() { return g_error; }
 

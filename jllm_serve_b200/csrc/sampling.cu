@@ -80,6 +80,8 @@ __device__ int block_argmax(const float* __restrict__ row, int vocab, ArgBest* s
 __global__ void __launch_bounds__(THREADS) argmax_kernel(const float* __restrict__ logits, int ld, int vocab,
                                                           int* __restrict__ out) {
     __shared__ ArgBest scratch[33];
+    pdl_wait();
+    pdl_trigger();
     const int t = block_argmax(logits + (size_t)blockIdx.x * ld, vocab, scratch);
     if (threadIdx.x == 0) out[blockIdx.x] = t;
 }
@@ -224,7 +226,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* 
 JLLM_EXPORT int jllm_argmax(const float* logits, int ld, int rows, int vocab, int* out, cudaStream_t stream) {
     JLLM_REQUIRE(rows >= 0 && vocab > 0 && ld >= vocab, "argmax: rows=%d vocab=%d ld=%d", rows, vocab, ld);
     if (rows == 0) return JLLM_OK;
-    argmax_kernel<<<rows, THREADS, 0, stream>>>(logits, ld, vocab, out);
+    jllm_launch(argmax_kernel, dim3(rows), dim3(THREADS), 0, stream, true, logits, ld, vocab, out);
     return jllm_check_launch("argmax");
 }
 
