@@ -43,7 +43,8 @@ __device__ __forceinline__ uint4 load_16_stream(const __nv_bfloat16* p) {
 template <int NT, int RT, int UNROLL, typename Tout>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_small_m_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w, int ldw,
-                    VecRef bias, int has_bias, Tout* __restrict__ out, int ldo, int accumulate, int M, int N, int K) {
+                    VecRef bias, int has_bias, Tout* __restrict__ out, int ldo, int accumulate, int M, int N, int K,
+                    int swiglu) {
     extern __shared__ float red[];  // [WARPS][RT * 16][NT * 8]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -142,6 +143,15 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfl
         float v = 0.f;
 #pragma unroll
         for (int wi = 0; wi < WARPS; ++wi) v += red[(size_t)wi * ROWS * TOK + e];
+        if (swiglu) {
+            // rows come in blocks of 16: 8 gate rows, then the 8 up rows of the same hidden units
+            if ((row & 15) >= 8) continue;
+            float u = 0.f;
+#pragma unroll
+            for (int wi = 0; wi < WARPS; ++wi) u += red[(size_t)wi * ROWS * TOK + e + 8];
+            out[(size_t)tok * ldo + (n >> 4) * 8 + (row & 7)] = from_float<Tout>(__fmul_rn(v / (1.f + expf(-v)), u));
+            continue;
+        }
         if (has_bias) v += bias[n];
         Tout* dst = out + (size_t)tok * ldo + n;
         if (accumulate) v += to_float(*dst);
@@ -151,19 +161,19 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfl
 
 template <int NT, int RT, int UNROLL>
 int launch(const void* a, int lda, const void* w, int ldw, VecRef bias, int has_bias, void* out, int out_dtype, int ldo,
-           int accumulate, int M, int N, int K, cudaStream_t stream) {
+           int accumulate, int M, int N, int K, int swiglu, cudaStream_t stream) {
     const int grid = (N + 16 * RT - 1) / (16 * RT);
     const size_t smem = (size_t)WARPS * RT * 16 * NT * 8 * sizeof(float);
     if (out_dtype == JLLM_F32) {
         auto kern = gemm_small_m_kernel<NT, RT, UNROLL, float>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         jllm_launch(kern, dim3(grid), dim3(WARPS * 32), smem, stream, true, (const __nv_bfloat16*)a, lda,
-                    (const __nv_bfloat16*)w, ldw, bias, has_bias, (float*)out, ldo, accumulate, M, N, K);
+                    (const __nv_bfloat16*)w, ldw, bias, has_bias, (float*)out, ldo, accumulate, M, N, K, swiglu);
     } else {
         auto kern = gemm_small_m_kernel<NT, RT, UNROLL, __nv_bfloat16>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         jllm_launch(kern, dim3(grid), dim3(WARPS * 32), smem, stream, true, (const __nv_bfloat16*)a, lda,
-                    (const __nv_bfloat16*)w, ldw, bias, has_bias, (__nv_bfloat16*)out, ldo, accumulate, M, N, K);
+                    (const __nv_bfloat16*)w, ldw, bias, has_bias, (__nv_bfloat16*)out, ldo, accumulate, M, N, K, swiglu);
     }
     return jllm_check_launch("gemm_small_m");
 }
@@ -178,11 +188,13 @@ JLLM_EXPORT int jllm_gemm_small_m_fits(const void* a, int lda, const void* w, in
 
 JLLM_EXPORT int jllm_gemm_small_m(const void* a, int lda, const void* w, int ldw, const void* bias, int bias_dtype,
                                   void* out, int out_dtype, int ldo, int accumulate, int M, int N, int K,
-                                  int tuning, cudaStream_t stream) {
+                                  int tuning, int swiglu, cudaStream_t stream) {
     JLLM_REQUIRE(jllm_gemm_small_m_fits(a, lda, w, ldw, M, N, K),
                  "gemm_small_m: needs 1 <= M <= 64, K %% 8 == 0 and 16-byte aligned rows (M=%d N=%d K=%d lda=%d ldw=%d)",
                  M, N, K, lda, ldw);
-    JLLM_REQUIRE(ldo >= N, "gemm_small_m: ldo=%d < N=%d", ldo, N);
+    JLLM_REQUIRE(ldo >= (swiglu ? N / 2 : N), "gemm_small_m: ldo=%d < N=%d", ldo, N);
+    JLLM_REQUIRE(!swiglu || (N % 16 == 0 && !bias && !accumulate),
+                 "gemm_small_m: the SwiGLU epilogue needs N %% 16 == 0, no bias and no accumulation (N=%d)", N);
     const VecRef b{bias, bias_dtype};
     const int hb = bias != nullptr;
     // 32 rows per block halve the activation reads and measured faster for every layer shape of an 8B
@@ -190,7 +202,7 @@ JLLM_EXPORT int jllm_gemm_small_m(const void* a, int lda, const void* w, int ldw
     bool wide = N >= 64 * 32;
     int deep = 0;
     if (tuning > 0) { wide = (tuning & 1) != 0; deep = (tuning >> 1) & 1; }
-#define JLLM_GO(NT, RT, UN) return launch<NT, RT, UN>(a, lda, w, ldw, b, hb, out, out_dtype, ldo, accumulate, M, N, K, stream)
+#define JLLM_GO(NT, RT, UN) return launch<NT, RT, UN>(a, lda, w, ldw, b, hb, out, out_dtype, ldo, accumulate, M, N, K, swiglu, stream)
     if (M <= 8) { if (wide) { if (deep) JLLM_GO(1, 2, 8); JLLM_GO(1, 2, 4); } if (deep) JLLM_GO(1, 1, 8); JLLM_GO(1, 1, 4); }
     if (M <= 16) { if (wide) JLLM_GO(2, 2, 4); if (deep) JLLM_GO(2, 1, 8); JLLM_GO(2, 1, 4); }
     if (M <= 32) { if (wide) JLLM_GO(4, 2, 2); JLLM_GO(4, 1, 4); }

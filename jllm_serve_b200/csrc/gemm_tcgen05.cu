@@ -120,7 +120,7 @@ constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >
 template <typename Tout>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, VecRef bias,
-                    int has_bias, Tout* __restrict__ out, int ldo, int accumulate, int M, int N, int K,
+                    int has_bias, Tout* __restrict__ out, int ldo, int accumulate, int M, int N, int K, int swiglu,
                     int* __restrict__ error_word) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzled tiles want 1024-byte alignment
@@ -226,7 +226,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 uint32_t v[32];
                 tmem_ld_32x32b_x32(taddr + c0, v);
                 tmem_ld_wait();
-                if (row < M) {
+                if (row < M && swiglu) {
+                    // columns come in blocks of 16: 8 gate columns, then the 8 up columns of the same hidden units
+                    const int n_base = n0 + c0;
+                    Tout* dst = out + (size_t)row * ldo + (n_base >> 1);
+                    // (the tensor-core path may use the fast exponential: its result is rounded to bfloat16 anyway)
+                    float hv[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int cg = (j >> 3) * 16 + (j & 7);
+                        const float gt = __uint_as_float(v[cg]), up = __uint_as_float(v[cg + 8]);
+                        hv[j] = __fdividef(gt, 1.f + __expf(-gt)) * up;
+                    }
+                    if (sizeof(Tout) == 2 && n_base + 32 <= N && ((((uintptr_t)dst) & 15u) == 0)) {
+                        uint32_t p[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            __nv_bfloat162 b2 = __floats2bfloat162_rn(hv[2 * j], hv[2 * j + 1]);
+                            p[j] = *reinterpret_cast<uint32_t*>(&b2);
+                        }
+                        reinterpret_cast<uint4*>(dst)[0] = make_uint4(p[0], p[1], p[2], p[3]);
+                        reinterpret_cast<uint4*>(dst)[1] = make_uint4(p[4], p[5], p[6], p[7]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int cg = (j >> 3) * 16 + (j & 7);
+                            if (n_base + cg + 8 < N) dst[j] = from_float<Tout>(hv[j]);
+                        }
+                    }
+                } else if (row < M) {
                     const int n_base = n0 + c0;
                     Tout* dst = out + (size_t)row * ldo + n_base;
                     if (n_base + 32 <= N) {
@@ -410,11 +438,13 @@ JLLM_EXPORT int jllm_gemm_tcgen05_error() {
 
 JLLM_EXPORT int jllm_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, const void* bias, int bias_dtype,
                                   void* out, int out_dtype, int ldo, int accumulate, int M, int N, int K, int max_blocks,
-                                  cudaStream_t stream) {
+                                  int swiglu, cudaStream_t stream) {
     JLLM_REQUIRE(jllm_gemm_tcgen05_fits(a, lda, w, ldw, M, N, K),
                  "gemm_tcgen05: needs K %% 8 == 0 and 16-byte aligned rows (M=%d N=%d K=%d lda=%d ldw=%d)", M, N, K, lda,
                  ldw);
-    JLLM_REQUIRE(ldo >= N, "gemm_tcgen05: ldo=%d < N=%d", ldo, N);
+    JLLM_REQUIRE(ldo >= (swiglu ? N / 2 : N), "gemm_tcgen05: ldo=%d < N=%d", ldo, N);
+    JLLM_REQUIRE(!swiglu || (N % 16 == 0 && !bias && !accumulate),
+                 "gemm_tcgen05: the SwiGLU epilogue needs N %% 16 == 0, no bias and no accumulation (N=%d)", N);
     CUtensorMap map_a, map_w;
     int rc = tensor_map_for(a, M, K, lda, BM, &map_a);
     if (rc != JLLM_OK) return rc;
@@ -436,12 +466,12 @@ JLLM_EXPORT int jllm_gemm_tcgen05(const void* a, int lda, const void* w, int ldw
         auto kern = gemm_tcgen05_kernel<float>;
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
         jllm_launch(kern, dim3(grid), dim3(THREADS), SMEM_BYTES, stream, true, map_a, map_w, b, (int)(bias != nullptr),
-                    (float*)out, ldo, accumulate, M, N, K, error_word);
+                    (float*)out, ldo, accumulate, M, N, K, swiglu, error_word);
     } else {
         auto kern = gemm_tcgen05_kernel<__nv_bfloat16>;
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
         jllm_launch(kern, dim3(grid), dim3(THREADS), SMEM_BYTES, stream, true, map_a, map_w, b, (int)(bias != nullptr),
-                    (__nv_bfloat16*)out, ldo, accumulate, M, N, K, error_word);
+                    (__nv_bfloat16*)out, ldo, accumulate, M, N, K, swiglu, error_word);
     }
     return jllm_check_launch("gemm_tcgen05");
 }

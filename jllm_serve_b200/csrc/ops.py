@@ -85,8 +85,8 @@ class _Signatures:
     jllm_swiglu = [P, P, I, I, I, P]
     jllm_qk_norm_rope_store = [P, I, P, P, I, I, F, P, P, I, P, P, P, P, I, I, I, I, I, I, I, P]
     jllm_gemm_plain = [P, I, I, P, I, P, I, P, I, I, I, I, I, I, P]
-    jllm_gemm_small_m = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, P]
-    jllm_gemm_tcgen05 = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, P]
+    jllm_gemm_small_m = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, I, P]
+    jllm_gemm_tcgen05 = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, I, P]
     jllm_gemm_tcgen05_error = []
     jllm_attention_plain = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P]
     jllm_attention_decode = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
@@ -177,21 +177,22 @@ def gemm_bf16_fits(a, w, out) -> bool:
 SMALL_M_ROWS = 32   # up to here the weight-streaming kernel wins; above, the tcgen05 tiles
 
 
-def gemm_bf16(a, w, out, bias=None, accumulate=False) -> None:
-    """out (+)= a @ w.T (+ bias) on the tensor cores: bfloat16 operands, float32 accumulation."""
+def gemm_bf16(a, w, out, bias=None, accumulate=False, swiglu=False) -> None:
+    """out (+)= a @ w.T (+ bias) on the tensor cores: bfloat16 operands, float32 accumulation. With `swiglu`
+    the rows of w are blocks of 8 gate rows followed by their 8 up rows and out[m, j] = silu(gate_j) * up_j."""
     if a.shape[0] <= SMALL_M_ROWS and _small_m_fits(a, w):
-        return gemm_small_m(a, w, out, bias, accumulate)
+        return gemm_small_m(a, w, out, bias, accumulate, swiglu=swiglu)
     if _tcgen05_fits(a, w):
-        return gemm_tcgen05(a, w, out, bias, accumulate)
+        return gemm_tcgen05(a, w, out, bias, accumulate, swiglu=swiglu)
     raise KernelError("the tensor-core matrix product is not built for this shape")
 
 
-def gemm_tcgen05(a, w, out, bias=None, accumulate=False, max_blocks: int = 0) -> None:
+def gemm_tcgen05(a, w, out, bias=None, accumulate=False, max_blocks: int = 0, swiglu=False) -> None:
     """The prefill product: TMA-fed tcgen05.mma tiles of 128 x 256 with the accumulator in tensor memory."""
     assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.stride(-1) == 1
     _call("jllm_gemm_tcgen05", a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), _p(bias),
           _DT[bias.dtype] if bias is not None else F32, out.data_ptr(), _DT[out.dtype], out.stride(0),
-          int(accumulate), a.shape[0], w.shape[0], a.shape[1], int(max_blocks), _stream())
+          int(accumulate), a.shape[0], w.shape[0], a.shape[1], int(max_blocks), int(swiglu), _stream())
 
 
 def gemm_tcgen05_error() -> int:
@@ -202,13 +203,13 @@ def gemm_tcgen05_error() -> int:
 _SMALL_M_TUNING = int(__import__("os").environ.get("JLLM_B200_SMALL_M_TUNING", "0"))   # experiments only
 
 
-def gemm_small_m(a, w, out, bias=None, accumulate=False, tuning: int = 0) -> None:
+def gemm_small_m(a, w, out, bias=None, accumulate=False, tuning: int = 0, swiglu=False) -> None:
     """The decode-step product (at most 64 rows): a weight stream through mma.sync with swapped operands."""
     tuning = tuning or _SMALL_M_TUNING
     assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.stride(-1) == 1
     _call("jllm_gemm_small_m", a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), _p(bias),
           _DT[bias.dtype] if bias is not None else F32, out.data_ptr(), _DT[out.dtype], out.stride(0),
-          int(accumulate), a.shape[0], w.shape[0], a.shape[1], int(tuning), _stream())
+          int(accumulate), a.shape[0], w.shape[0], a.shape[1], int(tuning), int(swiglu), _stream())
 
 
 def attention_decode_fits(dtype, heads, kv_heads, head_dim) -> bool:

@@ -58,11 +58,63 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, VecRef gain, Tout* _
     for (int i = threadIdx.x; i < dim; i += blockDim.x) dst[i] = from_float<Tout>(__fmul_rn(__fmul_rn(src[i], s), gain[i]));
 }
 
+// The same for widths that are a multiple of 4 and at most 8192: the row is read once, as float4, and kept in
+// registers between the sum of squares and the scaling.
+template <typename Tout>
+__global__ void __launch_bounds__(256)
+rmsnorm_vec_kernel(const float* __restrict__ x, VecRef gain, Tout* __restrict__ out, const int* __restrict__ row_index,
+                   int dim, float eps) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_trigger();
+    const int r = blockIdx.x, n4 = dim >> 2;
+    const float4* src = reinterpret_cast<const float4*>(x + (size_t)(row_index ? row_index[r] : r) * dim);
+    float4 v[8];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int i = threadIdx.x + 256 * j;
+        v[j] = i < n4 ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        ss = fmaf(v[j].x, v[j].x, ss);
+        ss = fmaf(v[j].y, v[j].y, ss);
+        ss = fmaf(v[j].z, v[j].z, ss);
+        ss = fmaf(v[j].w, v[j].w, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float s = rms_scale(ss, dim, eps);
+    Tout* dst = out + (size_t)r * dim;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int i = threadIdx.x + 256 * j;
+        if (i >= n4) break;
+        const float a = __fmul_rn(__fmul_rn(v[j].x, s), gain[4 * i + 0]), b = __fmul_rn(__fmul_rn(v[j].y, s), gain[4 * i + 1]);
+        const float c = __fmul_rn(__fmul_rn(v[j].z, s), gain[4 * i + 2]), d = __fmul_rn(__fmul_rn(v[j].w, s), gain[4 * i + 3]);
+        if constexpr (sizeof(Tout) == 4) {
+            reinterpret_cast<float4*>(dst)[i] = make_float4(a, b, c, d);
+        } else {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+            uint2 p;
+            p.x = *reinterpret_cast<uint32_t*>(&lo);
+            p.y = *reinterpret_cast<uint32_t*>(&hi);
+            reinterpret_cast<uint2*>(dst)[i] = p;
+        }
+    }
+}
+
 JLLM_EXPORT int jllm_rmsnorm(const float* x, const void* gain, int gain_dtype, void* out, int out_dtype,
                              const int* row_index, int rows, int dim, float eps, cudaStream_t stream) {
     JLLM_REQUIRE(rows >= 0 && dim > 0, "rmsnorm: rows=%d dim=%d", rows, dim);
     if (rows == 0) return JLLM_OK;
     const VecRef g{gain, gain_dtype};
+    if (dim % 4 == 0 && dim <= 8192 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+        if (out_dtype == JLLM_F32)
+            jllm_launch(rmsnorm_vec_kernel<float>, dim3(rows), dim3(256), 0, stream, true, x, g, (float*)out, row_index, dim,
+                        eps);
+        else
+            jllm_launch(rmsnorm_vec_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, stream, true, x, g,
+                        (__nv_bfloat16*)out, row_index, dim, eps);
+        return jllm_check_launch("rmsnorm");
+    }
     const int threads = dim >= 2048 ? 512 : 256;
     if (out_dtype == JLLM_F32)
         jllm_launch(rmsnorm_kernel<float>, dim3(rows), dim3(threads), 0, stream, true, x, g, (float*)out, row_index, dim, eps);
@@ -159,6 +211,69 @@ __global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, VecRef q_gain, Ve
     }
 }
 
+// The same with one warp per (row, head), for head sizes 64, 128 and 256 rotated over their whole width: lane l
+// owns V = head_dim / 64 neighbouring values of the first half and their partners in the second half, so the
+// rotation needs no exchange and the sum of squares is a warp shuffle; 8 heads per block, no shared memory.
+template <typename T, int V>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_store_warp_kernel(T* __restrict__ qkv, VecRef q_gain, VecRef k_gain, int use_norm, float eps,
+                               const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                               const int* __restrict__ positions, const int* __restrict__ slots, T* __restrict__ k_cache,
+                               T* __restrict__ v_cache, int heads, int kv_heads, int page_size, int row_stride,
+                               int heads_total, long long items) {
+    constexpr int HD = 64 * V, HALF = 32 * V;
+    pdl_wait();
+    pdl_trigger();
+    const long long item = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (item >= items) return;
+    const int r = (int)(item / heads_total), h = (int)(item % heads_total), lane = threadIdx.x & 31;
+    T* src = qkv + (size_t)r * row_stride + (size_t)h * HD;
+    const bool is_q = h < heads, is_k = !is_q && h < heads + kv_heads;
+    float a[V], b[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        a[i] = to_float(src[lane * V + i]);
+        b[i] = to_float(src[HALF + lane * V + i]);
+    }
+    if (is_q || is_k) {
+        if (use_norm) {
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < V; ++i) ss = fmaf(a[i], a[i], ss);
+#pragma unroll
+            for (int i = 0; i < V; ++i) ss = fmaf(b[i], b[i], ss);
+            ss = warp_sum(ss);
+            const float s = rms_scale(ss, HD, eps);
+            const VecRef g = is_q ? q_gain : k_gain;
+#pragma unroll
+            for (int i = 0; i < V; ++i) {
+                a[i] = __fmul_rn(__fmul_rn(a[i], s), g[lane * V + i]);
+                b[i] = __fmul_rn(__fmul_rn(b[i], s), g[HALF + lane * V + i]);
+            }
+        }
+        const float* c = cos_t + (size_t)positions[r] * HALF + lane * V;
+        const float* sn = sin_t + (size_t)positions[r] * HALF + lane * V;
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            const float x0 = a[i], x1 = b[i];
+            a[i] = __fsub_rn(__fmul_rn(x0, c[i]), __fmul_rn(x1, sn[i]));
+            b[i] = __fadd_rn(__fmul_rn(x1, c[i]), __fmul_rn(x0, sn[i]));
+        }
+    }
+    T* dst = src;
+    if (!is_q) {
+        const int kvh = is_k ? h - heads : h - heads - kv_heads;
+        const int slot = slots[r];
+        const size_t page = slot / page_size, off = slot % page_size;
+        dst = (is_k ? k_cache : v_cache) + ((page * kv_heads + kvh) * page_size + off) * HD;
+    }
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        dst[lane * V + i] = from_float<T>(a[i]);
+        dst[HALF + lane * V + i] = from_float<T>(b[i]);
+    }
+}
+
 JLLM_EXPORT int jllm_qk_norm_rope_store(void* qkv, int dtype, const void* q_gain, const void* k_gain, int gain_dtype,
                                         int use_norm, float eps, const float* cos_t, const float* sin_t,
                                         int rotary_dim, const int* positions, const int* slots, void* k_cache,
@@ -177,6 +292,24 @@ JLLM_EXPORT int jllm_qk_norm_rope_store(void* qkv, int dtype, const void* q_gain
     const int threads = head_dim <= 64 ? 32 : (head_dim <= 128 ? 64 : 128);
     const size_t smem = (head_dim + 33) * sizeof(float);
     const VecRef qg{q_gain, gain_dtype}, kg{k_gain, gain_dtype};
+    if ((head_dim == 64 || head_dim == 128 || head_dim == 256) && rotary_dim == head_dim) {
+        const int heads_total = write_kv ? heads + 2 * kv_heads : heads;
+        const long long items = (long long)rows * heads_total;
+        const dim3 wgrid((unsigned)((items + 7) / 8));
+#define JLLM_WARP_ROPE(T, V)                                                                                          \
+    jllm_launch(qk_norm_rope_store_warp_kernel<T, V>, wgrid, dim3(256), 0, stream, true, (T*)qkv, qg, kg, use_norm, eps, \
+                cos_t, sin_t, positions, slots, (T*)k_cache, (T*)v_cache, heads, kv_heads, page_size, row_stride,      \
+                heads_total, items)
+        const int v = head_dim / 64;
+        if (dtype == JLLM_F32) {
+            if (v == 1) JLLM_WARP_ROPE(float, 1); else if (v == 2) JLLM_WARP_ROPE(float, 2); else JLLM_WARP_ROPE(float, 4);
+        } else {
+            if (v == 1) JLLM_WARP_ROPE(__nv_bfloat16, 1); else if (v == 2) JLLM_WARP_ROPE(__nv_bfloat16, 2);
+            else JLLM_WARP_ROPE(__nv_bfloat16, 4);
+        }
+#undef JLLM_WARP_ROPE
+        return jllm_check_launch("qk_norm_rope_store");
+    }
     if (dtype == JLLM_F32)
         jllm_launch(qk_norm_rope_store_kernel<float>, grid, dim3(threads), smem, stream, true,
             (float*)qkv, qg, kg, use_norm, eps, cos_t, sin_t, rotary_dim, positions, slots, (float*)k_cache,

@@ -18,11 +18,14 @@ class Linear:
         self.weight, self.bias = weight, bias
         self.out_features, self.in_features = weight.shape
 
-    def forward(self, a: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
-        """a [rows, in] (compute dtype) -> out [rows, out]; `accumulate` adds into out (the float32 residual)."""
+    def forward(self, a: torch.Tensor, out: torch.Tensor, accumulate: bool = False, swiglu: bool = False) -> None:
+        """a [rows, in] (compute dtype) -> out [rows, out]; `accumulate` adds into out (the float32 residual);
+        `swiglu`: the weight's rows are interleaved gate / up blocks and out is [rows, out / 2]."""
         if a.shape[0] == 0:
             return
         if self.weight.dtype == torch.bfloat16 and ops.gemm_bf16_fits(a, self.weight, out):
-            ops.gemm_bf16(a, self.weight, out, self.bias, accumulate)
+            ops.gemm_bf16(a, self.weight, out, self.bias, accumulate, swiglu)
+        elif swiglu:
+            raise ops.KernelError("the fused SwiGLU epilogue exists in the tensor-core kernels only")
         else:
             ops.gemm_plain(a, self.weight, out, self.bias, accumulate)

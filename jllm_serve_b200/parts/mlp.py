@@ -19,7 +19,15 @@ class DenseGlu(FeedForward):
     def __init__(self, spec, dim: int, tensors: dict, prefix: str, runtime):
         self.hidden, self.dim, self.rt = spec.hidden, dim, runtime
         gate, up = tensors.pop(prefix + "gate_proj.weight"), tensors.pop(prefix + "up_proj.weight")
-        self.gate_up = Linear(torch.cat([gate, up], dim=0).contiguous())
+        # bfloat16: blocks of 8 gate rows followed by their 8 up rows, so that the product's epilogue holds a
+        # gate value and its up value together and applies SwiGLU itself (no [rows, 2 hidden] round trip)
+        self.fused = gate.dtype == torch.bfloat16 and dim % 8 == 0 and spec.hidden % 8 == 0
+        if self.fused:
+            stacked = torch.stack([gate.view(spec.hidden // 8, 8, dim), up.view(spec.hidden // 8, 8, dim)], dim=1)
+            self.gate_up = Linear(stacked.reshape(2 * spec.hidden, dim).contiguous())
+            del stacked
+        else:
+            self.gate_up = Linear(torch.cat([gate, up], dim=0).contiguous())
         del gate, up
         self.down = Linear(tensors.pop(prefix + "down_proj.weight"))
 
@@ -31,10 +39,13 @@ class DenseGlu(FeedForward):
 
     def forward(self, xb, x, batch) -> None:
         rows = xb.shape[0]
-        gate_up = self.rt.buffer("gate_up", 2 * self.hidden)[:rows]
         h = self.rt.buffer("ffn_hidden", self.hidden)[:rows]
-        self.gate_up.forward(xb, gate_up)
-        ops.swiglu(gate_up, h)
+        if self.fused:
+            self.gate_up.forward(xb, h, swiglu=True)
+        else:
+            gate_up = self.rt.buffer("gate_up", 2 * self.hidden)[:rows]
+            self.gate_up.forward(xb, gate_up)
+            ops.swiglu(gate_up, h)
         self.down.forward(h, x, accumulate=True)
 
 

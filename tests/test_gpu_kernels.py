@@ -134,6 +134,25 @@ def test_gemm_tcgen05(ops, M, N, K):
     assert float(out16[:, N:].abs().max()) == 0 and ops.gemm_tcgen05_error() == 0
 
 
+@pytest.mark.parametrize("M", [1, 8, 20, 33, 200])
+@pytest.mark.parametrize("hidden,K", [(8, 8), (200, 72), (12288, 4096), (1000, 136)])
+def test_gemm_with_swiglu_epilogue(ops, M, hidden, K):
+    """gate and up rows interleaved in blocks of 8: the product's epilogue gives silu(gate) * up directly."""
+    a = rnd(M, K, dtype=torch.bfloat16)
+    gate, up = rnd(hidden, K, dtype=torch.bfloat16, seed=1, scale=0.05), rnd(hidden, K, dtype=torch.bfloat16, seed=2, scale=0.05)
+    w = torch.stack([gate.view(hidden // 8, 8, K), up.view(hidden // 8, 8, K)], dim=1).reshape(2 * hidden, K).contiguous()
+    g, u = gemm_want(a, gate), gemm_want(a, up)
+    want = P.silu(g) * u
+    out = torch.full((M, hidden), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_bf16(a, w, out, swiglu=True)
+    assert ops.gemm_tcgen05_error() == 0
+    assert torch.allclose(out.float().cpu(), want, rtol=2 ** -7, atol=1e-3), float((out.float().cpu() - want).abs().max())
+    out32 = torch.full((M, hidden), float("nan"), device=DEV)
+    ops.gemm_tcgen05(a, w, out32, swiglu=True)
+    # float32 sums of K bfloat16 products differ from float64 by about 1e-4 sqrt(K) 0.05, times |up| of a few
+    assert torch.allclose(out32.cpu(), want, rtol=1e-3, atol=1e-4 * math.sqrt(K) * 0.05 * 4 + 1e-5)
+
+
 def test_gemm_small_m_refuses_what_it_cannot_do(ops):
     a, w = rnd(3, 12, dtype=torch.bfloat16), rnd(8, 12, dtype=torch.bfloat16)
     with pytest.raises(ops.KernelError, match="K % 8"):
@@ -145,7 +164,8 @@ def test_gemm_small_m_refuses_what_it_cannot_do(ops):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,Hkv,hd,rot,norm", [(6, 2, 48, 24, True), (4, 4, 16, 16, False), (8, 1, 128, 128, True),
-                                                (2, 2, 80, 0, True)])
+                                                (2, 2, 80, 0, True), (3, 1, 64, 64, True), (5, 5, 256, 256, False),
+                                                (4, 2, 128, 64, True)])
 def test_qk_norm_rope_store(ops, dtype, H, Hkv, hd, rot, norm):
     R, page, pages, eps = 11, 4, 9, 1e-5
     width = (H + 2 * Hkv) * hd
