@@ -1,8 +1,8 @@
 // Paged causal flash attention for prompt portions (bfloat16): rows of a batch attend to their own
-// request's cached keys and values, a tile of 64 query rows of one head per block.
+// request's cached keys and values, a tile of 128 query rows of one head per block.
 //
 // A block first finds its tile: tiles are numbered segment after segment (a segment = one request's rows
-// in this step), ceil(rows / 64) tiles each. Its 4 warps take 16 query rows each. Keys and values come
+// in this step), ceil(rows / 128) tiles each. Its 8 warps take 16 query rows each. Keys and values come
 // in tiles of 64 positions, gathered from the request's pages into shared memory with cp.async (16-byte
 // chunks, XOR-swizzled against bank conflicts, double-buffered so the next tile loads while this one is
 // used). Scores S = Q K^T and the output O += P V run on mma.sync.m16n8k16 with operands from ldmatrix;
@@ -19,7 +19,7 @@
 
 namespace {
 
-constexpr int BQ = 64, BKV = 64, WARPS = 4, THREADS = WARPS * 32;
+constexpr int BQ = 128, BKV = 64, WARPS = 8, THREADS = WARPS * 32;
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -96,6 +96,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
     const int first_key = window > 0 ? max(0, pos0 + 1 - window) : 0;
     const int kt_lo = first_key / BKV, kt_hi = pos_last / BKV;  // inclusive range of key tiles
     const size_t page_stride = (size_t)kv_heads * page_size * HD;
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
 
     auto load_kv = [&](int kt, int buf) {
         const uint32_t dk = s_k + buf * TILE_BYTES, dv = s_v + buf * TILE_BYTES;
@@ -105,8 +106,9 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
             const bool ok = key >= first_key && key <= pos_last;
             size_t off = 0;
             if (ok) {
-                const size_t page = table[key / page_size];
-                off = page * page_stride + ((size_t)kvh * page_size + key % page_size) * HD + c * 8;
+                const int pg = page_shift >= 0 ? key >> page_shift : key / page_size;
+                const int in_page = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
+                off = (size_t)table[pg] * page_stride + ((size_t)kvh * page_size + in_page) * HD + c * 8;
             }
             cp_async_16(dk + tile_offset<HD>(r, c), k_cache + off, ok ? 16 : 0);
             cp_async_16(dv + tile_offset<HD>(r, c), v_cache + off, ok ? 16 : 0);
@@ -143,72 +145,90 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
             cp_async_wait<0>();
         }
         __syncthreads();
-        const uint32_t sk = s_k + buf * TILE_BYTES, sv = s_v + buf * TILE_BYTES;
-        // ---- S = Q K^T: 16 rows x 64 keys per warp ----
-        float s[BKV / 8][4];
-#pragma unroll
-        for (int j = 0; j < BKV / 8; ++j)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) s[j][i] = 0.f;
-#pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
-#pragma unroll
-            for (int jp = 0; jp < BKV / 16; ++jp) {
-                uint32_t kf[4];
-                ldmatrix_x4(kf, sk + tile_offset<HD>(jp * 16 + (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1)));
-                mma_16816(s[2 * jp], qf[ks], kf[0], kf[1]);
-                mma_16816(s[2 * jp + 1], qf[ks], kf[2], kf[3]);
+        // a warp whose rows all lie before this key tile has nothing to do in it (causal), but still takes part
+        // in the loads and barriers
+        if (kt * BKV <= pos0 + min(warp * 16 + 15, rows_here - 1)) {
+            const uint32_t sk = s_k + buf * TILE_BYTES, sv = s_v + buf * TILE_BYTES;
+            // ---- S = Q K^T: 16 rows x 64 keys per warp ----
+            float s[BKV / 8][4];
+    #pragma unroll
+            for (int j = 0; j < BKV / 8; ++j)
+    #pragma unroll
+                for (int i = 0; i < 4; ++i) s[j][i] = 0.f;
+    #pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks) {
+    #pragma unroll
+                for (int jp = 0; jp < BKV / 16; ++jp) {
+                    uint32_t kf[4];
+                    ldmatrix_x4(kf, sk + tile_offset<HD>(jp * 16 + (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1)));
+                    mma_16816(s[2 * jp], qf[ks], kf[0], kf[1]);
+                    mma_16816(s[2 * jp + 1], qf[ks], kf[2], kf[3]);
+                }
             }
-        }
-        // ---- mask and online softmax ----
-        const int key0 = kt * BKV;
-        float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-        for (int j = 0; j < BKV / 8; ++j)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int key = key0 + j * 8 + 2 * t + (i & 1), P = pos_r[i >> 1];
-                const bool vis = key <= P && (window <= 0 || key >= P + 1 - window);
-                s[j][i] = vis ? s[j][i] * scale_log2 : -INFINITY;
-                mx[i >> 1] = fmaxf(mx[i >> 1], s[j][i]);
+            // ---- mask and online softmax ----
+            const int key0 = kt * BKV;
+            float mx[2] = {-INFINITY, -INFINITY};
+            // a tile that every row of this warp sees whole (all keys at or before the warp's first position and
+            // inside every row's window) needs no mask: true for all but the tiles on the diagonal and the window's edge
+            const int warp_first = pos0 + min(warp * 16, rows_here - 1), warp_last = pos0 + min(warp * 16 + 15, rows_here - 1);
+            const bool whole = key0 + BKV - 1 <= warp_first && (window <= 0 || key0 >= warp_last + 1 - window);
+            if (whole) {
+    #pragma unroll
+                for (int j = 0; j < BKV / 8; ++j)
+    #pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        s[j][i] *= scale_log2;
+                        mx[i >> 1] = fmaxf(mx[i >> 1], s[j][i]);
+                    }
+            } else {
+    #pragma unroll
+                for (int j = 0; j < BKV / 8; ++j)
+    #pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int key = key0 + j * 8 + 2 * t + (i & 1), P = pos_r[i >> 1];
+                        const bool vis = key <= P && (window <= 0 || key >= P + 1 - window);
+                        s[j][i] = vis ? s[j][i] * scale_log2 : -INFINITY;
+                        mx[i >> 1] = fmaxf(mx[i >> 1], s[j][i]);
+                    }
             }
-        float corr[2], m_use[2];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
-            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-            const float m_new = fmaxf(m_run[h], mx[h]);
-            m_use[h] = m_new == -INFINITY ? 0.f : m_new;        // a row that sees nothing yet: avoid inf - inf
-            corr[h] = exp2f(m_run[h] - m_use[h]);
-            m_run[h] = m_new;
-            l_run[h] *= corr[h];
-        }
-#pragma unroll
-        for (int j = 0; j < HD / 8; ++j) {
-            o[j][0] *= corr[0];
-            o[j][1] *= corr[0];
-            o[j][2] *= corr[1];
-            o[j][3] *= corr[1];
-        }
-        uint32_t pf[BKV / 16][4];
-#pragma unroll
-        for (int j = 0; j < BKV / 8; ++j) {
-            const float p0 = exp2f(s[j][0] - m_use[0]), p1 = exp2f(s[j][1] - m_use[0]);
-            const float p2 = exp2f(s[j][2] - m_use[1]), p3 = exp2f(s[j][3] - m_use[1]);
-            l_run[0] += p0 + p1;
-            l_run[1] += p2 + p3;
-            pf[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0, p1);
-            pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
-        }
-        // ---- O += P V ----
-#pragma unroll
-        for (int kk = 0; kk < BKV / 16; ++kk) {
-#pragma unroll
-            for (int jp = 0; jp < HD / 16; ++jp) {
-                uint32_t vf[4];
-                ldmatrix_x4_trans(vf, sv + tile_offset<HD>(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, jp * 2 + (lane >> 4)));
-                mma_16816(o[2 * jp], pf[kk], vf[0], vf[1]);
-                mma_16816(o[2 * jp + 1], pf[kk], vf[2], vf[3]);
+            float corr[2], m_use[2];
+    #pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+                const float m_new = fmaxf(m_run[h], mx[h]);
+                m_use[h] = m_new == -INFINITY ? 0.f : m_new;        // a row that sees nothing yet: avoid inf - inf
+                corr[h] = exp2f(m_run[h] - m_use[h]);
+                m_run[h] = m_new;
+                l_run[h] *= corr[h];
+            }
+    #pragma unroll
+            for (int j = 0; j < HD / 8; ++j) {
+                o[j][0] *= corr[0];
+                o[j][1] *= corr[0];
+                o[j][2] *= corr[1];
+                o[j][3] *= corr[1];
+            }
+            uint32_t pf[BKV / 16][4];
+    #pragma unroll
+            for (int j = 0; j < BKV / 8; ++j) {
+                const float p0 = exp2f(s[j][0] - m_use[0]), p1 = exp2f(s[j][1] - m_use[0]);
+                const float p2 = exp2f(s[j][2] - m_use[1]), p3 = exp2f(s[j][3] - m_use[1]);
+                l_run[0] += p0 + p1;
+                l_run[1] += p2 + p3;
+                pf[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0, p1);
+                pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+            }
+            // ---- O += P V ----
+    #pragma unroll
+            for (int kk = 0; kk < BKV / 16; ++kk) {
+    #pragma unroll
+                for (int jp = 0; jp < HD / 16; ++jp) {
+                    uint32_t vf[4];
+                    ldmatrix_x4_trans(vf, sv + tile_offset<HD>(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, jp * 2 + (lane >> 4)));
+                    mma_16816(o[2 * jp], pf[kk], vf[0], vf[1]);
+                    mma_16816(o[2 * jp + 1], pf[kk], vf[2], vf[3]);
+                }
             }
         }
         __syncthreads();   // everyone is done with this buffer before the load after next overwrites it
