@@ -26,6 +26,7 @@ using namespace tc;
 
 constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int JLLM_TC_MAX_TILES = 4096;  // counter words at the head of the split-K workspace
 constexpr int THREADS = 192;           // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
 constexpr int TMEM_COLS = 512;
 constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
@@ -38,7 +39,7 @@ template <typename Tout>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, VecRef bias,
                     int has_bias, Tout* __restrict__ out, int ldo, int accumulate, int M, int N, int K, int swiglu,
-                    int* __restrict__ error_word) {
+                    int splits, float* __restrict__ partials, int* __restrict__ counters, int* __restrict__ error_word) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzled tiles want 1024-byte alignment
     uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
@@ -50,10 +51,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     auto acc_empty_bar = [&](int b) { return bars + 8u * (2 * STAGES + 2 + b); };
     uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(aligned + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 4));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+    volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN, tiles = tiles_m * tiles_n;
     const int k_blocks = (K + BK - 1) / BK;
+    // With few tiles (few rows, a narrow matrix) K is split: a work unit is (tile, slice of the k blocks), so
+    // that every SM has a share of the weight stream. The slices' partial tiles meet in a workspace.
+    const int units = tiles * splits;
+    auto slice = [&](int s, int& lo, int& hi) {
+        const int q = k_blocks / splits, r = k_blocks % splits;
+        lo = s * q + min(s, r);
+        hi = lo + q + (s < r ? 1 : 0);
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -85,9 +95,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+            for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
+                const int tile = unit / splits;
                 const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                int lo, hi;
+                slice(unit % splits, lo, hi);
+                for (int kb = lo; kb < hi; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t parity = ((it / STAGES) & 1u) ^ 1u;
                     if (!mbar_wait(empty_bar(s), parity, abort_flag)) { ok = false; break; }
@@ -104,12 +117,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (lane == 0) {
             uint32_t it = 0, local_tile = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local_tile) {
+            for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++local_tile) {
                 const uint32_t buf = local_tile & 1u;
                 if (!mbar_wait(acc_empty_bar(buf), ((local_tile >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
                 tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + buf * BN;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                int lo, hi;
+                slice(unit % splits, lo, hi);
+                for (int kb = lo; kb < hi; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (!mbar_wait(full_bar(s), (it / STAGES) & 1u, abort_flag)) { ok = false; break; }
                     tcgen05_fence_after();
@@ -118,7 +133,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     for (int k = 0; k < BK / 16; ++k) {
                         // 16 bfloat16 = 32 bytes further along k inside the 128-byte swizzled rows
                         tcgen05_mma_bf16(tmem_d, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), IDESC,
-                                         (kb | k) != 0);
+                                         (kb > lo || k > 0) ? 1u : 0u);
                     }
                     tcgen05_commit(empty_bar(s));   // arrives when the MMAs above have read the stage
                 }
@@ -131,18 +146,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int quad = warp & 3;
         uint32_t local_tile = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local_tile) {
+        for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++local_tile) {
+            const int tile = unit / splits;
             const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
             const uint32_t buf = local_tile & 1u;
             if (!mbar_wait(acc_full_bar(buf), (local_tile >> 1) & 1u, abort_flag)) { ok = false; break; }
             tcgen05_fence_after();
             const int row = m0 + quad * 32 + lane;
             const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quad * 32) << 16);
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(taddr + c0, v);
-                tmem_ld_wait();
+            // bias / residual / SwiGLU and the store of 32 columns of this thread's row
+            auto finalize = [&](uint32_t (&v)[32], int c0) {
                 if (row < M && swiglu) {
                     // columns come in blocks of 16: 8 gate columns, then the 8 up columns of the same hidden units
                     const int n_base = n0 + c0;
@@ -240,10 +253,84 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         }
                     }
                 }
+            };
+            if (splits == 1) {
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(taddr + c0, v);
+                    tmem_ld_wait();
+                    finalize(v, c0);
+                }
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+                continue;
+            }
+            // ---- K was split: park this slice's partial tile ([unit][128 rows][256 columns]) ----
+            float4* mine = reinterpret_cast<float4*>(partials + ((size_t)unit * BM + quad * 32 + lane) * BN);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(taddr + c0, v);
+                tmem_ld_wait();
+                if (row < M) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        __stcg(mine + (c0 >> 2) + j, make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                                 __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3])));
+                }
             }
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+            asm volatile("bar.sync 1, 128;" ::: "memory");           // the four epilogue warps have written
+            if (warp == 2 && lane == 0) {
+                __threadfence();
+                const int seen = atomicAdd(&counters[tile], 1);
+                *last_flag = seen == splits - 1;
+                if (seen == splits - 1) {
+                    counters[tile] = 0;                               // back to zero for the next product
+                    __threadfence();
+                }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (*last_flag == 0) continue;
+            // ---- the block that came last adds the slices in slice order (deterministic) and finishes the tile ----
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                float acc[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) acc[j] = 0.f;
+                if (row < M) {
+                    for (int s0 = 0; s0 < splits; s0 += 4) {
+                        float4 part[4][8];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const float4* p = reinterpret_cast<const float4*>(
+                                partials + ((size_t)(tile * splits + min(s0 + u, splits - 1)) * BM + quad * 32 + lane) * BN) + (c0 >> 2);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) part[u][j] = __ldcg(p + j);
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            if (s0 + u < splits) {
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    acc[4 * j + 0] += part[u][j].x;
+                                    acc[4 * j + 1] += part[u][j].y;
+                                    acc[4 * j + 2] += part[u][j].z;
+                                    acc[4 * j + 3] += part[u][j].w;
+                                }
+                            }
+                        }
+                    }
+                }
+                uint32_t v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(acc[j]);
+                finalize(v, c0);
+            }
         }
         if (!ok && lane == 0) { *abort_flag = 1; atomicExch(error_word, 3); }
     }
@@ -292,7 +379,8 @@ JLLM_EXPORT int jllm_gemm_tcgen05_error() {
 
 JLLM_EXPORT int jllm_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, const void* bias, int bias_dtype,
                                   void* out, int out_dtype, int ldo, int accumulate, int M, int N, int K, int max_blocks,
-                                  int swiglu, cudaStream_t stream) {
+                                  int swiglu, float* workspace, long long workspace_floats, int force_splits,
+                                  cudaStream_t stream) {
     JLLM_REQUIRE(jllm_gemm_tcgen05_fits(a, lda, w, ldw, M, N, K),
                  "gemm_tcgen05: needs K %% 8 == 0 and 16-byte aligned rows (M=%d N=%d K=%d lda=%d ldw=%d)", M, N, K, lda,
                  ldw);
@@ -313,19 +401,34 @@ JLLM_EXPORT int jllm_gemm_tcgen05(const void* a, int lda, const void* w, int ldw
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     }
     const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-    int grid = tiles < sms ? tiles : sms;
+    const int k_blocks = (K + BK - 1) / BK;
+    // K can be split over blocks (force_splits), the slices meeting in the caller's workspace. It is not done by
+    // default: on the layer shapes of an 8B model with 64 rows the partial tiles' round trip through memory
+    // cost more than the idle SMs did (O projection 28 -> 49 us, QKV 28 -> 41 us, down 73 -> 61 us).
+    int splits = 1;
+    if (force_splits > 0) splits = force_splits > k_blocks ? k_blocks : force_splits;
+    const long long need = JLLM_TC_MAX_TILES + (long long)tiles * splits * BM * BN;
+    if (splits > 1) {
+        JLLM_REQUIRE(tiles <= JLLM_TC_MAX_TILES, "gemm_tcgen05: %d tiles with split K, at most %d", tiles, JLLM_TC_MAX_TILES);
+        JLLM_REQUIRE(workspace != nullptr && workspace_floats >= need,
+                     "gemm_tcgen05: split K needs a workspace of %lld floats, got %lld", need, workspace_floats);
+    }
+    int* counters = reinterpret_cast<int*>(workspace);
+    float* partials = workspace ? workspace + JLLM_TC_MAX_TILES : nullptr;
+    const int units = tiles * splits;
+    int grid = units < sms ? units : sms;
     if (max_blocks > 0 && grid > max_blocks) grid = max_blocks;
     const VecRef b{bias, bias_dtype};
     if (out_dtype == JLLM_F32) {
         auto kern = gemm_tcgen05_kernel<float>;
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
         jllm_launch(kern, dim3(grid), dim3(THREADS), SMEM_BYTES, stream, true, map_a, map_w, b, (int)(bias != nullptr),
-                    (float*)out, ldo, accumulate, M, N, K, swiglu, error_word);
+                    (float*)out, ldo, accumulate, M, N, K, swiglu, splits, partials, counters, error_word);
     } else {
         auto kern = gemm_tcgen05_kernel<__nv_bfloat16>;
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
         jllm_launch(kern, dim3(grid), dim3(THREADS), SMEM_BYTES, stream, true, map_a, map_w, b, (int)(bias != nullptr),
-                    (__nv_bfloat16*)out, ldo, accumulate, M, N, K, swiglu, error_word);
+                    (__nv_bfloat16*)out, ldo, accumulate, M, N, K, swiglu, splits, partials, counters, error_word);
     }
     return jllm_check_launch("gemm_tcgen05");
 }

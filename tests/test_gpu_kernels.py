@@ -132,6 +132,13 @@ def test_gemm_tcgen05(ops, M, N, K):
     ops.gemm_tcgen05(a, w, out16[:, :N])
     assert torch.allclose(out16[:, :N].float().cpu(), gemm_want(a, w), rtol=2 ** -7, atol=2e-3)
     assert float(out16[:, N:].abs().max()) == 0 and ops.gemm_tcgen05_error() == 0
+    # K split over blocks: the slices are added in slice order, so two runs give the same bits
+    if K >= 128:
+        one, two = base.clone(), base.clone()
+        ops.gemm_tcgen05(a, w, one, None, accumulate=True, force_splits=3)
+        ops.gemm_tcgen05(a, w, two, None, accumulate=True, force_splits=3)
+        assert torch.allclose(one.cpu(), gemm_want(a, w, None, base), rtol=1e-4, atol=tol) and torch.equal(one, two)
+        assert ops.gemm_tcgen05_error() == 0
 
 
 @pytest.mark.parametrize("M", [1, 7, 16, 17, 40, 64, 100, 128])
