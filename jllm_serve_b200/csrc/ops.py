@@ -284,9 +284,23 @@ def attention(q, k_cache, v_cache, out, batch, group, heads, kv_heads, head_dim,
         return attention_decode(q, k_cache, v_cache, out, batch.row_seg, batch.positions, batch.block_tables[group],
                                 batch.rows, heads, kv_heads, head_dim, page_size, window, scale, splits, scratch)
     if q.dtype == torch.bfloat16 and attention_prefill_fits(head_dim):
-        return attention_prefill(q, k_cache, v_cache, out, batch.seg_start, batch.seg_len, batch.seg_kv_len,
-                                 batch.block_tables[group], batch.rows, heads, kv_heads, head_dim, page_size, window,
-                                 scale)
+        # prompt portions through the flash kernel; the single rows riding beside them (the scheduler puts them
+        # last) through the decode kernel, which shares every key among the query heads of a kv head
+        ms, mr = batch.multi_segments, batch.multi_rows
+        if ms < 0 or mr == batch.rows or not attention_decode_fits(q.dtype, heads, kv_heads, head_dim):
+            ms, mr = batch.seg_start.numel(), batch.rows
+        if mr > 0:
+            attention_prefill(q[:mr], k_cache, v_cache, out[:mr], batch.seg_start[:ms], batch.seg_len[:ms],
+                              batch.seg_kv_len[:ms], batch.block_tables[group], mr, heads, kv_heads, head_dim, page_size,
+                              window, scale)
+        if mr < batch.rows:
+            n = batch.rows - mr
+            bucket = batch.kv_bucket if window <= 0 else max(1, min(batch.kv_bucket, window // 256))
+            splits = decode_splits(n, kv_heads, bucket, heads, head_dim, scratch)
+            attention_decode(q[mr:], k_cache, v_cache, out[mr:], batch.row_seg[mr:], batch.positions[mr:],
+                             batch.block_tables[group], n, heads, kv_heads, head_dim, page_size, window, scale, splits,
+                             scratch)
+        return
     attention_plain(q, q.stride(0), k_cache, v_cache, out, batch.row_seg, batch.positions, batch.block_tables[group],
                     batch.rows, heads, kv_heads, head_dim, page_size, window, scale)
 

@@ -45,6 +45,8 @@ class StepBatch:
     max_q_len: int
     max_kv_len: int
     kv_bucket: int = 1                     # max_kv_len in units of 256 keys, capped: picks the decode split
+    multi_segments: int = -1               # segments [0, multi_segments) bring several rows, the rest one row each;
+    multi_rows: int = 0                    # they cover rows [0, multi_rows); -1 = the batch is not of that form
     host_seg_start: List[int] = field(default_factory=list)
     host_state_slots: List[int] = field(default_factory=list)
 
@@ -108,6 +110,7 @@ class BatchBuilder:
         r = 0
         n_want = 0
         max_q = max_kv = 0
+        multi_segments, multi_rows, ordered = 0, 0, True
         ps = self.page_size
         for si, seg in enumerate(segments):
             n = len(seg.tokens)
@@ -138,6 +141,9 @@ class BatchBuilder:
                 tb = np.asarray(table, dtype=np.int32)
                 self._np_tables[g, si, :nb] = tb
                 slot_views[g][r:r + n] = tb[p // ps] * ps + p % ps
+            if n > 1:
+                ordered = ordered and multi_segments == si       # no single-row segment came before it
+                multi_segments, multi_rows = si + 1, r + n
             r += n
             max_q = max(max_q, n)
             max_kv = max(max_kv, seg.start + n)
@@ -160,4 +166,5 @@ class BatchBuilder:
             block_tables=[dt[g, :S] for g in range(self.groups)],
             num_wanted=n_want, max_q_len=max_q, max_kv_len=max_kv,
             kv_bucket=max(1, min(32, max_kv // 256, -(-296 // rows))),
+            multi_segments=multi_segments if ordered else -1, multi_rows=multi_rows,
             host_seg_start=[int(v) for v in sstart[:S]], host_state_slots=[int(v) for v in sslot[:S]])
