@@ -1,0 +1,123 @@
+"""Times the hand-written kernels alone on the layer shapes of a model, against their rooflines.
+
+    python -m jllm_serve_b200.kernel_bench [--rows 8] [--prompt 2048] [--context 4096] [--repeat 20] [--only NAME]
+
+Every kernel runs on random tensors of the shapes one layer of the Qwen3-8B configuration gives it
+(hidden 4096, 32/8 heads of 128, intermediate 12288), timed with CUDA events over `--repeat` calls that
+rotate through several copies of the weights, so every call streams them from HBM. It prints, per kernel,
+microseconds per call and the achieved GB/s (weight or cache bytes, the decode kernels) or TFLOP/s (the
+prefill kernels). With `--repeat 1` it is the small workload that profilers are pointed at.
+"""
+from __future__ import annotations
+
+import argparse
+import math
+import sys
+
+import torch
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
+    ap.add_argument("--rows", type=int, default=8, help="rows of a decode step")
+    ap.add_argument("--prompt", type=int, default=2048, help="rows of a prefill step")
+    ap.add_argument("--context", type=int, default=4096, help="cached positions per request in the decode attention")
+    ap.add_argument("--repeat", type=int, default=20)
+    ap.add_argument("--only", default="", help="run only the kernels whose name contains this")
+    args = ap.parse_args()
+
+    from .csrc import ops
+    ops.require_device()
+    dev = torch.device("cuda:0")
+    D, H, Hkv, hd, F, page = 4096, 32, 8, 128, 12288, 16
+    M, T, ctx = args.rows, args.prompt, args.context
+    bf = torch.bfloat16
+
+    def weights(n, k):
+        copies = max(2, int(300e6 // (n * k * 2)) + 1) if args.repeat > 1 else 1
+        return [(torch.randn(n, k, device=dev) * 0.02).to(bf) for _ in range(copies)]
+
+    def interleaved(n_hidden, k):
+        return weights(2 * n_hidden, k)      # the SwiGLU epilogue only needs the row count to be a multiple of 16
+
+    cases = []
+
+    def case(name, fn, copies, bytes_=0, flops=0):
+        if args.only in name:
+            cases.append((name, fn, copies, bytes_, flops))
+
+    # ---- decode: M rows ----
+    a_d, a_f = torch.randn(M, D, device=dev).to(bf), torch.randn(M, F, device=dev).to(bf)
+    x = torch.randn(M, D, device=dev)
+    qkv_d, h_d = torch.empty(M, (H + 2 * Hkv) * hd, device=dev, dtype=bf), torch.empty(M, F, device=dev, dtype=bf)
+    w_qkv, w_o, w_gu, w_down = weights((H + 2 * Hkv) * hd, D), weights(D, H * hd), interleaved(F, D), weights(D, F)
+    case("decode gemm qkv", lambda i: ops.gemm_bf16(a_d, w_qkv[i], qkv_d), len(w_qkv), w_qkv[0].numel() * 2)
+    case("decode gemm o (+= residual)", lambda i: ops.gemm_bf16(a_d, w_o[i], x, None, True), len(w_o), w_o[0].numel() * 2)
+    case("decode gemm gate_up + swiglu", lambda i: ops.gemm_bf16(a_d, w_gu[i], h_d, swiglu=True), len(w_gu),
+         w_gu[0].numel() * 2)
+    case("decode gemm down (+= residual)", lambda i: ops.gemm_bf16(a_f, w_down[i], x, None, True), len(w_down),
+         w_down[0].numel() * 2)
+    pages = M * (ctx // page + 1)
+    n_caches = max(2, int(300e6 // (pages * Hkv * page * hd * 4)) + 1) if args.repeat > 1 else 1
+    caches = [(torch.randn(pages, Hkv, page, hd, device=dev).to(bf), torch.randn(pages, Hkv, page, hd, device=dev).to(bf))
+              for _ in range(n_caches)]
+    tables = torch.arange(pages, dtype=torch.int32, device=dev).reshape(M, -1).contiguous()
+    q = torch.randn(M, H * hd, device=dev).to(bf)
+    out = torch.empty_like(q)
+    seg = torch.arange(M, dtype=torch.int32, device=dev)
+    pos = torch.full((M,), ctx - 1, dtype=torch.int32, device=dev)
+    scratch = torch.empty(2 << 20, device=dev)
+    splits = ops.decode_splits(M, Hkv, max(1, min(32, ctx // 256)), H, hd, scratch)
+    case(f"decode attention ({splits} splits)",
+         lambda i: ops.attention_decode(q, caches[i][0], caches[i][1], out, seg, pos, tables, M, H, Hkv, hd, page, 0,
+                                        1 / math.sqrt(hd), splits, scratch), n_caches, M * ctx * Hkv * hd * 4)
+    gain = torch.ones(D, device=dev, dtype=bf)
+    xb = torch.empty(M, D, device=dev, dtype=bf)
+    case("decode rmsnorm", lambda i: ops.rmsnorm(x, gain, 1e-6, xb), 1, M * D * 6)
+
+    # ---- prefill: T rows of one request ----
+    a_p = torch.randn(T, D, device=dev).to(bf)
+    h_p = torch.empty(T, F, device=dev, dtype=bf)
+    qkv_p = torch.empty(T, (H + 2 * Hkv) * hd, device=dev, dtype=bf)
+    x_p = torch.randn(T, D, device=dev)
+    case("prefill gemm qkv", lambda i: ops.gemm_bf16(a_p, w_qkv[i], qkv_p), len(w_qkv), flops=2 * T * D * qkv_p.shape[1])
+    case("prefill gemm gate_up + swiglu", lambda i: ops.gemm_bf16(a_p, w_gu[i], h_p, swiglu=True), len(w_gu),
+         flops=2 * T * D * 2 * F)
+    case("prefill gemm down (+= residual)", lambda i: ops.gemm_bf16(h_p, w_down[i], x_p, None, True), len(w_down),
+         flops=2 * T * D * F)
+    pp = T // page + 1
+    kc, vc = torch.randn(pp, Hkv, page, hd, device=dev).to(bf), torch.randn(pp, Hkv, page, hd, device=dev).to(bf)
+    tp = torch.arange(pp, dtype=torch.int32, device=dev).reshape(1, -1).contiguous()
+    qp = torch.randn(T, H * hd, device=dev).to(bf)
+    op = torch.empty_like(qp)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    s0, s1, s2 = i32([0]), i32([T]), i32([T])
+    case("prefill attention (causal)",
+         lambda i: ops.attention_prefill(qp, kc, vc, op, s0, s1, s2, tp, T, H, Hkv, hd, page, 0, 1 / math.sqrt(hd)), 1,
+         flops=4 * (T * (T + 1) // 2) * H * hd)
+    gp = torch.ones(D, device=dev, dtype=bf)
+    xbp = torch.empty(T, D, device=dev, dtype=bf)
+    case("prefill rmsnorm", lambda i: ops.rmsnorm(x_p, gp, 1e-6, xbp), 1, T * D * 6)
+
+    for name, fn, copies, bytes_, flops in cases:
+        for i in range(3 if args.repeat > 1 else 0):
+            fn(i % copies)
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for i in range(args.repeat):
+            fn(i % copies)
+        e.record()
+        torch.cuda.synchronize()
+        us = s.elapsed_time(e) / args.repeat * 1e3
+        rate = f"{bytes_ / us / 1e3:8.0f} GB/s" if bytes_ else f"{flops / us / 1e6:8.0f} TFLOP/s"
+        print(f"{name:36s} {us:9.1f} us {rate}", flush=True)
+    err = ops.gemm_tcgen05_error()
+    if err:
+        print(f"a tcgen05 kernel raised error {err}", file=sys.stderr)
+        return 1
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
