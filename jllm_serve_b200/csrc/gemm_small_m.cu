@@ -44,7 +44,7 @@ template <int NT, int RT, int UNROLL, typename Tout>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_small_m_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w, int ldw,
                     VecRef bias, int has_bias, Tout* __restrict__ out, int ldo, int accumulate, int M, int N, int K,
-                    int swiglu) {
+                    int swiglu, int prefetch_bytes) {
     extern __shared__ float red[];  // [WARPS][RT * 16][NT * 8]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -90,8 +90,14 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfl
         }
     };
     // The weights do not depend on the kernel before this one: the first batch is requested while that kernel
-    // is still running. (Pulling the block's whole slice into L2 ahead of time with a bulk prefetch was tried
-    // and made the step slower: it competes with the running kernel's own stream.)
+    // is still running, and the head of every row of the block's slice (prefetch_bytes, bounded by the host so
+    // that one product never asks for more than a fraction of L2) is pulled towards L2. The kernels between two
+    // products (norms, RoPE, the attention combine) are tiny: the weight stream would otherwise pause for them.
+    if (prefetch_bytes > 0 && threadIdx.x < RT * 16) {
+        const int n = n0 + threadIdx.x;
+        if (n < N)
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(w + (size_t)n * ldw), "r"(prefetch_bytes) : "memory");
+    }
     load_weights(warp);
     pdl_wait();
     pdl_trigger();
@@ -161,19 +167,19 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfl
 
 template <int NT, int RT, int UNROLL>
 int launch(const void* a, int lda, const void* w, int ldw, VecRef bias, int has_bias, void* out, int out_dtype, int ldo,
-           int accumulate, int M, int N, int K, int swiglu, cudaStream_t stream) {
+           int accumulate, int M, int N, int K, int swiglu, int prefetch_bytes, cudaStream_t stream) {
     const int grid = (N + 16 * RT - 1) / (16 * RT);
     const size_t smem = (size_t)WARPS * RT * 16 * NT * 8 * sizeof(float);
     if (out_dtype == JLLM_F32) {
         auto kern = gemm_small_m_kernel<NT, RT, UNROLL, float>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         jllm_launch(kern, dim3(grid), dim3(WARPS * 32), smem, stream, true, (const __nv_bfloat16*)a, lda,
-                    (const __nv_bfloat16*)w, ldw, bias, has_bias, (float*)out, ldo, accumulate, M, N, K, swiglu);
+                    (const __nv_bfloat16*)w, ldw, bias, has_bias, (float*)out, ldo, accumulate, M, N, K, swiglu, prefetch_bytes);
     } else {
         auto kern = gemm_small_m_kernel<NT, RT, UNROLL, __nv_bfloat16>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         jllm_launch(kern, dim3(grid), dim3(WARPS * 32), smem, stream, true, (const __nv_bfloat16*)a, lda,
-                    (const __nv_bfloat16*)w, ldw, bias, has_bias, (__nv_bfloat16*)out, ldo, accumulate, M, N, K, swiglu);
+                    (const __nv_bfloat16*)w, ldw, bias, has_bias, (__nv_bfloat16*)out, ldo, accumulate, M, N, K, swiglu, prefetch_bytes);
     }
     return jllm_check_launch("gemm_small_m");
 }
@@ -188,7 +194,7 @@ JLLM_EXPORT int jllm_gemm_small_m_fits(const void* a, int lda, const void* w, in
 
 JLLM_EXPORT int jllm_gemm_small_m(const void* a, int lda, const void* w, int ldw, const void* bias, int bias_dtype,
                                   void* out, int out_dtype, int ldo, int accumulate, int M, int N, int K,
-                                  int tuning, int swiglu, cudaStream_t stream) {
+                                  int tuning, int swiglu, int prefetch_mb, cudaStream_t stream) {
     JLLM_REQUIRE(jllm_gemm_small_m_fits(a, lda, w, ldw, M, N, K),
                  "gemm_small_m: needs 1 <= M <= 64, K %% 8 == 0 and 16-byte aligned rows (M=%d N=%d K=%d lda=%d ldw=%d)",
                  M, N, K, lda, ldw);
@@ -202,7 +208,11 @@ JLLM_EXPORT int jllm_gemm_small_m(const void* a, int lda, const void* w, int ldw
     bool wide = N >= 64 * 32;
     int deep = 0;
     if (tuning > 0) { wide = (tuning & 1) != 0; deep = (tuning >> 1) & 1; }
-#define JLLM_GO(NT, RT, UN) return launch<NT, RT, UN>(a, lda, w, ldw, b, hb, out, out_dtype, ldo, accumulate, M, N, K, swiglu, stream)
+    // at most prefetch_mb MB of this matrix are prefetched into L2, the same number of bytes from every row
+    long long per_row = prefetch_mb > 0 ? ((long long)prefetch_mb << 20) / N : 0;
+    if (per_row > (long long)K * 2) per_row = (long long)K * 2;
+    const int prefetch_bytes = (int)(per_row & ~15LL);
+#define JLLM_GO(NT, RT, UN) return launch<NT, RT, UN>(a, lda, w, ldw, b, hb, out, out_dtype, ldo, accumulate, M, N, K, swiglu, prefetch_bytes, stream)
     if (M <= 8) { if (wide) { if (deep) JLLM_GO(1, 2, 8); JLLM_GO(1, 2, 4); } if (deep) JLLM_GO(1, 1, 8); JLLM_GO(1, 1, 4); }
     if (M <= 16) { if (wide) JLLM_GO(2, 2, 4); if (deep) JLLM_GO(2, 1, 8); JLLM_GO(2, 1, 4); }
     if (M <= 32) { if (wide) JLLM_GO(4, 2, 2); JLLM_GO(4, 1, 4); }
