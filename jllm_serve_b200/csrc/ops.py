@@ -93,6 +93,8 @@ class _Signatures:
     jllm_attention_plain = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P]
     jllm_attention_decode = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
     jllm_attention_prefill = [P, I, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P]
+    jllm_attention_prefill_tc = [P, I, P, P, ctypes.c_longlong, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P]
+    jllm_attention_prefill_tc_error = []
     jllm_argmax = [P, I, I, I, P, P]
     jllm_sample = [P, I, I, I, P, P, P, P, P, P, P]
 
@@ -312,13 +314,33 @@ def attention_prefill_fits(head_dim) -> bool:
     return head_dim in (64, 128, 256)
 
 
+PREFILL_TC = int(__import__("os").environ.get("JLLM_B200_PREFILL_TC", "1"))
+
+
+def attention_prefill_tc_fits(q, out, k_cache, head_dim, page_size) -> bool:
+    return (head_dim == 128 and 1 <= page_size <= 128 and page_size & (page_size - 1) == 0 and q.stride(0) % 8 == 0
+            and out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0
+            and k_cache.is_contiguous())
+
+
 def attention_prefill(q, k_cache, v_cache, out, seg_start, seg_len, seg_kv_len, block_tables, rows, heads, kv_heads,
-                      head_dim, page_size, window, scale) -> None:
-    """Flash attention of prompt portions: segments of consecutive rows, each over its own request's pages."""
+                      head_dim, page_size, window, scale, kernel: str = "auto") -> None:
+    """Flash attention of prompt portions: segments of consecutive rows, each over its own request's pages.
+    Head size 128 runs on tcgen05 (both products, accumulators in tensor memory), other sizes on mma.sync."""
+    if kernel == "tc" or (kernel == "auto" and PREFILL_TC and attention_prefill_tc_fits(q, out, k_cache, head_dim, page_size)):
+        return _call("jllm_attention_prefill_tc", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+                     k_cache.shape[0], out.data_ptr(), out.stride(0), seg_start.data_ptr(), seg_len.data_ptr(),
+                     seg_kv_len.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), seg_start.numel(), rows,
+                     heads, kv_heads, head_dim, page_size, int(window), float(scale), _stream())
     _call("jllm_attention_prefill", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
           out.stride(0), seg_start.data_ptr(), seg_len.data_ptr(), seg_kv_len.data_ptr(), block_tables.data_ptr(),
           block_tables.stride(0), seg_start.numel(), rows, heads, kv_heads, head_dim, page_size, int(window),
           float(scale), _stream())
+
+
+def attention_prefill_tc_error() -> int:
+    """0, or the code the tcgen05 attention kernel raised because a bounded wait ran out (synchronises)."""
+    return library().jllm_attention_prefill_tc_error()
 
 
 def decode_splits(rows, kv_heads, kv_bucket, heads, head_dim, scratch, resident_blocks: int = 2 * 148) -> int:

@@ -289,12 +289,8 @@ def test_attention_plain(ops, dtype, H, Hkv, hd, page, window):
         assert torch.allclose(out.float().cpu(), want, **tol), float((out.float().cpu() - want).abs().max())
 
 
-@pytest.mark.parametrize("H,Hkv,hd,page,window", [(6, 2, 64, 16, 0), (4, 4, 128, 4, 0), (32, 8, 128, 16, 0),
-                                                   (6, 3, 64, 8, 21), (4, 1, 256, 16, 0), (2, 1, 64, 1, 7),
-                                                   (8, 2, 128, 16, 100)])
-def test_attention_prefill(ops, H, Hkv, hd, page, window):
-    """Portions of prompts (and single rows) of several requests in one launch, starting anywhere in a page."""
-    lens, q_lens, scale = [1, 17, 64, 131, 300, 1000, 77], [1, 17, 30, 131, 200, 65, 1], 1.0 / math.sqrt(hd)
+def check_attention_prefill(ops, H, Hkv, hd, page, window, lens, q_lens, kernel):
+    scale = 1.0 / math.sqrt(hd)
     for far in (False, True):
         q, kc, vc, out, rseg, rpos, tables, want, q_lens = attention_case(ops, torch.bfloat16, H, Hkv, hd, page, lens,
                                                                           window, scale, far, q_lens)
@@ -302,9 +298,31 @@ def test_attention_prefill(ops, H, Hkv, hd, page, window):
         starts = [sum(q_lens[:i]) for i in range(len(lens))]
         i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
         ops.attention_prefill(q, kc, vc, out, i32(starts), i32(q_lens), i32(lens), tables, q.shape[0], H, Hkv, hd, page,
-                              window, scale)
+                              window, scale, kernel=kernel)
+        assert ops.attention_prefill_tc_error() == 0
         assert torch.isfinite(out).all()
         assert torch.allclose(out.float().cpu(), want, rtol=2e-2, atol=2e-2), float((out.float().cpu() - want).abs().max())
+
+
+@pytest.mark.parametrize("kernel", ["mma", "tc"])
+@pytest.mark.parametrize("H,Hkv,hd,page,window", [(6, 2, 64, 16, 0), (4, 4, 128, 4, 0), (32, 8, 128, 16, 0),
+                                                   (6, 3, 64, 8, 21), (4, 1, 256, 16, 0), (2, 1, 64, 1, 7),
+                                                   (8, 2, 128, 16, 100)])
+def test_attention_prefill(ops, H, Hkv, hd, page, window, kernel):
+    """Portions of prompts (and single rows) of several requests in one launch, starting anywhere in a page."""
+    if kernel == "tc" and hd != 128:
+        pytest.skip("the tcgen05 kernel is built for head size 128")
+    check_attention_prefill(ops, H, Hkv, hd, page, window, [1, 17, 64, 131, 300, 1000, 77], [1, 17, 30, 131, 200, 65, 1],
+                            kernel)
+
+
+@pytest.mark.parametrize("H,Hkv,page,window", [(2, 1, 1, 0), (3, 3, 2, 0), (4, 2, 32, 0), (2, 2, 64, 300), (6, 1, 128, 0),
+                                               (4, 2, 16, 128), (2, 1, 8, 129), (2, 2, 16, 1)])
+def test_attention_prefill_tcgen05_tiles(ops, H, Hkv, page, window):
+    """The tcgen05 kernel over several query tiles and many key tiles: portions that start and end anywhere
+    relative to the 128-key tiles, every page size, windows at, below and above a tile."""
+    check_attention_prefill(ops, H, Hkv, 128, page, window, [128, 129, 700, 1500, 256, 383],
+                            [128, 2, 513, 300, 129, 255], "tc")
 
 
 @pytest.mark.parametrize("splits", [1, 3, 8])
