@@ -21,6 +21,7 @@ callable it is given (None in tests that need no device).
 """
 from __future__ import annotations
 
+import itertools
 from dataclasses import dataclass, field
 from typing import Callable, Dict, Hashable, List, Optional, Sequence, Tuple
 
@@ -76,6 +77,7 @@ class RequestCache:
     state_slot: int
     length: int = 0
     tables: List[List[int]] = field(default_factory=list)  # one per paged group
+    epoch: int = 0                         # changes whenever a table changed otherwise than by growing at its end
 
 
 class CacheManager:
@@ -113,6 +115,7 @@ class CacheManager:
             else:
                 raise TypeError(f"layer run {run}: unknown cache need {need!r}")
         self.slots = StateSlotPool(max_requests)
+        self._epochs = itertools.count(1)
         self.requests: Dict[Hashable, RequestCache] = {}
         if allocate is not None:
             for g in self.paged:
@@ -140,7 +143,7 @@ class CacheManager:
     def open(self, request: Hashable) -> RequestCache:
         if request in self.requests:
             raise ValueError(f"request {request!r} is open already")
-        rc = RequestCache(request, self.slots.alloc(request), 0, [[] for _ in self.paged])
+        rc = RequestCache(request, self.slots.alloc(request), 0, [[] for _ in self.paged], next(self._epochs))
         self.requests[request] = rc
         return rc
 
@@ -190,6 +193,7 @@ class CacheManager:
                     table.append(page)
                     taken.append((gi, page))
         except PoolExhausted:
+            rc.epoch = next(self._epochs)
             for gi, page in reversed(taken):
                 popped = rc.tables[gi].pop()
                 if popped != page:
@@ -214,6 +218,8 @@ class CacheManager:
                     g.pool.free(page, request)
                     rc.tables[gi][i] = RELEASED
                     released.append((gi, page))
+        if released:
+            rc.epoch = next(self._epochs)
         return released
 
     def truncate(self, request: Hashable, length: int) -> None:
@@ -228,6 +234,7 @@ class CacheManager:
                 if any(p == RELEASED for p in rc.tables[gi][self._first_needed_page(g, length):keep]):
                     raise ValueError(f"request {request!r}: a windowed group has released pages that a rewind "
                                      f"to {length} needs; recompute from the start")
+        rc.epoch = next(self._epochs)
         for gi, g in enumerate(self.paged):
             table = rc.tables[gi]
             while len(table) > keep:
@@ -240,6 +247,7 @@ class CacheManager:
         """Give back pages reserved beyond the committed length (a step that was reserved but did not run)."""
         rc = self.requests[request]
         keep = -(-rc.length // self.page_size)
+        rc.epoch = next(self._epochs)
         for gi, g in enumerate(self.paged):
             table = rc.tables[gi]
             while len(table) > keep:
@@ -258,6 +266,11 @@ class CacheManager:
 
     def table(self, request: Hashable, group: int) -> List[int]:
         return self.requests[request].tables[group]
+
+    def table_epoch(self, request: Hashable) -> int:
+        """A number that is new whenever the request's tables changed otherwise than by growing at their end
+        (and for every opening of a request): who keeps a copy of a table may extend it while this stays."""
+        return self.requests[request].epoch
 
     def state_slot(self, request: Hashable) -> int:
         return self.requests[request].state_slot

@@ -76,6 +76,8 @@ class BatchBuilder:
         self._copied = torch.cuda.Event() if torch.cuda.is_available() else None
         self._np_small = self._host_small.numpy()
         self._np_tables = self._host_tables.numpy().reshape(max(1, G), S, max_blocks)
+        # what each row of the host tables holds: (request, its table epoch, entries written)
+        self._table_rows = [[None] * S for _ in range(max(1, G))]
 
     def bytes_per_step(self, segments: int) -> int:
         """Bytes a step with `segments` segments copies from pinned host memory to the device."""
@@ -119,13 +121,19 @@ class BatchBuilder:
             if seg.request in seen:
                 raise ValueError(f"request {seg.request!r} appears twice in one step")
             seen.add(seg.request)
-            t = np.asarray(seg.tokens, dtype=np.int64)
-            if t.min() < 0 or t.max() >= vocab:
-                raise ValueError(f"request {seg.request!r}: token id outside [0, {vocab})")
-            tok[r:r + n] = t
-            p = np.arange(seg.start, seg.start + n, dtype=np.int32)
-            pos[r:r + n] = p
-            rseg[r:r + n] = si
+            if n == 1:
+                t0 = int(seg.tokens[0])
+                if not 0 <= t0 < vocab:
+                    raise ValueError(f"request {seg.request!r}: token id outside [0, {vocab})")
+                tok[r], pos[r], rseg[r] = t0, seg.start, si
+            else:
+                t = np.asarray(seg.tokens, dtype=np.int64)
+                if t.min() < 0 or t.max() >= vocab:
+                    raise ValueError(f"request {seg.request!r}: token id outside [0, {vocab})")
+                tok[r:r + n] = t
+                p = np.arange(seg.start, seg.start + n, dtype=np.int32)
+                pos[r:r + n] = p
+                rseg[r:r + n] = si
             sstart[si], slen[si], skv[si] = r, n, seg.start + n
             sslot[si] = cache.state_slot(seg.request)
             for w in seg.want:
@@ -133,14 +141,23 @@ class BatchBuilder:
                     raise ValueError(f"request {seg.request!r}: wanted place {w} is outside its {n} tokens")
                 lrows[n_want] = r + w
                 n_want += 1
+            epoch = cache.table_epoch(seg.request) if self.groups else 0
             for g in range(self.groups):
                 table = cache.table(seg.request, g)
                 nb = len(table)
                 if nb > self.max_blocks:
                     raise ValueError(f"request {seg.request!r} holds {nb} pages, tables have {self.max_blocks} columns")
-                tb = np.asarray(table, dtype=np.int32)
-                self._np_tables[g, si, :nb] = tb
-                slot_views[g][r:r + n] = tb[p // ps] * ps + p % ps
+                # the row of the host table: only what the request's table grew by since this row was last
+                # written for it, if nothing else about the table changed (its epoch)
+                held = self._table_rows[g][si]
+                lo = held[2] if held is not None and held[0] == seg.request and held[1] == epoch and held[2] <= nb else 0
+                if lo < nb:
+                    self._np_tables[g, si, lo:nb] = table[lo:nb]
+                self._table_rows[g][si] = (seg.request, epoch, nb)
+                if n == 1:
+                    slot_views[g][r] = table[seg.start // ps] * ps + seg.start % ps
+                else:
+                    slot_views[g][r:r + n] = self._np_tables[g, si, :nb][p // ps] * ps + p % ps
             if n > 1:
                 ordered = ordered and multi_segments == si       # no single-row segment came before it
                 multi_segments, multi_rows = si + 1, r + n

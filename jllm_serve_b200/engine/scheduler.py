@@ -53,6 +53,15 @@ class Request:
     def tokens(self) -> List[int]:
         return self.prompt + self.output
 
+    def tokens_between(self, lo: int, hi: int) -> List[int]:
+        """tokens[lo:hi] without joining the prompt and the output."""
+        n = len(self.prompt)
+        if lo >= n:
+            return self.output[lo - n:hi - n]
+        if hi <= n:
+            return self.prompt[lo:hi]
+        return self.prompt[lo:] + self.output[:hi - n]
+
     @property
     def remaining(self) -> int:
         return len(self.prompt) + len(self.output) - self.computed
@@ -200,7 +209,7 @@ class Scheduler:
             segments = []
             for p in picks:
                 r = p.ref
-                toks = r.tokens[r.computed:r.computed + p.rows]
+                toks = r.tokens_between(r.computed, r.computed + p.rows)
                 segments.append(PlannedSegment(r, r.computed, toks, r.computed + p.rows == len(r.prompt) + len(r.output)))
                 if p.kind == "chunk":
                     self.prefill_line.remove(r)

@@ -150,3 +150,74 @@ def test_random_orders_keep_the_books(seed):
         m.close(rid)
     m.check()
     assert m.free_pages() == [40, 40] and m.slots.num_free == 5
+
+
+def test_table_epoch_changes_with_everything_but_growth():
+    m = CacheManager([PagedKeysValues(2, 16, 0), PagedKeysValues(2, 16, 8)], page_size=4, num_pages=12, max_requests=2)
+    m.open("a")
+    e0 = m.table_epoch("a")
+    m.reserve("a", 0, 13)
+    assert m.table_epoch("a") == e0                      # growth at the end keeps it
+    m.commit("a", 13)
+    e1 = m.table_epoch("a")
+    assert e1 != e0                                      # the windowed group gave a page back
+    m.reserve("a", 13, 4)
+    assert m.table_epoch("a") == e1
+    m.trim("a")
+    e2 = m.table_epoch("a")
+    assert e2 != e1
+    m.close("a")
+    m.open("a")
+    assert m.table_epoch("a") not in (e0, e1, e2)        # a request opened again is another one
+    m.reserve("a", 0, 6)
+    m.commit("a", 6)
+    e3 = m.table_epoch("a")
+    m.truncate("a", 2)
+    assert m.table_epoch("a") != e3
+
+
+def test_batch_tables_follow_the_requests_tables():
+    """The batch builder extends its copy of a block table while the epoch stays; after a rewind, a request that
+    changed rows, or a request opened again, the row is written anew."""
+    import torch
+
+    from jllm_serve_b200.engine.batch import BatchBuilder, Segment
+    m = CacheManager([PagedKeysValues(1, 8, 0)], page_size=2, num_pages=64, max_requests=4)
+    b = BatchBuilder(torch.device("cpu"), max_rows=32, max_segments=4, max_blocks=16, num_paged_groups=1, page_size=2)
+    rng = random.Random(0)
+    lengths = {}
+
+    def step(reqs, n_of):
+        segs = []
+        for r in reqs:
+            if not m.is_open(r):
+                m.open(r)
+                lengths[r] = 0
+            m.reserve(r, lengths[r], n_of[r])
+            segs.append(Segment(r, [1] * n_of[r], lengths[r], [n_of[r] - 1]))
+        batch = b.build(segs, m, vocab=10)
+        row = 0
+        for si, r in enumerate(reqs):
+            table = m.table(r, 0)
+            assert batch.block_tables[0][si, :len(table)].tolist() == table
+            for i in range(n_of[r]):
+                p = lengths[r] + i
+                assert int(batch.slots[0][row]) == table[p // 2] * 2 + p % 2
+                row += 1
+            lengths[r] += n_of[r]
+            m.commit(r, lengths[r])
+
+    step(["a", "b"], {"a": 5, "b": 3})
+    for _ in range(6):
+        step(["a", "b"], {"a": 1, "b": 1})
+    step(["b", "a"], {"a": 1, "b": 1})                      # rows swapped
+    m.truncate("a", 3)                                      # a rewind, then other pages under the same indices
+    m.open("c")
+    m.reserve("c", 0, 7)
+    lengths["a"] = 3
+    step(["b", "a"], {"a": 4, "b": 1})
+    m.close("b")                                            # opened again under the same name
+    step(["b", "a"], {"a": 1, "b": 2})
+    for _ in range(8):
+        reqs = rng.sample(["a", "b"], 2)
+        step(reqs, {"a": rng.randint(1, 3), "b": 1})
