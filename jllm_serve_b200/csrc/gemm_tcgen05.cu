@@ -1,6 +1,7 @@
 // out[m, n] (+)= sum_k a[m, k] * w[n, k] (+ bias[n]) on the 5th-generation tensor cores (tcgen05), bfloat16.
 //
-// The prefill product. A persistent kernel, one block per SM, walks 128 x 256 output tiles:
+// The prefill product. A persistent kernel, one block per SM, walks 128 x BN output tiles (BN = 256 for big
+// products, narrower when the rows are few):
 //   * warp 0 (one lane) is the TMA producer: for every 64-wide k block it waits for a free stage and
 //     issues two tiled bulk copies (a 128 x 64 tile of A, a 256 x 64 tile of W) into 128-byte-swizzled
 //     shared memory, completing on the stage's "full" mbarrier (no cluster multicast anywhere);
@@ -24,22 +25,33 @@ namespace {
 
 using namespace tc;
 
-constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
-constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int BM = 128, BK = 64;
+constexpr int A_BYTES = BM * BK * 2;
+// The tile's width BN is a template parameter: 256 for the big products of a prefill; narrower tiles when the
+// rows are few (more than the weight-stream kernel takes, at most a few hundred), so that every SM has a tile of
+// the weight matrix to stream. Narrow tiles have small stages, so the ring is deeper.
+__host__ __device__ constexpr int stages_for(int bn) { return bn >= 256 ? 4 : bn >= 192 ? 5 : bn >= 128 ? 6 : 8; }
 constexpr int JLLM_TC_MAX_TILES = 4096;  // counter words at the head of the split-K workspace
 constexpr int THREADS = 192;           // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
 constexpr int TMEM_COLS = 512;
-constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+__host__ __device__ constexpr size_t smem_bytes_for(int bn) {
+    return (size_t)stages_for(bn) * (A_BYTES + bn * BK * 2) + 1024 /* alignment slack */ + 256 /* barriers */;
+}
 
 // Instruction descriptor of kind::f16: float32 accumulate (1 at [4,6)), A and B bfloat16 (1 at [7,10) and
 // [10,13)), both K-major (0 at 15 and 16), N >> 3 at [17,23), M >> 4 at [24,29).
-constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+__host__ __device__ constexpr uint32_t idesc_for(int bn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
 
-template <typename Tout>
+template <typename Tout, int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, VecRef bias,
                     int has_bias, Tout* __restrict__ out, int ldo, int accumulate, int M, int N, int K, int swiglu,
                     int splits, float* __restrict__ partials, int* __restrict__ counters, int* __restrict__ error_word) {
+    constexpr int STAGES = stages_for(BN), B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t IDESC = idesc_for(BN);
+    static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "tile width");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzled tiles want 1024-byte alignment
     uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
@@ -380,13 +392,33 @@ JLLM_EXPORT int jllm_gemm_tcgen05_error() {
 JLLM_EXPORT int jllm_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, const void* bias, int bias_dtype,
                                   void* out, int out_dtype, int ldo, int accumulate, int M, int N, int K, int max_blocks,
                                   int swiglu, float* workspace, long long workspace_floats, int force_splits,
-                                  cudaStream_t stream) {
+                                  int tile_width, cudaStream_t stream) {
     JLLM_REQUIRE(jllm_gemm_tcgen05_fits(a, lda, w, ldw, M, N, K),
                  "gemm_tcgen05: needs K %% 8 == 0 and 16-byte aligned rows (M=%d N=%d K=%d lda=%d ldw=%d)", M, N, K, lda,
                  ldw);
     JLLM_REQUIRE(ldo >= (swiglu ? N / 2 : N), "gemm_tcgen05: ldo=%d < N=%d", ldo, N);
     JLLM_REQUIRE(!swiglu || (N % 16 == 0 && !bias && !accumulate),
                  "gemm_tcgen05: the SwiGLU epilogue needs N %% 16 == 0, no bias and no accumulation (N=%d)", N);
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    // The tile width: a block's time for a tile grows with the bytes it pulls in (its rows of A and BN rows of W
+    // per k block), and the product takes as many rounds as the tiles need on the SMs there are.
+    const int widths[5] = {256, 192, 128, 64, 32};
+    const int tiles_m = (M + BM - 1) / BM, rows_per_tile = M < BM ? M : BM;
+    int BN = 256;
+    long long best = -1;
+    for (int i = 0; i < 5; ++i) {
+        const long long t = (long long)tiles_m * ((N + widths[i] - 1) / widths[i]);
+        const long long cost = ((t + sms - 1) / sms) * (rows_per_tile + widths[i]);
+        if (best < 0 || cost < best) { best = cost; BN = widths[i]; }
+    }
+    if (tile_width > 0) BN = tile_width;
+    JLLM_REQUIRE(BN == 256 || BN == 192 || BN == 128 || BN == 64 || BN == 32, "gemm_tcgen05: tile width %d", BN);
+    if (swiglu && BN % 32 != 0) BN = 256;
     CUtensorMap map_a, map_w;
     int rc = tensor_map_for(a, M, K, lda, BM, &map_a);
     if (rc != JLLM_OK) return rc;
@@ -394,17 +426,11 @@ JLLM_EXPORT int jllm_gemm_tcgen05(const void* a, int lda, const void* w, int ldw
     if (rc != JLLM_OK) return rc;
     int* error_word = error_word_for_device();
     if (!error_word) return jllm_fail(JLLM_CUDA_ERROR, "gemm_tcgen05: no error word");
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    }
-    const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int tiles = tiles_m * ((N + BN - 1) / BN);
     const int k_blocks = (K + BK - 1) / BK;
     // K can be split over blocks (force_splits), the slices meeting in the caller's workspace. It is not done by
     // default: on the layer shapes of an 8B model with 64 rows the partial tiles' round trip through memory
-    // cost more than the idle SMs did (O projection 28 -> 49 us, QKV 28 -> 41 us, down 73 -> 61 us).
+    // cost more than the idle SMs did.
     int splits = 1;
     if (force_splits > 0) splits = force_splits > k_blocks ? k_blocks : force_splits;
     const long long need = JLLM_TC_MAX_TILES + (long long)tiles * splits * BM * BN;
@@ -419,16 +445,28 @@ JLLM_EXPORT int jllm_gemm_tcgen05(const void* a, int lda, const void* w, int ldw
     int grid = units < sms ? units : sms;
     if (max_blocks > 0 && grid > max_blocks) grid = max_blocks;
     const VecRef b{bias, bias_dtype};
-    if (out_dtype == JLLM_F32) {
-        auto kern = gemm_tcgen05_kernel<float>;
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
-        jllm_launch(kern, dim3(grid), dim3(THREADS), SMEM_BYTES, stream, true, map_a, map_w, b, (int)(bias != nullptr),
-                    (float*)out, ldo, accumulate, M, N, K, swiglu, splits, partials, counters, error_word);
-    } else {
-        auto kern = gemm_tcgen05_kernel<__nv_bfloat16>;
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
-        jllm_launch(kern, dim3(grid), dim3(THREADS), SMEM_BYTES, stream, true, map_a, map_w, b, (int)(bias != nullptr),
-                    (__nv_bfloat16*)out, ldo, accumulate, M, N, K, swiglu, splits, partials, counters, error_word);
+#define JLLM_TC_GO(T, W)                                                                                              \
+    do {                                                                                                              \
+        auto kern = gemm_tcgen05_kernel<T, W>;                                                                        \
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes_for(W));             \
+        jllm_launch(kern, dim3(grid), dim3(THREADS), smem_bytes_for(W), stream, true, map_a, map_w, b,                \
+                    (int)(bias != nullptr), (T*)out, ldo, accumulate, M, N, K, swiglu, splits, partials, counters,    \
+                    error_word);                                                                                      \
+    } while (0)
+#define JLLM_TC_WIDTHS(T)                                                                                             \
+    switch (BN) {                                                                                                     \
+        case 256: JLLM_TC_GO(T, 256); break;                                                                          \
+        case 192: JLLM_TC_GO(T, 192); break;                                                                          \
+        case 128: JLLM_TC_GO(T, 128); break;                                                                          \
+        case 64: JLLM_TC_GO(T, 64); break;                                                                            \
+        default: JLLM_TC_GO(T, 32); break;                                                                            \
     }
+    if (out_dtype == JLLM_F32) {
+        JLLM_TC_WIDTHS(float)
+    } else {
+        JLLM_TC_WIDTHS(__nv_bfloat16)
+    }
+#undef JLLM_TC_WIDTHS
+#undef JLLM_TC_GO
     return jllm_check_launch("gemm_tcgen05");
 }

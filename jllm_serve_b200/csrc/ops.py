@@ -86,7 +86,7 @@ class _Signatures:
     jllm_qk_norm_rope_store = [P, I, P, P, I, I, F, P, P, I, P, P, P, P, I, I, I, I, I, I, I, P]
     jllm_gemm_plain = [P, I, I, P, I, P, I, P, I, I, I, I, I, I, P]
     jllm_gemm_small_m = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, I, I, P]
-    jllm_gemm_tcgen05 = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, I, P, ctypes.c_longlong, I, P]
+    jllm_gemm_tcgen05 = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, I, P, ctypes.c_longlong, I, I, P]
     jllm_gemm_tcgen05_error = []
     jllm_gemm_skinny = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, P, ctypes.c_longlong, I, P]
     jllm_gemm_skinny_error = []
@@ -225,18 +225,20 @@ def gemm_bf16(a, w, out, bias=None, accumulate=False, swiglu=False) -> None:
     raise KernelError("the tensor-core matrix product is not built for this shape")
 
 
-def gemm_tcgen05(a, w, out, bias=None, accumulate=False, max_blocks: int = 0, swiglu=False, force_splits: int = 0) -> None:
-    """The prefill product: TMA-fed tcgen05.mma tiles of 128 x 256 with the accumulator in tensor memory. With
-    few tiles (few rows) K is split over blocks and the partial tiles meet in a workspace."""
+def gemm_tcgen05(a, w, out, bias=None, accumulate=False, max_blocks: int = 0, swiglu=False, force_splits: int = 0,
+                 tile_width: int = 0) -> None:
+    """The prefill product: TMA-fed tcgen05.mma tiles of 128 x `tile_width` (0: chosen from the shape, 256 for big
+    products, down to 32 when the rows are few) with the accumulator in tensor memory. `force_splits` splits K
+    over blocks; the partial tiles meet in a workspace."""
     assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.stride(-1) == 1
     ws = None
     if force_splits:
-        tiles = -(-a.shape[0] // 128) * -(-w.shape[0] // 256)
-        ws = skinny_workspace(a.device, 4096 + tiles * force_splits * 128 * 256)
+        tiles = -(-a.shape[0] // 128) * -(-w.shape[0] // (tile_width or 32))
+        ws = skinny_workspace(a.device, 4096 + tiles * force_splits * 128 * (tile_width or 256))
     _call("jllm_gemm_tcgen05", a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), _p(bias),
           _DT[bias.dtype] if bias is not None else F32, out.data_ptr(), _DT[out.dtype], out.stride(0),
           int(accumulate), a.shape[0], w.shape[0], a.shape[1], int(max_blocks), int(swiglu), _p(ws),
-          ws.numel() if ws is not None else 0, int(force_splits), _stream())
+          ws.numel() if ws is not None else 0, int(force_splits), int(tile_width), _stream())
 
 
 def gemm_tcgen05_error() -> int:

@@ -141,6 +141,33 @@ def test_gemm_tcgen05(ops, M, N, K):
         assert ops.gemm_tcgen05_error() == 0
 
 
+@pytest.mark.parametrize("width", [32, 64, 128, 192, 256])
+@pytest.mark.parametrize("M,N,K", [(64, 4096, 4096), (33, 517, 72), (200, 1000, 1032), (128, 24576, 512)])
+def test_gemm_tcgen05_tile_widths(ops, M, N, K, width):
+    """Every width of the output tile, chosen by hand: the product, the residual add, K split over blocks and
+    the SwiGLU epilogue give what the default width gives."""
+    a, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=1, scale=0.05)
+    bias = rnd(N, dtype=torch.bfloat16, seed=2)
+    tol = 1e-4 * math.sqrt(K) * 0.05
+    out = torch.full((M, N), float("nan"), device=DEV)
+    ops.gemm_tcgen05(a, w, out, bias, tile_width=width)
+    assert torch.allclose(out.cpu(), gemm_want(a, w, bias), rtol=1e-4, atol=tol)
+    base = rnd(M, N, seed=3)
+    acc, split = base.clone(), base.clone()
+    ops.gemm_tcgen05(a, w, acc, None, accumulate=True, tile_width=width, max_blocks=5)
+    ops.gemm_tcgen05(a, w, split, None, accumulate=True, tile_width=width, force_splits=2)
+    want = gemm_want(a, w, None, base)
+    assert torch.allclose(acc.cpu(), want, rtol=1e-4, atol=tol) and torch.allclose(split.cpu(), want, rtol=1e-4, atol=tol)
+    if N % 16 == 0:
+        hidden = N // 2
+        g = gemm_want(a, w.view(hidden // 8, 2, 8, K)[:, 0].reshape(hidden, K))
+        u = gemm_want(a, w.view(hidden // 8, 2, 8, K)[:, 1].reshape(hidden, K))
+        h = torch.full((M, hidden), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.gemm_tcgen05(a, w, h, swiglu=True, tile_width=width)
+        assert torch.allclose(h.float().cpu(), P.silu(g) * u, rtol=2 ** -7, atol=1e-3)
+    assert ops.gemm_tcgen05_error() == 0
+
+
 @pytest.mark.parametrize("M", [1, 7, 16, 17, 40, 64, 100, 128])
 @pytest.mark.parametrize("N,K,splits", [(8, 8, 0), (517, 72, 0), (6144, 4096, 0), (4096, 12288, 0), (300, 4096, 7),
                                         (1000, 200, 3), (4096, 4096, 1), (151936, 256, 0)])
