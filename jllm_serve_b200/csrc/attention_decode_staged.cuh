@@ -8,7 +8,8 @@
 // every tile: S = Q K^T and O += P V with mma.sync.m16n8k16 from ldmatrix fragments, the G query heads
 // of the kv head being the 16 rows of the M side (rows beyond G are zero). Each warp keeps its own online
 // softmax state; the four are merged at the end exactly as in the direct kernel, and the per-split
-// partials go to the same scratch layout and combine kernel.
+// partials go to the same scratch layout; they are combined by a kernel of their own or, when the caller gives
+// counters, by the block of each (row, kv head) that finishes last.
 #pragma once
 
 namespace staged {
@@ -46,7 +47,7 @@ attention_decode_staged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
                                __nv_bfloat16* __restrict__ out, int out_stride, const int* __restrict__ row_seg,
                                const int* __restrict__ row_pos, const int* __restrict__ block_tables, int table_stride,
                                int heads, int kv_heads, int page_size, int window, float scale_log2, int splits,
-                               float* __restrict__ part_o, float* __restrict__ part_ml) {
+                               float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters) {
     constexpr int CHUNKS = HD / 8, TILE_BYTES = TILE * HD * 2, STAGE_BYTES = 2 * TILE_BYTES;
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const uint32_t s_q = (uint32_t)__cvta_generic_to_shared(smem_raw);
@@ -72,31 +73,45 @@ attention_decode_staged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
         const __nv_bfloat16* src = q + (size_t)r * q_stride + (size_t)(kvh * G + min(row, G - 1)) * HD + c * 8;
         cp16(s_q + off<HD>(row, c), src, row < G ? 16 : 0);
     }
+    // Where the rows of a tile lie in the cache (element offset of the key's first value, -1 past the end): looked
+    // up by one thread per row a tile ahead of the copies, so that no copy waits for a page-table load.
+    __shared__ long long s_row_base[2][TILE];
+    auto find_rows = [&](int i) {
+        if (i < n_tiles && threadIdx.x < TILE) {
+            const int key = first + (tile_lo + i) * TILE + threadIdx.x;
+            long long o = -1;
+            if (key <= P) {
+                const int pg = page_shift >= 0 ? key >> page_shift : key / page_size;
+                const int in_page = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
+                o = (long long)((size_t)table[pg] * page_stride + ((size_t)kvh * page_size + in_page) * HD);
+            }
+            s_row_base[i & 1][threadIdx.x] = o;
+        }
+    };
     auto load_tile = [&](int i) {   // tile i of this block's range into stage i % STAGES
         if (i < n_tiles) {
             const uint32_t dk = s_kv + (i % STAGES) * STAGE_BYTES, dv = dk + TILE_BYTES;
-            const int key0 = first + (tile_lo + i) * TILE;
-            // consecutive threads take consecutive 16-byte chunks of a row (coalesced reads, conflict-free
-            // writes); a power-of-two page size turns the page lookup into a shift and a mask
+            // consecutive threads take consecutive 16-byte chunks of a row (coalesced reads, conflict-free writes)
+#pragma unroll
             for (int j = threadIdx.x; j < TILE * CHUNKS; j += THREADS) {
                 const int row = j / CHUNKS, c = j % CHUNKS;
-                const int key = key0 + row;
-                const bool ok = key <= P;
-                size_t o = 0;
-                if (ok) {
-                    const int pg = page_shift >= 0 ? key >> page_shift : key / page_size;
-                    const int in_page = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
-                    o = (size_t)table[pg] * page_stride + ((size_t)kvh * page_size + in_page) * HD + c * 8;
-                }
+                const long long base_o = s_row_base[i & 1][row];
+                const bool ok = base_o >= 0;
+                const size_t o = ok ? (size_t)base_o + c * 8 : 0;
                 cp16(dk + off<HD>(row, c), k_cache + o, ok ? 16 : 0);
                 cp16(dv + off<HD>(row, c), v_cache + o, ok ? 16 : 0);
             }
         }
         commit();   // an empty group keeps the group count in step with the tile count
     };
+    static_assert(STAGES == 3, "the row look-ahead below is written for a ring of three stages");
+    find_rows(0);
+    find_rows(1);
+    __syncthreads();
     load_tile(0);           // group 0 also carries Q
-#pragma unroll
-    for (int i = 1; i < STAGES - 1; ++i) load_tile(i);
+    load_tile(1);
+    __syncthreads();        // everyone has read the rows of tile 0: its slot takes those of tile 2
+    find_rows(2);
 
     uint32_t qf[HD / 16][4];
     float o[HD / 8][4];
@@ -110,6 +125,7 @@ attention_decode_staged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
         wait_group<STAGES - 2>();   // tile i has landed (the groups of later tiles may still be in flight)
         __syncthreads();            // ... for every thread's part of it; and everyone is done with tile i - 1
         load_tile(i + STAGES - 1);  // refills the stage that tile i - 1 used
+        find_rows(i + STAGES);      // into the slot that tile i + 1's copies (issued an iteration ago) have left
         if (i == 0) {
 #pragma unroll
             for (int ks = 0; ks < HD / 16; ++ks) ldsm4(qf[ks], s_q + off<HD>(lane & 15, ks * 2 + (lane >> 4)));
@@ -144,6 +160,7 @@ attention_decode_staged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
             m[h] = m_new;
             l[h] *= corr[h];
         }
+        const bool rescale = !__all_sync(0xffffffffu, corr[0] == 1.f && corr[1] == 1.f);   // no row's maximum moved
         uint32_t pf[4];
 #pragma unroll
         for (int tile = 0; tile < 2; ++tile) {
@@ -159,12 +176,14 @@ attention_decode_staged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
         for (int jp = 0; jp < HD / 16; ++jp) {
             uint32_t vf[4];
             ldsm4t(vf, sv + off<HD>(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, jp * 2 + (lane >> 4)));
+            if (rescale) {
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                o[2 * jp + e][0] *= corr[0];
-                o[2 * jp + e][1] *= corr[0];
-                o[2 * jp + e][2] *= corr[1];
-                o[2 * jp + e][3] *= corr[1];
+                for (int e = 0; e < 2; ++e) {
+                    o[2 * jp + e][0] *= corr[0];
+                    o[2 * jp + e][1] *= corr[0];
+                    o[2 * jp + e][2] *= corr[1];
+                    o[2 * jp + e][3] *= corr[1];
+                }
             }
             mma(o[2 * jp], pf, vf[0], vf[1]);
             mma(o[2 * jp + 1], pf, vf[2], vf[3]);
@@ -222,13 +241,54 @@ attention_decode_staged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
             }
         }
     }
+    if (splits == 1 || counters == nullptr) return;
+    // ---- the block that finishes last among the splits of this (row, kv head) combines them ----
+    // Every block publishes its partials and counts itself; who finds all others counted reads the partials of all
+    // splits in split order (so the result does not depend on who came last) and writes the output. The counter
+    // goes back to zero for the next launch. Nobody waits for anybody.
+    __shared__ int s_last;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const int seen = atomicAdd(&counters[r * kv_heads + kvh], 1);
+        s_last = seen == splits - 1;
+        if (s_last) counters[r * kv_heads + kvh] = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    float* weight = reinterpret_cast<float*>(smem_raw);              // [16][32] weights of the splits, then [16] 1 / sum
+    float* inv_total = weight + 16 * 32;
+    for (int row = warp; row < G; row += WARPS) {
+        const size_t slot0 = ((size_t)r * heads + kvh * G + row) * splits;
+        const float ms = lane < splits ? __ldcg(part_ml + (slot0 + lane) * 2) : -INFINITY;
+        const float ls = lane < splits ? __ldcg(part_ml + (slot0 + lane) * 2 + 1) : 0.f;
+        float M = ms;
+#pragma unroll
+        for (int o2 = 16; o2 > 0; o2 >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o2));
+        const float w = ms == -INFINITY ? 0.f : exp2f(ms - M);
+        weight[row * 32 + lane] = w;
+        float L = 0.f;
+        for (int i = 0; i < splits; ++i) L += __shfl_sync(0xffffffffu, ls * w, i);
+        if (lane == 0) inv_total[row] = 1.f / L;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < G * HD; e += THREADS) {
+        const int row = e / HD, d = e % HD;
+        const int head = kvh * G + row;
+        const size_t slot0 = ((size_t)r * heads + head) * splits;
+        float acc = 0.f;
+#pragma unroll 8
+        for (int s2 = 0; s2 < splits; ++s2) acc += __ldcg(part_o + (slot0 + s2) * HD + d) * weight[row * 32 + s2];
+        out[(size_t)r * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc * inv_total[row]);
+    }
 }
 
 template <int HD>
 void launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out, int out_stride,
             const int* row_seg, const int* row_pos, const int* block_tables, int table_stride, int rows, int heads,
             int kv_heads, int page_size, int window, float scale_log2, int splits, float* part_o, float* part_ml,
-            cudaStream_t stream) {
+            int* counters, cudaStream_t stream) {
     const size_t stage_bytes = (size_t)STAGES * 2 * TILE * HD * 2;
     const size_t merge_bytes = ((size_t)WARPS * 16 * HD + WARPS * 16 * 2) * sizeof(float);
     const size_t smem = 16 * HD * 2 + (stage_bytes > merge_bytes ? stage_bytes : merge_bytes);
@@ -237,7 +297,7 @@ void launch(const void* q, int q_stride, const void* k_cache, const void* v_cach
     jllm_launch(kern, dim3(rows, kv_heads, splits), dim3(THREADS), smem, stream, true,
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
         (__nv_bfloat16*)out, out_stride, row_seg, row_pos, block_tables, table_stride, heads, kv_heads, page_size,
-        window, scale_log2, splits, part_o, part_ml);
+        window, scale_log2, splits, part_o, part_ml, counters);
 }
 
 }  // namespace staged
