@@ -41,7 +41,7 @@ __device__ __forceinline__ uint4 load_16_stream(const __nv_bfloat16* p) {
 }
 
 template <int NT, int RT, int UNROLL, typename Tout>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, 2)
 gemm_small_m_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w, int ldw,
                     VecRef bias, int has_bias, Tout* __restrict__ out, int ldo, int accumulate, int M, int N, int K,
                     int swiglu, int prefetch_bytes) {
@@ -203,10 +203,24 @@ JLLM_EXPORT int jllm_gemm_small_m(const void* a, int lda, const void* w, int ldw
                  "gemm_small_m: the SwiGLU epilogue needs N %% 16 == 0, no bias and no accumulation (N=%d)", N);
     const VecRef b{bias, bias_dtype};
     const int hb = bias != nullptr;
-    // 32 rows per block halve the activation reads and measured faster for every layer shape of an 8B
-    // model; tuning (experiments): bit 0 = 32 rows, bit 1 = deeper unroll, value 8 = 16 rows
-    bool wide = N >= 64 * 32;
+    // How many weight rows a block takes (16 or 32) and how many batches of loads a warp keeps in flight, measured
+    // on the layer shapes of an 8B model. What counts is that every SM has two resident blocks with enough bytes on
+    // their way: a matrix with few rows (at most one 32-row block per SM) is cut into 16-row blocks; up to 8 tokens
+    // the blocks are 16 rows with the deeper unroll, except where 32-row blocks make between one and two rounds.
+    // tuning (experiments): bit 0 = 32 rows, bit 1 = deeper unroll, value 8 = 16 rows
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    const int blocks32 = (N + 31) / 32;
+    bool wide = blocks32 > sms;
     int deep = 0;
+    if (M <= 8) {
+        wide = blocks32 > sms && blocks32 <= 2 * sms;
+        deep = !wide;
+    }
     if (tuning > 0) { wide = (tuning & 1) != 0; deep = (tuning >> 1) & 1; }
     // at most prefetch_mb MB of this matrix are prefetched into L2, the same number of bytes from every row
     long long per_row = prefetch_mb > 0 ? ((long long)prefetch_mb << 20) / N : 0;

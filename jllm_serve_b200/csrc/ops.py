@@ -247,9 +247,10 @@ def gemm_tcgen05_error() -> int:
     return library().jllm_gemm_tcgen05_error()
 
 
-# MB of each small-M product's weights pulled towards L2 before the product waits for its predecessor (measured on
-# the 8B shapes: 16 is 1 % faster than none, 32 and more are slower: prefetched lines evict one another)
-PREFETCH_MB = int(__import__("os").environ.get("JLLM_B200_PREFETCH_MB", "16"))
+# MB of each small-M product's weights pulled towards L2 before the product waits for its predecessor. Off: with
+# 16-row blocks and the deep unroll (two resident blocks per SM on every layer shape) the prefetch only got in
+# the way of the loads themselves (8B decode step, batch 8: 4.54 ms without, 4.56 with 8 MB, 4.70 with 16 MB).
+PREFETCH_MB = int(__import__("os").environ.get("JLLM_B200_PREFETCH_MB", "0"))
 _SMALL_M_TUNING = int(__import__("os").environ.get("JLLM_B200_SMALL_M_TUNING", "0"))   # experiments only
 
 
