@@ -42,6 +42,7 @@ class RopeTableSpec:
     theta: float
     scaling: RopeScaling = RopeScaling()
     pairing: str = "half"                  # half: (i, i + rotary_dim/2)
+    kind: str = field(default="rotary", init=False)   # which registered position encoding builds the table
 
     def __post_init__(self):
         if self.rotary_dim < 2 or self.rotary_dim % 2:
@@ -166,7 +167,7 @@ class Core:
 class Decoder:
     core: Core
     layers: Tuple[LayerSpec, ...]
-    rope_tables: Tuple[RopeTableSpec, ...]
+    rope_tables: Tuple[object, ...]       # position tables: RopeTableSpec, or any spec with a registered `kind`
     final_norm: NormSpec
     schedule: Tuple[LayerRun, ...] = ()
     names: ModelNames = ModelNames()
@@ -186,6 +187,9 @@ class Decoder:
                 if self.schedule[run.cache_of].cache_of is not None:
                     raise ConfigError(f"schedule entry {i} reads the cache of entry {run.cache_of}, "
                                       f"which keeps none of its own")
+        for t in self.rope_tables:
+            if not getattr(t, "kind", ""):
+                raise ConfigError(f"position table {t!r} names no kind of position encoding")
         for spec in self.layers:
             t = getattr(spec.mixer, "rope_table", -1)
             if t >= len(self.rope_tables):

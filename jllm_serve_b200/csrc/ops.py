@@ -242,6 +242,17 @@ def gemm_tcgen05(a, w, out, bias=None, accumulate=False, max_blocks: int = 0, sw
           ws.numel() if ws is not None else 0, int(force_splits), int(tile_width), _stream())
 
 
+def check_kernel_errors() -> None:
+    """Raises if a tcgen05 kernel gave up on one of its bounded waits since the last check (its results are then
+    not to be trusted). Reads three words from the device, so it synchronises."""
+    lib = library()
+    raised = {name: code for name, code in (("gemm_tcgen05", lib.jllm_gemm_tcgen05_error()),
+                                            ("gemm_skinny", lib.jllm_gemm_skinny_error()),
+                                            ("attention_prefill_tc", lib.jllm_attention_prefill_tc_error())) if code}
+    if raised:
+        raise KernelError("a bounded wait ran out inside " + ", ".join(f"{k} (code {v})" for k, v in raised.items()))
+
+
 def gemm_tcgen05_error() -> int:
     """0, or the code a tcgen05 kernel raised because one of its bounded waits ran out (synchronises)."""
     return library().jllm_gemm_tcgen05_error()

@@ -16,6 +16,7 @@ from typing import Hashable, List, Optional, Sequence, Union
 
 import torch
 
+from ..csrc import ops
 from ..sampling import RequestRng, Sampler, SamplingParams
 from .batch import Segment
 from .runner import ModelRunner
@@ -104,8 +105,13 @@ class Engine:
 
     def run_until_done(self) -> List[Request]:
         finished = []
+        steps = 0
         while self.scheduler.has_work():
             finished.extend(self.step_once())
+            steps += 1
+            if steps % 256 == 0:
+                ops.check_kernel_errors()
+        ops.check_kernel_errors()          # a kernel that gave up on a bounded wait must not pass for a result
         return finished
 
     def result_of(self, rid: Hashable) -> Result:

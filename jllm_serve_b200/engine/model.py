@@ -27,8 +27,11 @@ class DecoderModel:
         self.embedding = tensors.pop(names.embedding)
         head = self.embedding if core.tied else tensors.pop(names.head)
         self.head = Linear(head)
-        self.position_encodings = [part_class("position", "rotary")(t, runtime.max_positions, runtime.device)
-                                   for t in spec.rope_tables]
+        self.position_encodings = []
+        for t in spec.rope_tables:
+            cls = part_class("position", t.kind)
+            extra = {"tensors": tensors, "dim": core.dim} if cls.wants(t, core.dim, "") else {}
+            self.position_encodings.append(cls(t, runtime.max_positions, runtime.device, **extra))
         self.blocks = []
         for l, layer in enumerate(spec.layers):
             cls = part_class("block", layer.arrangement)
@@ -43,6 +46,8 @@ class DecoderModel:
         out = {names.embedding: TensorWant((core.vocab, core.dim))}
         if not core.tied:
             out[names.head] = TensorWant((core.vocab, core.dim))
+        for t in spec.rope_tables:
+            out.update(part_class("position", t.kind).wants(t, core.dim, ""))
         for l, layer in enumerate(spec.layers):
             out.update(part_class("block", layer.arrangement).wants(layer, core.dim, names.layer.format(l)))
         out.update(part_class("norm", spec.final_norm.kind).wants(spec.final_norm, core.dim, names.final_norm))

@@ -126,10 +126,7 @@ def main() -> int:
         us = s.elapsed_time(e) / args.repeat * 1e3
         rate = f"{bytes_ / us / 1e3:8.0f} GB/s" if bytes_ else f"{flops / us / 1e6:8.0f} TFLOP/s"
         print(f"{name:36s} {us:9.1f} us {rate}", flush=True)
-    err = ops.gemm_tcgen05_error()
-    if err:
-        print(f"a tcgen05 kernel raised error {err}", file=sys.stderr)
-        return 1
+    ops.check_kernel_errors()
     return 0
 
 

@@ -4,8 +4,11 @@ A part is built from its spec (sizes and constants), the model's width, its tens
 the `Runtime`; it never learns which model it is in. The kinds:
 
 * `Norm`:             `forward(x, out, row_index=None, rows=None)`; x float32 [rows, dim] -> out (compute dtype).
-* `PositionEncoding`: made once per table and context; a mixer that rotates asks it for `cos`, `sin`,
-                      `rotary_dim`; one that adds to the embedding overrides `on_embedding(x, batch)`.
+* `PositionEncoding`: made once per position table (`spec.kind` picks the class) and context, as
+                      `cls(spec, max_positions, device)`, with `tensors=` and `dim=` too if its `wants` names
+                      tensors (full checkpoint names; the prefix it is given is empty); a mixer that rotates asks
+                      it for `cos`, `sin`, `rotary_dim`; one that adds to the embedding overrides
+                      `on_embedding(x, batch)`.
 * `Mixer`:            `cache_need(spec)` says what it keeps between steps; `forward(xb, x, batch, cache)`
                       reads the normed rows `xb` and ADDS its result into the float32 residual stream `x`.
 * `FeedForward`:      `forward(xb, x, batch)`, same contract.

@@ -259,3 +259,139 @@ def test_toy_mixer_with_state_registers_builds_and_steps(dtype, tmp_path):
             assert runner.cache.slots.num_free == 3
     finally:
         unregister_architecture("toy_mean")
+
+
+# ---- a second toy architecture: learned positions added to the embedding, a feed-forward that routes --------------
+
+def routed_toy_pieces():
+    """Defines and registers a position encoding with a tensor of its own and a feed-forward with a router, and an
+    architecture that uses them in some layers and the framework's dense feed-forward in the others.
+    Returns (config dict, plain forward)."""
+    from jllm_serve_b200.config import (Core, Decoder, DenseGluSpec, FeedForwardSpec, GqaAttentionSpec, LayerSpec,
+                                        NormSpec, register_architecture)
+    from jllm_serve_b200.parts import FeedForward, PositionEncoding, register_feed_forward, register_position_encoding
+    from jllm_serve_b200.weights import TensorWant
+
+    @dataclass(frozen=True)
+    class LearnedPositionsSpec:
+        positions: int
+        kind: str = field(default="toy_learned_positions", init=False)
+
+    class LearnedPositions(PositionEncoding):
+        """x[r] += table[position of r]: nothing rotates, the mixers get no table."""
+        def __init__(self, spec, max_positions, device, tensors=None, dim=0):
+            self.table = tensors.pop("model.embed_positions.weight").float()
+            assert max_positions <= spec.positions
+
+        @classmethod
+        def wants(cls, spec, dim, prefix):
+            return {"model.embed_positions.weight": TensorWant((spec.positions, dim))}
+
+        def on_embedding(self, x, batch):
+            x += self.table[batch.positions.long()]
+
+    @dataclass(frozen=True)
+    class TopOneExpertsSpec(FeedForwardSpec):
+        kind: str = field(default="toy_top1_experts", init=False)
+        experts: int = 0
+        hidden: int = 0
+
+    class TopOneExperts(FeedForward):
+        """Each row goes to the expert with the largest router logit (the lowest index among equals) and gets
+        p_e * W2_e relu(W1_e xb), p = softmax of the float32 router logits. All on the device, no host decision."""
+        def __init__(self, spec, dim, tensors, prefix, runtime):
+            self.router = tensors.pop(prefix + "router.weight").float()
+            self.w1 = torch.stack([tensors.pop(f"{prefix}experts.{e}.w1.weight").float() for e in range(spec.experts)])
+            self.w2 = torch.stack([tensors.pop(f"{prefix}experts.{e}.w2.weight").float() for e in range(spec.experts)])
+
+        @classmethod
+        def wants(cls, spec, dim, prefix):
+            out = {prefix + "router.weight": TensorWant((spec.experts, dim))}
+            for e in range(spec.experts):
+                out[f"{prefix}experts.{e}.w1.weight"] = TensorWant((spec.hidden, dim))
+                out[f"{prefix}experts.{e}.w2.weight"] = TensorWant((dim, spec.hidden))
+            return out
+
+        def forward(self, xb, x, batch):
+            rows = xb.float()
+            logits = rows @ self.router.t()
+            p = torch.softmax(logits, dim=-1)
+            chosen = torch.argmax(logits, dim=-1)                       # torch takes the first of equal maxima
+            h = torch.relu(torch.einsum("rd,ehd->reh", rows, self.w1))
+            y = torch.einsum("reh,edh->red", h, self.w2)
+            pick = chosen[:, None, None].expand(-1, 1, y.shape[-1])
+            x += y.gather(1, pick)[:, 0] * p.gather(1, chosen[:, None])
+
+    register_position_encoding("toy_learned_positions", LearnedPositions, replace=True)
+    register_feed_forward("toy_top1_experts", TopOneExperts, replace=True)
+
+    def parse(values):
+        dim, layers = values["width"], values["depth"]
+        norm = NormSpec("rmsnorm", values["eps"])
+        attn = GqaAttentionSpec(heads=3, kv_heads=1, head_dim=16, rope_table=-1, qk_norm=True, qk_norm_eps=values["eps"],
+                                scale=0.25)
+        specs = tuple(LayerSpec(attn, DenseGluSpec(hidden=values["ffn"]) if l % 2 else
+                                TopOneExpertsSpec(experts=values["experts"], hidden=values["ffn"]), norm)
+                      for l in range(layers))
+        core = Core("ToyRoutedForCausalLM", "toy_routed", dim, layers, values["vocab"], values["eps"], False, -1, (), 96,
+                    "toy routed")
+        return Decoder(core, specs, (LearnedPositionsSpec(values["positions"]),), norm)
+
+    register_architecture("toy_routed", parse, replace=True)
+    config = dict(model_type="toy_routed", width=40, depth=3, ffn=56, vocab=83, eps=1e-5, experts=3, positions=96)
+
+    def plain_forward(w, tokens):
+        T = len(tokens)
+        x = P.embedding(w["model.embed_tokens.weight"], tokens) + w["model.embed_positions.weight"][:T]
+        cos, sin = torch.ones(T, 8), torch.zeros(T, 8)                    # no rotation
+        cfg = P.PlainConfig(dict(hidden_size=40, num_hidden_layers=3, vocab_size=83, num_attention_heads=3,
+                                 num_key_value_heads=1, head_dim=16, intermediate_size=56, rms_norm_eps=1e-5))
+        for l in range(3):
+            p = f"model.layers.{l}."
+            y, _ = P.attention_block(P.rmsnorm(x, w[p + "input_layernorm.weight"], 1e-5), w, p + "self_attn.", cfg, 0,
+                                     cos, sin)
+            x = x + y
+            xb = P.rmsnorm(x, w[p + "post_attention_layernorm.weight"], 1e-5)
+            if l % 2:
+                x = x + P.swiglu_feed_forward(xb, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
+                                              w[p + "mlp.down_proj.weight"])
+            else:
+                out = torch.zeros_like(x)
+                for r in range(T):
+                    logits = P.linear(xb[r:r + 1], w[p + "mlp.router.weight"])[0]
+                    e = P.argmax_lowest(logits)
+                    prob = torch.softmax(logits.double(), dim=-1)[e].float()
+                    h = torch.relu(P.linear(xb[r:r + 1], w[f"{p}mlp.experts.{e}.w1.weight"]))
+                    out[r] = P.linear(h, w[f"{p}mlp.experts.{e}.w2.weight"])[0] * prob
+                x = x + out
+        return P.linear(P.rmsnorm(x, w["model.norm.weight"], 1e-5), w["lm_head.weight"])
+
+    return config, plain_forward
+
+
+def test_toy_position_encoding_and_routed_feed_forward_register_build_and_step(tmp_path):
+    """Float32 only: in bfloat16 a row whose two best router logits are close may go to another expert than in
+    the oracle, which is rounding and no fault, and nothing here could tell the two apart."""
+    from jllm_serve_b200.config import unregister_architecture
+    from jllm_serve_b200.engine import ModelRunner
+    config, plain_forward = routed_toy_pieces()
+    try:
+        folder = make_model_folder(config, 5, tmp_path / "toy_routed")
+        w = {k: v.float() for k, v in P.read_safetensors(folder / "model.safetensors").items()}
+        assert "model.embed_positions.weight" in w and "model.layers.0.mlp.router.weight" in w
+        assert "model.layers.1.mlp.gate_proj.weight" in w and "lm_head.weight" in w
+        reqs = {f"r{i}": random_tokens(n, 83, 70 + i) for i, n in enumerate((2, 33, 64, 17, 50))}
+        for steps in (traces.whole(reqs), traces.prompt_then_decode(reqs, 16), traces.changing_portions(reqs),
+                      traces.mixed(reqs, max_live=3, portion=9)):
+            runner = ModelRunner(folder, dtype="float32", page_size=4, num_pages=50, max_batch_tokens=96, max_requests=3,
+                                 ctx=96, poison_freed_pages=True)
+            assert runner.graph_safe
+            got = replay(runner, steps)
+            scale = 0.0
+            for rid, toks in reqs.items():
+                want = plain_forward(w, toks)
+                scale = max(scale, float(want.abs().max()))
+                for p in range(len(toks)):
+                    assert float((got[(rid, p)] - want[p]).abs().max()) <= TOL["float32"] * scale, (rid, p)
+    finally:
+        unregister_architecture("toy_routed")
