@@ -3,6 +3,8 @@
 //
 // All arithmetic is 32-bit float whatever the storage type; each row's result depends on that row
 // alone (fixed reduction order), so it is the same in any batch.
+#include <cstdlib>
+
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------------------------------
@@ -274,6 +276,88 @@ qk_norm_rope_store_warp_kernel(T* __restrict__ qkv, VecRef q_gain, VecRef k_gain
     }
 }
 
+// The same for bfloat16 with 16-byte accesses: 4 V lanes share one (row, head), each owning 8 neighbouring values of
+// the first half and their partners in the second half; a warp takes 8 / V heads of a row side by side (they are
+// neighbours in memory), so that it has 1 KB of loads in flight instead of 128 bytes. The arithmetic of one value
+// is that of the kernels above.
+template <int V>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_store_vec_kernel(__nv_bfloat16* __restrict__ qkv, VecRef q_gain, VecRef k_gain, int use_norm, float eps,
+                              const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                              const int* __restrict__ positions, const int* __restrict__ slots,
+                              __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int heads,
+                              int kv_heads, int page_size, int row_stride, int heads_total, long long items) {
+    constexpr int HD = 64 * V, HALF = 32 * V, LANES = 4 * V, PER_WARP = 32 / LANES;
+    pdl_wait();
+    pdl_trigger();
+    const int lane = threadIdx.x & 31, sub = lane % LANES;
+    const long long item = ((long long)blockIdx.x * 8 + (threadIdx.x >> 5)) * PER_WARP + lane / LANES;
+    const bool live = item < items;
+    const int r = live ? (int)(item / heads_total) : 0, h = live ? (int)(item % heads_total) : 0;
+    __nv_bfloat16* src = qkv + (size_t)r * row_stride + (size_t)h * HD;
+    const bool is_q = h < heads, is_k = !is_q && h < heads + kv_heads;
+    float a[8], b[8];
+    {
+        const uint4 ua = live ? *reinterpret_cast<const uint4*>(src + sub * 8) : make_uint4(0, 0, 0, 0);
+        const uint4 ub = live ? *reinterpret_cast<const uint4*>(src + HALF + sub * 8) : make_uint4(0, 0, 0, 0);
+        const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&ua);
+        const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&ub);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 fa = __bfloat1622float2(pa[i]), fb = __bfloat1622float2(pb[i]);
+            a[2 * i] = fa.x; a[2 * i + 1] = fa.y;
+            b[2 * i] = fb.x; b[2 * i + 1] = fb.y;
+        }
+    }
+    if (is_q || is_k) {
+        if (use_norm) {
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss = fmaf(a[i], a[i], ss);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss = fmaf(b[i], b[i], ss);
+#pragma unroll
+            for (int o = LANES / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            const float s = rms_scale(ss, HD, eps);
+            const VecRef g = is_q ? q_gain : k_gain;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                a[i] = __fmul_rn(__fmul_rn(a[i], s), g[sub * 8 + i]);
+                b[i] = __fmul_rn(__fmul_rn(b[i], s), g[HALF + sub * 8 + i]);
+            }
+        }
+        const float4* c4 = reinterpret_cast<const float4*>(cos_t + (size_t)positions[r] * HALF + sub * 8);
+        const float4* s4 = reinterpret_cast<const float4*>(sin_t + (size_t)positions[r] * HALF + sub * 8);
+        const float4 c0 = c4[0], c1 = c4[1], s0 = s4[0], s1 = s4[1];
+        const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float x0 = a[i], x1 = b[i];
+            a[i] = __fsub_rn(__fmul_rn(x0, c[i]), __fmul_rn(x1, sn[i]));
+            b[i] = __fadd_rn(__fmul_rn(x1, c[i]), __fmul_rn(x0, sn[i]));
+        }
+    }
+    if (!live) return;
+    __nv_bfloat16* dst = src;
+    if (!is_q) {
+        const int kvh = is_k ? h - heads : h - heads - kv_heads;
+        const int slot = slots[r];
+        const size_t page = slot / page_size, off = slot % page_size;
+        dst = (is_k ? k_cache : v_cache) + ((page * kv_heads + kvh) * page_size + off) * HD;
+    }
+    uint4 oa, ob;
+    __nv_bfloat162* qa = reinterpret_cast<__nv_bfloat162*>(&oa);
+    __nv_bfloat162* qb = reinterpret_cast<__nv_bfloat162*>(&ob);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        qa[i] = __floats2bfloat162_rn(a[2 * i], a[2 * i + 1]);
+        qb[i] = __floats2bfloat162_rn(b[2 * i], b[2 * i + 1]);
+    }
+    *reinterpret_cast<uint4*>(dst + sub * 8) = oa;
+    *reinterpret_cast<uint4*>(dst + HALF + sub * 8) = ob;
+}
+
 JLLM_EXPORT int jllm_qk_norm_rope_store(void* qkv, int dtype, const void* q_gain, const void* k_gain, int gain_dtype,
                                         int use_norm, float eps, const float* cos_t, const float* sin_t,
                                         int rotary_dim, const int* positions, const int* slots, void* k_cache,
@@ -301,6 +385,23 @@ JLLM_EXPORT int jllm_qk_norm_rope_store(void* qkv, int dtype, const void* q_gain
                 cos_t, sin_t, positions, slots, (T*)k_cache, (T*)v_cache, heads, kv_heads, page_size, row_stride,      \
                 heads_total, items)
         const int v = head_dim / 64;
+        // the 16-byte kernel from 32 rows on (fewer rows are too few warps for it; JLLM_B200_ROPE_VEC_MIN_ROWS moves that)
+        static const int vec_min_rows = [] {
+            const char* e = getenv("JLLM_B200_ROPE_VEC_MIN_ROWS");
+            return e ? atoi(e) : 32;
+        }();
+        if (dtype == JLLM_BF16 && rows >= vec_min_rows && row_stride % 8 == 0 && ((uintptr_t)qkv % 16) == 0 && ((uintptr_t)k_cache % 16) == 0 &&
+            ((uintptr_t)v_cache % 16) == 0 && ((uintptr_t)cos_t % 16) == 0 && ((uintptr_t)sin_t % 16) == 0) {
+            const long long per_block = 8 * (8 / v);
+            const dim3 vgrid((unsigned)((items + per_block - 1) / per_block));
+#define JLLM_VEC_ROPE(V)                                                                                              \
+    jllm_launch(qk_norm_rope_store_vec_kernel<V>, vgrid, dim3(256), 0, stream, true, (__nv_bfloat16*)qkv, qg, kg,     \
+                use_norm, eps, cos_t, sin_t, positions, slots, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, heads, \
+                kv_heads, page_size, row_stride, heads_total, items)
+            if (v == 1) JLLM_VEC_ROPE(1); else if (v == 2) JLLM_VEC_ROPE(2); else JLLM_VEC_ROPE(4);
+#undef JLLM_VEC_ROPE
+            return jllm_check_launch("qk_norm_rope_store");
+        }
         if (dtype == JLLM_F32) {
             if (v == 1) JLLM_WARP_ROPE(float, 1); else if (v == 2) JLLM_WARP_ROPE(float, 2); else JLLM_WARP_ROPE(float, 4);
         } else {

@@ -73,6 +73,14 @@ def main() -> int:
     case(f"decode attention ({splits} splits)",
          lambda i: ops.attention_decode(q, caches[i][0], caches[i][1], out, seg, pos, tables, M, H, Hkv, hd, page, 0,
                                         1 / math.sqrt(hd), splits, scratch), n_caches, M * ctx * Hkv * hd * 4)
+    ctx_pad = max(ctx, T) + page
+    ang = torch.outer(torch.arange(ctx_pad, dtype=torch.float64), 1e6 ** (-torch.arange(hd // 2, dtype=torch.float64) * 2 / hd))
+    cos_t, sin_t = ang.cos().float().to(dev), ang.sin().float().to(dev)
+    hg = torch.ones(hd, device=dev, dtype=bf)
+    slots_d = (tables[:, -1].long() * page + (ctx - 1) % page).to(torch.int32)
+    case("decode q/k norm + rope + cache write",
+         lambda i: ops.qk_norm_rope_store(qkv_d, hg, hg, 1e-6, cos_t, sin_t, hd, pos, slots_d, caches[0][0], caches[0][1],
+                                          H, Hkv, hd, page), 1, M * (H + 2 * Hkv) * hd * 4)
     gain = torch.ones(D, device=dev, dtype=bf)
     xb = torch.empty(M, D, device=dev, dtype=bf)
     case("decode rmsnorm", lambda i: ops.rmsnorm(x, gain, 1e-6, xb), 1, M * D * 6)
@@ -97,6 +105,10 @@ def main() -> int:
     case("prefill attention (causal)",
          lambda i: ops.attention_prefill(qp, kc, vc, op, s0, s1, s2, tp, T, H, Hkv, hd, page, 0, 1 / math.sqrt(hd)), 1,
          flops=4 * (T * (T + 1) // 2) * H * hd)
+    pos_p = torch.arange(T, dtype=torch.int32, device=dev)
+    case("prefill q/k norm + rope + cache write",
+         lambda i: ops.qk_norm_rope_store(qkv_p, hg, hg, 1e-6, cos_t, sin_t, hd, pos_p, pos_p, kc, vc, H, Hkv, hd, page), 1,
+         T * (H + 2 * Hkv) * hd * 4)
     gp = torch.ones(D, device=dev, dtype=bf)
     xbp = torch.empty(T, D, device=dev, dtype=bf)
     case("prefill rmsnorm", lambda i: ops.rmsnorm(x_p, gp, 1e-6, xbp), 1, T * D * 6)
