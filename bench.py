@@ -215,8 +215,9 @@ def main() -> int:
         runner.finish(tag)
         return s.elapsed_time(e)
 
-    times = [prefill_once(f"p{i}") for i in range(5)] if not args.skip_prefill else [float("nan")] * 5
-    pre_ms = statistics.median(times[2:])
+    # 4 warm-up prefills, then the median of 9: a single 30 ms prefill follows the clock of the moment
+    times = [prefill_once(f"p{i}") for i in range(13)] if not args.skip_prefill else [float("nan")] * 13
+    pre_ms = statistics.median(times[4:])
     flops = 2.0 * nums["layer_params"] * args.layers * PREFILL_TOKENS + nums["attn_flops_per_layer"](PREFILL_TOKENS) \
         * args.layers + 2.0 * nums["head_params"]
     prefill = {"value": round(PREFILL_TOKENS / pre_ms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),

@@ -33,43 +33,6 @@ constexpr float LOG2E = 1.4426950408889634f;
 constexpr size_t SMEM_BYTES = 6 * TILE_BYTES + 1024 + 256;
 constexpr int TMEM_COLS = 512;                      // S0 at 0, S1 at 128, O at 256
 
-__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,"
-        "%30,%31,%32};" ::"r"(taddr),
-        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
-        "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
-        "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-        : "memory");
-}
-__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ float fast_exp2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
-}
-
-// MN-major operand, 128-byte swizzle: 64 MN elements (128 bytes) contiguous, K rows 128 bytes apart, 8-row
-// groups 1024 bytes apart (stride byte offset), 64-element MN atoms `atom_bytes` apart (leading byte offset).
-__device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t addr, uint32_t atom_bytes) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)((atom_bytes >> 4) & 0x3FFF) << 16;
-    d |= (uint64_t)(1024 >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
-// kind::f16, float32 accumulate, bfloat16 A and B, A K-major, M = 128, N = 128; B K-major or MN-major (bit 16)
-constexpr uint32_t IDESC_KK = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
-constexpr uint32_t IDESC_KMN = IDESC_KK | (1u << 16);
-
 __global__ void __launch_bounds__(THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const __nv_bfloat16* __restrict__ k_cache,
@@ -202,7 +165,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k) {
                     const uint32_t o = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-                    tcgen05_mma_bf16(d, smem_desc_sw128(s_q + o), smem_desc_sw128(s_k(b) + o), IDESC_KK, k > 0);
+                    tcgen05_mma_bf16(d, smem_desc_sw128(s_q + o), smem_desc_sw128(s_k(b) + o), IDESC_128x128_KK, k > 0);
                 }
                 tcgen05_commit(bar(S_FULL + b));
                 tcgen05_commit(bar(K_EMPTY + b));
@@ -223,7 +186,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 for (int k = 0; k < BKV / 16; ++k) {
                     // A: 16 keys further along P's rows; B: 16 key rows further down V (two 8-row groups)
                     const uint32_t pa = s_p + (k >> 2) * HALF_BYTES + (k & 3) * 32;
-                    tcgen05_mma_bf16(d, smem_desc_sw128(pa), smem_desc_mn_sw128(s_v(b) + k * 2048, HALF_BYTES), IDESC_KMN,
+                    tcgen05_mma_bf16(d, smem_desc_sw128(pa), smem_desc_mn_sw128(s_v(b) + k * 2048, HALF_BYTES), IDESC_128x128_KMN,
                                      (j > 0 || k > 0) ? 1u : 0u);
                 }
                 tcgen05_commit(bar(PV_DONE));
@@ -363,6 +326,9 @@ int* attention_tc_error_word() {
 }
 
 }  // namespace
+
+// the error word of the tcgen05 attention kernels (this one and the two-tile kernel of attention_prefill_pair.cu)
+int* jllm_attention_tc_error_word_ptr() { return attention_tc_error_word(); }
 
 JLLM_EXPORT int jllm_attention_prefill_tc_fits(int head_dim, int page_size, int q_stride, int out_stride) {
     return head_dim == 128 && page_size >= 1 && page_size <= 128 && (page_size & (page_size - 1)) == 0 &&

@@ -96,6 +96,7 @@ class _Signatures:
     jllm_attention_prefill = [P, I, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P]
     jllm_attention_prefill_tc = [P, I, P, P, ctypes.c_longlong, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P]
     jllm_attention_prefill_tc_error = []
+    jllm_attention_prefill_pair = [P, I, P, P, ctypes.c_longlong, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P]
     jllm_argmax = [P, I, I, I, P, P]
     jllm_sample = [P, I, I, I, P, P, P, P, P, P, P]
 
@@ -364,9 +365,14 @@ def attention_prefill_tc_fits(q, out, k_cache, head_dim, page_size) -> bool:
 def attention_prefill(q, k_cache, v_cache, out, seg_start, seg_len, seg_kv_len, block_tables, rows, heads, kv_heads,
                       head_dim, page_size, window, scale, kernel: str = "auto") -> None:
     """Flash attention of prompt portions: segments of consecutive rows, each over its own request's pages.
-    Head size 128 runs on tcgen05 (both products, accumulators in tensor memory), other sizes on mma.sync."""
-    if kernel == "tc" or (kernel == "auto" and PREFILL_TC and attention_prefill_tc_fits(q, out, k_cache, head_dim, page_size)):
-        return _call("jllm_attention_prefill_tc", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+    Head size 128 runs on tcgen05 (both products, accumulators in tensor memory; kernel "pair" or "tc"), other
+    sizes on mma.sync ("mma")."""
+    if kernel == "auto" and PREFILL_TC and attention_prefill_tc_fits(q, out, k_cache, head_dim, page_size):
+        # two query tiles per block where the portions are long enough to fill them (the tiles take turns on the
+        # tensor cores); one tile per block, with two S buffers, for short portions
+        kernel = "pair" if rows > 128 * seg_start.numel() and PREFILL_TC != 3 else "tc"
+    if kernel in ("tc", "pair"):
+        return _call("jllm_attention_prefill_tc" if kernel == "tc" else "jllm_attention_prefill_pair", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
                      k_cache.shape[0], out.data_ptr(), out.stride(0), seg_start.data_ptr(), seg_len.data_ptr(),
                      seg_kv_len.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), seg_start.numel(), rows,
                      heads, kv_heads, head_dim, page_size, int(window), float(scale), _stream())

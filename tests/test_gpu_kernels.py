@@ -331,25 +331,26 @@ def check_attention_prefill(ops, H, Hkv, hd, page, window, lens, q_lens, kernel)
         assert torch.allclose(out.float().cpu(), want, rtol=2e-2, atol=2e-2), float((out.float().cpu() - want).abs().max())
 
 
-@pytest.mark.parametrize("kernel", ["mma", "tc"])
+@pytest.mark.parametrize("kernel", ["mma", "tc", "pair"])
 @pytest.mark.parametrize("H,Hkv,hd,page,window", [(6, 2, 64, 16, 0), (4, 4, 128, 4, 0), (32, 8, 128, 16, 0),
                                                    (6, 3, 64, 8, 21), (4, 1, 256, 16, 0), (2, 1, 64, 1, 7),
                                                    (8, 2, 128, 16, 100)])
 def test_attention_prefill(ops, H, Hkv, hd, page, window, kernel):
     """Portions of prompts (and single rows) of several requests in one launch, starting anywhere in a page."""
-    if kernel == "tc" and hd != 128:
-        pytest.skip("the tcgen05 kernel is built for head size 128")
+    if kernel != "mma" and hd != 128:
+        pytest.skip("the tcgen05 kernels are built for head size 128")
     check_attention_prefill(ops, H, Hkv, hd, page, window, [1, 17, 64, 131, 300, 1000, 77], [1, 17, 30, 131, 200, 65, 1],
                             kernel)
 
 
+@pytest.mark.parametrize("kernel", ["tc", "pair"])
 @pytest.mark.parametrize("H,Hkv,page,window", [(2, 1, 1, 0), (3, 3, 2, 0), (4, 2, 32, 0), (2, 2, 64, 300), (6, 1, 128, 0),
                                                (4, 2, 16, 128), (2, 1, 8, 129), (2, 2, 16, 1)])
-def test_attention_prefill_tcgen05_tiles(ops, H, Hkv, page, window):
+def test_attention_prefill_tcgen05_tiles(ops, H, Hkv, page, window, kernel):
     """The tcgen05 kernel over several query tiles and many key tiles: portions that start and end anywhere
     relative to the 128-key tiles, every page size, windows at, below and above a tile."""
     check_attention_prefill(ops, H, Hkv, 128, page, window, [128, 129, 700, 1500, 256, 383],
-                            [128, 2, 513, 300, 129, 255], "tc")
+                            [128, 2, 513, 300, 129, 255], kernel)
 
 
 @pytest.mark.parametrize("fused", [False, True])
