@@ -33,6 +33,12 @@ __device__ __forceinline__ void ldsm4t(uint32_t (&r)[4], uint32_t addr) {
 __device__ __forceinline__ void cp16(uint32_t dst, const void* src, int bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
 }
+// 2^x by the special-function unit alone (the bfloat16 path rounds the result to 8 bits of mantissa anyway)
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ void commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void wait_group() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
@@ -156,7 +162,7 @@ attention_decode_staged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
             mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
             mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
             const float m_new = fmaxf(m[h], mx[h]);   // finite: key0 <= P, so the warp sees at least one key
-            corr[h] = exp2f(m[h] - m_new);
+            corr[h] = ex2(m[h] - m_new);
             m[h] = m_new;
             l[h] *= corr[h];
         }
@@ -164,8 +170,8 @@ attention_decode_staged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
         uint32_t pf[4];
 #pragma unroll
         for (int tile = 0; tile < 2; ++tile) {
-            const float p0 = exp2f(s[tile][0] - m[0]), p1 = exp2f(s[tile][1] - m[0]);
-            const float p2 = exp2f(s[tile][2] - m[1]), p3 = exp2f(s[tile][3] - m[1]);
+            const float p0 = ex2(s[tile][0] - m[0]), p1 = ex2(s[tile][1] - m[0]);
+            const float p2 = ex2(s[tile][2] - m[1]), p3 = ex2(s[tile][3] - m[1]);
             l[0] += p0 + p1;
             l[1] += p2 + p3;
             __nv_bfloat162 a = __floats2bfloat162_rn(p0, p1), b = __floats2bfloat162_rn(p2, p3);
