@@ -32,6 +32,10 @@ QWEN3_8B = dict(model_type="qwen3", architectures=["Qwen3ForCausalLM"], hidden_s
                 num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288,
                 vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
                 attention_bias=False, use_sliding_window=False, max_position_embeddings=40960, hidden_act="silu")
+# the layer shapes of BASELINE.json's other configurations (same architecture; random weights): --shape
+SHAPES = {"8b": QWEN3_8B,
+          "14b": dict(QWEN3_8B, hidden_size=5120, num_hidden_layers=40, num_attention_heads=40, intermediate_size=17408),
+          "32b": dict(QWEN3_8B, hidden_size=5120, num_hidden_layers=64, num_attention_heads=64, intermediate_size=25600)}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 PAGE = 16
@@ -105,8 +109,12 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"],
+    ap.add_argument("--layers", type=int, default=0,
                     help="run fewer layers than the configuration has (named in the record)")
+    ap.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="layer sizes: Qwen3-8B (default), 14B or 32B")
+    ap.add_argument("--context", type=int, default=CONTEXT, help="context length at which the decode steps are timed")
+    ap.add_argument("--mixed-chunk", type=int, default=0,
+                    help="rows of a prompt portion that rides in every timed step beside the decoding requests")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true")
@@ -127,15 +135,21 @@ def main() -> int:
     from jllm_serve_b200.engine import Engine, Segment
     from jllm_serve_b200.sampling import SamplingParams
 
-    cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
+    shape = SHAPES[args.shape]
+    args.layers = args.layers or shape["num_hidden_layers"]
+    ctx = args.context
+    default_run = args.shape == "8b" and ctx == CONTEXT and not args.mixed_chunk
+    if not default_run:
+        args.skip_points = args.skip_e2e = True
+    cfg = dict(shape, num_hidden_layers=args.layers)
     nums = model_numbers(cfg, args.layers)
     pk = peaks()
     dev = torch.device("cuda:0")
     biggest = 64 if not args.skip_points else args.batch
-    pool_tokens = biggest * CONTEXT + 2 * PREFILL_TOKENS
+    pool_tokens = biggest * ctx + 2 * PREFILL_TOKENS + args.mixed_chunk
     t0 = time.time()
-    engine = Engine(config=cfg, seed=0, dtype="bfloat16", ctx=CONTEXT, page_size=PAGE, num_pages=pool_tokens // PAGE,
-                    max_batch_tokens=PREFILL_TOKENS + 64, chunk=PREFILL_TOKENS, max_running=biggest)
+    engine = Engine(config=cfg, seed=0, dtype="bfloat16", ctx=ctx, page_size=PAGE, num_pages=pool_tokens // PAGE,
+                    max_batch_tokens=PREFILL_TOKENS + 64, chunk=PREFILL_TOKENS, max_running=biggest + 1)
     runner = engine.runner
     print(f"bench: {runner.describe()} (built in {time.time() - t0:.0f} s)", file=sys.stderr, flush=True)
     for g in runner.cache.paged:      # any cached values do for timing; zeros would be kinder to the memory system
@@ -146,10 +160,13 @@ def main() -> int:
         return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
     def decode_device_timed(batch: int, steps: int, warmup: int):
-        """`batch` requests whose contexts END at CONTEXT after warmup + steps decoded tokens; the cache content
-        is synthetic. Returns (ms per step, mean context during the timed steps, kernels launched)."""
+        """`batch` requests whose contexts END at the context length after warmup + steps decoded tokens; the
+        cache content is synthetic. With --mixed-chunk a portion of a prompt (rows 1,024 onwards of a request that
+        is given back after the step) runs in every step before them.
+        Returns (ms per step, mean context during the timed steps, kernels launched)."""
         ids = [f"d{batch}-{i}" for i in range(batch)]
-        start = CONTEXT - warmup - steps
+        start = ctx - warmup - steps
+        portions = [0]
         for i in ids:
             runner.cache.open(i)
             runner.cache.reserve(i, 0, start)
@@ -157,8 +174,17 @@ def main() -> int:
 
         def one_step():
             segs = [Segment(i, [1 + k], runner.cache.length(i), [0]) for k, i in enumerate(ids)]
+            if args.mixed_chunk:
+                portions[0] += 1
+                rid = f"portion{portions[0]}"
+                runner.cache.open(rid)
+                runner.cache.reserve(rid, 0, 1024)
+                runner.cache.commit(rid, 1024)
+                segs.insert(0, Segment(rid, list(range(1, args.mixed_chunk + 1)), 1024, []))
             logits = runner.step(segs)
             ops.argmax(logits, out_tok[:batch])
+            if args.mixed_chunk:
+                runner.finish(segs[0].request)
 
         for _ in range(warmup):
             one_step()
@@ -174,7 +200,7 @@ def main() -> int:
         launched = ops.launch_count - before
         for i in ids:
             runner.finish(i)
-        return ms, CONTEXT - steps / 2.0, launched
+        return ms, ctx - steps / 2.0, launched
 
     def decode_bytes(batch: int, context: float) -> float:
         return nums["weight_bytes"] + batch * context * nums["kv_bytes_per_token"]
@@ -236,14 +262,17 @@ def main() -> int:
         e2e = end_to_end(engine, args.batch, args.steps, args.warmup, cfg["vocab_size"])
 
     record = {
-        "metric": "decode tok/s @ batch 8, context 4096 (Qwen3-8B shape, bf16, random weights)",
+        "metric": (f"decode tok/s @ batch {args.batch}, context {ctx} (Qwen3-{args.shape.upper()} shape, bf16, random weights"
+                   + (f", a {args.mixed_chunk}-row prompt portion in every step)" if args.mixed_chunk else ")")),
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic token ids, random-init weights N(0, 0.02); device-timed cache content synthetic",
-        "config": {"model": "Qwen3-8B shape", "layers": args.layers, "layers_of_config": QWEN3_8B["num_hidden_layers"],
-                   "hidden": 4096, "heads": 32, "kv_heads": 8, "head_dim": 128, "intermediate": 12288,
-                   "vocab": 151936, "global_batch": args.batch, "seq_len": CONTEXT, "page_size": PAGE,
-                   "parallelism": "single GPU", "l2": "inputs larger than L2 (weights 15 GB per step)",
+        "config": {"model": f"Qwen3-{args.shape.upper()} shape", "layers": args.layers,
+                   "layers_of_config": shape["num_hidden_layers"], "hidden": cfg["hidden_size"],
+                   "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": args.batch,
+                   "seq_len": ctx, "page_size": PAGE, "mixed_chunk": args.mixed_chunk, "parallelism": "single GPU",
+                   "l2": f"inputs larger than L2 (weights {nums['weight_bytes'] / 1e9:.0f} GB per step)",
                    "cuda_graphs": runner.use_graphs},
         "clocks": clock_record, "e2e": e2e, "gpu_launches": launches, "prefill": prefill, "roofline": roofline,
         "points": points,
