@@ -185,6 +185,7 @@ def gemm_bf16_fits(a, w, out) -> bool:
 # is correct for M <= 128 but was slower than both on those shapes; JLLM_B200_SKINNY_ROWS switches it in.
 SMALL_M_ROWS = int(__import__("os").environ.get("JLLM_B200_SMALL_M_ROWS", "32"))
 SKINNY_ROWS = int(__import__("os").environ.get("JLLM_B200_SKINNY_ROWS", "0"))
+WIDE_ROWS = int(__import__("os").environ.get("JLLM_B200_WIDE_ROWS", "16384"))
 _skinny_workspaces = {}
 
 
@@ -218,7 +219,11 @@ def gemm_skinny_error() -> int:
 def gemm_bf16(a, w, out, bias=None, accumulate=False, swiglu=False) -> None:
     """out (+)= a @ w.T (+ bias) on the tensor cores: bfloat16 operands, float32 accumulation. With `swiglu`
     the rows of w are blocks of 8 gate rows followed by their 8 up rows and out[m, j] = silu(gate_j) * up_j."""
-    if a.shape[0] <= SMALL_M_ROWS and _small_m_fits(a, w):
+    M, N = a.shape[0], w.shape[0]
+    # 16 to 32 rows against a wide matrix (gate_up): 128 or more 192-wide tcgen05 tiles stream it faster than the
+    # weight-stream kernel, whose blocks have half their loads in flight once they hold more than two token tiles
+    wide = M >= 16 and N >= WIDE_ROWS and _tcgen05_fits(a, w)
+    if M <= SMALL_M_ROWS and _small_m_fits(a, w) and not wide:
         return gemm_small_m(a, w, out, bias, accumulate, swiglu=swiglu)
     if a.shape[0] <= SKINNY_ROWS and _tcgen05_fits(a, w) and w.shape[0] <= 4096 * 128:
         return gemm_skinny(a, w, out, bias, accumulate, swiglu)
