@@ -31,7 +31,7 @@ constexpr int A_BYTES = BM * BK * 2;
 // rows are few (more than the weight-stream kernel takes, at most a few hundred), so that every SM has a tile of
 // the weight matrix to stream. Narrow tiles have small stages, so the ring is deeper.
 __host__ __device__ constexpr int stages_for(int bn) { return bn >= 256 ? 4 : bn >= 192 ? 5 : bn >= 128 ? 6 : 8; }
-constexpr int JLLM_TC_MAX_TILES = 4096;  // counter words at the head of the split-K workspace
+constexpr int JLLM_TC_MAX_TILES = 65536;  // counter words at the head of the workspace of streamed products
 constexpr int THREADS = 192;           // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
 constexpr int TMEM_COLS = 512;
 __host__ __device__ constexpr size_t smem_bytes_for(int bn) {
@@ -48,7 +48,7 @@ template <typename Tout, int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, VecRef bias,
                     int has_bias, Tout* __restrict__ out, int ldo, int accumulate, int M, int N, int K, int swiglu,
-                    int splits, float* __restrict__ partials, int* __restrict__ counters, int* __restrict__ error_word) {
+                    int stream, float* __restrict__ partials, int* __restrict__ counters, int* __restrict__ error_word) {
     constexpr int STAGES = stages_for(BN), B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
     constexpr uint32_t IDESC = idesc_for(BN);
     static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "tile width");
@@ -68,13 +68,36 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN, tiles = tiles_m * tiles_n;
     const int k_blocks = (K + BK - 1) / BK;
-    // With few tiles (few rows, a narrow matrix) K is split: a work unit is (tile, slice of the k blocks), so
-    // that every SM has a share of the weight stream. The slices' partial tiles meet in a workspace.
-    const int units = tiles * splits;
-    auto slice = [&](int s, int& lo, int& hi) {
-        const int q = k_blocks / splits, r = k_blocks % splits;
-        lo = s * q + min(s, r);
-        hi = lo + q + (s < r ? 1 : 0);
+    // The work of a block: whole tiles, tile = block, block + grid, ... as long as full rounds of tiles last. The
+    // tiles of a last, partly filled round are streamed instead (stream-K): their (tile, k block) pairs, in tile
+    // order, are cut into one equal run per block, so that no SM idles through that round; a tile whose k blocks
+    // lie in several blocks' runs is finished by whichever of them comes last (below). Blocks that run at the
+    // same time always work on neighbouring tiles, which share their W and A tiles in L2. All three roles walk
+    // the same units with this.
+    const int whole_tiles = stream ? tiles / (int)gridDim.x * (int)gridDim.x : tiles;
+    const long long sk_kb = (long long)(tiles - whole_tiles) * k_blocks;     // streamed (tile, k block) pairs
+    const long long run_lo = sk_kb * blockIdx.x / gridDim.x, run_hi = sk_kb * (blockIdx.x + 1) / gridDim.x;
+    struct Walk {
+        long long at;
+        int i;
+    };
+    auto first_unit = [&]() { return Walk{run_lo, 0}; };
+    auto next_unit = [&](Walk& w, int& tile, int& lo, int& hi) {
+        const int t = blockIdx.x + w.i * gridDim.x;
+        if (t < whole_tiles) {
+            tile = t;
+            lo = 0;
+            hi = k_blocks;
+            ++w.i;
+            return true;
+        }
+        if (w.at >= run_hi) return false;
+        const int st = (int)(w.at / k_blocks);
+        tile = whole_tiles + st;
+        lo = (int)(w.at - (long long)st * k_blocks);
+        hi = (int)min((long long)k_blocks, lo + (run_hi - w.at));
+        w.at += hi - lo;
+        return true;
     };
 
     if (threadIdx.x == 0) {
@@ -107,11 +130,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
-                const int tile = unit / splits;
+            Walk walk = first_unit();
+            int tile, lo, hi;
+            while (ok && next_unit(walk, tile, lo, hi)) {
                 const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
-                int lo, hi;
-                slice(unit % splits, lo, hi);
                 for (int kb = lo; kb < hi; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t parity = ((it / STAGES) & 1u) ^ 1u;
@@ -129,13 +151,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (lane == 0) {
             uint32_t it = 0, local_tile = 0;
             bool ok = true;
-            for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++local_tile) {
+            Walk walk = first_unit();
+            int tile, lo, hi;
+            for (; ok && next_unit(walk, tile, lo, hi); ++local_tile) {
                 const uint32_t buf = local_tile & 1u;
                 if (!mbar_wait(acc_empty_bar(buf), ((local_tile >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
                 tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + buf * BN;
-                int lo, hi;
-                slice(unit % splits, lo, hi);
                 for (int kb = lo; kb < hi; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (!mbar_wait(full_bar(s), (it / STAGES) & 1u, abort_flag)) { ok = false; break; }
@@ -158,8 +180,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int quad = warp & 3;
         uint32_t local_tile = 0;
         bool ok = true;
-        for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++local_tile) {
-            const int tile = unit / splits;
+        Walk walk = first_unit();
+        int tile, k_lo, k_hi;
+        for (; ok && next_unit(walk, tile, k_lo, k_hi); ++local_tile) {
             const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
             const uint32_t buf = local_tile & 1u;
             if (!mbar_wait(acc_full_bar(buf), (local_tile >> 1) & 1u, abort_flag)) { ok = false; break; }
@@ -266,7 +289,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     }
                 }
             };
-            if (splits == 1) {
+            if (k_lo == 0 && k_hi == k_blocks) {      // the whole tile is this block's
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 32) {
                     uint32_t v[32];
@@ -279,19 +302,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if (lane == 0) mbar_arrive(acc_empty_bar(buf));
                 continue;
             }
-            // ---- K was split: park this slice's partial tile ([unit][128 rows][256 columns]) ----
-            float4* mine = reinterpret_cast<float4*>(partials + ((size_t)unit * BM + quad * 32 + lane) * BN);
+            // ---- the tile's k blocks are spread over several blocks: park this part ([block][first or later unit
+            // of the block][BN columns][128 rows]: a warp's 32 rows of one column are 128 contiguous bytes); the
+            // blocks that hold parts of the tile are consecutive ----
+            auto run_start = [&](long long c) { return sk_kb * c / gridDim.x; };
+            auto block_of = [&](long long kb_index) {   // the block whose run holds this streamed (tile, k block) pair
+                return (int)(((kb_index + 1) * gridDim.x + sk_kb - 1) / sk_kb - 1);
+            };
+            const long long tile_kb0 = (long long)(tile - whole_tiles) * k_blocks;
+            const int c_first = block_of(tile_kb0), parts = block_of(tile_kb0 + k_blocks - 1) - c_first + 1;
+            auto part_of = [&](int c) {                 // where block c parked its part of this tile
+                const int slot = run_start(c) >= tile_kb0 ? 0 : 1;
+                return partials + (size_t)(2 * c + slot) * BM * BN + quad * 32 + lane;
+            };
+            float* mine = part_of(blockIdx.x);
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t v[32];
                 tmem_ld_32x32b_x32(taddr + c0, v);
                 tmem_ld_wait();
-                if (row < M) {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                        __stcg(mine + (c0 >> 2) + j, make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                                                 __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3])));
-                }
+                for (int j = 0; j < 32; ++j) __stcg(mine + (size_t)(c0 + j) * BM, __uint_as_float(v[j]));
             }
             tcgen05_fence_before();
             __syncwarp();
@@ -300,43 +331,32 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (warp == 2 && lane == 0) {
                 __threadfence();
                 const int seen = atomicAdd(&counters[tile], 1);
-                *last_flag = seen == splits - 1;
-                if (seen == splits - 1) {
+                *last_flag = seen == parts - 1;
+                if (seen == parts - 1) {
                     counters[tile] = 0;                               // back to zero for the next product
                     __threadfence();
                 }
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (*last_flag == 0) continue;
-            // ---- the block that came last adds the slices in slice order (deterministic) and finishes the tile ----
+            // ---- the block that came last adds the parts in k order (deterministic) and finishes the tile ----
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 float acc[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) acc[j] = 0.f;
-                if (row < M) {
-                    for (int s0 = 0; s0 < splits; s0 += 4) {
-                        float4 part[4][8];
+                for (int s0 = 0; s0 < parts; s0 += 2) {     // two parts' loads in flight at a time, added in k order
+                    const float* p0 = part_of(c_first + s0) + (size_t)c0 * BM;
+                    const float* p1 = part_of(c_first + min(s0 + 1, parts - 1)) + (size_t)c0 * BM;
+                    float x0[32], x1[32];
 #pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            const float4* p = reinterpret_cast<const float4*>(
-                                partials + ((size_t)(tile * splits + min(s0 + u, splits - 1)) * BM + quad * 32 + lane) * BN) + (c0 >> 2);
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) part[u][j] = __ldcg(p + j);
-                        }
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            if (s0 + u < splits) {
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) {
-                                    acc[4 * j + 0] += part[u][j].x;
-                                    acc[4 * j + 1] += part[u][j].y;
-                                    acc[4 * j + 2] += part[u][j].z;
-                                    acc[4 * j + 3] += part[u][j].w;
-                                }
-                            }
-                        }
+                    for (int j = 0; j < 32; ++j) {
+                        x0[j] = __ldcg(p0 + (size_t)j * BM);
+                        x1[j] = __ldcg(p1 + (size_t)j * BM);
                     }
+                    const bool two = s0 + 1 < parts;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) acc[j] = two ? (acc[j] + x0[j]) + x1[j] : acc[j] + x0[j];
                 }
                 uint32_t v[32];
 #pragma unroll
@@ -391,7 +411,7 @@ JLLM_EXPORT int jllm_gemm_tcgen05_error() {
 
 JLLM_EXPORT int jllm_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, const void* bias, int bias_dtype,
                                   void* out, int out_dtype, int ldo, int accumulate, int M, int N, int K, int max_blocks,
-                                  int swiglu, float* workspace, long long workspace_floats, int force_splits,
+                                  int swiglu, float* workspace, long long workspace_floats, int stream_mode,
                                   int tile_width, cudaStream_t stream) {
     JLLM_REQUIRE(jllm_gemm_tcgen05_fits(a, lda, w, ldw, M, N, K),
                  "gemm_tcgen05: needs K %% 8 == 0 and 16-byte aligned rows (M=%d N=%d K=%d lda=%d ldw=%d)", M, N, K, lda,
@@ -416,9 +436,12 @@ JLLM_EXPORT int jllm_gemm_tcgen05(const void* a, int lda, const void* w, int ldw
         const long long cost = ((t + sms - 1) / sms) * (rows_per_tile + widths[i]);
         if (best < 0 || cost < best) { best = cost; BN = widths[i]; }
     }
+    // The tiles of a last, partly filled round can be streamed (stream-K, stream_mode 1). It is not done by default:
+    // on the layer shapes of an 8B model with 2,048 rows the parked partial tiles and their adding up cost what the
+    // idle SMs of the last round cost (QKV 92 us streamed, 81 us plain; gate_up 307 / 291; down 207 / 178).
+    bool streamed = false;
     if (tile_width > 0) BN = tile_width;
     JLLM_REQUIRE(BN == 256 || BN == 192 || BN == 128 || BN == 64 || BN == 32, "gemm_tcgen05: tile width %d", BN);
-    if (swiglu && BN % 32 != 0) BN = 256;
     CUtensorMap map_a, map_w;
     int rc = tensor_map_for(a, M, K, lda, BM, &map_a);
     if (rc != JLLM_OK) return rc;
@@ -428,22 +451,23 @@ JLLM_EXPORT int jllm_gemm_tcgen05(const void* a, int lda, const void* w, int ldw
     if (!error_word) return jllm_fail(JLLM_CUDA_ERROR, "gemm_tcgen05: no error word");
     const int tiles = tiles_m * ((N + BN - 1) / BN);
     const int k_blocks = (K + BK - 1) / BK;
-    // K can be split over blocks (force_splits), the slices meeting in the caller's workspace. It is not done by
-    // default: on the layer shapes of an 8B model with 64 rows the partial tiles' round trip through memory
-    // cost more than the idle SMs did.
-    int splits = 1;
-    if (force_splits > 0) splits = force_splits > k_blocks ? k_blocks : force_splits;
-    const long long need = JLLM_TC_MAX_TILES + (long long)tiles * splits * BM * BN;
-    if (splits > 1) {
-        JLLM_REQUIRE(tiles <= JLLM_TC_MAX_TILES, "gemm_tcgen05: %d tiles with split K, at most %d", tiles, JLLM_TC_MAX_TILES);
-        JLLM_REQUIRE(workspace != nullptr && workspace_floats >= need,
-                     "gemm_tcgen05: split K needs a workspace of %lld floats, got %lld", need, workspace_floats);
+    // stream_mode: 1 = streamed, else plain. The workspace of a streamed product holds one counter per tile (zero
+    // before the first product, left zero by every product) and two parked partial tiles per block.
+    int grid = tiles < sms ? tiles : sms;
+    if (stream_mode > 0) {
+        streamed = true;
+        const long long all_kb = (long long)tiles * k_blocks;
+        grid = all_kb < sms ? (int)all_kb : sms;
     }
+    if (max_blocks > 0 && grid > max_blocks) grid = max_blocks;
+    const long long need = JLLM_TC_MAX_TILES + (long long)grid * 2 * BM * BN;
+    const bool room = workspace != nullptr && workspace_floats >= need && tiles <= JLLM_TC_MAX_TILES;
+    if (streamed)
+        JLLM_REQUIRE(room, "gemm_tcgen05: a streamed product of %d tiles on %d blocks needs a workspace of %lld floats "
+                           "(got %lld) and at most %d tiles", tiles, grid, need, workspace_floats, JLLM_TC_MAX_TILES);
     int* counters = reinterpret_cast<int*>(workspace);
     float* partials = workspace ? workspace + JLLM_TC_MAX_TILES : nullptr;
-    const int units = tiles * splits;
-    int grid = units < sms ? units : sms;
-    if (max_blocks > 0 && grid > max_blocks) grid = max_blocks;
+    const int splits = streamed ? 1 : 0;      // the kernel's `stream` argument
     const VecRef b{bias, bias_dtype};
 #define JLLM_TC_GO(T, W)                                                                                              \
     do {                                                                                                              \

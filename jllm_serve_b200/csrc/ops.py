@@ -187,6 +187,8 @@ SMALL_M_ROWS = int(__import__("os").environ.get("JLLM_B200_SMALL_M_ROWS", "32"))
 SKINNY_ROWS = int(__import__("os").environ.get("JLLM_B200_SKINNY_ROWS", "0"))
 WIDE_ROWS = int(__import__("os").environ.get("JLLM_B200_WIDE_ROWS", "16384"))
 _skinny_workspaces = {}
+# counters of up to 65,536 tiles, then two parked 128 x 256 partial tiles for each of up to 160 blocks
+STREAM_WORKSPACE_FLOATS = 65536 + 160 * 2 * 128 * 256
 
 
 def skinny_workspace(device, floats: int = 8 << 20) -> torch.Tensor:
@@ -232,20 +234,18 @@ def gemm_bf16(a, w, out, bias=None, accumulate=False, swiglu=False) -> None:
     raise KernelError("the tensor-core matrix product is not built for this shape")
 
 
-def gemm_tcgen05(a, w, out, bias=None, accumulate=False, max_blocks: int = 0, swiglu=False, force_splits: int = 0,
+def gemm_tcgen05(a, w, out, bias=None, accumulate=False, max_blocks: int = 0, swiglu=False, stream_mode: int = 0,
                  tile_width: int = 0) -> None:
     """The prefill product: TMA-fed tcgen05.mma tiles of 128 x `tile_width` (0: chosen from the shape, 256 for big
-    products, down to 32 when the rows are few) with the accumulator in tensor memory. `force_splits` splits K
-    over blocks; the partial tiles meet in a workspace."""
+    products, down to 32 when the rows are few) with the accumulator in tensor memory. `stream_mode` 1: the tiles
+    of a last, partly filled round are streamed (stream-K: equal runs of (tile, k block) pairs per block, partial
+    tiles meeting in a workspace); off by default (measured slower on 8B layer shapes)."""
     assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.stride(-1) == 1
-    ws = None
-    if force_splits:
-        tiles = -(-a.shape[0] // 128) * -(-w.shape[0] // (tile_width or 32))
-        ws = skinny_workspace(a.device, 4096 + tiles * force_splits * 128 * (tile_width or 256))
+    ws = skinny_workspace(a.device, STREAM_WORKSPACE_FLOATS) if stream_mode > 0 else None
     _call("jllm_gemm_tcgen05", a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), _p(bias),
           _DT[bias.dtype] if bias is not None else F32, out.data_ptr(), _DT[out.dtype], out.stride(0),
           int(accumulate), a.shape[0], w.shape[0], a.shape[1], int(max_blocks), int(swiglu), _p(ws),
-          ws.numel() if ws is not None else 0, int(force_splits), int(tile_width), _stream())
+          ws.numel() if ws is not None else 0, int(stream_mode), int(tile_width), _stream())
 
 
 def check_kernel_errors() -> None:

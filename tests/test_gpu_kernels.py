@@ -132,19 +132,22 @@ def test_gemm_tcgen05(ops, M, N, K):
     ops.gemm_tcgen05(a, w, out16[:, :N])
     assert torch.allclose(out16[:, :N].float().cpu(), gemm_want(a, w), rtol=2 ** -7, atol=2e-3)
     assert float(out16[:, N:].abs().max()) == 0 and ops.gemm_tcgen05_error() == 0
-    # K split over blocks: the slices are added in slice order, so two runs give the same bits
-    if K >= 128:
+    # streamed (equal runs of (tile, k block) pairs per block, also with few blocks): the parts of a tile are added
+    # in k order by whichever block comes last, so two runs give the same bits
+    for blocks in (0, 5):
         one, two = base.clone(), base.clone()
-        ops.gemm_tcgen05(a, w, one, None, accumulate=True, force_splits=3)
-        ops.gemm_tcgen05(a, w, two, None, accumulate=True, force_splits=3)
+        ops.gemm_tcgen05(a, w, one, None, accumulate=True, stream_mode=1, max_blocks=blocks)
+        ops.gemm_tcgen05(a, w, two, None, accumulate=True, stream_mode=1, max_blocks=blocks)
         assert torch.allclose(one.cpu(), gemm_want(a, w, None, base), rtol=1e-4, atol=tol) and torch.equal(one, two)
-        assert ops.gemm_tcgen05_error() == 0
+    ops.gemm_tcgen05(a, w, out16[:, :N], stream_mode=1)
+    assert torch.allclose(out16[:, :N].float().cpu(), gemm_want(a, w), rtol=2 ** -7, atol=2e-3)
+    assert ops.gemm_tcgen05_error() == 0
 
 
 @pytest.mark.parametrize("width", [32, 64, 128, 192, 256])
 @pytest.mark.parametrize("M,N,K", [(64, 4096, 4096), (33, 517, 72), (200, 1000, 1032), (128, 24576, 512)])
 def test_gemm_tcgen05_tile_widths(ops, M, N, K, width):
-    """Every width of the output tile, chosen by hand: the product, the residual add, K split over blocks and
+    """Every width of the output tile, chosen by hand: the product, the residual add, the streamed product and
     the SwiGLU epilogue give what the default width gives."""
     a, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=1, scale=0.05)
     bias = rnd(N, dtype=torch.bfloat16, seed=2)
@@ -155,7 +158,7 @@ def test_gemm_tcgen05_tile_widths(ops, M, N, K, width):
     base = rnd(M, N, seed=3)
     acc, split = base.clone(), base.clone()
     ops.gemm_tcgen05(a, w, acc, None, accumulate=True, tile_width=width, max_blocks=5)
-    ops.gemm_tcgen05(a, w, split, None, accumulate=True, tile_width=width, force_splits=2)
+    ops.gemm_tcgen05(a, w, split, None, accumulate=True, tile_width=width, stream_mode=1)
     want = gemm_want(a, w, None, base)
     assert torch.allclose(acc.cpu(), want, rtol=1e-4, atol=tol) and torch.allclose(split.cpu(), want, rtol=1e-4, atol=tol)
     if N % 16 == 0:
