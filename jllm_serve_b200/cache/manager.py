@@ -17,15 +17,19 @@ and raises `PoolExhausted`. After the step `commit(request, length)` records the
 length and releases what a window has passed. `close` gives everything back.
 
 The manager is host bookkeeping; the device memory of a group is made by the `allocate`
-callable it is given (None in tests that need no device).
+callable it is given (None in tests that need no device). The books themselves (pools, tables,
+lengths, slots) are kept by the C++ host library (csrc/host/host_runtime.cpp), which also packs
+a step's batch tables from them; this class chooses the groups, owns the device memory and the
+names of the requests, and is the library's face towards the rest of the engine.
 """
 from __future__ import annotations
 
-import itertools
-from dataclasses import dataclass, field
-from typing import Callable, Dict, Hashable, List, Optional, Sequence, Tuple
+import ctypes
+from dataclasses import dataclass
+from typing import Callable, Dict, Hashable, Iterator, List, Optional, Sequence, Tuple
 
-from .pages import PageBookkeepingError, PagePool, PoolExhausted, StateSlotPool
+from . import native
+from .pages import PageBookkeepingError, PoolExhausted, PoolView  # noqa: F401
 
 RELEASED = -1  # table entry of a page that a window has passed
 
@@ -52,7 +56,7 @@ class FixedState(CacheNeed):
 class PagedGroup:
     need: PagedKeysValues
     runs: List[int]                        # schedule indices of the member layer runs
-    pool: PagePool
+    pool: Optional[PoolView] = None        # a view of the group's page pool
     storage: object = None                 # [len(runs), 2, pages, kv_heads, page_size, head_dim]
 
     def keys_values(self, run: int):
@@ -73,11 +77,46 @@ class StateGroup:
 
 @dataclass
 class RequestCache:
+    """A snapshot of what a request holds (the live books are the library's)."""
     request: Hashable
     state_slot: int
-    length: int = 0
-    tables: List[List[int]] = field(default_factory=list)  # one per paged group
-    epoch: int = 0                         # changes whenever a table changed otherwise than by growing at its end
+    length: int
+    tables: List[List[int]]                # one per paged group; -1 = a page that a window has passed
+    epoch: int                             # changes whenever a table changed otherwise than by growing at its end
+
+
+class _Requests:
+    """The open requests, as a read-only mapping name -> RequestCache snapshot."""
+
+    def __init__(self, manager: "CacheManager"):
+        self._m = manager
+
+    def __len__(self) -> int:
+        return native.lib().jh_cache_num_requests(self._m._ptr)
+
+    def __bool__(self) -> bool:
+        return len(self) > 0
+
+    def __contains__(self, request) -> bool:
+        return self._m.is_open(request)
+
+    def __iter__(self) -> Iterator:
+        n = len(self)
+        buf = (ctypes.c_longlong * max(1, n))()
+        got = native.lib().jh_cache_request_ids(self._m._ptr, buf, n)
+        return iter([self._m._names.name(buf[i]) for i in range(got)])
+
+    def __getitem__(self, request) -> RequestCache:
+        return self._m._snapshot(request)
+
+    def get(self, request, default=None):
+        return self._m._snapshot(request) if self._m.is_open(request) else default
+
+    def keys(self):
+        return list(iter(self))
+
+    def values(self):
+        return [self._m._snapshot(r) for r in self]
 
 
 class CacheManager:
@@ -86,6 +125,8 @@ class CacheManager:
         """`needs[i]` is the need of schedule entry i (None for a run that keeps nothing or reads another's cache)."""
         if page_size < 1:
             raise ValueError(f"page_size={page_size} must be at least 1")
+        if num_pages < 1:
+            raise ValueError(f"a pool needs at least one page, got {num_pages}")
         self.page_size = page_size
         self.num_pages = num_pages
         self.paged: List[PagedGroup] = []
@@ -101,7 +142,7 @@ class CacheManager:
                         break
                 else:
                     gi = len(self.paged)
-                    self.paged.append(PagedGroup(need, [run], PagePool(num_pages, f"group{gi}")))
+                    self.paged.append(PagedGroup(need, [run]))
                 self.group_of_run[run] = ("paged", gi)
             elif isinstance(need, FixedState):
                 for gi, g in enumerate(self.fixed):
@@ -114,14 +155,40 @@ class CacheManager:
                 self.group_of_run[run] = ("fixed", gi)
             else:
                 raise TypeError(f"layer run {run}: unknown cache need {need!r}")
-        self.slots = StateSlotPool(max_requests)
-        self._epochs = itertools.count(1)
-        self.requests: Dict[Hashable, RequestCache] = {}
+        L = native.lib()
+        G = len(self.paged)
+        windows = (ctypes.c_int * max(1, G))(*[g.need.window for g in self.paged])
+        self._names = native.Names()
+        self._ptr = L.jh_cache_new(G, windows, page_size, num_pages, max_requests)
+        if not self._ptr:
+            native.check(1)
+        for gi, g in enumerate(self.paged):
+            g.pool = PoolView(L.jh_cache_pool(self._ptr, gi), self._names, num_pages, f"group{gi}")
+            g.pool.num_pages = num_pages
+        self.slots = PoolView(L.jh_cache_pool(self._ptr, -1), self._names, max_requests, "state slots")
+        self.slots.num_slots = max_requests
+        self.requests = _Requests(self)
+        self._ints = (ctypes.c_int * max(8, G))()
         if allocate is not None:
             for g in self.paged:
                 g.storage = allocate((len(g.runs), 2, num_pages, g.need.kv_heads, page_size, g.need.head_dim), "kv")
             for g in self.fixed:
                 g.storage = allocate((len(g.runs), max_requests) + tuple(g.need.shape), g.need.dtype)
+
+    def __del__(self):
+        try:
+            if getattr(self, "_ptr", None):
+                native.lib().jh_cache_delete(self._ptr)
+                self._ptr = None
+        except Exception:        # the interpreter is shutting down and the module is gone
+            pass
+
+    def _h(self, request: Hashable) -> int:
+        return self._names.handle(request)
+
+    def _check(self, code: int) -> None:
+        if code:
+            native.check(code, self._names)
 
     # ---- what a layer run reads and writes ----------------------------------------------------------------
     def paged_group_of(self, run: int) -> int:
@@ -141,160 +208,95 @@ class CacheManager:
 
     # ---- requests ---------------------------------------------------------------------------------------
     def open(self, request: Hashable) -> RequestCache:
-        if request in self.requests:
+        if self.is_open(request):
             raise ValueError(f"request {request!r} is open already")
-        rc = RequestCache(request, self.slots.alloc(request), 0, [[] for _ in self.paged], next(self._epochs))
-        self.requests[request] = rc
-        return rc
+        h = self._names.handle(request, make=True)
+        code = native.lib().jh_cache_open(self._ptr, h, None)
+        if code:
+            self._names.forget(request)
+            self._check(code)
+        return self._snapshot(request)
 
     def is_open(self, request: Hashable) -> bool:
-        return request in self.requests
+        return request in self._names._handle      # the names that have a handle are the open requests
+
+    def _info(self, request: Hashable):
+        length, slot, epoch = ctypes.c_int(), ctypes.c_int(), ctypes.c_longlong()
+        code = native.lib().jh_cache_request(self._ptr, self._h(request), ctypes.byref(length), ctypes.byref(slot),
+                                             ctypes.byref(epoch), self._ints)
+        if code:
+            raise KeyError(request)
+        return length.value, slot.value, epoch.value, [self._ints[g] for g in range(len(self.paged))]
+
+    def _snapshot(self, request: Hashable) -> RequestCache:
+        length, slot, epoch, _ = self._info(request)
+        return RequestCache(request, slot, length, [self.table(request, g) for g in range(len(self.paged))], epoch)
 
     def length(self, request: Hashable) -> int:
-        return self.requests[request].length
-
-    def _first_needed_page(self, g: PagedGroup, length: int) -> int:
-        """Pages below this index hold only positions that no later query of the request can see."""
-        if g.need.window <= 0:
-            return 0
-        return max(0, length + 1 - g.need.window) // self.page_size
+        return self._info(request)[0]
 
     def pages_missing(self, request: Hashable, start: int, n: int) -> List[int]:
         """How many pages each paged group would have to take for positions [start, start + n)."""
-        rc = self.requests.get(request)
-        out = []
-        for gi, g in enumerate(self.paged):
-            have = len(rc.tables[gi]) if rc is not None else 0
-            if rc is not None and start < rc.length:
-                have = min(have, -(-start // self.page_size))
-            out.append(max(0, -(-(start + n) // self.page_size) - have))
-        return out
+        native.lib().jh_cache_pages_missing(self._ptr, self._h(request), start, n, self._ints)
+        return [self._ints[g] for g in range(len(self.paged))]
 
     def can_reserve(self, request: Hashable, start: int, n: int) -> bool:
-        return all(m <= g.pool.num_free for m, g in zip(self.pages_missing(request, start, n), self.paged))
+        return bool(native.lib().jh_cache_can_reserve(self._ptr, self._h(request), start, n))
 
     def reserve(self, request: Hashable, start: int, n: int) -> None:
         """Pages for positions [start, start + n) in every group, all or none; positions from `start`
         on that an earlier step wrote are dropped first (a rewind)."""
-        rc = self.requests[request]
-        if start < 0 or n < 1:
-            raise ValueError(f"reserve: start={start} n={n}")
-        if start > rc.length:
-            raise ValueError(f"request {request!r} holds {rc.length} positions, a step cannot start at {start}")
-        if start < rc.length:
-            self.truncate(request, start)
-        taken: List[Tuple[int, int]] = []
-        want_pages = -(-(start + n) // self.page_size)
-        try:
-            for gi, g in enumerate(self.paged):
-                table = rc.tables[gi]
-                while len(table) < want_pages:
-                    page = g.pool.alloc(request)
-                    table.append(page)
-                    taken.append((gi, page))
-        except PoolExhausted:
-            rc.epoch = next(self._epochs)
-            for gi, page in reversed(taken):
-                popped = rc.tables[gi].pop()
-                if popped != page:
-                    raise PageBookkeepingError("rollback of a failed reserve lost track of a page")
-                self.paged[gi].pool.free(page, request)
-            raise
+        self._check(native.lib().jh_cache_reserve(self._ptr, self._h(request), start, n))
 
     def commit(self, request: Hashable, length: int) -> List[Tuple[int, int]]:
         """The request now holds `length` positions. Returns the (group, page) pairs given back
         because a window has passed them."""
-        rc = self.requests[request]
-        if length < rc.length:
-            raise ValueError(f"commit cannot shorten a request ({rc.length} -> {length}); use truncate")
-        rc.length = length
-        released = []
-        for gi, g in enumerate(self.paged):
-            if length > len(rc.tables[gi]) * self.page_size:
-                raise PageBookkeepingError(f"request {request!r} committed {length} positions beyond its pages")
-            for i in range(min(self._first_needed_page(g, length), len(rc.tables[gi]))):
-                page = rc.tables[gi][i]
-                if page != RELEASED:
-                    g.pool.free(page, request)
-                    rc.tables[gi][i] = RELEASED
-                    released.append((gi, page))
-        if released:
-            rc.epoch = next(self._epochs)
-        return released
+        cap = 2 * (self.num_pages if any(g.need.window > 0 for g in self.paged) else 0) * max(1, len(self.paged))
+        buf = (ctypes.c_int * max(2, cap))()
+        count = ctypes.c_int()
+        self._check(native.lib().jh_cache_commit(self._ptr, self._h(request), length, buf, cap, ctypes.byref(count)))
+        return [(buf[2 * i], buf[2 * i + 1]) for i in range(count.value)]
 
     def truncate(self, request: Hashable, length: int) -> None:
         """Forget positions >= length: pages wholly past it go back (KvSequence.java:149-157). A windowed
         group cannot go back behind pages it has given up already."""
-        rc = self.requests[request]
-        if length >= rc.length:
-            return
-        keep = -(-length // self.page_size)
-        for gi, g in enumerate(self.paged):    # first look, then touch: a refused rewind changes nothing
-            if g.need.window > 0 and self._first_needed_page(g, rc.length) > self._first_needed_page(g, length):
-                if any(p == RELEASED for p in rc.tables[gi][self._first_needed_page(g, length):keep]):
-                    raise ValueError(f"request {request!r}: a windowed group has released pages that a rewind "
-                                     f"to {length} needs; recompute from the start")
-        rc.epoch = next(self._epochs)
-        for gi, g in enumerate(self.paged):
-            table = rc.tables[gi]
-            while len(table) > keep:
-                page = table.pop()
-                if page != RELEASED:
-                    g.pool.free(page, request)
-        rc.length = length
+        self._check(native.lib().jh_cache_truncate(self._ptr, self._h(request), length))
 
     def trim(self, request: Hashable) -> None:
         """Give back pages reserved beyond the committed length (a step that was reserved but did not run)."""
-        rc = self.requests[request]
-        keep = -(-rc.length // self.page_size)
-        rc.epoch = next(self._epochs)
-        for gi, g in enumerate(self.paged):
-            table = rc.tables[gi]
-            while len(table) > keep:
-                page = table.pop()
-                if page != RELEASED:
-                    g.pool.free(page, request)
+        self._check(native.lib().jh_cache_trim(self._ptr, self._h(request)))
 
     def close(self, request: Hashable) -> None:
-        rc = self.requests.pop(request)
-        for gi, g in enumerate(self.paged):
-            for page in rc.tables[gi]:
-                if page != RELEASED:
-                    g.pool.free(page, request)
-            rc.tables[gi] = []
-        self.slots.free(rc.state_slot, request)
+        code = native.lib().jh_cache_close(self._ptr, self._h(request))
+        if code == 4:
+            raise KeyError(request)
+        self._check(code)
+        self._names.forget(request)
 
     def table(self, request: Hashable, group: int) -> List[int]:
-        return self.requests[request].tables[group]
+        """A copy of the request's block table of one group."""
+        entries = self._info(request)[3][group]
+        buf = (ctypes.c_int * max(1, entries))()
+        self._check(native.lib().jh_cache_table(self._ptr, self._h(request), group, buf, entries))
+        return list(buf[:entries])
 
     def table_epoch(self, request: Hashable) -> int:
         """A number that is new whenever the request's tables changed otherwise than by growing at their end
         (and for every opening of a request): who keeps a copy of a table may extend it while this stays."""
-        return self.requests[request].epoch
+        return self._info(request)[2]
 
     def state_slot(self, request: Hashable) -> int:
-        return self.requests[request].state_slot
+        return self._info(request)[1]
+
+    # ---- a whole step at once (the runner's path) --------------------------------------------------------------
+    def handles(self, requests: Sequence[Hashable]) -> List[int]:
+        return [self._names.handle(r) for r in requests]
 
     # ---- books ---------------------------------------------------------------------------------------------
     def free_pages(self) -> List[int]:
-        return [g.pool.num_free for g in self.paged]
+        native.lib().jh_cache_free_pages(self._ptr, self._ints)
+        return [self._ints[g] for g in range(len(self.paged))]
 
     def check(self) -> None:
         """No page lost, none held twice: every held page is in exactly one table, once, under its holder."""
-        self.slots.check()
-        for gi, g in enumerate(self.paged):
-            g.pool.check()
-            seen = {}
-            for rc in self.requests.values():
-                for page in rc.tables[gi]:
-                    if page == RELEASED:
-                        continue
-                    if page in seen:
-                        raise PageBookkeepingError(f"group {gi}: page {page} is in the tables of {seen[page]!r} "
-                                                   f"and {rc.request!r}")
-                    seen[page] = rc.request
-                    if g.pool.holder(page) != rc.request:
-                        raise PageBookkeepingError(f"group {gi}: page {page} is in the table of {rc.request!r} "
-                                                   f"but held by {g.pool.holder(page)!r}")
-            if len(seen) != g.pool.num_held:
-                raise PageBookkeepingError(f"group {gi}: {g.pool.num_held} pages are held, {len(seen)} are in tables")
+        self._check(native.lib().jh_cache_check(self._ptr))

@@ -1,4 +1,5 @@
-"""Builds the kernel library from the .cu files beside this file, in-tree, with nvcc for sm_100a.
+"""Builds the kernel library from the .cu files beside this file, in-tree, with nvcc for sm_100a, and the
+host library (csrc/host/*.cpp: pools, block tables, batch tables) with the system's C++ compiler.
 
 The library is compiled at the first call that needs it and again whenever a source, a
 header or a flag changes (a hash of all of them is kept beside the library). Each .cu
@@ -150,5 +151,61 @@ def ensure_built(force: bool = False, verbose: bool = False) -> Path:
         return lib
 
 
+# ---- the host library: plain C++, no CUDA ---------------------------------------------------------------------------
+
+HOST_LIB_NAME = "libjllm_host.so"
+HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall"]
+
+
+def find_cxx() -> str:
+    for cand in (os.environ.get("JLLM_B200_CXX"), os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"),
+                 shutil.which("clang++")):
+        if cand and (Path(cand).is_file() or shutil.which(cand)):
+            return cand
+    raise BuildError("no C++ compiler found (looked at $JLLM_B200_CXX, $CXX, g++, c++, clang++): the host side of the "
+                     "engine (page pools, block tables, batch tables) cannot be built")
+
+
+def host_sources() -> list:
+    return sorted((CSRC / "host").glob("*.cpp"))
+
+
+def ensure_host_built(force: bool = False) -> Path:
+    """The C++ library of the host-side bookkeeping (csrc/host/*.cpp), built with the system's C++ compiler; it needs
+    neither nvcc nor a GPU."""
+    with _lock:
+        out_dir = build_dir()
+        lib, stamp = out_dir / HOST_LIB_NAME, out_dir / "host_stamp.json"
+        try:
+            cxx = find_cxx()
+        except BuildError:
+            if lib.is_file() and not force:
+                return lib
+            raise
+        h = hashlib.sha256()
+        h.update((cxx + " ".join(HOST_FLAGS)).encode())
+        for p in host_sources():
+            h.update(p.name.encode())
+            h.update(p.read_bytes())
+        want = h.hexdigest()
+        if not force and lib.is_file() and stamp.is_file():
+            try:
+                if json.loads(stamp.read_text()).get("fingerprint") == want:
+                    return lib
+            except (json.JSONDecodeError, OSError):
+                pass
+        t0 = time.time()
+        tmp = out_dir / (HOST_LIB_NAME + f".tmp{os.getpid()}")
+        proc = subprocess.run([cxx, *HOST_FLAGS, "-o", str(tmp), *[str(p) for p in host_sources()]],
+                              capture_output=True, text=True)
+        if proc.returncode != 0:
+            raise BuildError(f"{cxx} failed on the host library:\n{proc.stdout}\n{proc.stderr}")
+        os.replace(tmp, lib)
+        stamp.write_text(json.dumps({"fingerprint": want, "seconds": round(time.time() - t0, 1)}))
+        _say(f"built {lib.name} in {time.time() - t0:.0f} s")
+        return lib
+
+
 if __name__ == "__main__":
+    print(ensure_host_built(force="--force" in sys.argv))
     print(ensure_built(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -8,7 +8,8 @@ segments are laid side by side, segment after segment; row-wise kernels see one 
 
 `BatchBuilder` owns one pinned host buffer and one device buffer of fixed size, so the
 device addresses never change (a captured decode step can be replayed) and a step costs
-two host-to-device copies.
+two host-to-device copies. The tables are packed by the C++ host library straight from the
+cache's books into the pinned buffers.
 """
 from __future__ import annotations
 
@@ -17,6 +18,8 @@ from typing import Hashable, List, Sequence
 
 import numpy as np
 import torch
+
+from ..cache import native
 
 
 @dataclass
@@ -76,8 +79,40 @@ class BatchBuilder:
         self._copied = torch.cuda.Event() if torch.cuda.is_available() else None
         self._np_small = self._host_small.numpy()
         self._np_tables = self._host_tables.numpy().reshape(max(1, G), S, max_blocks)
-        # what each row of the host tables holds: (request, its table epoch, entries written)
-        self._table_rows = [[None] * S for _ in range(max(1, G))]
+        self._p_small, self._p_tables = self._host_small.data_ptr(), self._host_tables.data_ptr()
+        # the arguments of the library's calls, kept between steps
+        arrays = {"ids": np.zeros(S, np.int64), "starts": np.zeros(S, np.int32), "counts": np.zeros(S, np.int32),
+                  "want_at": np.zeros(S + 1, np.int32), "tokens": np.zeros(R, np.int32), "wants": np.zeros(R, np.int32),
+                  "info": np.zeros(8, np.int32), "lengths": np.zeros(S, np.int32),
+                  "released": np.zeros(2 * max(64, S * max_blocks * max(1, G)), np.int32)}
+        self._args = dict(arrays)
+        self._args.update({"p_" + k: v.ctypes.data for k, v in arrays.items()})
+        self._builder = native.lib().jh_builder_new(R, S, max_blocks, G, page_size)
+        self._built = 0
+        self._views = {}
+
+    def commit(self, cache) -> list:
+        """After the step that was built last has been launched: every segment's request now holds its new
+        positions. Returns the (group, page) pairs that windows have passed."""
+        a, S = self._args, self._built
+        np.add(a["starts"][:S], a["counts"][:S], out=a["lengths"][:S])
+        cap = a["released"].shape[0]
+        code = native.lib().jh_step_commit(cache._ptr, S, a["p_ids"], a["p_lengths"], a["p_released"], cap, a["p_info"])
+        if code:
+            native.check(code, cache._names)
+        n = int(a["info"][0])
+        if 2 * n > cap:
+            raise RuntimeError(f"{n} pages released in one step, room for {cap // 2}")
+        rel = a["released"]
+        return [(int(rel[2 * i]), int(rel[2 * i + 1])) for i in range(n)]
+
+    def __del__(self):
+        try:
+            if getattr(self, "_builder", None):
+                native.lib().jh_builder_delete(self._builder)
+                self._builder = None
+        except Exception:        # the interpreter is shutting down and the module is gone
+            pass
 
     def bytes_per_step(self, segments: int) -> int:
         """Bytes a step with `segments` segments copies from pinned host memory to the device."""
@@ -92,8 +127,10 @@ class BatchBuilder:
         S = self.max_segments
         return buf[base + i * S: base + (i + 1) * S]
 
-    def build(self, segments: List[Segment], cache, vocab: int) -> StepBatch:
-        """Fills the tables from the segments and the cache manager's block tables (pages must be reserved)."""
+    def build(self, segments: List[Segment], cache, vocab: int, reserve: bool = False) -> StepBatch:
+        """Fills the tables from the segments and the cache manager's block tables. With `reserve` the pages of
+        every segment are taken first, all or none (else they must have been reserved). Reserving and packing are
+        the host library's (`jh_step_reserve`, `jh_builder_build`): two calls per step."""
         if self._copied is not None:
             self._copied.synchronize()     # the last step's copies have left the pinned buffers
         S = len(segments)
@@ -101,69 +138,58 @@ class BatchBuilder:
             raise ValueError("a step needs at least one segment")
         if S > self.max_segments:
             raise ValueError(f"{S} segments in one step, the engine was made for {self.max_segments}")
-        rows = sum(len(s.tokens) for s in segments)
-        if rows > self.max_rows:
-            raise ValueError(f"{rows} rows in one step, the engine was made for {self.max_rows}")
-        seen = set()
-        h = self._np_small
-        tok, pos, rseg, lrows = (self._row_view(h, i) for i in range(4))
-        slot_views = [self._row_view(h, 4 + g) for g in range(self.groups)]
-        sstart, slen, skv, sslot = (self._seg_view(h, i) for i in range(4))
-        r = 0
-        n_want = 0
-        max_q = max_kv = 0
-        multi_segments, multi_rows, ordered = 0, 0, True
-        ps = self.page_size
+        a = self._args
+        ids, starts, counts, want_at = a["ids"], a["starts"], a["counts"], a["want_at"]
+        handles = cache.handles([seg.request for seg in segments])
+        n_tok = n_want = 0
+        single = True
         for si, seg in enumerate(segments):
             n = len(seg.tokens)
-            if n < 1:
-                raise ValueError(f"request {seg.request!r}: a segment needs at least one token")
-            if seg.request in seen:
-                raise ValueError(f"request {seg.request!r} appears twice in one step")
-            seen.add(seg.request)
-            if n == 1:
-                t0 = int(seg.tokens[0])
-                if not 0 <= t0 < vocab:
-                    raise ValueError(f"request {seg.request!r}: token id outside [0, {vocab})")
-                tok[r], pos[r], rseg[r] = t0, seg.start, si
+            ids[si], starts[si], counts[si], want_at[si] = handles[si], seg.start, n, n_want
+            n_tok += n
+            n_want += len(seg.want)
+            single = single and n == 1
+        want_at[S] = n_want
+        if n_tok > self.max_rows:
+            raise ValueError(f"{n_tok} rows in one step, the engine was made for {self.max_rows}")
+        tokens, wants = a["tokens"], a["wants"]
+        if n_want > wants.shape[0]:
+            raise ValueError(f"{n_want} wanted places in one step, the engine was made for {wants.shape[0]}")
+        try:
+            if single:
+                for si, seg in enumerate(segments):
+                    tokens[si] = seg.tokens[0]
             else:
-                t = np.asarray(seg.tokens, dtype=np.int64)
-                if t.min() < 0 or t.max() >= vocab:
-                    raise ValueError(f"request {seg.request!r}: token id outside [0, {vocab})")
-                tok[r:r + n] = t
-                p = np.arange(seg.start, seg.start + n, dtype=np.int32)
-                pos[r:r + n] = p
-                rseg[r:r + n] = si
-            sstart[si], slen[si], skv[si] = r, n, seg.start + n
-            sslot[si] = cache.state_slot(seg.request)
+                at = 0
+                for seg in segments:
+                    n = len(seg.tokens)
+                    tokens[at:at + n] = seg.tokens
+                    at += n
+        except OverflowError:
+            raise ValueError(f"a token id outside [0, {vocab})") from None
+        at = 0
+        for seg in segments:
             for w in seg.want:
-                if not 0 <= w < n:
-                    raise ValueError(f"request {seg.request!r}: wanted place {w} is outside its {n} tokens")
-                lrows[n_want] = r + w
-                n_want += 1
-            epoch = cache.table_epoch(seg.request) if self.groups else 0
-            for g in range(self.groups):
-                table = cache.table(seg.request, g)
-                nb = len(table)
-                if nb > self.max_blocks:
-                    raise ValueError(f"request {seg.request!r} holds {nb} pages, tables have {self.max_blocks} columns")
-                # the row of the host table: only what the request's table grew by since this row was last
-                # written for it, if nothing else about the table changed (its epoch)
-                held = self._table_rows[g][si]
-                lo = held[2] if held is not None and held[0] == seg.request and held[1] == epoch and held[2] <= nb else 0
-                if lo < nb:
-                    self._np_tables[g, si, lo:nb] = table[lo:nb]
-                self._table_rows[g][si] = (seg.request, epoch, nb)
-                if n == 1:
-                    slot_views[g][r] = table[seg.start // ps] * ps + seg.start % ps
-                else:
-                    slot_views[g][r:r + n] = self._np_tables[g, si, :nb][p // ps] * ps + p % ps
-            if n > 1:
-                ordered = ordered and multi_segments == si       # no single-row segment came before it
-                multi_segments, multi_rows = si + 1, r + n
-            r += n
-            max_q = max(max_q, n)
-            max_kv = max(max_kv, seg.start + n)
+                wants[at] = w
+                at += 1
+        info = a["info"]
+        if reserve:
+            code = native.lib().jh_step_reserve(cache._ptr, S, a["p_ids"], a["p_starts"], a["p_counts"])
+            if code:
+                native.check(code, cache._names)
+        code = native.lib().jh_builder_build(self._builder, cache._ptr, S, a["p_ids"], a["p_starts"], a["p_counts"],
+                                             a["p_tokens"], a["p_want_at"], a["p_wants"], vocab, self._p_small,
+                                             self._p_tables, a["p_info"])
+        if code:
+            if reserve:
+                for seg in segments:
+                    if cache.is_open(seg.request):
+                        cache.trim(seg.request)
+            native.check(code, cache._names)
+        rows, n_want, max_q, max_kv, multi_segments, multi_rows = (int(v) for v in info[:6])
+        self._built = S
+        h = self._np_small
+        sstart, sslot = self._seg_view(h, 0), self._seg_view(h, 3)
         self._dev_small.copy_(self._host_small, non_blocking=True)
         MB = self.max_blocks
         for g in range(self.groups):
@@ -171,17 +197,21 @@ class BatchBuilder:
             self._dev_tables[lo:lo + S * MB].copy_(self._host_tables[lo:lo + S * MB], non_blocking=True)
         if self._copied is not None:
             self._copied.record()
-        d = self._dev_small
-        dt = self._dev_tables.view(max(1, self.groups), self.max_segments, MB)
+        views = self._views.get((rows, S, n_want))
+        if views is None:       # the device views of a shape are made once: slicing tensors is the dearest thing left here
+            d = self._dev_small
+            dt = self._dev_tables.view(max(1, self.groups), self.max_segments, MB)
+            views = dict(
+                token_ids=self._row_view(d, 0)[:rows], positions=self._row_view(d, 1)[:rows],
+                row_seg=self._row_view(d, 2)[:rows], logit_rows=self._row_view(d, 3)[:n_want],
+                slots=[self._row_view(d, 4 + g)[:rows] for g in range(self.groups)],
+                seg_start=self._seg_view(d, 0)[:S], seg_len=self._seg_view(d, 1)[:S],
+                seg_kv_len=self._seg_view(d, 2)[:S], state_slots=self._seg_view(d, 3)[:S],
+                block_tables=[dt[g, :S] for g in range(self.groups)])
+            if len(self._views) < 4096:
+                self._views[(rows, S, n_want)] = views
         return StepBatch(
-            rows=rows, segments=list(segments),
-            token_ids=self._row_view(d, 0)[:rows], positions=self._row_view(d, 1)[:rows],
-            row_seg=self._row_view(d, 2)[:rows], logit_rows=self._row_view(d, 3)[:n_want],
-            slots=[self._row_view(d, 4 + g)[:rows] for g in range(self.groups)],
-            seg_start=self._seg_view(d, 0)[:S], seg_len=self._seg_view(d, 1)[:S], seg_kv_len=self._seg_view(d, 2)[:S],
-            state_slots=self._seg_view(d, 3)[:S],
-            block_tables=[dt[g, :S] for g in range(self.groups)],
-            num_wanted=n_want, max_q_len=max_q, max_kv_len=max_kv,
+            rows=rows, segments=list(segments), num_wanted=n_want, max_q_len=max_q, max_kv_len=max_kv,
             kv_bucket=max(1, min(32, max_kv // 256, -(-296 // rows))),
-            multi_segments=multi_segments if ordered else -1, multi_rows=multi_rows,
-            host_seg_start=[int(v) for v in sstart[:S]], host_state_slots=[int(v) for v in sslot[:S]])
+            multi_segments=multi_segments, multi_rows=multi_rows,
+            host_seg_start=sstart[:S].tolist(), host_state_slots=sslot[:S].tolist(), **views)

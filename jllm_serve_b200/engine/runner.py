@@ -137,7 +137,7 @@ class ModelRunner:
         return out
 
     def _step_once(self, segments, logits_out):
-        opened, reserved = [], []
+        opened = []
         try:
             for seg in segments:
                 if seg.start + len(seg.tokens) > self.ctx:
@@ -146,20 +146,15 @@ class ModelRunner:
                 if not self.cache.is_open(seg.request):
                     self.cache.open(seg.request)
                     opened.append(seg.request)
-                self.cache.reserve(seg.request, seg.start, len(seg.tokens))
-                reserved.append(seg.request)
-            batch = self.builder.build(segments, self.cache, self.vocab)
+            batch = self.builder.build(segments, self.cache, self.vocab, reserve=True)   # all pages or none
         except Exception:
-            for r in reserved:
-                self.cache.trim(r)
             for r in opened:
                 self.cache.close(r)
             raise
         logits = self._run_model(batch, logits_out)
-        for seg in segments:
-            released = self.cache.commit(seg.request, seg.start + len(seg.tokens))
-            if self.poison:
-                self._poison(released)
+        released = self.builder.commit(self.cache)
+        if self.poison:
+            self._poison(released)
         self.steps += 1
         self.last_batch = batch
         return logits

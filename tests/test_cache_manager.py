@@ -193,9 +193,8 @@ def test_batch_tables_follow_the_requests_tables():
             if not m.is_open(r):
                 m.open(r)
                 lengths[r] = 0
-            m.reserve(r, lengths[r], n_of[r])
             segs.append(Segment(r, [1] * n_of[r], lengths[r], [n_of[r] - 1]))
-        batch = b.build(segs, m, vocab=10)
+        batch = b.build(segs, m, vocab=10, reserve=True)
         row = 0
         for si, r in enumerate(reqs):
             table = m.table(r, 0)
@@ -205,7 +204,7 @@ def test_batch_tables_follow_the_requests_tables():
                 assert int(batch.slots[0][row]) == table[p // 2] * 2 + p % 2
                 row += 1
             lengths[r] += n_of[r]
-            m.commit(r, lengths[r])
+        assert b.commit(m) == [] and all(m.length(r) == lengths[r] for r in reqs)
 
     step(["a", "b"], {"a": 5, "b": 3})
     for _ in range(6):
