@@ -310,7 +310,7 @@ def end_to_end(engine, batch: int, steps: int, warmup: int, vocab: int):
     engine.run_until_done()
     for i in ids:
         engine.scheduler.finished.pop(i, None)
-    return {"value": round(done / dt, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * batch,
+    return {"value": round(done / dt, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * engine.sampler.max_rows,
             "ms_per_step": round(dt / steps * 1e3, 4)}
 
 

@@ -255,8 +255,7 @@ class Scheduler:
             if not seg.wants_logits:
                 continue
             tok = next(it)
-            stops = self.eos | set(r.params.stop_token_ids)
-            if tok in stops and not r.params.ignore_eos:
+            if not r.params.ignore_eos and (tok in self.eos or tok in r.params.stop_token_ids):
                 reason = "stop"            # the stop token is not part of the output
             else:
                 r.output.append(tok)

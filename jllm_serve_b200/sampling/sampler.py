@@ -42,6 +42,7 @@ class Sampler:
         self._u = torch.empty(max_rows, dtype=torch.float64, device=device)
         self._out = torch.empty(max_rows, dtype=torch.int32, device=device)
         self._out_host = torch.empty(max_rows, dtype=torch.int32).pin_memory()
+        self._out_host_np = self._out_host.numpy()
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], uniforms: Sequence[float]) -> List[int]:
         """logits float32 [n, vocab] on the device -> n token ids on the host."""
@@ -62,6 +63,6 @@ class Sampler:
             self._u.copy_(self._host_u, non_blocking=True)
             ops.sample(logits, self._f[0, :n], self._k[:n], self._f[1, :n], self._f[2, :n], self._u[:n], out,
                        self.sample_vocab)
-        self._out_host[:n].copy_(out, non_blocking=True)
+        self._out_host.copy_(self._out, non_blocking=True)     # all of the small buffer: no views to make
         torch.cuda.current_stream().synchronize()
-        return self._out_host[:n].tolist()
+        return self._out_host_np[:n].tolist()
