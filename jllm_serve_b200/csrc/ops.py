@@ -88,8 +88,6 @@ class _Signatures:
     jllm_gemm_small_m = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, I, I, P]
     jllm_gemm_tcgen05 = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, I, P, ctypes.c_longlong, I, I, P]
     jllm_gemm_tcgen05_error = []
-    jllm_gemm_skinny = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, P, ctypes.c_longlong, I, P]
-    jllm_gemm_skinny_error = []
     jllm_attention_plain = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P]
     jllm_attention_decode = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
     jllm_attention_decode_fused = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P, P]
@@ -181,41 +179,21 @@ def gemm_bf16_fits(a, w, out) -> bool:
 
 
 # Which kernel takes a product of M rows (measured on the layer shapes of an 8B model): up to SMALL_M_ROWS the
-# mma.sync weight stream; above, the 128 x 256 tcgen05 tiles. The swapped-operand tcgen05 kernel (gemm_skinny)
-# is correct for M <= 128 but was slower than both on those shapes; JLLM_B200_SKINNY_ROWS switches it in.
+# mma.sync weight stream; above, the tcgen05 tiles (128 x 256, narrower when the rows are few).
 SMALL_M_ROWS = int(__import__("os").environ.get("JLLM_B200_SMALL_M_ROWS", "32"))
-SKINNY_ROWS = int(__import__("os").environ.get("JLLM_B200_SKINNY_ROWS", "0"))
 WIDE_ROWS = int(__import__("os").environ.get("JLLM_B200_WIDE_ROWS", "16384"))
-_skinny_workspaces = {}
+_workspaces = {}
 # counters of up to 65,536 tiles, then two parked 128 x 256 partial tiles for each of up to 160 blocks
 STREAM_WORKSPACE_FLOATS = 65536 + 160 * 2 * 128 * 256
 
 
-def skinny_workspace(device, floats: int = 8 << 20) -> torch.Tensor:
-    """Zero-initialised workspace of the skinny product (tile counters, then split partials), one per device,
+def gemm_workspace(device, floats: int = 8 << 20) -> torch.Tensor:
+    """Zero-initialised workspace of a streamed product (tile counters, then parked partial tiles), one per device,
     grown when a product needs more; earlier ones stay alive because captured graphs may point at them."""
-    held = _skinny_workspaces.setdefault(device, [])
+    held = _workspaces.setdefault(device, [])
     if not held or held[-1].numel() < floats:
         held.append(torch.zeros(max(floats, 8 << 20), dtype=torch.float32, device=device))
     return held[-1]
-
-
-def gemm_skinny(a, w, out, bias=None, accumulate=False, swiglu=False, force_splits: int = 0) -> None:
-    """Up to 128 rows: weights as the M side of tcgen05.mma, streamed through a deep TMA ring, K split over blocks."""
-    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.stride(-1) == 1
-    M, K = a.shape
-    N = w.shape[0]
-    tiles, tok_pad = -(-N // 128), (16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128)
-    ws = skinny_workspace(a.device, 4096 + tiles * 32 * tok_pad * 128 if force_splits else
-                          4096 + tiles * min(32, max(1, -(-296 // tiles))) * tok_pad * 128)
-    _call("jllm_gemm_skinny", a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), _p(bias),
-          _DT[bias.dtype] if bias is not None else F32, out.data_ptr(), _DT[out.dtype], out.stride(0), int(accumulate),
-          M, N, K, int(swiglu), ws.data_ptr(), ws.numel(), int(force_splits), _stream())
-
-
-def gemm_skinny_error() -> int:
-    return library().jllm_gemm_skinny_error()
-
 
 
 def gemm_bf16(a, w, out, bias=None, accumulate=False, swiglu=False) -> None:
@@ -227,8 +205,6 @@ def gemm_bf16(a, w, out, bias=None, accumulate=False, swiglu=False) -> None:
     wide = M >= 16 and N >= WIDE_ROWS and _tcgen05_fits(a, w)
     if M <= SMALL_M_ROWS and _small_m_fits(a, w) and not wide:
         return gemm_small_m(a, w, out, bias, accumulate, swiglu=swiglu)
-    if a.shape[0] <= SKINNY_ROWS and _tcgen05_fits(a, w) and w.shape[0] <= 4096 * 128:
-        return gemm_skinny(a, w, out, bias, accumulate, swiglu)
     if _tcgen05_fits(a, w):
         return gemm_tcgen05(a, w, out, bias, accumulate, swiglu=swiglu)
     raise KernelError("the tensor-core matrix product is not built for this shape")
@@ -241,7 +217,7 @@ def gemm_tcgen05(a, w, out, bias=None, accumulate=False, max_blocks: int = 0, sw
     of a last, partly filled round are streamed (stream-K: equal runs of (tile, k block) pairs per block, partial
     tiles meeting in a workspace); off by default (measured slower on 8B layer shapes)."""
     assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.stride(-1) == 1
-    ws = skinny_workspace(a.device, STREAM_WORKSPACE_FLOATS) if stream_mode > 0 else None
+    ws = gemm_workspace(a.device, STREAM_WORKSPACE_FLOATS) if stream_mode > 0 else None
     _call("jllm_gemm_tcgen05", a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), _p(bias),
           _DT[bias.dtype] if bias is not None else F32, out.data_ptr(), _DT[out.dtype], out.stride(0),
           int(accumulate), a.shape[0], w.shape[0], a.shape[1], int(max_blocks), int(swiglu), _p(ws),
@@ -253,7 +229,6 @@ def check_kernel_errors() -> None:
     not to be trusted). Reads three words from the device, so it synchronises."""
     lib = library()
     raised = {name: code for name, code in (("gemm_tcgen05", lib.jllm_gemm_tcgen05_error()),
-                                            ("gemm_skinny", lib.jllm_gemm_skinny_error()),
                                             ("attention_prefill_tc", lib.jllm_attention_prefill_tc_error())) if code}
     if raised:
         raise KernelError("a bounded wait ran out inside " + ", ".join(f"{k} (code {v})" for k, v in raised.items()))

@@ -171,31 +171,6 @@ def test_gemm_tcgen05_tile_widths(ops, M, N, K, width):
     assert ops.gemm_tcgen05_error() == 0
 
 
-@pytest.mark.parametrize("M", [1, 7, 16, 17, 40, 64, 100, 128])
-@pytest.mark.parametrize("N,K,splits", [(8, 8, 0), (517, 72, 0), (6144, 4096, 0), (4096, 12288, 0), (300, 4096, 7),
-                                        (1000, 200, 3), (4096, 4096, 1), (151936, 256, 0)])
-def test_gemm_skinny(ops, M, N, K, splits):
-    a, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=1, scale=0.05)
-    bias = rnd(N, dtype=torch.bfloat16, seed=2)
-    want = gemm_want(a, w, bias)
-    out = torch.full((M, N), float("nan"), device=DEV)
-    ops.gemm_skinny(a, w, out, bias, force_splits=splits)
-    assert ops.gemm_skinny_error() == 0
-    tol = 1e-4 * math.sqrt(K) * 0.05
-    assert torch.allclose(out.cpu(), want, rtol=1e-4, atol=tol), float((out.cpu() - want).abs().max())
-    base = rnd(M, N, seed=3)
-    acc = base.clone()
-    ops.gemm_skinny(a, w, acc, None, accumulate=True, force_splits=splits)
-    again = base.clone()
-    ops.gemm_skinny(a, w, again, None, accumulate=True, force_splits=splits)
-    assert torch.allclose(acc.cpu(), gemm_want(a, w, None, base), rtol=1e-4, atol=tol)
-    assert torch.equal(acc, again)                    # split partials are added in slice order: bit-identical runs
-    out16 = torch.zeros(M, N + 8, dtype=torch.bfloat16, device=DEV)
-    ops.gemm_skinny(a, w, out16[:, :N], force_splits=splits)
-    assert torch.allclose(out16[:, :N].float().cpu(), gemm_want(a, w), rtol=2 ** -7, atol=2e-3)
-    assert float(out16[:, N:].abs().max()) == 0 and ops.gemm_skinny_error() == 0
-
-
 @pytest.mark.parametrize("M", [1, 8, 20, 33, 200])
 @pytest.mark.parametrize("hidden,K", [(8, 8), (200, 72), (12288, 4096), (1000, 136)])
 def test_gemm_with_swiglu_epilogue(ops, M, hidden, K):
