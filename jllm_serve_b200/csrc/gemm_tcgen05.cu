@@ -128,20 +128,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            uint32_t it = 0;
+            // (stage and phase are counted, not divided out: with narrow tiles this one thread's instructions per
+            // k block are what the product waits for)
+            int s = 0;
+            uint32_t parity = 1, dst = base;
             bool ok = true;
             Walk walk = first_unit();
             int tile, lo, hi;
             while (ok && next_unit(walk, tile, lo, hi)) {
                 const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
-                for (int kb = lo; kb < hi; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    const uint32_t parity = ((it / STAGES) & 1u) ^ 1u;
+                for (int kb = lo; kb < hi; ++kb) {
                     if (!mbar_wait(empty_bar(s), parity, abort_flag)) { ok = false; break; }
-                    const uint32_t dst = base + s * STAGE_BYTES;
                     mbar_expect_tx(full_bar(s), STAGE_BYTES);
                     tma_load_2d(dst, &map_a, kb * BK, m0, full_bar(s));
                     tma_load_2d(dst + A_BYTES, &map_w, kb * BK, n0, full_bar(s));
+                    dst += STAGE_BYTES;
+                    if (++s == STAGES) { s = 0; parity ^= 1u; dst = base; }
                 }
             }
             if (!ok) { *abort_flag = 1; atomicExch(error_word, 1); }
@@ -149,7 +151,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            uint32_t it = 0, local_tile = 0;
+            uint32_t local_tile = 0, parity = 0, a_addr = base;
+            int s = 0;
             bool ok = true;
             Walk walk = first_unit();
             int tile, lo, hi;
@@ -158,11 +161,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if (!mbar_wait(acc_empty_bar(buf), ((local_tile >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
                 tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + buf * BN;
-                for (int kb = lo; kb < hi; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    if (!mbar_wait(full_bar(s), (it / STAGES) & 1u, abort_flag)) { ok = false; break; }
+                for (int kb = lo; kb < hi; ++kb) {
+                    if (!mbar_wait(full_bar(s), parity, abort_flag)) { ok = false; break; }
                     tcgen05_fence_after();
-                    const uint32_t a_addr = base + s * STAGE_BYTES, b_addr = a_addr + A_BYTES;
+                    const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k) {
                         // 16 bfloat16 = 32 bytes further along k inside the 128-byte swizzled rows
@@ -170,6 +172,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                          (kb > lo || k > 0) ? 1u : 0u);
                     }
                     tcgen05_commit(empty_bar(s));   // arrives when the MMAs above have read the stage
+                    a_addr += STAGE_BYTES;
+                    if (++s == STAGES) { s = 0; parity ^= 1u; a_addr = base; }
                 }
                 if (ok) tcgen05_commit(acc_full_bar(buf));
             }
