@@ -4,7 +4,7 @@
 // products, narrower when the rows are few):
 //   * warp 0 (one lane) is the TMA producer: for every 64-wide k block it waits for a free stage and
 //     issues two tiled bulk copies (a 128 x 64 tile of A, a 256 x 64 tile of W) into 128-byte-swizzled
-//     shared memory, completing on the stage's "full" mbarrier (no cluster multicast anywhere);
+//     shared memory, completing on the stage's "full" mbarrier (every block loads its own copy);
 //   * warp 1 (one lane) issues the MMAs: 4 x tcgen05.mma (M 128, N 256, K 16) per k block, operands
 //     described by shared-memory descriptors, the float32 accumulator in tensor memory (TMEM);
 //     tcgen05.commit frees the stage, and after the last k block signals "accumulator full";
