@@ -285,40 +285,10 @@ JLLM_EXPORT long long jllm_attention_decode_scratch_floats(int rows, int heads, 
     return splits <= 1 ? 0 : (long long)rows * heads * splits * (head_dim + 2);
 }
 
-namespace {
-int attention_decode_impl(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out, int out_stride,
-                          const int* row_seg, const int* row_pos, const int* block_tables, int table_stride, int rows,
-                          int heads, int kv_heads, int head_dim, int page_size, int window, float scale, int splits,
-                          float* scratch, int* counters, cudaStream_t stream);
-}
-
 JLLM_EXPORT int jllm_attention_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
                                       int out_stride, const int* row_seg, const int* row_pos, const int* block_tables,
                                       int table_stride, int rows, int heads, int kv_heads, int head_dim, int page_size,
                                       int window, float scale, int splits, float* scratch, cudaStream_t stream) {
-    return attention_decode_impl(q, q_stride, k_cache, v_cache, out, out_stride, row_seg, row_pos, block_tables,
-                                 table_stride, rows, heads, kv_heads, head_dim, page_size, window, scale, splits, scratch,
-                                 nullptr, stream);
-}
-
-// As jllm_attention_decode, with rows * kv_heads counter words that are zero before the first call (every call
-// leaves them zero): for head sizes 64, 128 and 256 the splits of a row are then combined inside the attention
-// kernel by whichever block finishes last, and the combine kernel is not launched.
-JLLM_EXPORT int jllm_attention_decode_fused(const void* q, int q_stride, const void* k_cache, const void* v_cache,
-                                            void* out, int out_stride, const int* row_seg, const int* row_pos,
-                                            const int* block_tables, int table_stride, int rows, int heads, int kv_heads,
-                                            int head_dim, int page_size, int window, float scale, int splits,
-                                            float* scratch, int* counters, cudaStream_t stream) {
-    return attention_decode_impl(q, q_stride, k_cache, v_cache, out, out_stride, row_seg, row_pos, block_tables,
-                                 table_stride, rows, heads, kv_heads, head_dim, page_size, window, scale, splits, scratch,
-                                 counters, stream);
-}
-
-namespace {
-int attention_decode_impl(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out, int out_stride,
-                          const int* row_seg, const int* row_pos, const int* block_tables, int table_stride, int rows,
-                          int heads, int kv_heads, int head_dim, int page_size, int window, float scale, int splits,
-                          float* scratch, int* counters, cudaStream_t stream) {
     JLLM_REQUIRE(rows >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && page_size > 0,
                  "attention_decode: rows=%d heads=%d kv_heads=%d page_size=%d", rows, heads, kv_heads, page_size);
     JLLM_REQUIRE(head_dim % 16 == 0 && head_dim >= 16 && head_dim <= 256,
@@ -340,11 +310,11 @@ int attention_decode_impl(const void* q, int q_stride, const void* k_cache, cons
         // the common head sizes stream the cache through a shared-memory ring (attention_decode_staged.cuh)
 #define JLLM_STAGED(HD)                                                                                             \
     staged::launch<HD>(q, q_stride, k_cache, v_cache, out, out_stride, row_seg, row_pos, block_tables, table_stride, \
-                       rows, heads, kv_heads, page_size, window, scale_log2, splits, part_o, part_ml, counters, stream)
+                       rows, heads, kv_heads, page_size, window, scale_log2, splits, part_o, part_ml, stream)
         if (head_dim == 64) JLLM_STAGED(64); else if (head_dim == 128) JLLM_STAGED(128); else JLLM_STAGED(256);
 #undef JLLM_STAGED
         int rc2 = jllm_check_launch("attention_decode_staged");
-        if (rc2 != JLLM_OK || splits == 1 || counters != nullptr) return rc2;
+        if (rc2 != JLLM_OK || splits == 1) return rc2;
         jllm_launch(attention_combine_kernel, dim3(rows, heads), dim3(128), 0, stream, true, (const float*)part_o,
                     (const float*)part_ml, (__nv_bfloat16*)out, out_stride, heads, head_dim, splits);
         return jllm_check_launch("attention_combine");
@@ -366,7 +336,6 @@ int attention_decode_impl(const void* q, int q_stride, const void* k_cache, cons
                                                                    heads, head_dim, splits);
     return jllm_check_launch("attention_combine");
 }
-}  // namespace
 
 // ---------------------------------------------------------------------------------------------------
 // The same attention with the split scratch inside the library: see attention_decode_static.h.

@@ -8,8 +8,7 @@
 // every tile: S = Q K^T and O += P V with mma.sync.m16n8k16 from ldmatrix fragments, the G query heads
 // of the kv head being the 16 rows of the M side (rows beyond G are zero). Each warp keeps its own online
 // softmax state; the four are merged at the end exactly as in the direct kernel, and the per-split
-// partials go to the same scratch layout; they are combined by a kernel of their own or, when the caller gives
-// counters, by the block of each (row, kv head) that finishes last.
+// partials go to the same scratch layout and combine kernel.
 #pragma once
 
 namespace staged {
@@ -46,30 +45,21 @@ __device__ __forceinline__ void wait_group() { asm volatile("cp.async.wait_group
 template <int HD>
 __device__ __forceinline__ uint32_t off(int r, int c) { return (uint32_t)((r * (HD / 8) + (c ^ (r & 7))) * 16); }
 
+// The keys [first + tile_lo * 64, ...) of n_tiles tiles of one (row, kv head), for the G query heads of that kv head:
+// the result goes to `out` if these are all the row's keys (`whole`), else as a partial (sums, maximum, weight) for
+// head j of the group to part_o + j * o_stride and part_ml + j * ml_stride. All threads of the block call it.
 template <int HD>
-__global__ void __launch_bounds__(THREADS)
-attention_decode_staged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
-                               const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
-                               __nv_bfloat16* __restrict__ out, int out_stride, const int* __restrict__ row_seg,
-                               const int* __restrict__ row_pos, const int* __restrict__ block_tables, int table_stride,
-                               int heads, int kv_heads, int page_size, int window, float scale_log2, int splits,
-                               float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters) {
+__device__ __forceinline__ void attend(uint8_t* smem_raw, const __nv_bfloat16* __restrict__ q, int q_stride,
+                                       const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
+                                       __nv_bfloat16* __restrict__ out, int out_stride, const int* __restrict__ table,
+                                       int heads, int kv_heads, int page_size, float scale_log2, int r, int kvh, int P,
+                                       int first, int tile_lo, int n_tiles, bool whole, float* __restrict__ part_o,
+                                       size_t o_stride, float* __restrict__ part_ml, size_t ml_stride) {
     constexpr int CHUNKS = HD / 8, TILE_BYTES = TILE * HD * 2, STAGE_BYTES = 2 * TILE_BYTES;
-    extern __shared__ __align__(128) uint8_t smem_raw[];
     const uint32_t s_q = (uint32_t)__cvta_generic_to_shared(smem_raw);
     const uint32_t s_kv = s_q + 16 * HD * 2;
-    const int r = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int G = heads / kv_heads;
-    pdl_wait();      // the newest key and value of every row were written by the kernel before this one
-    pdl_trigger();
-    const int P = row_pos[r];
-    const int first = window > 0 ? max(0, P + 1 - window) : 0;
-    const int tiles_total = (P + 1 - first + TILE - 1) / TILE;
-    const int tiles_per_split = (tiles_total + splits - 1) / splits;
-    const int tile_lo = split * tiles_per_split, tile_hi = min(tiles_total, tile_lo + tiles_per_split);
-    const int n_tiles = max(0, tile_hi - tile_lo);
-    const int* table = block_tables + (size_t)row_seg[r] * table_stride;
     const size_t page_stride = (size_t)kv_heads * page_size * HD;
     const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
 
@@ -235,66 +225,49 @@ attention_decode_staged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
             const float mw = sml[(w * 16 + row) * 2];
             ll += mw == -INFINITY ? 0.f : sml[(w * 16 + row) * 2 + 1] * exp2f(mw - mm);
         }
-        const int head = kvh * G + row;
-        if (splits == 1) {
-            out[(size_t)r * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc / ll);
+        if (whole) {
+            out[(size_t)r * out_stride + (size_t)(kvh * G + row) * HD + d] = __float2bfloat16_rn(acc / ll);
         } else {
-            const size_t slot = ((size_t)r * heads + head) * splits + split;
-            part_o[slot * HD + d] = acc;
+            part_o[(size_t)row * o_stride + d] = acc;
             if (d == 0) {
-                part_ml[slot * 2 + 0] = mm;
-                part_ml[slot * 2 + 1] = ll;
+                part_ml[(size_t)row * ml_stride + 0] = mm;
+                part_ml[(size_t)row * ml_stride + 1] = ll;
             }
         }
     }
-    if (splits == 1 || counters == nullptr) return;
-    // ---- the block that finishes last among the splits of this (row, kv head) combines them ----
-    // Every block publishes its partials and counts itself; who finds all others counted reads the partials of all
-    // splits in split order (so the result does not depend on who came last) and writes the output. The counter
-    // goes back to zero for the next launch. Nobody waits for anybody.
-    __shared__ int s_last;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence();
-        const int seen = atomicAdd(&counters[r * kv_heads + kvh], 1);
-        s_last = seen == splits - 1;
-        if (s_last) counters[r * kv_heads + kvh] = 0;
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    float* weight = reinterpret_cast<float*>(smem_raw);              // [16][32] weights of the splits, then [16] 1 / sum
-    float* inv_total = weight + 16 * 32;
-    for (int row = warp; row < G; row += WARPS) {
-        const size_t slot0 = ((size_t)r * heads + kvh * G + row) * splits;
-        const float ms = lane < splits ? __ldcg(part_ml + (slot0 + lane) * 2) : -INFINITY;
-        const float ls = lane < splits ? __ldcg(part_ml + (slot0 + lane) * 2 + 1) : 0.f;
-        float M = ms;
-#pragma unroll
-        for (int o2 = 16; o2 > 0; o2 >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o2));
-        const float w = ms == -INFINITY ? 0.f : exp2f(ms - M);
-        weight[row * 32 + lane] = w;
-        float L = 0.f;
-        for (int i = 0; i < splits; ++i) L += __shfl_sync(0xffffffffu, ls * w, i);
-        if (lane == 0) inv_total[row] = 1.f / L;
-    }
-    __syncthreads();
-    for (int e = threadIdx.x; e < G * HD; e += THREADS) {
-        const int row = e / HD, d = e % HD;
-        const int head = kvh * G + row;
-        const size_t slot0 = ((size_t)r * heads + head) * splits;
-        float acc = 0.f;
-#pragma unroll 8
-        for (int s2 = 0; s2 < splits; ++s2) acc += __ldcg(part_o + (slot0 + s2) * HD + d) * weight[row * 32 + s2];
-        out[(size_t)r * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc * inv_total[row]);
-    }
+}
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS)
+attention_decode_staged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
+                               const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
+                               __nv_bfloat16* __restrict__ out, int out_stride, const int* __restrict__ row_seg,
+                               const int* __restrict__ row_pos, const int* __restrict__ block_tables, int table_stride,
+                               int heads, int kv_heads, int page_size, int window, float scale_log2, int splits,
+                               float* __restrict__ part_o, float* __restrict__ part_ml) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    const int r = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int G = heads / kv_heads;
+    pdl_wait();      // the newest key and value of every row were written by the kernel before this one
+    pdl_trigger();
+    const int P = row_pos[r];
+    const int first = window > 0 ? max(0, P + 1 - window) : 0;
+    const int tiles_total = (P + 1 - first + TILE - 1) / TILE;
+    const int tiles_per_split = (tiles_total + splits - 1) / splits;
+    const int tile_lo = split * tiles_per_split, tile_hi = min(tiles_total, tile_lo + tiles_per_split);
+    const int* table = block_tables + (size_t)row_seg[r] * table_stride;
+    // partials: (row, head, split) -> head_dim sums in part_o, (maximum, weight) in part_ml
+    const size_t slot = ((size_t)r * heads + kvh * G) * splits + split;
+    attend<HD>(smem_raw, q, q_stride, k_cache, v_cache, out, out_stride, table, heads, kv_heads, page_size, scale_log2, r,
+               kvh, P, first, tile_lo, max(0, tile_hi - tile_lo), splits == 1, part_o + slot * HD, (size_t)splits * HD,
+               part_ml + slot * 2, (size_t)splits * 2);
 }
 
 template <int HD>
 void launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out, int out_stride,
             const int* row_seg, const int* row_pos, const int* block_tables, int table_stride, int rows, int heads,
             int kv_heads, int page_size, int window, float scale_log2, int splits, float* part_o, float* part_ml,
-            int* counters, cudaStream_t stream) {
+            cudaStream_t stream) {
     const size_t stage_bytes = (size_t)STAGES * 2 * TILE * HD * 2;
     const size_t merge_bytes = ((size_t)WARPS * 16 * HD + WARPS * 16 * 2) * sizeof(float);
     const size_t smem = 16 * HD * 2 + (stage_bytes > merge_bytes ? stage_bytes : merge_bytes);
@@ -303,7 +276,7 @@ void launch(const void* q, int q_stride, const void* k_cache, const void* v_cach
     jllm_launch(kern, dim3(rows, kv_heads, splits), dim3(THREADS), smem, stream, true,
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
         (__nv_bfloat16*)out, out_stride, row_seg, row_pos, block_tables, table_stride, heads, kv_heads, page_size,
-        window, scale_log2, splits, part_o, part_ml, counters);
+        window, scale_log2, splits, part_o, part_ml);
 }
 
 }  // namespace staged

@@ -90,7 +90,6 @@ class _Signatures:
     jllm_gemm_tcgen05_error = []
     jllm_attention_plain = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P]
     jllm_attention_decode = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
-    jllm_attention_decode_fused = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P, P]
     jllm_attention_prefill = [P, I, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P]
     jllm_attention_prefill_tc = [P, I, P, P, ctypes.c_longlong, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P]
     jllm_attention_prefill_tc_error = []
@@ -263,36 +262,13 @@ def attention_decode_scratch_floats(rows, heads, head_dim, splits) -> int:
     return 0 if splits <= 1 else rows * heads * splits * (head_dim + 2)
 
 
-_decode_counters = {}
-# measured on the 8B decode step: 5.36 ms with the fused combine, 5.27 ms with the combine kernel (the last block's
-# dependent loads cost more than the launch they save), so the separate kernel is the default
-FUSED_COMBINE = int(__import__("os").environ.get("JLLM_B200_FUSED_COMBINE", "0"))
-
-
-def decode_counters(device, words: int) -> torch.Tensor:
-    """Zeroed counter words of the fused split combine, one tensor per device (the kernels leave them zero);
-    earlier ones stay alive because captured graphs may point at them."""
-    held = _decode_counters.setdefault(device, [])
-    if not held or held[-1].numel() < words:
-        held.append(torch.zeros(max(words, 1 << 14), dtype=torch.int32, device=device))
-    return held[-1]
-
-
 def attention_decode(q, k_cache, v_cache, out, row_seg, row_pos, block_tables, rows, heads, kv_heads, head_dim,
-                     page_size, window, scale, splits=1, scratch=None, fused: bool | None = None) -> None:
-    """One query position per row; the key range of a row may be split over `splits` blocks (needs scratch). The
-    splits are combined by the block that finishes last (`fused`, head sizes 64, 128, 256) or by a second kernel."""
+                     page_size, window, scale, splits=1, scratch=None) -> None:
+    """One query position per row; the key range of a row may be split over `splits` blocks (needs scratch)."""
     if splits > 1:
         assert scratch is not None and scratch.dtype == torch.float32 and \
             scratch.numel() >= attention_decode_scratch_floats(rows, heads, head_dim, splits)
-    fused = (bool(FUSED_COMBINE) if fused is None else fused) and splits > 1 and head_dim in (64, 128, 256)
     global launch_count
-    if fused:
-        counters = decode_counters(q.device, rows * kv_heads)
-        return _call("jllm_attention_decode_fused", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
-                     out.data_ptr(), out.stride(0), row_seg.data_ptr(), row_pos.data_ptr(), block_tables.data_ptr(),
-                     block_tables.stride(0), rows, heads, kv_heads, head_dim, page_size, int(window), float(scale),
-                     int(splits), _p(scratch), counters.data_ptr(), _stream())
     launch_count += 1 if splits > 1 else 0     # the combine kernel
     _call("jllm_attention_decode", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
           out.stride(0), row_seg.data_ptr(), row_pos.data_ptr(), block_tables.data_ptr(), block_tables.stride(0),
