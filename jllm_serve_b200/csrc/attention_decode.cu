@@ -337,6 +337,43 @@ JLLM_EXPORT int jllm_attention_decode(const void* q, int q_stride, const void* k
     return jllm_check_launch("attention_combine");
 }
 
+// Floats of scratch of the evenly dealt variant: (head_dim + 2) per head of a kv head, for every pair and every block.
+JLLM_EXPORT long long jllm_attention_decode_flat_scratch_floats(int rows, int heads, int kv_heads, int head_dim, int blocks) {
+    return ((long long)rows * kv_heads + blocks) * (heads / kv_heads) * (head_dim + 2);
+}
+
+// Decode attention with the key tiles of all (row, kv head) pairs dealt out evenly over `blocks` blocks (head sizes
+// 64, 128, 256; at most 1,024 rows; at most 62 blocks per kv head, so that a pair's tiles fall to at most 64 blocks).
+JLLM_EXPORT int jllm_attention_decode_flat(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
+                                           int out_stride, const int* row_seg, const int* row_pos, const int* block_tables,
+                                           int table_stride, int rows, int heads, int kv_heads, int head_dim, int page_size,
+                                           int window, float scale, int blocks, float* scratch, cudaStream_t stream) {
+    JLLM_REQUIRE(rows >= 0 && rows <= staged::FLAT_MAX_ROWS && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 &&
+                     page_size > 0 && heads / kv_heads <= 16,
+                 "attention_decode_flat: rows=%d (at most %d) heads=%d kv_heads=%d page_size=%d", rows,
+                 staged::FLAT_MAX_ROWS, heads, kv_heads, page_size);
+    JLLM_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256, "attention_decode_flat: head_dim=%d is not 64, 128 or 256",
+                 head_dim);
+    JLLM_REQUIRE(q_stride % 8 == 0 && ((uintptr_t)q % 16) == 0 && ((uintptr_t)k_cache % 16) == 0 &&
+                     ((uintptr_t)v_cache % 16) == 0,
+                 "attention_decode_flat: q, K and V must be 16-byte aligned (q_stride=%d)", q_stride);
+    // a pair holds at most 1 / kv_heads of all tiles, so its tiles fall to at most blocks / kv_heads + 2 blocks: 64 at most
+    JLLM_REQUIRE(blocks >= 1 && blocks <= 62 * kv_heads && scratch != nullptr,
+                 "attention_decode_flat: %d blocks with %d kv heads (at most 62 per kv head), scratch %p", blocks, kv_heads,
+                 (void*)scratch);
+    if (rows == 0) return JLLM_OK;
+    const int G = heads / kv_heads;
+    float* part_o = scratch;
+    float* part_ml = scratch + ((size_t)rows * kv_heads + blocks) * G * head_dim;
+    const float scale_log2 = scale * LOG2E;
+#define JLLM_FLAT(HD)                                                                                                  \
+    staged::launch_flat<HD>(q, q_stride, k_cache, v_cache, out, out_stride, row_seg, row_pos, block_tables, table_stride, \
+                            rows, heads, kv_heads, page_size, window, scale_log2, blocks, part_o, part_ml, stream)
+    if (head_dim == 64) JLLM_FLAT(64); else if (head_dim == 128) JLLM_FLAT(128); else JLLM_FLAT(256);
+#undef JLLM_FLAT
+    return jllm_check_launch("attention_decode_flat");
+}
+
 // ---------------------------------------------------------------------------------------------------
 // The same attention with the split scratch inside the library: see attention_decode_static.h.
 // ---------------------------------------------------------------------------------------------------

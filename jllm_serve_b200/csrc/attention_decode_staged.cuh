@@ -263,6 +263,149 @@ attention_decode_staged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
                part_ml + slot * 2, (size_t)splits * 2);
 }
 
+// ---- the same attention with the key tiles of all (row, kv head) pairs dealt out evenly ----------------------------------
+// With one block per (row, kv head, split) the blocks of a step rarely fill the SMs evenly (8 rows x 8 kv heads x 4
+// splits are 256 blocks for 296 places: most SMs carry two blocks, the rest one, and the step waits for the former).
+// Here the key tiles of all pairs, in the order (row, kv head, tile), are cut into one equal run per block, as many
+// blocks as there are places. A block's run may end inside a pair and go on in the next one: for every stretch it
+// writes a partial (sums, maximum, weight) at slot pair + block, a number no other stretch has, and the combine kernel
+// adds the partials of a pair in block order.
+constexpr int FLAT_MAX_ROWS = 1024;
+
+// s_cum[i] = key tiles of rows 0 .. i - 1 (of one kv head each); called by warp 0
+__device__ __forceinline__ void flat_prefix(const int* __restrict__ row_pos, int rows, int window, int* s_cum) {
+    const int lane = threadIdx.x & 31;
+    int carry = 0;
+    for (int base = 0; base < rows; base += 32) {
+        const int r = base + lane;
+        int incl = 0;
+        if (r < rows) {
+            const int P = row_pos[r], first = window > 0 ? max(0, P + 1 - window) : 0;
+            incl = (P + 1 - first + TILE - 1) / TILE;
+        }
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += v;
+        }
+        if (r < rows) s_cum[r + 1] = carry + incl;
+        carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) s_cum[0] = 0;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS)
+attention_decode_flat_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_cache,
+                             const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out, int out_stride,
+                             const int* __restrict__ row_seg, const int* __restrict__ row_pos,
+                             const int* __restrict__ block_tables, int table_stride, int rows, int heads, int kv_heads,
+                             int page_size, int window, float scale_log2, float* __restrict__ part_o,
+                             float* __restrict__ part_ml) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    __shared__ int s_cum[FLAT_MAX_ROWS + 1];
+    pdl_wait();
+    pdl_trigger();
+    if (threadIdx.x < 32) flat_prefix(row_pos, rows, window, s_cum);
+    __syncthreads();
+    const int G = heads / kv_heads;
+    const long long all = (long long)kv_heads * s_cum[rows];
+    long long at = all * blockIdx.x / gridDim.x;
+    const long long end = all * (blockIdx.x + 1) / gridDim.x;
+    int lo = 0, hi = rows - 1;                       // the row whose tiles hold position `at`
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if ((long long)kv_heads * s_cum[mid + 1] <= at) lo = mid + 1; else hi = mid;
+    }
+    int r = lo;
+    while (at < end) {
+        while ((long long)kv_heads * s_cum[r + 1] <= at) ++r;
+        const int tiles_r = s_cum[r + 1] - s_cum[r];
+        const long long in_row = at - (long long)kv_heads * s_cum[r];
+        const int kvh = (int)(in_row / tiles_r), tile_lo = (int)(in_row % tiles_r);
+        const int n = (int)min((long long)(tiles_r - tile_lo), end - at);
+        const int P = row_pos[r], first = window > 0 ? max(0, P + 1 - window) : 0;
+        const size_t slot = (size_t)r * kv_heads + kvh + blockIdx.x;
+        attend<HD>(smem_raw, q, q_stride, k_cache, v_cache, out, out_stride, block_tables + (size_t)row_seg[r] * table_stride,
+                   heads, kv_heads, page_size, scale_log2, r, kvh, P, first, tile_lo, n, false, part_o + slot * G * HD,
+                   (size_t)HD, part_ml + slot * G * 2, (size_t)2);
+        at += n;
+        __syncthreads();                              // shared memory is the next stretch's
+    }
+}
+
+// out[r, head] from the partials of the blocks whose runs met the pair (r, kv head of the head), in block order
+__global__ void attention_combine_flat_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                              __nv_bfloat16* __restrict__ out, int out_stride,
+                                              const int* __restrict__ row_pos, int rows, int heads, int kv_heads,
+                                              int head_dim, int window, int blocks) {
+    constexpr int MAX_PARTS = 64;
+    __shared__ int s_cum[FLAT_MAX_ROWS + 1];
+    __shared__ float weight[MAX_PARTS];
+    __shared__ float inv_total;
+    pdl_wait();
+    pdl_trigger();
+    if (threadIdx.x < 32) flat_prefix(row_pos, rows, window, s_cum);
+    __syncthreads();
+    const int r = blockIdx.x, head = blockIdx.y, G = heads / kv_heads, kvh = head / G, row = head % G;
+    const long long all = (long long)kv_heads * s_cum[rows];
+    const int tiles_r = s_cum[r + 1] - s_cum[r];
+    const long long start = (long long)kv_heads * s_cum[r] + (long long)kvh * tiles_r;
+    auto block_of = [&](long long tile) { return (int)(((tile + 1) * blocks + all - 1) / all - 1); };
+    const int b_first = block_of(start), parts = min(MAX_PARTS, block_of(start + tiles_r - 1) - b_first + 1);
+    const size_t slot0 = (size_t)r * kv_heads + kvh + b_first;      // the slots of the pair's parts follow one another
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        float ms[2], ls[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int p = lane + 32 * h;
+            // a block between the first and the last whose run is empty (more blocks than tiles) wrote nothing
+            const long long lo = all * (b_first + p) / blocks, hi = all * (b_first + p + 1) / blocks;
+            const bool wrote = p < parts && max(lo, start) < min(hi, start + tiles_r);
+            ms[h] = wrote ? part_ml[((slot0 + p) * G + row) * 2] : -INFINITY;
+            ls[h] = wrote ? part_ml[((slot0 + p) * G + row) * 2 + 1] : 0.f;
+        }
+        float M = fmaxf(ms[0], ms[1]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        float L = 0.f;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const float w = ms[h] == -INFINITY ? 0.f : exp2f(ms[h] - M);
+            weight[lane + 32 * h] = w;
+            for (int i = 0; i < 32 && i + 32 * h < parts; ++i) L += __shfl_sync(0xffffffffu, ls[h] * w, i);
+        }
+        if (lane == 0) inv_total = 1.f / L;
+    }
+    __syncthreads();
+    const float inv = inv_total;
+    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+        float acc = 0.f;
+#pragma unroll 4
+        for (int p = 0; p < parts; ++p)
+            if (weight[p] != 0.f) acc += part_o[((slot0 + p) * G + row) * head_dim + d] * weight[p];
+        out[(size_t)r * out_stride + (size_t)head * head_dim + d] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+template <int HD>
+void launch_flat(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out, int out_stride,
+                 const int* row_seg, const int* row_pos, const int* block_tables, int table_stride, int rows, int heads,
+                 int kv_heads, int page_size, int window, float scale_log2, int blocks, float* part_o, float* part_ml,
+                 cudaStream_t stream) {
+    const size_t stage_bytes = (size_t)STAGES * 2 * TILE * HD * 2;
+    const size_t merge_bytes = ((size_t)WARPS * 16 * HD + WARPS * 16 * 2) * sizeof(float);
+    const size_t smem = 16 * HD * 2 + (stage_bytes > merge_bytes ? stage_bytes : merge_bytes);
+    auto kern = attention_decode_flat_kernel<HD>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    jllm_launch(kern, dim3(blocks), dim3(THREADS), smem, stream, true, (const __nv_bfloat16*)q, q_stride,
+                (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out, out_stride, row_seg,
+                row_pos, block_tables, table_stride, rows, heads, kv_heads, page_size, window, scale_log2, part_o, part_ml);
+    jllm_launch(attention_combine_flat_kernel, dim3(rows, heads), dim3(128), 0, stream, true, (const float*)part_o,
+                (const float*)part_ml, (__nv_bfloat16*)out, out_stride, row_pos, rows, heads, kv_heads, HD, window, blocks);
+}
+
 template <int HD>
 void launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out, int out_stride,
             const int* row_seg, const int* row_pos, const int* block_tables, int table_stride, int rows, int heads,

@@ -90,6 +90,7 @@ class _Signatures:
     jllm_gemm_tcgen05_error = []
     jllm_attention_plain = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P]
     jllm_attention_decode = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
+    jllm_attention_decode_flat = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
     jllm_attention_prefill = [P, I, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P]
     jllm_attention_prefill_tc = [P, I, P, P, ctypes.c_longlong, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P]
     jllm_attention_prefill_tc_error = []
@@ -275,14 +276,62 @@ def attention_decode(q, k_cache, v_cache, out, row_seg, row_pos, block_tables, r
           rows, heads, kv_heads, head_dim, page_size, int(window), float(scale), int(splits), _p(scratch), _stream())
 
 
+def attention_decode_flat_scratch_floats(rows, heads, kv_heads, head_dim, blocks) -> int:
+    return (rows * kv_heads + blocks) * (heads // kv_heads) * (head_dim + 2)
+
+
+def attention_decode_flat(q, k_cache, v_cache, out, row_seg, row_pos, block_tables, rows, heads, kv_heads, head_dim,
+                          page_size, window, scale, blocks, scratch) -> None:
+    """One query position per row, the key tiles of all (row, kv head) pairs dealt out evenly over `blocks` blocks."""
+    assert scratch.dtype == torch.float32 and \
+        scratch.numel() >= attention_decode_flat_scratch_floats(rows, heads, kv_heads, head_dim, blocks)
+    global launch_count
+    launch_count += 1                          # the combine kernel
+    _call("jllm_attention_decode_flat", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+          out.stride(0), row_seg.data_ptr(), row_pos.data_ptr(), block_tables.data_ptr(), block_tables.stride(0),
+          rows, heads, kv_heads, head_dim, page_size, int(window), float(scale), int(blocks), scratch.data_ptr(), _stream())
+
+
+FLAT_DECODE = int(__import__("os").environ.get("JLLM_B200_FLAT_DECODE", "1"))
+
+
+def decode_plan(rows, kv_heads, kv_bucket, heads, head_dim, scratch, resident_blocks: int = 2 * 148):
+    """("flat", blocks) or ("split", splits) for a decode step's attention: one block per (row, kv head, split), or,
+    when there are more (row, kv head) pairs than places for blocks and they would fill the last round of places
+    badly (by less than 93 %), the key tiles of all pairs dealt out evenly over as many blocks as there are places
+    (measured at context 4,096: 188 against 195 us at batch 64; with fewer pairs than places the even deal was the
+    slower one, 34.5 against 32.4 us at batch 8). `kv_bucket` = the longest request's keys in units of 256."""
+    splits = decode_splits(rows, kv_heads, kv_bucket, heads, head_dim, scratch, resident_blocks)
+    uniform = rows * kv_heads * splits
+    rounds = -(-uniform // resident_blocks)
+    if (not FLAT_DECODE or scratch is None or head_dim not in (64, 128, 256) or rows > 1024
+            or rows * kv_heads <= resident_blocks or uniform * 100 >= rounds * resident_blocks * 93):
+        return "split", splits
+    tiles = rows * kv_heads * kv_bucket * 4                    # 64 keys a tile; an upper bound, like the bucket
+    blocks = max(1, min(resident_blocks, 62 * kv_heads, tiles // 2))
+    if attention_decode_flat_scratch_floats(rows, heads, kv_heads, head_dim, blocks) > scratch.numel():
+        return "split", splits
+    return "flat", blocks
+
+
+def _attention_decode_rows(q, k_cache, v_cache, out, row_seg, positions, table, rows, heads, kv_heads, head_dim, page_size,
+                           window, scale, kv_bucket, scratch):
+    bucket = kv_bucket if window <= 0 else max(1, min(kv_bucket, window // 256))
+    how, n = decode_plan(rows, kv_heads, bucket, heads, head_dim, scratch)
+    if how == "flat":
+        return attention_decode_flat(q, k_cache, v_cache, out, row_seg, positions, table, rows, heads, kv_heads, head_dim,
+                                     page_size, window, scale, n, scratch)
+    return attention_decode(q, k_cache, v_cache, out, row_seg, positions, table, rows, heads, kv_heads, head_dim, page_size,
+                            window, scale, n, scratch)
+
+
 def attention(q, k_cache, v_cache, out, batch, group, heads, kv_heads, head_dim, page_size, window, scale,
               scratch=None) -> None:
     """Causal attention of every row of the batch over its own request's cached keys and values."""
     if batch.decode_only and attention_decode_fits(q.dtype, heads, kv_heads, head_dim):
-        bucket = batch.kv_bucket if window <= 0 else max(1, min(batch.kv_bucket, window // 256))
-        splits = decode_splits(batch.rows, kv_heads, bucket, heads, head_dim, scratch)
-        return attention_decode(q, k_cache, v_cache, out, batch.row_seg, batch.positions, batch.block_tables[group],
-                                batch.rows, heads, kv_heads, head_dim, page_size, window, scale, splits, scratch)
+        return _attention_decode_rows(q, k_cache, v_cache, out, batch.row_seg, batch.positions, batch.block_tables[group],
+                                      batch.rows, heads, kv_heads, head_dim, page_size, window, scale, batch.kv_bucket,
+                                      scratch)
     if q.dtype == torch.bfloat16 and attention_prefill_fits(head_dim):
         # prompt portions through the flash kernel; the single rows riding beside them (the scheduler puts them
         # last) through the decode kernel, which shares every key among the query heads of a kv head
@@ -295,11 +344,9 @@ def attention(q, k_cache, v_cache, out, batch, group, heads, kv_heads, head_dim,
                               window, scale)
         if mr < batch.rows:
             n = batch.rows - mr
-            bucket = batch.kv_bucket if window <= 0 else max(1, min(batch.kv_bucket, window // 256))
-            splits = decode_splits(n, kv_heads, bucket, heads, head_dim, scratch)
-            attention_decode(q[mr:], k_cache, v_cache, out[mr:], batch.row_seg[mr:], batch.positions[mr:],
-                             batch.block_tables[group], n, heads, kv_heads, head_dim, page_size, window, scale, splits,
-                             scratch)
+            _attention_decode_rows(q[mr:], k_cache, v_cache, out[mr:], batch.row_seg[mr:], batch.positions[mr:],
+                                   batch.block_tables[group], n, heads, kv_heads, head_dim, page_size, window, scale,
+                                   batch.kv_bucket, scratch)
         return
     attention_plain(q, q.stride(0), k_cache, v_cache, out, batch.row_seg, batch.positions, batch.block_tables[group],
                     batch.rows, heads, kv_heads, head_dim, page_size, window, scale)

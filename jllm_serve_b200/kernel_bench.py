@@ -69,10 +69,15 @@ def main() -> int:
     seg = torch.arange(M, dtype=torch.int32, device=dev)
     pos = torch.full((M,), ctx - 1, dtype=torch.int32, device=dev)
     scratch = torch.empty(2 << 20, device=dev)
-    splits = ops.decode_splits(M, Hkv, max(1, min(32, ctx // 256)), H, hd, scratch)
-    case(f"decode attention ({splits} splits)",
-         lambda i: ops.attention_decode(q, caches[i][0], caches[i][1], out, seg, pos, tables, M, H, Hkv, hd, page, 0,
-                                        1 / math.sqrt(hd), splits, scratch), n_caches, M * ctx * Hkv * hd * 4)
+    how, n = ops.decode_plan(M, Hkv, max(1, min(32, ctx // 256, -(-296 // M))), H, hd, scratch)
+    if how == "flat":
+        case(f"decode attention (dealt out over {n} blocks)",
+             lambda i: ops.attention_decode_flat(q, caches[i][0], caches[i][1], out, seg, pos, tables, M, H, Hkv, hd, page, 0,
+                                                 1 / math.sqrt(hd), n, scratch), n_caches, M * ctx * Hkv * hd * 4)
+    else:
+        case(f"decode attention ({n} splits)",
+             lambda i: ops.attention_decode(q, caches[i][0], caches[i][1], out, seg, pos, tables, M, H, Hkv, hd, page, 0,
+                                            1 / math.sqrt(hd), n, scratch), n_caches, M * ctx * Hkv * hd * 4)
     ctx_pad = max(ctx, T) + page
     ang = torch.outer(torch.arange(ctx_pad, dtype=torch.float64), 1e6 ** (-torch.arange(hd // 2, dtype=torch.float64) * 2 / hd))
     cos_t, sin_t = ang.cos().float().to(dev), ang.sin().float().to(dev)

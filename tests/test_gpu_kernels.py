@@ -353,6 +353,28 @@ def test_attention_decode(ops, H, Hkv, hd, page, window, splits):
         assert torch.allclose(out1.float().cpu(), want1, rtol=2e-2, atol=2e-2), float((out1.float().cpu() - want1).abs().max())
 
 
+@pytest.mark.parametrize("blocks", [1, 7, 40, 296])
+@pytest.mark.parametrize("H,Hkv,hd,page,window", [(32, 8, 128, 16, 0), (16, 1, 256, 16, 0), (8, 2, 64, 16, 100),
+                                                   (6, 3, 64, 8, 21), (4, 4, 128, 4, 0)])
+def test_attention_decode_dealt_out_evenly(ops, H, Hkv, hd, page, window, blocks):
+    """The key tiles of all (row, kv head) pairs in equal runs over `blocks` blocks: runs that end inside a pair,
+    pairs that spread over many blocks, blocks with nothing to do."""
+    lens, scale = [1, 17, 64, 131, 300, 1000, 65, 2], 1.0 / math.sqrt(hd)
+    blocks = min(blocks, 62 * Hkv)
+    for far in (False, True):
+        q, kc, vc, out, rseg, rpos, tables, want, q_lens = attention_case(ops, torch.bfloat16, H, Hkv, hd, page, lens,
+                                                                          window, scale, far)
+        last = torch.tensor([sum(q_lens[:i + 1]) - 1 for i in range(len(lens))], device=DEV)
+        q1, rseg1, rpos1, want1 = q[last].contiguous(), rseg[last].contiguous(), rpos[last].contiguous(), want[last.cpu()]
+        out1 = torch.full_like(q1, float("nan"))
+        scratch = torch.full((ops.attention_decode_flat_scratch_floats(len(lens), H, Hkv, hd, blocks),), float("nan"),
+                             device=DEV)
+        ops.attention_decode_flat(q1, kc, vc, out1, rseg1, rpos1, tables, len(lens), H, Hkv, hd, page, window, scale,
+                                  blocks, scratch)
+        assert torch.isfinite(out1).all()
+        assert torch.allclose(out1.float().cpu(), want1, rtol=2e-2, atol=2e-2), float((out1.float().cpu() - want1).abs().max())
+
+
 # ---- choosing tokens -----------------------------------------------------------------------------------------
 
 def test_argmax_lowest_index_among_equals(ops):
