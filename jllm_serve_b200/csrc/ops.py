@@ -54,13 +54,18 @@ def require_device() -> None:
 launch_count = 0   # kernels of this library launched (or captured into a graph) by this process
 
 
+_functions = {}
+
+
 def _call(name, *args):
     global launch_count
-    lib = library()
+    fn = _functions.get(name)
+    if fn is None:
+        fn = _functions[name] = getattr(library(), name)
     launch_count += 1
-    code = getattr(lib, name)(*args)
+    code = fn(*args)
     if code != 0:
-        raise KernelError(f"{name} failed ({code}): {lib.jllm_last_error().decode(errors='replace')}")
+        raise KernelError(f"{name} failed ({code}): {library().jllm_last_error().decode(errors='replace')}")
 
 
 def set_dependent_launch(on: bool) -> None:
@@ -68,7 +73,13 @@ def set_dependent_launch(on: bool) -> None:
     library().jllm_set_pdl(int(on))
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream():
+    """The current CUDA stream's handle (asked for at every launch: the quick way if torch has it)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
