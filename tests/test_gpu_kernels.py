@@ -375,6 +375,26 @@ def test_attention_decode_dealt_out_evenly(ops, H, Hkv, hd, page, window, blocks
         assert torch.allclose(out1.float().cpu(), want1, rtol=2e-2, atol=2e-2), float((out1.float().cpu() - want1).abs().max())
 
 
+def test_attention_decode_dealt_out_evenly_random_shapes(ops):
+    """Random numbers of rows, lengths and blocks: the evenly dealt kernel against one block per (row, kv head)."""
+    import random
+    rng = random.Random(7)
+    H, Hkv, hd, page, scale = 8, 2, 128, 16, 1.0 / math.sqrt(128)
+    for trial in range(12):
+        lens = [rng.choice([1, 2, 63, 64, 65, rng.randint(1, 900)]) for _ in range(rng.randint(1, 12))]
+        blocks = rng.randint(1, 62 * Hkv)
+        q, kc, vc, out, rseg, rpos, tables, want, q_lens = attention_case(ops, torch.bfloat16, H, Hkv, hd, page, lens, 0,
+                                                                          scale, False, [1] * len(lens))
+        a, b = torch.full_like(q, float("nan")), torch.full_like(q, float("nan"))
+        scratch = torch.full((ops.attention_decode_flat_scratch_floats(len(lens), H, Hkv, hd, blocks),), float("nan"),
+                             device=DEV)
+        ops.attention_decode_flat(q, kc, vc, a, rseg, rpos, tables, len(lens), H, Hkv, hd, page, 0, scale, blocks, scratch)
+        ops.attention_decode(q, kc, vc, b, rseg, rpos, tables, len(lens), H, Hkv, hd, page, 0, scale)
+        assert torch.isfinite(a).all(), (trial, lens, blocks)
+        assert torch.allclose(a.float(), b.float(), rtol=2e-2, atol=1e-2), (trial, lens, blocks)
+        assert torch.allclose(a.float().cpu(), want, rtol=2e-2, atol=2e-2), (trial, lens, blocks)
+
+
 # ---- choosing tokens -----------------------------------------------------------------------------------------
 
 def test_argmax_lowest_index_among_equals(ops):
