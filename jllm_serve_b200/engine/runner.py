@@ -88,6 +88,7 @@ class ModelRunner:
         self.graph_safe = all(getattr(b.mixer, "graph_safe", True) and getattr(b.feed_forward, "graph_safe", True)
                               for b in getattr(self.model, "blocks", []))
         self._graphs, self._graph_seen, self._static_logits, self._graph_kernels = {}, set(), None, {}
+        self.max_graphs = 256          # captured decode shapes kept (rows x wanted rows x key-range bucket)
 
     def _allocate(self, shape, kind):
         if kind == "kv":
@@ -183,6 +184,9 @@ class ModelRunner:
             before = ops.launch_count
             with torch.cuda.graph(graph):
                 self.model.forward(batch, self.cache, self._static_logits)
+            if len(self._graphs) >= self.max_graphs:       # the shape that was captured first makes room
+                oldest = next(iter(self._graphs))
+                del self._graphs[oldest], self._graph_kernels[oldest]
             self._graphs[key] = graph
             self._graph_kernels[key] = ops.launch_count - before
             ops.launch_count = before
