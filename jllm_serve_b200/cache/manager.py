@@ -288,9 +288,17 @@ class CacheManager:
     def state_slot(self, request: Hashable) -> int:
         return self._info(request)[1]
 
-    # ---- a whole step at once (the runner's path) --------------------------------------------------------------
+    # ---- a whole step at once ------------------------------------------------------------------------------------
     def handles(self, requests: Sequence[Hashable]) -> List[int]:
         return [self._names.handle(r) for r in requests]
+
+    def reserve_all(self, requests: Sequence[Hashable], starts: Sequence[int], counts: Sequence[int]) -> None:
+        """`reserve` for every request of a step in one call: all of them get their pages, or none does (what the
+        earlier ones took is given back) and `PoolExhausted` is raised."""
+        n = len(requests)
+        ids = (ctypes.c_longlong * n)(*self.handles(requests))
+        a, b = (ctypes.c_int * n)(*starts), (ctypes.c_int * n)(*counts)
+        self._check(native.lib().jh_step_reserve(self._ptr, n, ids, a, b))
 
     # ---- books ---------------------------------------------------------------------------------------------
     def free_pages(self) -> List[int]:

@@ -62,7 +62,7 @@ class Engine:
                                   cuda_graphs=cuda_graphs)
         core = self.runner.spec.core
         self.scheduler = Scheduler(self.runner.cache, self.runner.ctx, max_batch_tokens, chunk, min_chunk, max_running,
-                                   eos_ids=core.eos)
+                                   eos_ids=core.eos, commits=False)       # the runner commits every step it ran
         self.sampler = Sampler(self.runner.device, max_running, core.vocab, sample_vocab)
         self._rngs = {}
         self._times = {}

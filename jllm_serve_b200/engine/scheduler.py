@@ -121,8 +121,10 @@ class PlannedSegment:
 
 class Scheduler:
     def __init__(self, cache, ctx: int, max_batch_tokens: int, chunk: int = 512, min_chunk: int = 16,
-                 max_running: int = 64, eos_ids: Sequence[int] = ()):
-        self.cache, self.ctx = cache, ctx
+                 max_running: int = 64, eos_ids: Sequence[int] = (), commits: bool = True):
+        """`commits`: whether `complete` records the new lengths in the cache (False when whoever runs the steps
+        does that itself, as the model runner does)."""
+        self.cache, self.ctx, self.commits = cache, ctx, commits
         self.budget, self.chunk, self.min_chunk, self.max_running = max_batch_tokens, chunk, min_chunk, max_running
         self.eos = set(eos_ids)
         self.waiting: List[Request] = []
@@ -188,15 +190,10 @@ class Scheduler:
             if not items:
                 return []
             picks = plan_pass(items, self.budget, self.min_chunk)
-            reserved: List[Request] = []
-            try:
-                for p in picks:
-                    r = p.ref
-                    self.cache.reserve(r.id, r.computed, p.rows)
-                    reserved.append(r)
+            try:      # pages for every pick, or for none
+                self.cache.reserve_all([p.ref.id for p in picks], [p.ref.computed for p in picks],
+                                       [p.rows for p in picks])
             except PoolExhausted:
-                for r in reserved:
-                    self.cache.trim(r.id)
                 if not self._preempt_one():
                     # a single running request that cannot grow: it ends here
                     r = self.running[0]
@@ -251,7 +248,8 @@ class Scheduler:
         for seg in segments:
             r = seg.request
             r.computed = seg.start + len(seg.tokens)
-            self.cache.commit(r.id, r.computed)
+            if self.commits:
+                self.cache.commit(r.id, r.computed)
             if not seg.wants_logits:
                 continue
             tok = next(it)
