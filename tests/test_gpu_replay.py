@@ -16,8 +16,9 @@ from tests.tiny import CONFIGS
 pytestmark = pytest.mark.gpu
 
 ROOT = Path(__file__).resolve().parent.parent
-LENGTHS = {"A": (5, 17, 33, 70), "B": (1, 7, 64, 129), "C": (3, 50, 97, 130), "D": (2, 65, 150, 260)}
-PAGE = {"A": 4, "B": 8, "C": 16, "D": 16}
+LENGTHS = {"A": (5, 17, 33, 70), "B": (1, 7, 64, 129), "C": (3, 50, 97, 130), "D": (2, 65, 150, 260),
+           "E": (4, 129, 300, 470)}         # E: portions of more than 128 and of more than 256 rows in one step
+PAGE = {"A": 4, "B": 8, "C": 16, "D": 16, "E": 16}
 
 
 def make_runner(name, dtype, steps=None, **kw):
@@ -30,7 +31,7 @@ def make_runner(name, dtype, steps=None, **kw):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_whole_requests(name, dtype):
     reqs = requests_for(name, LENGTHS[name])
     steps = traces.whole(reqs)
@@ -39,7 +40,7 @@ def test_whole_requests(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_last_32_tokens_one_by_one(name, dtype):
     reqs = requests_for(name, LENGTHS[name])
     steps = traces.prompt_then_decode(reqs, 32)
@@ -48,7 +49,7 @@ def test_last_32_tokens_one_by_one(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_portions_of_changing_size(name, dtype):
     reqs = requests_for(name, LENGTHS[name])
     steps = traces.changing_portions(reqs)
@@ -57,7 +58,7 @@ def test_portions_of_changing_size(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_mixed_batches_with_pages_used_again(name, dtype):
     reqs = requests_for(name, LENGTHS[name] + (41, 90, 12), seed=23)
     steps = traces.mixed(reqs, max_live=4)

@@ -29,7 +29,15 @@ TINY_D = dict(model_type="qwen3", architectures=["Qwen3ForCausalLM"], hidden_siz
               use_sliding_window=True, sliding_window=70, max_window_layers=2, max_position_embeddings=2048,
               hidden_act="silu")
 
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+# E: head_dim 128 (the size of the tcgen05 attention kernels and of the staged decode kernel), group 2, a window on
+# the last layer only, widths that are no powers of two
+TINY_E = dict(model_type="qwen3", architectures=["Qwen3ForCausalLM"], hidden_size=168, num_hidden_layers=3,
+              num_attention_heads=4, num_key_value_heads=2, head_dim=128, intermediate_size=312, vocab_size=421,
+              rope_theta=500000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, attention_bias=False,
+              use_sliding_window=True, sliding_window=150, max_window_layers=2, max_position_embeddings=4096,
+              hidden_act="silu")
+
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
 
 
 def make_model_folder(config: dict, seed: int, where=None, vector_dtype=None) -> Path:
