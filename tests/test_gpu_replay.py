@@ -69,6 +69,23 @@ def test_mixed_batches_with_pages_used_again(name, dtype):
     assert all(g.pool.num_free == g.pool.num_pages for g in runner.cache.paged), "pages were not all given back"
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_hundred_requests_decode_side_by_side(dtype):
+    """More (row, kv head) pairs in a decode step than the SMs have places for blocks: in bfloat16 the attention
+    deals the key tiles of all pairs out evenly over the blocks."""
+    from jllm_serve_b200.engine import ModelRunner
+    lengths = tuple(6 + (7 * i) % 23 for i in range(104))
+    reqs = requests_for("D", lengths, seed=5)
+    steps = traces.all_together(reqs, tail=4)
+    runner = ModelRunner(model_folder("D"), dtype=dtype, page_size=16, num_pages=260, max_batch_tokens=2048,
+                         max_requests=104, ctx=64, poison_freed_pages=True)
+    got = replay(runner, steps)
+    compare_with_plain(got, model_folder("D"), reqs, dtype, what="D a hundred side by side")
+    from jllm_serve_b200.csrc import ops
+    scratch = torch.empty(2 << 20, device="cuda:0")
+    assert ops.decode_plan(104, 3, 1, 6, 64, scratch)[0] == "flat"      # 312 pairs for 296 places
+
+
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_float32_cuts_agree_bit_for_bit(name):
     """In float32 every row's arithmetic is independent of the batch it rides in, so all ways of cutting

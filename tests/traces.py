@@ -34,6 +34,28 @@ def prompt_then_decode(requests: dict, tail: int = 32) -> list:
     return steps
 
 
+def all_together(requests: dict, tail: int = 4) -> list:
+    """Every request's head in one step, then their last `tail` tokens one step each, all requests side by side:
+    decode steps with as many rows as there are requests."""
+    heads = {rid: max(1, len(toks) - tail) for rid, toks in requests.items()}
+    steps = [{"step": 0, "entries": [{"id": rid, "tokens": toks[:heads[rid]], "want": list(range(heads[rid]))}
+                                     for rid, toks in requests.items()], "end": []}]
+    longest = max(len(toks) - heads[rid] for rid, toks in requests.items())
+    for k in range(longest):
+        entries, end = [], []
+        for rid, toks in requests.items():
+            p = heads[rid] + k
+            if p < len(toks):
+                entries.append({"id": rid, "tokens": toks[p:p + 1], "want": [0]})
+                if p == len(toks) - 1:
+                    end.append(rid)
+        steps.append({"step": len(steps), "entries": entries, "end": end})
+    for rid, toks in requests.items():        # a request that is all head ends with the first step
+        if heads[rid] == len(toks):
+            steps[0]["end"].append(rid)
+    return steps
+
+
 def changing_portions(requests: dict, sizes=(7, 2, 33, 3, 16, 2, 64, 5)) -> list:
     """Each request alone, in portions of changing size, down to two tokens."""
     steps = []
