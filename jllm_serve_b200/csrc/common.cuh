@@ -40,14 +40,25 @@ int jllm_check_launch(const char* what);
 // pdl_wait() before it reads anything a predecessor wrote or writes anything a predecessor may read, and
 // only then pdl_trigger(), so at most one successor is resident early. Without the launch attribute both
 // calls return at once.
+//
+// One thing limits this. An SM cannot change how its memory is split between shared memory and L1 while blocks
+// are resident on it. A kernel whose blocks arrive while a predecessor with a large shared-memory allocation (the
+// staged decode attention, the tcgen05 kernels) still holds the SM runs with that predecessor's split, that is
+// with little L1, and so does every kernel that overlaps it in turn, until one launch waits for the SMs to drain.
+// The decode products re-read their activations through L1 (every block reads all of them): behind a tcgen05
+// product a 16 x 4096 x 12288 product took 47 us as a dependent launch and 22 us launched plainly, and a decode
+// step at batch 16 6.8 ms instead of 5.6. A launch that says it wants L1 (LAUNCH_DEPENDENT_WANTS_L1) is
+// therefore made plainly when a large-shared-memory kernel has been launched since the last plain launch.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 bool jllm_pdl_enabled();
+enum : int { LAUNCH_PLAIN = 0, LAUNCH_DEPENDENT = 1, LAUNCH_DEPENDENT_WANTS_L1 = 2 };
+bool jllm_launch_overlaps(size_t dynamic_smem, int how);     // decides, and keeps the record the decision needs
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t jllm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                               bool dependent, Args... args) {
+                               int how, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -57,7 +68,7 @@ inline cudaError_t jllm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, 
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = (dependent && jllm_pdl_enabled()) ? 1 : 0;
+    cfg.numAttrs = jllm_launch_overlaps(smem, how) ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

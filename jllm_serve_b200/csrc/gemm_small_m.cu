@@ -173,12 +173,12 @@ int launch(const void* a, int lda, const void* w, int ldw, VecRef bias, int has_
     if (out_dtype == JLLM_F32) {
         auto kern = gemm_small_m_kernel<NT, RT, UNROLL, float>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        jllm_launch(kern, dim3(grid), dim3(WARPS * 32), smem, stream, true, (const __nv_bfloat16*)a, lda,
+        jllm_launch(kern, dim3(grid), dim3(WARPS * 32), smem, stream, LAUNCH_DEPENDENT_WANTS_L1, (const __nv_bfloat16*)a, lda,
                     (const __nv_bfloat16*)w, ldw, bias, has_bias, (float*)out, ldo, accumulate, M, N, K, swiglu, prefetch_bytes);
     } else {
         auto kern = gemm_small_m_kernel<NT, RT, UNROLL, __nv_bfloat16>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        jllm_launch(kern, dim3(grid), dim3(WARPS * 32), smem, stream, true, (const __nv_bfloat16*)a, lda,
+        jllm_launch(kern, dim3(grid), dim3(WARPS * 32), smem, stream, LAUNCH_DEPENDENT_WANTS_L1, (const __nv_bfloat16*)a, lda,
                     (const __nv_bfloat16*)w, ldw, bias, has_bias, (__nv_bfloat16*)out, ldo, accumulate, M, N, K, swiglu, prefetch_bytes);
     }
     return jllm_check_launch("gemm_small_m");

@@ -190,8 +190,9 @@ def gemm_bf16_fits(a, w, out) -> bool:
 
 
 # Which kernel takes a product of M rows (measured on the layer shapes of an 8B model): up to SMALL_M_ROWS the
-# mma.sync weight stream; above, the tcgen05 tiles (128 x 256, narrower when the rows are few).
-SMALL_M_ROWS = int(__import__("os").environ.get("JLLM_B200_SMALL_M_ROWS", "32"))
+# mma.sync weight stream (a decode step at batch 40: 9.5 ms with it, 10.0 ms with tcgen05 tiles above 32 rows; at
+# 64 rows the two meet); above, the tcgen05 tiles (128 x 256, narrower when the rows are few).
+SMALL_M_ROWS = int(__import__("os").environ.get("JLLM_B200_SMALL_M_ROWS", "64"))
 WIDE_ROWS = int(__import__("os").environ.get("JLLM_B200_WIDE_ROWS", "16384"))
 _workspaces = {}
 # counters of up to 65,536 tiles, then two parked 128 x 256 partial tiles for each of up to 160 blocks
@@ -211,7 +212,7 @@ def gemm_bf16(a, w, out, bias=None, accumulate=False, swiglu=False) -> None:
     """out (+)= a @ w.T (+ bias) on the tensor cores: bfloat16 operands, float32 accumulation. With `swiglu`
     the rows of w are blocks of 8 gate rows followed by their 8 up rows and out[m, j] = silu(gate_j) * up_j."""
     M, N = a.shape[0], w.shape[0]
-    # 16 to 32 rows against a wide matrix (gate_up): 128 or more 192-wide tcgen05 tiles stream it faster than the
+    # 16 or more rows against a wide matrix (gate_up): 128 or more 192-wide tcgen05 tiles stream it faster than the
     # weight-stream kernel, whose blocks have half their loads in flight once they hold more than two token tiles
     wide = M >= 16 and N >= WIDE_ROWS and _tcgen05_fits(a, w)
     if M <= SMALL_M_ROWS and _small_m_fits(a, w) and not wide:

@@ -34,6 +34,18 @@ bool jllm_pdl_enabled() {
     return g_pdl == 1;
 }
 
+namespace {
+bool g_little_l1 = false;      // a kernel with a large shared-memory allocation was launched since the last plain launch
+}
+
+bool jllm_launch_overlaps(size_t dynamic_smem, int how) {
+    bool overlaps = how != LAUNCH_PLAIN && jllm_pdl_enabled();
+    if (how == LAUNCH_DEPENDENT_WANTS_L1 && g_little_l1) overlaps = false;
+    if (!overlaps) g_little_l1 = false;                     // the SMs drain before this kernel starts
+    if (dynamic_smem > 48 * 1024) g_little_l1 = true;       // what needs the opt-in allocation shrinks L1
+    return overlaps;
+}
+
 // 1 = kernels of a step are launched as programmatic dependents of their predecessors (default), 0 = plainly.
 JLLM_EXPORT void jllm_set_pdl(int on) { g_pdl = on ? 1 : 0; }
 
