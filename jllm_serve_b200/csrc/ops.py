@@ -73,6 +73,13 @@ def set_dependent_launch(on: bool) -> None:
     library().jllm_set_pdl(int(on))
 
 
+def launch_plan(dynamic_smem: int, how: int) -> bool:
+    """What the library's launcher decides for a kernel of `dynamic_smem` bytes launched plainly (how 0), as a
+    programmatic dependent (1) or as one that wants L1 (2): whether it may overlap its predecessor. Keeps the same
+    record as a launch does; launches nothing (a test's view of the rule)."""
+    return bool(library().jllm_launch_plan(int(dynamic_smem), int(how)))
+
+
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 
 
@@ -91,6 +98,7 @@ class _Signatures:
     P, I, F = c_void_p, c_int, c_float
     jllm_check_device = []
     jllm_set_pdl = [I]
+    jllm_launch_plan = [ctypes.c_longlong, I]
     jllm_embed_rows = [P, P, I, P, I, I, I, P]
     jllm_rmsnorm = [P, P, I, P, I, P, I, I, F, P]
     jllm_swiglu = [P, P, I, I, I, P]

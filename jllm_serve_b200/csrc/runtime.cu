@@ -46,6 +46,13 @@ bool jllm_launch_overlaps(size_t dynamic_smem, int how) {
     return overlaps;
 }
 
+// What jllm_launch would decide for a kernel with this much dynamic shared memory launched this way (0 plain,
+// 1 dependent, 2 dependent and wants L1), with the same record kept: 1 = it overlaps its predecessor. For tests
+// of the rule; launches nothing.
+JLLM_EXPORT int jllm_launch_plan(long long dynamic_smem, int how) {
+    return jllm_launch_overlaps((size_t)dynamic_smem, how) ? 1 : 0;
+}
+
 // 1 = kernels of a step are launched as programmatic dependents of their predecessors (default), 0 = plainly.
 JLLM_EXPORT void jllm_set_pdl(int on) { g_pdl = on ? 1 : 0; }
 
