@@ -7,6 +7,7 @@ these functions: without the library or without a B200 they raise.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_char_p, c_double, c_float, c_int, c_void_p
 
 import torch
@@ -200,8 +201,8 @@ def gemm_bf16_fits(a, w, out) -> bool:
 # Which kernel takes a product of M rows (measured on the layer shapes of an 8B model): up to SMALL_M_ROWS the
 # mma.sync weight stream (a decode step at batch 40: 9.5 ms with it, 10.0 ms with tcgen05 tiles above 32 rows; at
 # 64 rows the two meet); above, the tcgen05 tiles (128 x 256, narrower when the rows are few).
-SMALL_M_ROWS = int(__import__("os").environ.get("JLLM_B200_SMALL_M_ROWS", "64"))
-WIDE_ROWS = int(__import__("os").environ.get("JLLM_B200_WIDE_ROWS", "16384"))
+SMALL_M_ROWS = int(os.environ.get("JLLM_B200_SMALL_M_ROWS", "64"))
+WIDE_ROWS = int(os.environ.get("JLLM_B200_WIDE_ROWS", "16384"))
 _workspaces = {}
 # counters of up to 65,536 tiles, then two parked 128 x 256 partial tiles for each of up to 160 blocks
 STREAM_WORKSPACE_FLOATS = 65536 + 160 * 2 * 128 * 256
@@ -262,8 +263,8 @@ def gemm_tcgen05_error() -> int:
 # MB of each small-M product's weights pulled towards L2 before the product waits for its predecessor. Off: with
 # 16-row blocks and the deep unroll (two resident blocks per SM on every layer shape) the prefetch only got in
 # the way of the loads themselves (8B decode step, batch 8: 4.54 ms without, 4.56 with 8 MB, 4.70 with 16 MB).
-PREFETCH_MB = int(__import__("os").environ.get("JLLM_B200_PREFETCH_MB", "0"))
-_SMALL_M_TUNING = int(__import__("os").environ.get("JLLM_B200_SMALL_M_TUNING", "0"))   # experiments only
+PREFETCH_MB = int(os.environ.get("JLLM_B200_PREFETCH_MB", "0"))
+_SMALL_M_TUNING = int(os.environ.get("JLLM_B200_SMALL_M_TUNING", "0"))   # experiments only
 
 
 def gemm_small_m(a, w, out, bias=None, accumulate=False, tuning: int = 0, swiglu=False) -> None:
@@ -312,7 +313,7 @@ def attention_decode_flat(q, k_cache, v_cache, out, row_seg, row_pos, block_tabl
           rows, heads, kv_heads, head_dim, page_size, int(window), float(scale), int(blocks), scratch.data_ptr(), _stream())
 
 
-FLAT_DECODE = int(__import__("os").environ.get("JLLM_B200_FLAT_DECODE", "1"))
+FLAT_DECODE = int(os.environ.get("JLLM_B200_FLAT_DECODE", "1"))
 
 
 def decode_plan(rows, kv_heads, kv_bucket, heads, head_dim, scratch, resident_blocks: int = 2 * 148):
@@ -376,7 +377,7 @@ def attention_prefill_fits(head_dim) -> bool:
     return head_dim in (64, 128, 256)
 
 
-PREFILL_TC = int(__import__("os").environ.get("JLLM_B200_PREFILL_TC", "1"))
+PREFILL_TC = int(os.environ.get("JLLM_B200_PREFILL_TC", "1"))
 
 
 def attention_prefill_tc_fits(q, out, k_cache, head_dim, page_size) -> bool:
