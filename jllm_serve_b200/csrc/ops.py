@@ -217,16 +217,24 @@ def gemm_workspace(device, floats: int = 8 << 20) -> torch.Tensor:
     return held[-1]
 
 
+def gemm_kernel_for(rows: int, out_features: int, stream_fits: bool = True, tiles_fit: bool = True) -> str:
+    """"stream" (the mma.sync weight stream), "tiles" (tcgen05) or "" for a bfloat16 product of `rows` rows against
+    `out_features` weight rows, given which kernels take its strides and alignment."""
+    # 16 or more rows against a wide matrix (gate_up): 128 or more 192-wide tcgen05 tiles stream it faster than the
+    # weight-stream kernel, whose blocks have half their loads in flight once they hold more than two token tiles
+    wide = rows >= 16 and out_features >= WIDE_ROWS and tiles_fit
+    if rows <= min(SMALL_M_ROWS, 64) and stream_fits and not wide:
+        return "stream"
+    return "tiles" if tiles_fit else ""
+
+
 def gemm_bf16(a, w, out, bias=None, accumulate=False, swiglu=False) -> None:
     """out (+)= a @ w.T (+ bias) on the tensor cores: bfloat16 operands, float32 accumulation. With `swiglu`
     the rows of w are blocks of 8 gate rows followed by their 8 up rows and out[m, j] = silu(gate_j) * up_j."""
-    M, N = a.shape[0], w.shape[0]
-    # 16 or more rows against a wide matrix (gate_up): 128 or more 192-wide tcgen05 tiles stream it faster than the
-    # weight-stream kernel, whose blocks have half their loads in flight once they hold more than two token tiles
-    wide = M >= 16 and N >= WIDE_ROWS and _tcgen05_fits(a, w)
-    if M <= SMALL_M_ROWS and _small_m_fits(a, w) and not wide:
+    kernel = gemm_kernel_for(a.shape[0], w.shape[0], _small_m_fits(a, w), _tcgen05_fits(a, w))
+    if kernel == "stream":
         return gemm_small_m(a, w, out, bias, accumulate, swiglu=swiglu)
-    if _tcgen05_fits(a, w):
+    if kernel == "tiles":
         return gemm_tcgen05(a, w, out, bias, accumulate, swiglu=swiglu)
     raise KernelError("the tensor-core matrix product is not built for this shape")
 

@@ -1,0 +1,41 @@
+"""Which kernel a step's work goes to: decisions taken on the host from sizes alone (no GPU, nothing launched)."""
+import torch
+
+from jllm_serve_b200.csrc import ops
+
+
+def test_product_kernel_by_rows_and_width():
+    assert ops.gemm_kernel_for(1, 4096) == "stream"
+    assert ops.gemm_kernel_for(8, 24576) == "stream"               # few rows: even the widest matrix is a stream
+    assert ops.gemm_kernel_for(16, 24576) == "tiles"               # 16 rows against gate_up: tcgen05 tiles
+    assert ops.gemm_kernel_for(16, 4096) == "stream"
+    assert ops.gemm_kernel_for(64, 6144) == "stream"
+    assert ops.gemm_kernel_for(65, 6144) == "tiles"
+    assert ops.gemm_kernel_for(2048, 4096) == "tiles"
+    assert ops.gemm_kernel_for(16, 24576, tiles_fit=False) == "stream"
+    assert ops.gemm_kernel_for(8, 4096, stream_fits=False) == "tiles"
+    assert ops.gemm_kernel_for(8, 4096, stream_fits=False, tiles_fit=False) == ""
+
+
+def test_decode_attention_splits_fill_the_gpu_once():
+    scratch = torch.empty(2 << 20)
+    # 8 rows x 8 kv heads = 64 pairs for 296 places: 4 blocks per pair; 16 keys-of-256 allow up to 32
+    assert ops.decode_splits(8, 8, 16, 32, 128, scratch) == 4
+    assert ops.decode_splits(1, 8, 16, 32, 128, scratch) == 32      # one row: as many as the keys allow, 32 at most
+    assert ops.decode_splits(1, 8, 2, 32, 128, scratch) == 4        # 512 keys: blocks of at least 128
+    assert ops.decode_splits(64, 8, 16, 32, 128, scratch) == 1
+    assert ops.decode_splits(8, 8, 16, 32, 128, None) == 1          # no scratch, no partial results
+    tiny = torch.empty(8 * 32 * 2 * (128 + 2))                      # room for two splits only
+    assert ops.decode_splits(8, 8, 16, 32, 128, tiny) == 2
+
+
+def test_decode_attention_is_dealt_out_evenly_only_where_that_pays():
+    scratch = torch.empty(2 << 20)
+    assert ops.decode_plan(8, 8, 16, 32, 128, scratch) == ("split", 4)          # fewer pairs than places
+    assert ops.decode_plan(37, 8, 16, 32, 128, scratch) == ("split", 1)         # 296 pairs: one full round
+    how, blocks = ops.decode_plan(64, 8, 16, 32, 128, scratch)                  # 512 pairs: 1.73 rounds
+    assert how == "flat" and blocks == 296
+    how, blocks = ops.decode_plan(104, 3, 1, 6, 64, scratch)                    # few kv heads bound the blocks
+    assert how == "flat" and blocks == 62 * 3
+    assert ops.decode_plan(64, 8, 16, 32, 80, scratch)[0] == "split"            # a head size the flat kernel lacks
+    assert ops.decode_plan(64, 8, 16, 32, 128, torch.empty(1000))[0] == "split"  # no room for its partial results
