@@ -74,6 +74,7 @@ class Item:
     kind: str                              # "rider" (a decoding request's rows, all wanted) or "chunk"
     rows: int
     enqueued: int
+    more: bool = False                     # a chunk whose prompt goes on after these rows
 
 
 @dataclass(frozen=True)
@@ -83,12 +84,15 @@ class Pick:
     rows: int
 
 
-def plan_pass(pending: Sequence[Item], budget: int, min_chunk: int) -> List[Pick]:
+def plan_pass(pending: Sequence[Item], budget: int, min_chunk: int, row_quantum: int = 0) -> List[Pick]:
     """The picks of the next pass: the chunk (if any) first, then the riders by arrival.
 
     Riders that do not fit are left for the next pass, never trimmed; the chunk is the head of the
     `pending` chunks in the order given, trimmed to the room left, and waits if the room is smaller
-    than min(min_chunk, its rows)."""
+    than min(min_chunk, its rows). With `row_quantum` (the rows of a matrix-product tile) a chunk that is cut
+    anyway, because its prompt goes on after it, is cut so that the pass has a whole number of tiles: the rows
+    beyond the last full tile would cost a tile of their own (measured, 8B shape, 32 riders: 544 rows 15.7 ms,
+    512 rows 14.4 ms)."""
     if budget < 1:
         raise ValueError("a pass needs a budget of at least one row")
     riders = sorted((i for i in pending if i.kind != "chunk"), key=lambda i: i.enqueued)
@@ -102,6 +106,9 @@ def plan_pass(pending: Sequence[Item], budget: int, min_chunk: int) -> List[Pick
     if chunks:
         c = chunks[0]
         rows = min(c.rows, budget - used)
+        over = (used + rows) % row_quantum if row_quantum > 1 else 0
+        if over and used + rows > row_quantum and (c.more or rows < c.rows) and rows - over >= max(min_chunk, 1):
+            rows -= over
         if rows >= min(min_chunk, c.rows) and rows > 0:
             out.append(Pick(c.ref, "chunk", rows))
     out.extend(rider_picks)
@@ -121,10 +128,10 @@ class PlannedSegment:
 
 class Scheduler:
     def __init__(self, cache, ctx: int, max_batch_tokens: int, chunk: int = 512, min_chunk: int = 16,
-                 max_running: int = 64, eos_ids: Sequence[int] = (), commits: bool = True):
+                 max_running: int = 64, eos_ids: Sequence[int] = (), commits: bool = True, row_quantum: int = 0):
         """`commits`: whether `complete` records the new lengths in the cache (False when whoever runs the steps
-        does that itself, as the model runner does)."""
-        self.cache, self.ctx, self.commits = cache, ctx, commits
+        does that itself, as the model runner does). `row_quantum`: see `plan_pass`."""
+        self.cache, self.ctx, self.commits, self.row_quantum = cache, ctx, commits, row_quantum
         self.budget, self.chunk, self.min_chunk, self.max_running = max_batch_tokens, chunk, min_chunk, max_running
         self.eos = set(eos_ids)
         self.waiting: List[Request] = []
@@ -186,10 +193,10 @@ class Scheduler:
                 if r.remaining == 1:
                     items.append(Item(r, "rider", 1, r.arrival))
             for r in self.prefill_line:
-                items.append(Item(r, "chunk", min(r.remaining, self.chunk), r.arrival))
+                items.append(Item(r, "chunk", min(r.remaining, self.chunk), r.arrival, r.remaining > self.chunk + 1))
             if not items:
                 return []
-            picks = plan_pass(items, self.budget, self.min_chunk)
+            picks = plan_pass(items, self.budget, self.min_chunk, self.row_quantum)
             try:      # pages for every pick, or for none
                 self.cache.reserve_all([p.ref.id for p in picks], [p.ref.computed for p in picks],
                                        [p.rows for p in picks])

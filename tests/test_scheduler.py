@@ -45,6 +45,29 @@ def test_small_chunk_runs_whole_and_nothing_stalls():
     assert plan_pass([], 64, 16) == []
 
 
+def test_a_chunk_that_is_cut_anyway_is_cut_at_a_whole_number_of_tiles():
+    riders = [Item(f"D{i}", "rider", 1, i) for i in range(32)]
+    # 32 riders + 512 rows would be four tiles of 128 rows and 32 rows of a fifth: the portion gives 32 rows up
+    picks = plan_pass(riders + [Item("P", "chunk", 512, 99, True)], 2048, 16, row_quantum=128)
+    assert names(picks)[0] == "P:480" and sum(p.rows for p in picks) == 512
+    # the last portion of a prompt is not cut (that would only add a step)
+    picks = plan_pass(riders + [Item("P", "chunk", 512, 99, False)], 2048, 16, row_quantum=128)
+    assert names(picks)[0] == "P:512"
+    # ... unless the budget cuts it already
+    picks = plan_pass(riders + [Item("P", "chunk", 512, 99, False)], 300, 16, row_quantum=128)
+    assert names(picks)[0] == "P:224" and sum(p.rows for p in picks) == 256
+    # a pass of less than a tile stays as it is, and so does one that is whole already
+    assert names(plan_pass([Item("D", "rider", 1, 0), Item("P", "chunk", 100, 1, True)], 2048, 16, 128))[0] == "P:100"
+    assert names(plan_pass(riders + [Item("P", "chunk", 96, 99, True)], 2048, 16, 128))[0] == "P:96"
+    # never below the smallest portion
+    assert names(plan_pass(riders[:2] + [Item("P", "chunk", 140, 99, True)], 2048, 16, 128))[0] == "P:126"
+    run = [Item("V", "rider", 120, 0)]
+    assert names(plan_pass(run + [Item("P", "chunk", 20, 99, True)], 2048, 16, 128))[0] == "P:20"
+    assert names(plan_pass(run + [Item("P", "chunk", 20, 99, True)], 2048, 8, 128))[0] == "P:8"
+    # no quantum, no cutting
+    assert names(plan_pass(riders + [Item("P", "chunk", 512, 99, True)], 2048, 16))[0] == "P:512"
+
+
 # ---- the scheduler over a real cache manager, with a fake model -------------------------------------------
 
 def make(pages=64, page_size=4, budget=32, chunk=16, max_running=4, ctx=256, eos=()):
