@@ -201,6 +201,7 @@ def gemm_bf16_fits(a, w, out) -> bool:
 # Which kernel takes a product of M rows (measured on the layer shapes of an 8B model): up to SMALL_M_ROWS the
 # mma.sync weight stream (a decode step at batch 40: 9.5 ms with it, 10.0 ms with tcgen05 tiles above 32 rows; at
 # 64 rows the two meet); above, the tcgen05 tiles (128 x 256, narrower when the rows are few).
+TILE_ROWS = 128          # rows of a tcgen05 product tile (BM in gemm_tcgen05.cu): a step of 129 rows pays for 256
 SMALL_M_ROWS = int(os.environ.get("JLLM_B200_SMALL_M_ROWS", "64"))
 WIDE_ROWS = int(os.environ.get("JLLM_B200_WIDE_ROWS", "16384"))
 _workspaces = {}

@@ -63,7 +63,7 @@ class Engine:
         core = self.runner.spec.core
         self.scheduler = Scheduler(self.runner.cache, self.runner.ctx, max_batch_tokens, chunk, min_chunk, max_running,
                                    eos_ids=core.eos, commits=False,       # the runner commits every step it ran
-                                   row_quantum=128 if self.runner.dtype == torch.bfloat16 else 0)   # tcgen05 tiles
+                                   row_quantum=ops.TILE_ROWS if self.runner.dtype == torch.bfloat16 else 0)
         self.sampler = Sampler(self.runner.device, max_running, core.vocab, sample_vocab)
         self._rngs = {}
         self._times = {}
