@@ -70,9 +70,10 @@ def test_a_chunk_that_is_cut_anyway_is_cut_at_a_whole_number_of_tiles():
 
 # ---- the scheduler over a real cache manager, with a fake model -------------------------------------------
 
-def make(pages=64, page_size=4, budget=32, chunk=16, max_running=4, ctx=256, eos=()):
+def make(pages=64, page_size=4, budget=32, chunk=16, max_running=4, ctx=256, eos=(), row_quantum=0):
     cache = CacheManager([PagedKeysValues(1, 8)], page_size, pages, max_running)
-    return Scheduler(cache, ctx, budget, chunk, min_chunk=4, max_running=max_running, eos_ids=eos), cache
+    return Scheduler(cache, ctx, budget, chunk, min_chunk=4, max_running=max_running, eos_ids=eos,
+                     row_quantum=row_quantum), cache
 
 
 def drive(s, cache, token_of=lambda r: 7, limit=10000):
@@ -87,6 +88,20 @@ def drive(s, cache, token_of=lambda r: 7, limit=10000):
         cache.check()
         assert len(steps) < limit
     return steps
+
+
+def test_portions_beside_decoding_rows_fill_whole_tiles():
+    s, cache = make(pages=200, budget=64, chunk=30, row_quantum=8)
+    s.add(Request("a", [1, 2], SamplingParams.greedy_params(40)))
+    for _ in range(3):                                                 # "a" is decoding now
+        plan = s.plan()
+        s.complete(plan, [7 for p in plan if p.wants_logits])
+    s.add(Request("b", list(range(100)), SamplingParams.greedy_params(2)))
+    steps = drive(s, cache)
+    cut = [sum(rows for _, _, rows, _ in st) for st in steps if any(rid == "b" and rows > 1 for rid, _, rows, _ in st)]
+    # every step that holds a portion of b's prompt (but its last) beside a's row has a multiple of 8 rows
+    assert cut and all(n % 8 == 0 for n in cut[:-1]), cut
+    assert s.finished["b"].finish_reason == "length" and len(s.finished["b"].output) == 2
 
 
 def test_prompt_is_cut_into_portions_and_decoding_rides_along():
@@ -168,10 +183,11 @@ def test_request_that_can_never_fit_ends_with_kv_exhausted():
     assert cache2.free_pages() == [3]
 
 
+@pytest.mark.parametrize("row_quantum", [0, 8])
 @pytest.mark.parametrize("seed", range(4))
-def test_random_load_always_finishes(seed):
+def test_random_load_always_finishes(seed, row_quantum):
     rng = random.Random(seed)
-    s, cache = make(pages=24, page_size=4, budget=24, chunk=12, max_running=4, ctx=128)
+    s, cache = make(pages=24, page_size=4, budget=24, chunk=12, max_running=4, ctx=128, row_quantum=row_quantum)
     want = {}
     for i in range(12):
         n, m = rng.randrange(1, 40), rng.randrange(1, 20)
