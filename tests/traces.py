@@ -131,3 +131,56 @@ def collect(steps: list, logits_of_step) -> dict:
         for rid in st["end"]:
             fed.pop(rid, None)
     return out
+
+
+def scheduled(requests: dict, prompt_lens: dict, max_live: int = 4, portions=(300, 129, 512, 200, 257, 140)) -> list:
+    """Steps of the form the scheduler makes: ONE portion of a prompt first (the head of the line of prompts, which
+    then goes to the back of it), then one row for every request that is decoding, in order of admission. The
+    first `prompt_lens[rid]` tokens of a request are its prompt, the rest is fed one token a step as if it had
+    been decoded. Requests are admitted in order while fewer than `max_live` are live. The portion sizes cycle
+    through `portions`, so portions of more than one and more than two 128-row tiles stand beside single rows."""
+    waiting = list(requests.items())
+    live, line = {}, []        # rid -> [tokens, fed, prompt_len]; the line of prompts that still have portions to run
+    steps, k = [], 0
+    while waiting or live:
+        while waiting and len(live) < max_live:
+            rid, toks = waiting.pop(0)
+            live[rid] = [toks, 0, max(1, min(len(toks), prompt_lens[rid]))]
+            line.append(rid)
+        entries, ended = [], []
+        if line:
+            rid = line.pop(0)
+            toks, fed, pre = live[rid]
+            n = min(portions[k % len(portions)], pre - fed)
+            k += 1
+            entries.append({"id": rid, "tokens": toks[fed:fed + n], "want": list(range(n))})
+            live[rid][1] = fed + n
+            if fed + n < pre:
+                line.append(rid)
+            portion_of = rid
+        else:
+            portion_of = None
+        for rid, st in live.items():
+            toks, fed, pre = st
+            if rid == portion_of or rid in line or fed < pre or fed >= len(toks):
+                continue
+            entries.append({"id": rid, "tokens": toks[fed:fed + 1], "want": [0]})
+            st[1] = fed + 1
+        for rid, st in list(live.items()):
+            if st[1] == len(st[0]):
+                ended.append(rid)
+                del live[rid]
+        steps.append({"step": len(steps), "entries": entries, "end": ended})
+    return steps
+
+
+def shape_of(steps: list) -> list:
+    """For every step (rows of its leading multi-row entries, single-row entries behind them), or None where a
+    multi-row entry follows a single row: the scheduler never forms such a step."""
+    out = []
+    for st in steps:
+        sizes = [len(e["tokens"]) for e in st["entries"]]
+        multi = [n for n in sizes if n > 1]
+        ok = sizes[:len(multi)] == multi
+        out.append((sum(multi), len(sizes) - len(multi)) if ok else None)
+    return out
