@@ -9,7 +9,8 @@ the batch tables copied to the device, the captured decode graph replayed, argma
 token lists in, sampled tokens read back on the host every step, prompts prefilled by the engine
 itself. `prefill` times one 2,048-token prompt; `roofline` compares the bytes a decode step has to
 read (every weight once plus the cache of the live requests) with the measured copy bandwidth;
-`points` holds decode at batch 1 and 64. Peaks come from MEASURED_PEAKS.json when it exists.
+`points` holds decode at batch 1 and 64; `check` compares the bfloat16 logits with the 32-bit path's at these
+layer sizes (two layers, untimed). Peaks come from MEASURED_PEAKS.json when it exists.
 
 The engine runs on one GPU; for --gpus above 1 the program says so and exits with 2.
 """
@@ -119,6 +120,8 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true")
     ap.add_argument("--prefill-only", action="store_true", help="profiling aid: time the prefill alone and print it")
+    ap.add_argument("--skip-check", action="store_true",
+                    help="leave out the comparison of the bfloat16 path with the 32-bit path at these layer sizes")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "beniaminp/jllm-serve is a Java 26 program with an Apple "
@@ -147,6 +150,15 @@ def main() -> int:
     dev = torch.device("cuda:0")
     biggest = 64 if not args.skip_points else args.batch
     pool_tokens = biggest * ctx + 2 * PREFILL_TOKENS + args.mixed_chunk
+    check = None
+    if not (args.skip_check or args.prefill_only):
+        # the 32-bit path against the bfloat16 path at these layer sizes, on two layers (untimed, before the model)
+        from jllm_serve_b200.precision_check import compare_precisions
+        got = compare_precisions(dict(shape, num_hidden_layers=2), seed=0)["mixed"]
+        check = {"what": "bfloat16 logits against the 32-bit path, a 256+44-row prompt beside 2 decoding requests, "
+                         "then 16 tokens one by one", "layers": 2, "layers_of_config": shape["num_hidden_layers"],
+                 "rows": got["rows"], "max_rel": round(got["max_rel"], 5), "rms_rel": round(got["rms_rel"], 5),
+                 "argmax_agree": round(got["argmax_agree"], 4), "choice_gap_rel": round(got["worst_choice_gap_rel"], 5)}
     t0 = time.time()
     engine = Engine(config=cfg, seed=0, dtype="bfloat16", ctx=ctx, page_size=PAGE, num_pages=pool_tokens // PAGE,
                     max_batch_tokens=PREFILL_TOKENS + 64, chunk=PREFILL_TOKENS, max_running=biggest + 1)
@@ -275,7 +287,7 @@ def main() -> int:
                    "l2": f"inputs larger than L2 (weights {nums['weight_bytes'] / 1e9:.0f} GB per step)",
                    "cuda_graphs": runner.use_graphs},
         "clocks": clock_record, "e2e": e2e, "gpu_launches": launches, "prefill": prefill, "roofline": roofline,
-        "points": points,
+        "points": points, "check": check,
     }
     print(json.dumps(record))
     return 0

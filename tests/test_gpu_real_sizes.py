@@ -1,0 +1,39 @@
+"""The bfloat16 path against the 32-bit path at the layer sizes of Qwen3-8B (GPU).
+
+Every other comparison of logits in this suite runs at widths of up to 168. Here the products sum over 4,096
+and 12,288 terms, the head has 151,936 rows and the attention 32 query heads over 8 kv heads of size 128: the
+sizes that are benchmarked. Two layers instead of 36 (the sizes of a layer are what matters; both numbers are
+named). The 32-bit path is the one the plain implementation pins at small sizes.
+
+The bounds are wider than those of the tiny models, and for a reason that is a model of the error, not a guess:
+with 4,096 inputs of N(0, 0.02) weights the layers' outputs dwarf the embedding (which is exact in both paths and
+dominates the residual stream of a tiny model), so the logits carry the bfloat16 roundings of the activations
+undiluted. One layer measured stage by stage: q, k and v 2.6e-3 of their rms (two roundings of 2^-8 / sqrt(3)
+each), the attention's output 4.6e-3 (scores from 128 products of twice-rounded values, P and the output rounded
+once more), the feed-forward's hidden values 7.8e-3 (gate and up both inherit the attention's error), the logits
+7.9e-3; two layers 9.8e-3. With 151,936 random logits a row's two best are often closer than that, so the best
+token is not always the same one; where it differs the 32-bit path must hold the other choice for nearly as good.
+"""
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+QWEN3_8B_LAYERS = 36
+CONFIG = dict(model_type="qwen3", architectures=["Qwen3ForCausalLM"], hidden_size=4096, num_hidden_layers=2,
+              num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288,
+              vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+              attention_bias=False, use_sliding_window=False, max_position_embeddings=40960, hidden_act="silu")
+
+
+def test_bfloat16_follows_float32_at_8b_layer_sizes():
+    from jllm_serve_b200.precision_check import compare_precisions
+    got = compare_precisions(CONFIG, seed=3)
+    print(f"layers {CONFIG['num_hidden_layers']} of {QWEN3_8B_LAYERS}: {got}")
+    for name in ("alone", "mixed"):
+        s = got[name]
+        assert s["rows"] >= 316
+        assert s["max_rel"] <= 1.5e-2, (name, s)
+        assert s["rms_rel"] <= 1.3e-2, (name, s)
+        assert s["argmax_agree"] >= 0.96, (name, s)
+        # where the two paths choose differently, the 32-bit path holds the other choice for almost as good
+        assert s["worst_choice_gap_rel"] <= 1e-2, (name, s)
