@@ -8,7 +8,8 @@ and every request has one block table per group (position p of the request lives
 reference, which has a single group because its layers always move together, :395-397).
 A windowed group gives pages back as soon as the window has passed them; the others keep
 theirs until the request ends. A fixed-state group has storage [slots, ...] and each
-request one slot.
+request one slot, which is zeroed when the request is opened. A mixer may name several needs
+(paged keys and values and one or more states): its run is then a member of a group of each.
 
 Before a step, `reserve(request, start, n)` makes sure pages exist for positions
 [start, start + n) in every group (the reference's `beginWrite`,
@@ -119,6 +120,50 @@ class _Requests:
         return [self._m._snapshot(r) for r in self]
 
 
+def needs_of(need) -> Tuple[CacheNeed, ...]:
+    """What a mixer's `cache_need` returned, as a tuple: nothing, one need, or several (a mixer that keeps paged
+    keys and values AND a state of fixed size says both)."""
+    if need is None:
+        return ()
+    if isinstance(need, CacheNeed):
+        return () if type(need) is CacheNeed else (need,)
+    if isinstance(need, (tuple, list)):
+        return tuple(n for one in need for n in needs_of(one))
+    raise TypeError(f"unknown cache need {need!r}")
+
+
+def group_runs(needs: Sequence) -> tuple:
+    """Layer runs with the same need share a group: (paged groups, fixed-state groups, {run: paged group},
+    {run: [fixed-state groups, in the order the run named them]}). A run may have at most one paged need."""
+    paged: List[PagedGroup] = []
+    fixed: List[StateGroup] = []
+    paged_of_run: Dict[int, int] = {}
+    fixed_of_run: Dict[int, List[int]] = {}
+    for run, need in enumerate(needs):
+        for one in needs_of(need):
+            if isinstance(one, PagedKeysValues):
+                if run in paged_of_run:
+                    raise TypeError(f"layer run {run} names two needs of paged keys and values; one is built")
+                groups, kind = paged, PagedGroup
+            elif isinstance(one, FixedState):
+                groups, kind = fixed, StateGroup
+            else:
+                raise TypeError(f"layer run {run}: unknown cache need {one!r}")
+            for gi, g in enumerate(groups):
+                # a run that wants two states of the same shape gets two groups: a group holds a run once
+                if g.need == one and run not in g.runs:
+                    g.runs.append(run)
+                    break
+            else:
+                gi = len(groups)
+                groups.append(kind(one, [run]))
+            if kind is PagedGroup:
+                paged_of_run[run] = gi
+            else:
+                fixed_of_run.setdefault(run, []).append(gi)
+    return paged, fixed, paged_of_run, fixed_of_run
+
+
 class CacheManager:
     def __init__(self, needs: Sequence[Optional[CacheNeed]], page_size: int, num_pages: int, max_requests: int,
                  allocate: Optional[Callable] = None):
@@ -129,32 +174,7 @@ class CacheManager:
             raise ValueError(f"a pool needs at least one page, got {num_pages}")
         self.page_size = page_size
         self.num_pages = num_pages
-        self.paged: List[PagedGroup] = []
-        self.fixed: List[StateGroup] = []
-        self.group_of_run: Dict[int, Tuple[str, int]] = {}
-        for run, need in enumerate(needs):
-            if need is None or type(need) is CacheNeed:
-                continue
-            if isinstance(need, PagedKeysValues):
-                for gi, g in enumerate(self.paged):
-                    if g.need == need:
-                        g.runs.append(run)
-                        break
-                else:
-                    gi = len(self.paged)
-                    self.paged.append(PagedGroup(need, [run]))
-                self.group_of_run[run] = ("paged", gi)
-            elif isinstance(need, FixedState):
-                for gi, g in enumerate(self.fixed):
-                    if g.need == need:
-                        g.runs.append(run)
-                        break
-                else:
-                    gi = len(self.fixed)
-                    self.fixed.append(StateGroup(need, [run]))
-                self.group_of_run[run] = ("fixed", gi)
-            else:
-                raise TypeError(f"layer run {run}: unknown cache need {need!r}")
+        self.paged, self.fixed, self.paged_of_run, self.fixed_of_run = group_runs(needs)
         L = native.lib()
         G = len(self.paged)
         windows = (ctypes.c_int * max(1, G))(*[g.need.window for g in self.paged])
@@ -192,19 +212,29 @@ class CacheManager:
 
     # ---- what a layer run reads and writes ----------------------------------------------------------------
     def paged_group_of(self, run: int) -> int:
-        kind, gi = self.group_of_run[run]
-        if kind != "paged":
+        if run not in self.paged_of_run:
             raise KeyError(f"layer run {run} keeps no keys and values")
-        return gi
+        return self.paged_of_run[run]
 
     def keys_values(self, run: int):
         return self.paged[self.paged_group_of(run)].keys_values(run)
 
-    def state(self, run: int):
-        kind, gi = self.group_of_run[run]
-        if kind != "fixed":
-            raise KeyError(f"layer run {run} keeps no fixed-size state")
-        return self.fixed[gi].state(run)
+    def states(self, run: int) -> list:
+        """The fixed-size states of a run, [slots, ...] each, in the order its mixer named them."""
+        return [self.fixed[gi].state(run) for gi in self.fixed_of_run.get(run, ())]
+
+    def state(self, run: int, which: int = 0):
+        held = self.fixed_of_run.get(run, ())
+        if which >= len(held):
+            raise KeyError(f"layer run {run} keeps no fixed-size state" + (f" number {which}" if held else ""))
+        return self.fixed[held[which]].state(run)
+
+    @staticmethod
+    def page_bytes(needs: Sequence, page_size: int, element_bytes: int) -> List[int]:
+        """Bytes of one page of every paged group these needs would form (for sizing the pool before it exists)."""
+        from .budget import group_page_bytes
+        return [group_page_bytes(len(g.runs), g.need.kv_heads, g.need.head_dim, page_size, element_bytes)
+                for g in group_runs(needs)[0]]
 
     # ---- requests ---------------------------------------------------------------------------------------
     def open(self, request: Hashable) -> RequestCache:
@@ -215,7 +245,11 @@ class CacheManager:
         if code:
             self._names.forget(request)
             self._check(code)
-        return self._snapshot(request)
+        snap = self._snapshot(request)
+        for g in self.fixed:          # a slot is handed out clean: whoever held it before left its state there
+            if g.storage is not None:
+                g.storage[:, snap.state_slot].zero_()
+        return snap
 
     def is_open(self, request: Hashable) -> bool:
         return request in self._names._handle      # the names that have a handle are the open requests

@@ -27,7 +27,9 @@ DEFAULTS: Dict[str, Tuple[str, str]] = {
     "backend.ctx": ("0", "context length; 0 = the model's max_position_embeddings"),
     "backend.batch": ("512", "rows of one prompt portion (the reference's backend.batch)"),
     "backend.kv-block": ("16", "positions per cache page"),
-    "backend.num-pages": ("0", "pages of the cache pool; 0 = enough for ctx x 4 tokens"),
+    "backend.num-pages": ("auto", "pages of the cache pool; auto = backend.kv-share of the free device memory; "
+                                  "0 = enough for ctx x 4 tokens"),
+    "backend.kv-share": ("0.6", "auto: the part of the free device memory the cache pool may take"),
     "engine.pass-budget": ("0", "most rows in one step; 0 = backend.batch + engine.mixed-reserve"),
     "engine.mixed-reserve": ("32", "rows kept for decoding requests beside a prompt portion"),
     "engine.min-chunk": ("16", "a portion is trimmed to the room left only down to this many rows"),
@@ -48,7 +50,8 @@ DEFAULTS: Dict[str, Tuple[str, str]] = {
 ALIASES = {
     "model": "model.dir", "dir": "model.dir", "random-weights": "model.random-weights", "model-config": "model.config",
     "dtype": "backend.dtype", "ctx": "backend.ctx", "batch": "backend.batch", "chunk": "backend.batch",
-    "page-size": "backend.kv-block", "num-pages": "backend.num-pages", "max-batch-tokens": "engine.pass-budget",
+    "page-size": "backend.kv-block", "num-pages": "backend.num-pages", "kv-share": "backend.kv-share",
+    "max-batch-tokens": "engine.pass-budget",
     "max-running": "engine.max-running", "temp": "sampling.temperature", "temperature": "sampling.temperature",
     "top-k": "sampling.top-k", "top-p": "sampling.top-p", "min-p": "sampling.min-p", "seed": "sampling.seed",
     "max-tokens": "sampling.max-tokens", "ignore-eos": "sampling.ignore-eos",
@@ -144,7 +147,10 @@ class Settings:
         self.integer("backend.ctx", 0)
         self.integer("backend.batch", 1)
         self.integer("backend.kv-block", 1)
-        self.integer("backend.num-pages", 0)
+        if self.get("backend.num-pages") != "auto":
+            self.integer("backend.num-pages", 0)
+        if not 0 < self.number("backend.kv-share") <= 1:
+            raise SettingsError(f"backend.kv-share must be in (0, 1], got '{self.get('backend.kv-share')}'")
         self.integer("engine.pass-budget", 0)
         self.integer("engine.mixed-reserve", 0)
         self.integer("engine.min-chunk", 1)
@@ -177,7 +183,8 @@ USAGE = """usage: jllm <command> [options]
   config     print the effective configuration and where each value comes from
 options (override with --config <file> or flags):
   --model <dir>   --random-weights <seed> --model-config <config.json>   --dtype bf16|fp32
-  --ctx <n>  --batch <n>  --page-size <n>  --num-pages <n>  --max-batch-tokens <n>  --max-running <n>
+  --ctx <n>  --batch <n>  --page-size <n>  --num-pages <n|auto>  --kv-share <0..1>  --max-batch-tokens <n>
+  --max-running <n>
   --temp <t> --top-k <k> --top-p <p> --min-p <p> --seed <s> --max-tokens <n> --ignore-eos
   any property key directly, e.g. --bench.rounds=5
 """
@@ -190,7 +197,8 @@ def build_engine(s: Settings):
     batch = s.integer("backend.batch")
     budget = s.integer("engine.pass-budget") or batch + s.integer("engine.mixed-reserve")
     kw = dict(dtype=s.get("backend.dtype"), ctx=s.integer("backend.ctx") or None,
-              page_size=s.integer("backend.kv-block"), num_pages=s.integer("backend.num-pages") or None,
+              page_size=s.integer("backend.kv-block"), kv_share=s.number("backend.kv-share"),
+              num_pages="auto" if s.get("backend.num-pages") == "auto" else (s.integer("backend.num-pages") or None),
               max_batch_tokens=budget, chunk=batch, min_chunk=s.integer("engine.min-chunk"),
               max_running=s.integer("engine.max-running"), cuda_graphs=s.boolean("engine.cuda-graphs"))
     if s.get("model.random-weights"):
@@ -217,9 +225,15 @@ def _prompt(s: Settings, vocab: int, default_len=None) -> List[int]:
     return torch.randint(0, vocab, (n,), generator=g).tolist()
 
 
+def _describe(engine) -> None:
+    print(f"Model: {engine.describe()}", file=sys.stderr)
+    for note in engine.runner.notes:
+        print(f"note: {note}", file=sys.stderr)
+
+
 def cmd_run(s: Settings) -> int:
     engine = build_engine(s)
-    print(f"Model: {engine.describe()}", file=sys.stderr)
+    _describe(engine)
     res = engine.generate([_prompt(s, engine.runner.vocab)], s.sampling())[0]
     print(",".join(str(t) for t in res.tokens))
     print(f"[{res.finish_reason}] {res.stats.line()}", file=sys.stderr)
@@ -230,7 +244,7 @@ def cmd_bench(s: Settings) -> int:
     """Prefill and decode throughput of one request, the best of `bench.rounds` (Main.java:363-382)."""
     from .sampling import SamplingParams
     engine = build_engine(s)
-    print(f"Model: {engine.describe()}", file=sys.stderr)
+    _describe(engine)
     prompt = _prompt(s, engine.runner.vocab, s.integer("bench.prompt-tokens"))
     params = SamplingParams.greedy_params(max_tokens=s.integer("bench.max-tokens"), ignore_eos=True)
     best = None

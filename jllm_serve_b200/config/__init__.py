@@ -4,6 +4,6 @@ from .specs import (ConfigError, Core, Decoder, DenseGluSpec, FeedForwardSpec, G
 from .reader import ConfigReader
 from .registry import (architecture_entry, load_config, parse_config, register_architecture, supported_architectures,
                        unregister_architecture)
-from .families import parse_qwen3, parse_rope_scaling
+from .families import DecoderDraft, parse_qwen3, parse_rope_scaling
 
 register_architecture("qwen3", parse_qwen3, replace=True)

@@ -25,6 +25,7 @@ enum JllmError : int {
 
 int jllm_fail(int code, const char* fmt, ...);
 int jllm_check_launch(const char* what);
+int jllm_device_sm_count();      // SMs of the current device (asked once), 0 if unknown
 
 #define JLLM_REQUIRE(cond, ...)                                   \
     do {                                                          \

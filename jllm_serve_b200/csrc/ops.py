@@ -52,6 +52,25 @@ def require_device() -> None:
     _device_ok = True
 
 
+_sm_count = 0
+
+
+def sm_count() -> int:
+    """SMs of the current device, asked of the library once (it asks the driver)."""
+    global _sm_count
+    if not _sm_count:
+        n = library().jllm_sm_count()
+        if n <= 0:
+            raise KernelError("the device does not say how many SMs it has")
+        _sm_count = n
+    return _sm_count
+
+
+def resident_blocks() -> int:
+    """Places for blocks of the decode attention on the device: two per SM."""
+    return 2 * sm_count()
+
+
 launch_count = 0   # kernels of this library launched (or captured into a graph) by this process
 
 
@@ -98,6 +117,7 @@ def _p(t):
 class _Signatures:
     P, I, F = c_void_p, c_int, c_float
     jllm_check_device = []
+    jllm_sm_count = []
     jllm_set_pdl = [I]
     jllm_launch_plan = [ctypes.c_longlong, I]
     jllm_embed_rows = [P, P, I, P, I, I, I, P]
@@ -325,20 +345,22 @@ def attention_decode_flat(q, k_cache, v_cache, out, row_seg, row_pos, block_tabl
 FLAT_DECODE = int(os.environ.get("JLLM_B200_FLAT_DECODE", "1"))
 
 
-def decode_plan(rows, kv_heads, kv_bucket, heads, head_dim, scratch, resident_blocks: int = 2 * 148):
+def decode_plan(rows, kv_heads, kv_bucket, heads, head_dim, scratch, places: int = 0):
     """("flat", blocks) or ("split", splits) for a decode step's attention: one block per (row, kv head, split), or,
-    when there are more (row, kv head) pairs than places for blocks and they would fill the last round of places
+    when there are more (row, kv head) pairs than places for blocks (`places`, by default two per SM of the device)
+    and they would fill the last round of places
     badly (by less than 93 %), the key tiles of all pairs dealt out evenly over as many blocks as there are places
     (measured at context 4,096: 188 against 195 us at batch 64; with fewer pairs than places the even deal was the
     slower one, 34.5 against 32.4 us at batch 8). `kv_bucket` = the longest request's keys in units of 256."""
-    splits = decode_splits(rows, kv_heads, kv_bucket, heads, head_dim, scratch, resident_blocks)
+    places = places or resident_blocks()
+    splits = decode_splits(rows, kv_heads, kv_bucket, heads, head_dim, scratch, places)
     uniform = rows * kv_heads * splits
-    rounds = -(-uniform // resident_blocks)
+    rounds = -(-uniform // places)
     if (not FLAT_DECODE or scratch is None or head_dim not in (64, 128, 256) or rows > 1024
-            or rows * kv_heads <= resident_blocks or uniform * 100 >= rounds * resident_blocks * 93):
+            or rows * kv_heads <= places or uniform * 100 >= rounds * places * 93):
         return "split", splits
     tiles = rows * kv_heads * kv_bucket * 4                    # 64 keys a tile; an upper bound, like the bucket
-    blocks = max(1, min(resident_blocks, 62 * kv_heads, tiles // 2))
+    blocks = max(1, min(places, 62 * kv_heads, tiles // 2))
     if attention_decode_flat_scratch_floats(rows, heads, kv_heads, head_dim, blocks) > scratch.numel():
         return "split", splits
     return "flat", blocks
@@ -420,11 +442,11 @@ def attention_prefill_tc_error() -> int:
     return library().jllm_attention_prefill_tc_error()
 
 
-def decode_splits(rows, kv_heads, kv_bucket, heads, head_dim, scratch, resident_blocks: int = 2 * 148) -> int:
+def decode_splits(rows, kv_heads, kv_bucket, heads, head_dim, scratch, places: int = 0) -> int:
     """How many blocks share one row's keys: as many as fit on the GPU at once (two blocks per SM; one block
     more than that would cost a whole second wave), each with at least 128 keys (`kv_bucket` = the longest
     request's keys in units of 256)."""
-    want = resident_blocks // max(1, rows * kv_heads)
+    want = (places or resident_blocks()) // max(1, rows * kv_heads)
     splits = max(1, min(want, 2 * kv_bucket, 32))
     if scratch is None:
         return 1

@@ -145,7 +145,8 @@ JLLM_EXPORT int jllm_swiglu(const void* gate_up, void* h, int dtype, int rows, i
     JLLM_REQUIRE(rows >= 0 && hidden > 0, "swiglu: rows=%d hidden=%d", rows, hidden);
     if (rows == 0) return JLLM_OK;
     const size_t total = (size_t)rows * hidden;
-    const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+    const size_t most = (size_t)(jllm_device_sm_count() > 0 ? jllm_device_sm_count() : 1) * 16;   // the kernel strides
+    const int blocks = (int)((total + 255) / 256 > most ? most : (total + 255) / 256);
     if (dtype == JLLM_F32)
         jllm_launch(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, stream, true, (const float*)gate_up, (float*)h, hidden,
                     total);

@@ -72,4 +72,19 @@ JLLM_EXPORT int jllm_check_device() {
     return JLLM_OK;
 }
 
+// The SMs of the current device, asked once per device (0 if it cannot be asked). Grids and split counts are sized
+// from this, never from a number written into the code.
+int jllm_device_sm_count() {
+    static int counts[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    if (counts[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess) counts[dev] = n;
+    }
+    return counts[dev];
+}
+
+JLLM_EXPORT int jllm_sm_count() { return jllm_device_sm_count(); }
+
 JLLM_EXPORT int jllm_abi_version() { return 1; }

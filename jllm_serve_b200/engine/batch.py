@@ -60,8 +60,10 @@ class StepBatch:
 
 class BatchBuilder:
     def __init__(self, device, max_rows: int, max_segments: int, max_blocks: int, num_paged_groups: int,
-                 page_size: int):
-        self.device = device
+                 page_size: int, resident_blocks: int):
+        """`resident_blocks`: places for blocks of the decode attention on the device (the runner asks the device);
+        a step's key-range bucket, which is part of a captured step's key, is capped by it."""
+        self.device, self.resident_blocks = device, max(1, int(resident_blocks))
         self.max_rows, self.max_segments, self.max_blocks = max_rows, max_segments, max_blocks
         self.groups, self.page_size = num_paged_groups, page_size
         R, S, G = max_rows, max_segments, num_paged_groups
@@ -212,6 +214,6 @@ class BatchBuilder:
                 self._views[(rows, S, n_want)] = views
         return StepBatch(
             rows=rows, segments=list(segments), num_wanted=n_want, max_q_len=max_q, max_kv_len=max_kv,
-            kv_bucket=max(1, min(32, max_kv // 256, -(-296 // rows))),
+            kv_bucket=max(1, min(32, max_kv // 256, -(-self.resident_blocks // rows))),
             multi_segments=multi_segments, multi_rows=multi_rows,
             host_seg_start=sstart[:S].tolist(), host_state_slots=sslot[:S].tolist(), **views)

@@ -53,13 +53,16 @@ class Result:
 class Engine:
     def __init__(self, model_dir=None, *, config: Optional[dict] = None, seed: Optional[int] = None,
                  dtype="bfloat16", device="cuda:0", ctx: Optional[int] = None, page_size: int = 16,
-                 num_pages: Optional[int] = None, max_tokens_cached: Optional[int] = None,
+                 num_pages=None, max_tokens_cached: Optional[int] = None,
                  max_batch_tokens: int = 2048, chunk: int = 512, min_chunk: int = 16, max_running: int = 64,
-                 sample_vocab: Optional[int] = None, cuda_graphs: bool = True):
+                 sample_vocab: Optional[int] = None, cuda_graphs: bool = True, kv_share: float = 0.6):
+        """`num_pages`: pages of the cache pool, or "auto" for the share `kv_share` of the device memory that is
+        free once the weights are loaded; without it the pool holds `max_tokens_cached` tokens (default: four
+        full contexts)."""
         self.runner = ModelRunner(model_dir, config=config, seed=seed, dtype=dtype, device=device,
                                   page_size=page_size, num_pages=num_pages, max_tokens=max_tokens_cached,
                                   max_batch_tokens=max_batch_tokens, max_requests=max_running, ctx=ctx,
-                                  cuda_graphs=cuda_graphs)
+                                  cuda_graphs=cuda_graphs, kv_share=kv_share)
         core = self.runner.spec.core
         self.scheduler = Scheduler(self.runner.cache, self.runner.ctx, max_batch_tokens, chunk, min_chunk, max_running,
                                    eos_ids=core.eos, commits=False,       # the runner commits every step it ran
@@ -85,10 +88,16 @@ class Engine:
         return rid
 
     def step_once(self) -> List[Request]:
-        """One scheduler step: plan, run, sample, complete. Returns the requests that finished."""
+        """One scheduler step: plan, run, sample, complete. Returns the requests that finished, those included
+        that the scheduler ended while planning because the pool can never hold them (`kv_exhausted`)."""
         plan = self.scheduler.plan()
+        ended = self.scheduler.take_ended()
+        now = time.perf_counter()
+        for r in ended:
+            self._times[r.id]["end"] = now
+            self._rngs.pop(r.id, None)
         if not plan:
-            return []
+            return ended
         segments = [Segment(p.request.id, p.tokens, p.start, [len(p.tokens) - 1] if p.wants_logits else [])
                     for p in plan]
         logits = self.runner.step(segments)
@@ -102,7 +111,8 @@ class Engine:
         done = self.scheduler.complete(plan, sampled)
         for r in done:
             self._times[r.id]["end"] = now
-        return done
+            self._rngs.pop(r.id, None)
+        return ended + done
 
     def run_until_done(self) -> List[Request]:
         finished = []

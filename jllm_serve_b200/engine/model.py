@@ -4,8 +4,9 @@ The model is what a registry entry builds from a `Decoder` spec. It knows the or
 layer runs (data: `spec.schedule`), hands every run the cache it reads or writes, and
 computes logits only for the rows that were asked for, as the reference does
 (src/main/java/org/robomiri/jllm/cpu/CpuBackend.java:895-928,980-985). The head is the
-embedding when `tie_word_embeddings` is set, else `lm_head.weight`, which must then exist
-(model/ModelWeights.java:37).
+embedding when `tie_word_embeddings` is set (a `lm_head.weight` that the file still has is
+left unread, as the reference's converter drops it: model/ModelConverter.java:663-665), else
+`lm_head.weight`, and the embedding again if the file has none (model/ModelWeights.java:37).
 """
 from __future__ import annotations
 
@@ -25,8 +26,10 @@ class DecoderModel:
         core, names = spec.core, spec.names
         tensors = dict(tensors)
         self.embedding = tensors.pop(names.embedding)
-        head = self.embedding if core.tied else tensors.pop(names.head)
-        self.head = Linear(head)
+        head = None if core.tied else tensors.pop(names.head, None)
+        if head is None and not core.tied:
+            runtime.notes.append(f"{names.head} is not in the checkpoint: the embedding serves as the head")
+        self.head = Linear(self.embedding if head is None else head)
         self.position_encodings = []
         for t in spec.rope_tables:
             cls = part_class("position", t.kind)
@@ -45,7 +48,7 @@ class DecoderModel:
         core, names = spec.core, spec.names
         out = {names.embedding: TensorWant((core.vocab, core.dim))}
         if not core.tied:
-            out[names.head] = TensorWant((core.vocab, core.dim))
+            out[names.head] = TensorWant((core.vocab, core.dim), optional=True)
         for t in spec.rope_tables:
             out.update(part_class("position", t.kind).wants(t, core.dim, ""))
         for l, layer in enumerate(spec.layers):
@@ -53,8 +56,14 @@ class DecoderModel:
         out.update(part_class("norm", spec.final_norm.kind).wants(spec.final_norm, core.dim, names.final_norm))
         return out
 
+    @property
+    def graph_safe(self) -> bool:
+        """Whether a decode step of this model may be captured once and replayed: every part says so of itself."""
+        return all(b.graph_safe for b in self.blocks) and all(pe.graph_safe for pe in self.position_encodings)
+
     def cache_needs(self) -> List[Optional[object]]:
-        """One entry per scheduled run: what it keeps between steps (None if it reads another run's cache)."""
+        """One entry per scheduled run: what it keeps between steps (None if it reads another run's cache; a
+        tuple if the mixer keeps several things, say paged keys and values and a state of fixed size)."""
         needs = []
         for run in self.spec.schedule:
             mixer = self.spec.layers[run.layer].mixer
@@ -64,13 +73,14 @@ class DecoderModel:
     def _run_cache(self, cache, i: int) -> RunCache:
         run = self.spec.schedule[i]
         owner = i if run.cache_of is None else run.cache_of
-        kind, group = cache.group_of_run.get(owner, (None, -1))
-        if kind == "paged":
-            k, v = cache.keys_values(owner)
-            return RunCache(owner, run.cache_of is None, group, k, v)
-        if kind == "fixed":
-            return RunCache(owner, run.cache_of is None, -1, state=cache.state(owner))
-        return RunCache(owner, run.cache_of is None)
+        out = RunCache(owner, run.cache_of is None)
+        if owner in cache.paged_of_run:
+            out.group = cache.paged_of_run[owner]
+            out.keys, out.values = cache.keys_values(owner)
+        states = cache.states(owner)
+        if states:
+            out.states, out.state = tuple(states), states[0]
+        return out
 
     def forward(self, batch, cache, logits_out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Runs the batch's rows through every scheduled layer; returns float32 logits [wanted rows, vocab]."""

@@ -15,6 +15,7 @@ from typing import Hashable, List, Optional, Sequence
 import torch
 
 from ..cache import CacheManager, PoolExhausted
+from ..cache.budget import DEFAULT_SHARE, plan_pages
 from ..config.registry import architecture_entry, load_config, parse_config
 from ..csrc import ops
 from ..parts import Runtime
@@ -37,12 +38,14 @@ def _as_dtype(dtype) -> torch.dtype:
 
 class ModelRunner:
     def __init__(self, model_dir=None, *, config: Optional[dict] = None, seed: Optional[int] = None,
-                 dtype="bfloat16", device="cuda:0", page_size: int = 16, num_pages: Optional[int] = None,
+                 dtype="bfloat16", device="cuda:0", page_size: int = 16, num_pages=None,
                  max_tokens: Optional[int] = None, max_batch_tokens: int = 2048, max_requests: int = 64,
                  ctx: Optional[int] = None, schedule=None, poison_freed_pages: bool = False,
-                 cuda_graphs: bool = True):
+                 cuda_graphs: bool = True, kv_share: float = DEFAULT_SHARE):
         """Either `model_dir` (config.json + model.safetensors) or `config` + `seed` (random weights made on
-        the device). The pool holds `num_pages` pages per group, or enough for `max_tokens` cached tokens."""
+        the device). The pool holds `num_pages` pages per group, or enough for `max_tokens` cached tokens, or,
+        with `num_pages="auto"`, the share `kv_share` of the device memory that is free once the weights are
+        loaded (never more than `max_requests` full contexts need)."""
         ops.require_device()
         self.device = torch.device(device)
         torch.cuda.set_device(self.device)
@@ -71,22 +74,34 @@ class ModelRunner:
             tensors = convert_checked(made, wants, self.dtype, self.device)
             del made
         self.model = build_model(entry, spec, tensors, rt)
+        self.notes.extend(rt.notes)
         del tensors
         self.runtime = rt
         self.vocab = spec.core.vocab
-        if num_pages is None:
+        needs = self.model.cache_needs()
+        self.page_plan = None
+        if num_pages == "auto":
+            free, total = torch.cuda.mem_get_info(self.device)
+            element = torch.empty((), dtype=self.dtype).element_size()
+            # the parts' scratch buffers and the logits are made at the first steps: some tens of bytes per element
+            # of a step's residual stream, taken off before the share
+            held = self.max_rows * int(getattr(spec.core, "dim", 0)) * 64 + 2 * self.max_requests * self.vocab * 4
+            self.page_plan = plan_pages(free, total, CacheManager.page_bytes(needs, self.page_size, element),
+                                        self.page_size, self.ctx, self.max_requests, kv_share, held)
+            num_pages = self.page_plan.pages
+            self.notes.append(f"cache pool: {num_pages} pages ({self.page_plan.pool_bytes / 1e9:.1f} GB), limited by "
+                              f"{self.page_plan.limited_by}: {self.page_plan.basis}")
+        elif num_pages is None:
             tokens = max_tokens if max_tokens is not None else self.ctx * min(self.max_requests, 4)
             num_pages = max(1, -(-int(tokens) // self.page_size))
         self.poison = poison_freed_pages
-        self.cache = CacheManager(self.model.cache_needs(), self.page_size, int(num_pages), self.max_requests,
-                                  allocate=self._allocate)
+        self.cache = CacheManager(needs, self.page_size, int(num_pages), self.max_requests, allocate=self._allocate)
         max_blocks = -(-self.ctx // self.page_size)
         self.builder = BatchBuilder(self.device, self.max_rows, self.max_requests, max_blocks, len(self.cache.paged),
-                                    self.page_size)
+                                    self.page_size, ops.resident_blocks())
         self.steps = 0
         self.use_graphs = bool(cuda_graphs)
-        self.graph_safe = all(getattr(b.mixer, "graph_safe", True) and getattr(b.feed_forward, "graph_safe", True)
-                              for b in getattr(self.model, "blocks", []))
+        self.graph_safe = bool(getattr(self.model, "graph_safe", False))    # a model that does not say is not replayed
         self._graphs, self._graph_seen, self._static_logits, self._graph_kernels = {}, set(), None, {}
         self.max_graphs = 256          # captured decode shapes kept (rows x wanted rows x key-range bucket)
 
@@ -108,7 +123,17 @@ class ModelRunner:
 
     def _step_in_parts(self, segments, logits_out):
         """More rows than one batch holds: the same tokens as several batches, one after the other. The
-        logits come back in the order that was asked for."""
+        logits come back in the order that was asked for. The pages of ALL the parts are reserved before the first
+        part runs, so a pool that is too small refuses the step before anything of it ran (a windowed group then
+        needs pages for the whole span at once, more than running part by part would)."""
+        opened = self._open(segments)
+        try:
+            self.cache.reserve_all([s.request for s in segments], [s.start for s in segments],
+                                   [len(s.tokens) for s in segments])
+        except Exception:
+            for r in opened:
+                self.cache.close(r)
+            raise
         wanted = sum(len(s.want) for s in segments)
         out = logits_out[:wanted] if logits_out is not None else \
             torch.empty((wanted, self.vocab), dtype=torch.float32, device=self.device)
@@ -131,13 +156,21 @@ class ModelRunner:
                 parts[-1].append(Segment(seg.request, seg.tokens[lo:lo + n], seg.start + lo, want))
                 lo += n
                 room -= n
-        for part, idx in zip(parts, order):
-            logits = self._step_once(part, None)
-            if idx:
-                out[torch.tensor(idx, device=self.device)] = logits
+        try:
+            for part, idx in zip(parts, order):
+                logits = self._step_once(part, None, reserve=False)
+                if idx:
+                    out[torch.tensor(idx, device=self.device)] = logits
+        except Exception:
+            # a part failed while running: the parts before it stay committed (their rows are in the cache); what
+            # was reserved beyond that goes back, and requests that this call opened are closed
+            self._give_back(segments, opened)
+            raise
         return out
 
-    def _step_once(self, segments, logits_out):
+    def _open(self, segments) -> list:
+        """Opens the requests of a step that are not open yet; returns those it opened. Nothing stays open if a
+        segment does not fit the context."""
         opened = []
         try:
             for seg in segments:
@@ -147,12 +180,35 @@ class ModelRunner:
                 if not self.cache.is_open(seg.request):
                     self.cache.open(seg.request)
                     opened.append(seg.request)
-            batch = self.builder.build(segments, self.cache, self.vocab, reserve=True)   # all pages or none
         except Exception:
             for r in opened:
                 self.cache.close(r)
             raise
-        logits = self._run_model(batch, logits_out)
+        return opened
+
+    def _give_back(self, segments, opened) -> None:
+        for seg in segments:
+            if seg.request in opened:
+                if self.cache.is_open(seg.request):
+                    self.cache.close(seg.request)
+            elif self.cache.is_open(seg.request):
+                self.cache.trim(seg.request)
+
+    def _step_once(self, segments, logits_out, reserve: bool = True):
+        opened = self._open(segments)
+        try:
+            batch = self.builder.build(segments, self.cache, self.vocab, reserve=reserve)   # all pages or none
+        except Exception:
+            for r in opened:
+                self.cache.close(r)
+            raise
+        try:
+            logits = self._run_model(batch, logits_out)
+        except Exception:
+            # the step did not run to its end: its pages go back and the books say what they said before it, so
+            # the cache and whoever drives the steps still agree
+            self._give_back(segments, opened)
+            raise
         released = self.builder.commit(self.cache)
         if self.poison:
             self._poison(released)

@@ -142,6 +142,7 @@ class Scheduler:
         self._admissions = itertools.count()
         self.preemptions = 0
         self.on_finish: Optional[Callable[[Request], None]] = None
+        self._ended_planning: List[Request] = []
 
     # ---- requests in -------------------------------------------------------------------------------------
     def add(self, request: Request) -> None:
@@ -157,6 +158,12 @@ class Scheduler:
 
     def has_work(self) -> bool:
         return bool(self.waiting or self.running)
+
+    def take_ended(self) -> List[Request]:
+        """The requests that `plan` ended itself since the last call (they can never fit the pool: `kv_exhausted`).
+        They never reach `complete`, so whoever drives the steps learns of them here."""
+        out, self._ended_planning = self._ended_planning, []
+        return out
 
     # ---- one step ------------------------------------------------------------------------------------------
     def _admit(self) -> None:
@@ -244,6 +251,8 @@ class Scheduler:
     def _finish(self, r: Request, reason: str) -> None:
         r.state, r.finish_reason = FINISHED, reason
         self.finished[r.id] = r
+        if reason == "kv_exhausted":
+            self._ended_planning.append(r)
         if self.on_finish:
             self.on_finish(r)
 

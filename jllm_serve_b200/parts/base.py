@@ -9,8 +9,9 @@ the `Runtime`; it never learns which model it is in. The kinds:
                       tensors (full checkpoint names; the prefix it is given is empty); a mixer that rotates asks
                       it for `cos`, `sin`, `rotary_dim`; one that adds to the embedding overrides
                       `on_embedding(x, batch)`.
-* `Mixer`:            `cache_need(spec)` says what it keeps between steps; `forward(xb, x, batch, cache)`
-                      reads the normed rows `xb` and ADDS its result into the float32 residual stream `x`.
+* `Mixer`:            `cache_need(spec)` says what it keeps between steps (one need, a tuple of needs, or None);
+                      `forward(xb, x, batch, cache)` reads the normed rows `xb` and ADDS its result into the
+                      float32 residual stream `x`.
 * `FeedForward`:      `forward(xb, x, batch)`, same contract.
 * `Block`:            the arrangement of norm, mixer and feed-forward in one layer.
 
@@ -37,6 +38,7 @@ class Runtime:
 
     def __post_init__(self):
         self._buffers: Dict[str, torch.Tensor] = {}
+        self.notes: list = []              # what a part wants the user to know about how it was built
 
     def buffer(self, name: str, cols: int, dtype: Optional[torch.dtype] = None, rows: Optional[int] = None):
         """A persistent [rows or max_rows, cols] scratch tensor: the same memory at every step, so that a
@@ -58,11 +60,15 @@ class Part:
 
 
 class Norm(Part):
+    graph_safe = True
+
     def forward(self, x, out, row_index=None, rows=None):
         raise NotImplementedError
 
 
 class PositionEncoding(Part):
+    graph_safe = True
+
     def on_embedding(self, x, batch) -> None:
         """Hook for encodings that add to the embedded rows; rotary tables leave them alone."""
 
@@ -89,6 +95,10 @@ class FeedForward(Part):
 
 
 class Block(Part):
+    # an arrangement says itself whether its step can be captured and replayed (usually: whether all its parts
+    # can); one that does not say is run launch by launch
+    graph_safe = False
+
     def forward(self, x, batch, cache) -> None:
         raise NotImplementedError
 
@@ -101,7 +111,9 @@ class RunCache:
     group: int = -1                        # paged group index (block tables and write slots of the batch), -1 = none
     keys: Optional[torch.Tensor] = None    # [pages, kv_heads, page_size, head_dim]
     values: Optional[torch.Tensor] = None
-    state: Optional[torch.Tensor] = None   # [slots, ...] for a fixed-state mixer
+    state: Optional[torch.Tensor] = None   # [slots, ...] for a fixed-state mixer (the first of `states`)
+    states: tuple = ()                     # every fixed-size state the mixer named, in its order; a mixer may hold
+                                           # these beside paged keys and values
 
 
 _REGISTRIES: Dict[str, Dict[str, Callable]] = {"mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}}

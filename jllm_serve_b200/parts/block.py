@@ -24,6 +24,10 @@ class PreNormBlock(Block):
         self.feed_forward = part_class("feed_forward", spec.feed_forward.kind)(
             spec.feed_forward, dim, tensors, prefix + names.feed_forward, runtime)
 
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(p, "graph_safe", False) for p in (self.mixer_norm, self.ffn_norm, self.mixer, self.feed_forward))
+
     @classmethod
     def wants(cls, spec, dim: int, prefix: str) -> dict:
         names = spec.names

@@ -63,6 +63,7 @@ class PlainConfig:
         self.theta = c.get("rope_theta", 10000.0)
         self.tied = c.get("tie_word_embeddings", False)
         self.bias = c.get("attention_bias", False)
+        self.qk_norm = True               # qwen3: qkNorm = true (J/model/Families.java:168); a test of another family clears it
         self.partial = c.get("partial_rotary_factor", 1.0)
         self.rotary_dim = int(self.head_dim * self.partial) & ~1
         self.scaling = c.get("rope_scaling")
@@ -217,11 +218,11 @@ def attention_block(xb, w: dict, prefix: str, cfg: PlainConfig, window: int, cos
     T = xb.shape[0]
     b = (lambda n: w[prefix + n + ".bias"]) if cfg.bias else (lambda n: None)
     q = linear(xb, w[prefix + "q_proj.weight"], b("q_proj")).reshape(T, cfg.heads, cfg.head_dim)
-    q = apply_rope(rmsnorm(q, w[prefix + "q_norm.weight"], cfg.eps), cos, sin)
+    q = apply_rope(rmsnorm(q, w[prefix + "q_norm.weight"], cfg.eps) if cfg.qk_norm else q, cos, sin)
     if k_v_from is None:
         k = linear(xb, w[prefix + "k_proj.weight"], b("k_proj")).reshape(T, cfg.kv_heads, cfg.head_dim)
         v = linear(xb, w[prefix + "v_proj.weight"], b("v_proj")).reshape(T, cfg.kv_heads, cfg.head_dim)
-        k = apply_rope(rmsnorm(k, w[prefix + "k_norm.weight"], cfg.eps), cos, sin)
+        k = apply_rope(rmsnorm(k, w[prefix + "k_norm.weight"], cfg.eps) if cfg.qk_norm else k, cos, sin)
     else:
         k, v = k_v_from
     scale = 1.0 / math.sqrt(cfg.head_dim)  # J/model/Families.java:861

@@ -183,7 +183,7 @@ def test_batch_tables_follow_the_requests_tables():
 
     from jllm_serve_b200.engine.batch import BatchBuilder, Segment
     m = CacheManager([PagedKeysValues(1, 8, 0)], page_size=2, num_pages=64, max_requests=4)
-    b = BatchBuilder(torch.device("cpu"), max_rows=32, max_segments=4, max_blocks=16, num_paged_groups=1, page_size=2)
+    b = BatchBuilder(torch.device("cpu"), max_rows=32, max_segments=4, max_blocks=16, num_paged_groups=1, page_size=2, resident_blocks=296)
     rng = random.Random(0)
     lengths = {}
 

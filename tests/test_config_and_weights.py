@@ -81,6 +81,59 @@ def test_registry_takes_another_architecture():
         unregister_architecture("qwen3_twin")
 
 
+def test_a_dense_family_is_a_few_switches_on_the_shared_reader():
+    """The reference's families are a shared draft plus switches (model/Families.java:166-171,611-733): a family
+    with biases on q, k, v always, no q/k norm, the window on every layer and tied embeddings by default."""
+    from jllm_serve_b200.config import DecoderDraft
+
+    def parse_toy(values):
+        d = DecoderDraft(values, "toy_dense", "ToyDenseForCausalLM")
+        d.bias, d.qk_norm, d.window, d.tied_default, d.theta_default = "always", False, "all", True, 5e5
+        return d.build()
+
+    register_architecture("toy_dense", parse_toy)
+    try:
+        c = dict(model_type="toy_dense", hidden_size=64, num_hidden_layers=2, vocab_size=50, num_attention_heads=4,
+                 num_key_value_heads=2, intermediate_size=24, sliding_window=9)
+        d = parse_config(c)
+        a = d.layers[1].mixer
+        assert (a.bias, a.out_bias, a.qk_norm, a.window) == (True, False, False, 9)
+        assert d.core.tied and d.rope_tables[0].theta == 5e5 and d.core.architecture == "ToyDenseForCausalLM"
+        wants = DecoderModel.wants(d)
+        assert "model.layers.0.self_attn.q_proj.bias" in wants and "model.layers.0.self_attn.o_proj.bias" not in wants
+        assert "model.layers.0.self_attn.q_norm.weight" not in wants and "lm_head.weight" not in wants
+        with pytest.raises(ConfigError, match="ToyDenseForCausalLM"):
+            parse_config(dict(c, architectures=["Qwen3ForCausalLM"]))
+        # newer configs nest the rope keys; the top-level key wins when both are there
+        nested = parse_config(dict(c, rope_parameters={"rope_theta": 123.0, "rope_type": "linear", "factor": 2.0}))
+        assert nested.rope_tables[0].theta == 123.0 and nested.rope_tables[0].scaling.kind == "linear"
+        assert parse_config(dict(c, rope_theta=7.0, rope_parameters={"rope_theta": 123.0})).rope_tables[0].theta == 7.0
+    finally:
+        unregister_architecture("toy_dense")
+
+    def parse_strict(values):          # the default switches are Llama's: attention_bias is not a key of the family
+        return DecoderDraft(values, "toy_strict", "ToyStrictForCausalLM").build()
+
+    register_architecture("toy_strict", parse_strict)
+    try:
+        c = dict(model_type="toy_strict", hidden_size=64, num_hidden_layers=1, vocab_size=50, num_attention_heads=4,
+                 intermediate_size=24, sliding_window=9)
+        assert parse_config(c).layers[0].mixer.window == 0 and not parse_config(c).layers[0].mixer.qk_norm
+        with pytest.raises(ConfigError, match="attention_bias"):
+            parse_config(dict(c, attention_bias=True))
+    finally:
+        unregister_architecture("toy_strict")
+
+
+def test_the_reference_reads_qwen3_this_way():
+    """The cases of the reference's own test (src/test/java/org/robomiri/jllm/SmokeTest.java:844-846): a qwen3
+    config gets the q/k norm, and attention_bias biases q, k, v AND o_proj."""
+    plain = parse_config(dict(TINY_A)).layers[0].mixer
+    assert plain.qk_norm and not plain.bias and not plain.out_bias
+    biased = parse_config(dict(TINY_A, attention_bias=True)).layers[0].mixer
+    assert biased.qk_norm and biased.bias and biased.out_bias
+
+
 def test_schedule_is_data():
     d = parse_config(TINY_A)
     assert [(r.layer, r.cache_of) for r in d.schedule] == [(0, None), (1, None)]
@@ -97,12 +150,8 @@ def test_yarn_parameters():
                                                  "original_max_position_embeddings": 128}))
     s = d.rope_tables[0].scaling
     assert (s.kind, s.factor, s.original_max_positions, s.beta_fast, s.beta_slow) == ("yarn", 4.0, 128, 32.0, 1.0)
-    from jllm_serve_b200.parts.rope import amplitude, inverse_frequencies
-    from tests.plain import qwen3_plain as P
-    want = P.rope_inverse_frequencies(32, 1e6, {"rope_type": "yarn", "factor": 4.0,
-                                                "original_max_position_embeddings": 128}, 512)
-    assert torch.allclose(inverse_frequencies(d.rope_tables[0], 512), torch.tensor(want, dtype=torch.float64))
-    assert abs(amplitude(s) - (0.1 * torch.log(torch.tensor(4.0)).item() + 1)) < 1e-9
+    # the frequencies and the amplitude themselves are checked against the reference's own numbers in
+    # tests/test_reference_literals.py
 
 
 # ---- weights ------------------------------------------------------------------------------------------------
@@ -162,14 +211,61 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     assert e.value.missing and e.value.unexpected and e.value.wrong_shape
 
 
-def test_untied_model_without_head_is_an_error(tmp_path):
+def test_untied_model_without_head_uses_the_embedding(tmp_path):
+    """`lmHead = file.has("lm_head.weight") ? that : embed` (model/ModelWeights.java:37 of the reference)."""
+    from jllm_serve_b200.parts import Runtime
     folder = write_model_folder(TINY_B, 1, tmp_path / "m")
     src = TensorSource(folder)
     tensors = {n: src.tensor(n).clone() for n in src.names() if n != "lm_head.weight"}
     write_safetensors(folder / "model.safetensors", tensors)
     spec, _ = load_config(folder)
-    with pytest.raises(WeightError, match="missing .*lm_head.weight"):
-        load_checked(TensorSource(folder), DecoderModel.wants(spec), torch.bfloat16, "cpu")
+    loaded = load_checked(TensorSource(folder), DecoderModel.wants(spec), torch.float32, "cpu")
+    assert "lm_head.weight" not in loaded
+    rt = Runtime(torch.device("cpu"), torch.float32, 64, 8, 4)
+    model = DecoderModel(spec, loaded, rt)
+    assert model.head.weight is model.embedding and any("embedding serves as the head" in n for n in rt.notes)
+
+
+def test_tensors_the_model_does_not_ask_for_are_noted_not_refused(tmp_path):
+    """A tied checkpoint that still ships lm_head.weight, an old one with rotary_emb.inv_freq: read what is needed,
+    note the rest; `strict` turns them into the error."""
+    folder = write_model_folder(TINY_A, 1, tmp_path / "m")
+    src = TensorSource(folder)
+    tensors = {n: src.tensor(n).clone() for n in src.names()}
+    tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"].clone()
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    write_safetensors(folder / "model.safetensors", tensors)
+    spec, _ = load_config(folder)
+    notes = []
+    loaded = load_checked(TensorSource(folder), DecoderModel.wants(spec), torch.bfloat16, "cpu", notes)
+    assert "lm_head.weight" not in loaded and set(loaded) == set(DecoderModel.wants(spec))
+    assert len(notes) == 1 and "2 tensors" in notes[0] and "rotary_emb.inv_freq" in notes[0]
+    with pytest.raises(WeightError, match=r"unexpected \(2\)"):
+        load_checked(TensorSource(folder), DecoderModel.wants(spec), torch.bfloat16, "cpu", strict=True)
+
+
+def test_multimodal_prefixes_are_dropped(tmp_path):
+    """`model.language_model.X` and `language_model.model.X` are read as `model.X` (model/ModelConverter.java:977-988
+    of the reference); a vision tower beside them is left alone."""
+    folder = write_model_folder(TINY_B, 1, tmp_path / "m")
+    src = TensorSource(folder)
+    plain = {n: src.tensor(n).clone() for n in src.names()}
+    spec, _ = load_config(folder)
+    want = load_checked(TensorSource(folder), DecoderModel.wants(spec), torch.float32, "cpu")
+    for prefix, head in (("model.language_model.", "lm_head."), ("language_model.model.", "language_model.lm_head.")):
+        renamed = {(prefix + n[len("model."):] if n.startswith("model.") else head + n[len("lm_head."):]): t
+                   for n, t in plain.items()}
+        renamed["model.visual.patch_embed.weight"] = torch.zeros(4, 4)
+        write_safetensors(folder / "model.safetensors", renamed)
+        notes = []
+        got = load_checked(TensorSource(folder), DecoderModel.wants(spec), torch.float32, "cpu", notes)
+        assert set(got) == set(want) and all(torch.equal(got[n], want[n]) for n in want)
+        assert any("model.visual.patch_embed.weight" in n for n in notes)
+    both = dict(plain)
+    both["model.language_model.norm.weight"] = plain["model.norm.weight"].clone()
+    write_safetensors(folder / "model.safetensors", both)
+    with pytest.raises(WeightError, match="are both 'model.norm.weight'"):
+        load_checked(TensorSource(folder), DecoderModel.wants(spec), torch.float32, "cpu")
 
 
 def _raw_file(path, header: dict, data: bytes):

@@ -20,22 +20,22 @@ def test_product_kernel_by_rows_and_width():
 def test_decode_attention_splits_fill_the_gpu_once():
     scratch = torch.empty(2 << 20)
     # 8 rows x 8 kv heads = 64 pairs for 296 places: 4 blocks per pair; 16 keys-of-256 allow up to 32
-    assert ops.decode_splits(8, 8, 16, 32, 128, scratch) == 4
-    assert ops.decode_splits(1, 8, 16, 32, 128, scratch) == 32      # one row: as many as the keys allow, 32 at most
-    assert ops.decode_splits(1, 8, 2, 32, 128, scratch) == 4        # 512 keys: blocks of at least 128
-    assert ops.decode_splits(64, 8, 16, 32, 128, scratch) == 1
-    assert ops.decode_splits(8, 8, 16, 32, 128, None) == 1          # no scratch, no partial results
+    assert ops.decode_splits(8, 8, 16, 32, 128, scratch, places=296) == 4
+    assert ops.decode_splits(1, 8, 16, 32, 128, scratch, places=296) == 32      # one row: as many as the keys allow, 32 at most
+    assert ops.decode_splits(1, 8, 2, 32, 128, scratch, places=296) == 4        # 512 keys: blocks of at least 128
+    assert ops.decode_splits(64, 8, 16, 32, 128, scratch, places=296) == 1
+    assert ops.decode_splits(8, 8, 16, 32, 128, None, places=296) == 1          # no scratch, no partial results
     tiny = torch.empty(8 * 32 * 2 * (128 + 2))                      # room for two splits only
-    assert ops.decode_splits(8, 8, 16, 32, 128, tiny) == 2
+    assert ops.decode_splits(8, 8, 16, 32, 128, tiny, places=296) == 2
 
 
 def test_decode_attention_is_dealt_out_evenly_only_where_that_pays():
     scratch = torch.empty(2 << 20)
-    assert ops.decode_plan(8, 8, 16, 32, 128, scratch) == ("split", 4)          # fewer pairs than places
-    assert ops.decode_plan(37, 8, 16, 32, 128, scratch) == ("split", 1)         # 296 pairs: one full round
-    how, blocks = ops.decode_plan(64, 8, 16, 32, 128, scratch)                  # 512 pairs: 1.73 rounds
+    assert ops.decode_plan(8, 8, 16, 32, 128, scratch, places=296) == ("split", 4)          # fewer pairs than places
+    assert ops.decode_plan(37, 8, 16, 32, 128, scratch, places=296) == ("split", 1)         # 296 pairs: one full round
+    how, blocks = ops.decode_plan(64, 8, 16, 32, 128, scratch, places=296)                  # 512 pairs: 1.73 rounds
     assert how == "flat" and blocks == 296
-    how, blocks = ops.decode_plan(104, 3, 1, 6, 64, scratch)                    # few kv heads bound the blocks
+    how, blocks = ops.decode_plan(104, 3, 1, 6, 64, scratch, places=296)                    # few kv heads bound the blocks
     assert how == "flat" and blocks == 62 * 3
-    assert ops.decode_plan(64, 8, 16, 32, 80, scratch)[0] == "split"            # a head size the flat kernel lacks
-    assert ops.decode_plan(64, 8, 16, 32, 128, torch.empty(1000))[0] == "split"  # no room for its partial results
+    assert ops.decode_plan(64, 8, 16, 32, 80, scratch, places=296)[0] == "split"            # a head size the flat kernel lacks
+    assert ops.decode_plan(64, 8, 16, 32, 128, torch.empty(1000), places=296)[0] == "split"  # no room for its partial results
