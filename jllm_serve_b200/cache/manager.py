@@ -247,7 +247,7 @@ class CacheManager:
             self._check(code)
         snap = self._snapshot(request)
         for g in self.fixed:          # a slot is handed out clean: whoever held it before left its state there
-            if g.storage is not None:
+            if hasattr(g.storage, "zero_"):
                 g.storage[:, snap.state_slot].zero_()
         return snap
 

@@ -49,8 +49,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
                         const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out, int out_stride,
                         const int* __restrict__ row_seg, const int* __restrict__ row_pos,
                         const int* __restrict__ block_tables, int table_stride, int heads, int kv_heads, int head_dim,
-                        int page_size, int window, float scale_log2, int splits, float* __restrict__ part_o,
-                        float* __restrict__ part_ml) {
+                        int page_size, int num_pages, int window, float scale_log2, int splits,
+                        float* __restrict__ part_o, float* __restrict__ part_ml) {
     extern __shared__ float smem[];  // [WARPS][16][head_dim] outputs, then [WARPS][16][2] (max, sum)
     const int r = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -96,11 +96,12 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
 #pragma unroll
         for (int tile = 0; tile < 2; ++tile) {
             const int key = base + tile * 8 + g;
-            const bool ok = key <= P;
+            bool ok = key <= P;
             const __nv_bfloat16* krow = nullptr;
             if (ok) {
-                const size_t page = table[key / page_size];
-                krow = k_cache + page * page_stride + ((size_t)kvh * page_size + key % page_size) * head_dim;
+                const long long page = jllm_page_of(table, key / page_size, table_stride, num_pages);
+                if (kCheckBounds && page < 0) ok = false;      // checked build: a bad table entry reads nothing
+                else krow = k_cache + (size_t)page * page_stride + ((size_t)kvh * page_size + key % page_size) * head_dim;
             }
 #pragma unroll
             for (int c = 0; c < KC; ++c) {
@@ -149,8 +150,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
             vok[i] = key <= P;
             vrow[i] = nullptr;
             if (vok[i]) {
-                const size_t page = table[key / page_size];
-                vrow[i] = v_cache + page * page_stride + ((size_t)kvh * page_size + key % page_size) * head_dim;
+                const long long page = jllm_page_of(table, key / page_size, table_stride, num_pages);
+                if (kCheckBounds && page < 0) vok[i] = false;
+                else vrow[i] = v_cache + (size_t)page * page_stride + ((size_t)kvh * page_size + key % page_size) * head_dim;
             }
         }
 #pragma unroll
@@ -278,6 +280,8 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
 
 }  // namespace
 
+JLLM_BOUNDS_READER(attention_decode)
+
 #include "attention_decode_staged.cuh"
 
 // Floats of scratch the split path needs: (head_dim + 2) per (row, head, split).
@@ -326,7 +330,8 @@ JLLM_EXPORT int jllm_attention_decode(const void* q, int q_stride, const void* k
         kern<<<grid, WARPS * 32, smem, stream>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache,  \
                                                  (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out, out_stride,    \
                                                  row_seg, row_pos, block_tables, table_stride, heads, kv_heads,     \
-                                                 head_dim, page_size, window, scale_log2, splits, part_o, part_ml); \
+                                                 head_dim, page_size, jllm_pool_pages(), window, scale_log2, splits, \
+                                                 part_o, part_ml);                                                  \
     }
     if (hdc == 1) JLLM_LAUNCH(1) else if (hdc == 2) JLLM_LAUNCH(2) else if (hdc == 3) JLLM_LAUNCH(3) else JLLM_LAUNCH(4)
 #undef JLLM_LAUNCH

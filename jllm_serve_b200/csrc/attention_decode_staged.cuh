@@ -52,7 +52,8 @@ template <int HD>
 __device__ __forceinline__ void attend(uint8_t* smem_raw, const __nv_bfloat16* __restrict__ q, int q_stride,
                                        const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
                                        __nv_bfloat16* __restrict__ out, int out_stride, const int* __restrict__ table,
-                                       int heads, int kv_heads, int page_size, float scale_log2, int r, int kvh, int P,
+                                       int table_len, int num_pages, int heads, int kv_heads, int page_size,
+                                       float scale_log2, int r, int kvh, int P,
                                        int first, int tile_lo, int n_tiles, bool whole, float* __restrict__ part_o,
                                        size_t o_stride, float* __restrict__ part_ml, size_t ml_stride) {
     constexpr int CHUNKS = HD / 8, TILE_BYTES = TILE * HD * 2, STAGE_BYTES = 2 * TILE_BYTES;
@@ -79,7 +80,9 @@ __device__ __forceinline__ void attend(uint8_t* smem_raw, const __nv_bfloat16* _
             if (key <= P) {
                 const int pg = page_shift >= 0 ? key >> page_shift : key / page_size;
                 const int in_page = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
-                o = (long long)((size_t)table[pg] * page_stride + ((size_t)kvh * page_size + in_page) * HD);
+                const long long page = jllm_page_of(table, pg, table_len, num_pages);   // -1: checked build, bad entry
+                if (!kCheckBounds || page >= 0)
+                    o = (long long)((size_t)page * page_stride + ((size_t)kvh * page_size + in_page) * HD);
             }
             s_row_base[i & 1][threadIdx.x] = o;
         }
@@ -243,8 +246,8 @@ attention_decode_staged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
                                const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
                                __nv_bfloat16* __restrict__ out, int out_stride, const int* __restrict__ row_seg,
                                const int* __restrict__ row_pos, const int* __restrict__ block_tables, int table_stride,
-                               int heads, int kv_heads, int page_size, int window, float scale_log2, int splits,
-                               float* __restrict__ part_o, float* __restrict__ part_ml) {
+                               int heads, int kv_heads, int page_size, int num_pages, int window, float scale_log2,
+                               int splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const int r = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int G = heads / kv_heads;
@@ -258,8 +261,8 @@ attention_decode_staged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
     const int* table = block_tables + (size_t)row_seg[r] * table_stride;
     // partials: (row, head, split) -> head_dim sums in part_o, (maximum, weight) in part_ml
     const size_t slot = ((size_t)r * heads + kvh * G) * splits + split;
-    attend<HD>(smem_raw, q, q_stride, k_cache, v_cache, out, out_stride, table, heads, kv_heads, page_size, scale_log2, r,
-               kvh, P, first, tile_lo, max(0, tile_hi - tile_lo), splits == 1, part_o + slot * HD, (size_t)splits * HD,
+    attend<HD>(smem_raw, q, q_stride, k_cache, v_cache, out, out_stride, table, table_stride, num_pages, heads, kv_heads,
+               page_size, scale_log2, r, kvh, P, first, tile_lo, max(0, tile_hi - tile_lo), splits == 1, part_o + slot * HD, (size_t)splits * HD,
                part_ml + slot * 2, (size_t)splits * 2);
 }
 
@@ -300,7 +303,7 @@ attention_decode_flat_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, 
                              const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out, int out_stride,
                              const int* __restrict__ row_seg, const int* __restrict__ row_pos,
                              const int* __restrict__ block_tables, int table_stride, int rows, int heads, int kv_heads,
-                             int page_size, int window, float scale_log2, float* __restrict__ part_o,
+                             int page_size, int num_pages, int window, float scale_log2, float* __restrict__ part_o,
                              float* __restrict__ part_ml) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ int s_cum[FLAT_MAX_ROWS + 1];
@@ -327,7 +330,8 @@ attention_decode_flat_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, 
         const int P = row_pos[r], first = window > 0 ? max(0, P + 1 - window) : 0;
         const size_t slot = (size_t)r * kv_heads + kvh + blockIdx.x;
         attend<HD>(smem_raw, q, q_stride, k_cache, v_cache, out, out_stride, block_tables + (size_t)row_seg[r] * table_stride,
-                   heads, kv_heads, page_size, scale_log2, r, kvh, P, first, tile_lo, n, false, part_o + slot * G * HD,
+                   table_stride, num_pages, heads, kv_heads, page_size, scale_log2, r, kvh, P, first, tile_lo, n, false,
+                   part_o + slot * G * HD,
                    (size_t)HD, part_ml + slot * G * 2, (size_t)2);
         at += n;
         __syncthreads();                              // shared memory is the next stretch's
@@ -401,7 +405,8 @@ void launch_flat(const void* q, int q_stride, const void* k_cache, const void* v
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     jllm_launch(kern, dim3(blocks), dim3(THREADS), smem, stream, true, (const __nv_bfloat16*)q, q_stride,
                 (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out, out_stride, row_seg,
-                row_pos, block_tables, table_stride, rows, heads, kv_heads, page_size, window, scale_log2, part_o, part_ml);
+                row_pos, block_tables, table_stride, rows, heads, kv_heads, page_size, jllm_pool_pages(), window, scale_log2,
+                part_o, part_ml);
     jllm_launch(attention_combine_flat_kernel, dim3(rows, heads), dim3(128), 0, stream, true, (const float*)part_o,
                 (const float*)part_ml, (__nv_bfloat16*)out, out_stride, row_pos, rows, heads, kv_heads, HD, window, blocks);
 }
@@ -419,7 +424,7 @@ void launch(const void* q, int q_stride, const void* k_cache, const void* v_cach
     jllm_launch(kern, dim3(rows, kv_heads, splits), dim3(THREADS), smem, stream, true,
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
         (__nv_bfloat16*)out, out_stride, row_seg, row_pos, block_tables, table_stride, heads, kv_heads, page_size,
-        window, scale_log2, splits, part_o, part_ml);
+        jllm_pool_pages(), window, scale_log2, splits, part_o, part_ml);
 }
 
 }  // namespace staged

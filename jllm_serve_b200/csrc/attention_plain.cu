@@ -23,7 +23,7 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, const T* __restric
                        const T* __restrict__ v_cache, T* __restrict__ out, int out_stride,
                        const int* __restrict__ row_seg, const int* __restrict__ row_pos,
                        const int* __restrict__ block_tables, int table_stride, int heads, int kv_heads, int head_dim,
-                       int page_size, int window, float scale) {
+                       int page_size, int num_pages, int window, float scale) {
     extern __shared__ float smem[];
     float* qs = smem;                  // head_dim
     float* es = qs + head_dim;         // THREADS
@@ -37,12 +37,14 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, const T* __restric
     for (int i = tid; i < head_dim; i += THREADS) qs[i] = to_float(qrow[i]);
     __syncthreads();
 
-    auto key_row = [&](const T* cache, int s) -> const T* {
-        const size_t page = table[s / page_size];
-        return cache + ((page * kv_heads + kvh) * page_size + (s % page_size)) * head_dim;
+    auto key_row = [&](const T* cache, int s) -> const T* {   // nullptr only in the checked build, for a bad table
+        const long long page = jllm_page_of(table, s / page_size, table_stride, num_pages);
+        if (kCheckBounds && page < 0) return nullptr;
+        return cache + (((size_t)page * kv_heads + kvh) * page_size + (s % page_size)) * head_dim;
     };
     auto score_of = [&](int s) -> float {
         const T* kr = key_row(k_cache, s);
+        if (kCheckBounds && kr == nullptr) return -INFINITY;
         float acc = 0.f;
         for (int i = 0; i < head_dim; ++i) acc = fmaf(qs[i], to_float(kr[i]), acc);
         return __fmul_rn(acc, scale);
@@ -64,6 +66,7 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, const T* __restric
             const float e = es[j];
             sum += e;
             const T* vr = key_row(v_cache, s0 + j);
+            if (kCheckBounds && vr == nullptr) continue;
 #pragma unroll
             for (int c = 0; c < MAX_DIMS_PER_THREAD; ++c) {
                 const int d = tid + c * THREADS;
@@ -82,6 +85,8 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, const T* __restric
 
 }  // namespace
 
+JLLM_BOUNDS_READER(attention_plain)
+
 JLLM_EXPORT int jllm_attention_plain(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
                                      int out_stride, const int* row_seg, const int* row_pos, const int* block_tables,
                                      int table_stride, int rows, int heads, int kv_heads, int head_dim, int page_size,
@@ -94,15 +99,16 @@ JLLM_EXPORT int jllm_attention_plain(const void* q, int q_stride, const void* k_
     JLLM_REQUIRE(heads <= 65535 && window >= 0, "attention: heads=%d window=%d", heads, window);
     if (rows == 0) return JLLM_OK;
     const dim3 grid(rows, heads);
+    const int num_pages = jllm_pool_pages();
     const size_t smem = (head_dim + THREADS + 33) * sizeof(float);
     if (dtype == JLLM_F32)
         attention_plain_kernel<float><<<grid, THREADS, smem, stream>>>(
             (const float*)q, q_stride, (const float*)k_cache, (const float*)v_cache, (float*)out, out_stride, row_seg,
-            row_pos, block_tables, table_stride, heads, kv_heads, head_dim, page_size, window, scale);
+            row_pos, block_tables, table_stride, heads, kv_heads, head_dim, page_size, num_pages, window, scale);
     else
         attention_plain_kernel<__nv_bfloat16><<<grid, THREADS, smem, stream>>>(
             (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
             (__nv_bfloat16*)out, out_stride, row_seg, row_pos, block_tables, table_stride, heads, kv_heads, head_dim,
-            page_size, window, scale);
+            page_size, num_pages, window, scale);
     return jllm_check_launch("attention_plain");
 }

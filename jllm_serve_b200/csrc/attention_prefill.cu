@@ -60,7 +60,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
                          const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out, int out_stride,
                          const int* __restrict__ seg_start, const int* __restrict__ seg_len,
                          const int* __restrict__ seg_kv_len, const int* __restrict__ block_tables, int table_stride,
-                         int num_segs, int heads, int kv_heads, int page_size, int window, float scale_log2) {
+                         int num_segs, int heads, int kv_heads, int page_size, int num_pages, int window,
+                         float scale_log2) {
     constexpr int CHUNKS = HD / 8;               // 16-byte chunks per row
     constexpr int TILE_BYTES = BKV * HD * 2;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -103,12 +104,14 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
         for (int i = threadIdx.x; i < BKV * CHUNKS; i += THREADS) {
             const int r = i / CHUNKS, c = i % CHUNKS;
             const int key = kt * BKV + r;
-            const bool ok = key >= first_key && key <= pos_last;
+            bool ok = key >= first_key && key <= pos_last;
             size_t off = 0;
             if (ok) {
                 const int pg = page_shift >= 0 ? key >> page_shift : key / page_size;
                 const int in_page = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
-                off = (size_t)table[pg] * page_stride + ((size_t)kvh * page_size + in_page) * HD + c * 8;
+                const long long page = jllm_page_of(table, pg, table_stride, num_pages);
+                if (kCheckBounds && page < 0) ok = false;       // checked build: a bad table entry reads nothing
+                else off = (size_t)page * page_stride + ((size_t)kvh * page_size + in_page) * HD + c * 8;
             }
             cp_async_16(dk + tile_offset<HD>(r, c), k_cache + off, ok ? 16 : 0);
             cp_async_16(dv + tile_offset<HD>(r, c), v_cache + off, ok ? 16 : 0);
@@ -265,11 +268,13 @@ int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache
     kern<<<grid, THREADS, smem, stream>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache,
                                           (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out, out_stride, seg_start,
                                           seg_len, seg_kv_len, block_tables, table_stride, num_segs, heads, kv_heads,
-                                          page_size, window, scale * LOG2E);
+                                          page_size, jllm_pool_pages(), window, scale * LOG2E);
     return jllm_check_launch("attention_prefill");
 }
 
 }  // namespace
+
+JLLM_BOUNDS_READER(attention_prefill)
 
 JLLM_EXPORT int jllm_attention_prefill_fits(int head_dim) { return head_dim == 64 || head_dim == 128 || head_dim == 256; }
 

@@ -48,7 +48,7 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
                               const int* __restrict__ seg_start, const int* __restrict__ seg_len,
                               const int* __restrict__ seg_kv_len, const int* __restrict__ block_tables,
                               int table_stride, int num_segs, int heads, int kv_heads, int page_size, int page_shift,
-                              int window, float scale_log2, int* __restrict__ error_word) {
+                              int num_pages, int window, float scale_log2, int* __restrict__ error_word) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
@@ -139,7 +139,9 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
                     const CUtensorMap* map = which ? &map_v : &map_k;
                     const int first_page = key0 >> page_shift;
                     for (int p = lane; p < (BKV >> page_shift); p += 32) {
-                        const int y = (table[first_page + p] * kv_heads + kvh) * page_size;
+                        // checked build: a bad entry gives -1 and a box of negative rows, which TMA fills with zeros
+                        const long long pg = jllm_page_of(table, first_page + p, table_stride, num_pages);
+                        const int y = (int)((pg * kv_heads + kvh) * page_size);
                         const uint32_t d = dst + ((p << page_shift) << 7);
                         tma_load_2d(d, map, 0, y, bar(full));
                         tma_load_2d(d + HALF_BYTES, map, 64, y, bar(full));
@@ -150,10 +152,13 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
                     for (int i = lane; i < BKV * 16; i += 32) {
                         const int r = i >> 4, c = i & 15;
                         const int key = key0 + r;
-                        const bool live = key >= first_key && key <= pos_last;
+                        bool live = key >= first_key && key <= pos_last;
                         size_t off = 0;
-                        if (live)
-                            off = (((size_t)table[key >> page_shift] * kv_heads + kvh) * page_size + (key & (page_size - 1))) * HD + c * 8;
+                        if (live) {
+                            const long long pg = jllm_page_of(table, key >> page_shift, table_stride, num_pages);
+                            if (kCheckBounds && pg < 0) live = false;
+                            else off = (((size_t)pg * kv_heads + kvh) * page_size + (key & (page_size - 1))) * HD + c * 8;
+                        }
                         const uint32_t d = dst + (c >> 3) * HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4);
                         cp_async_16(d, cache + off, live ? 16 : 0);
                     }
@@ -327,6 +332,8 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
 
 int* jllm_attention_tc_error_word_ptr();   // attention_prefill_tc.cu: one error word for both tcgen05 attention kernels
 
+JLLM_BOUNDS_READER(attention_prefill_pair)
+
 JLLM_EXPORT int jllm_attention_prefill_pair(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                                             long long cache_pages, void* out, int out_stride, const int* seg_start,
                                             const int* seg_len, const int* seg_kv_len, const int* block_tables,
@@ -362,7 +369,7 @@ JLLM_EXPORT int jllm_attention_prefill_pair(const void* q, int q_stride, const v
     const dim3 grid(heads, (rows + 2 * BQ - 1) / (2 * BQ) + num_segs);
     jllm_launch(kern, grid, dim3(THREADS), SMEM_BYTES, stream, true, map_q, map_k, map_v, (const __nv_bfloat16*)k_cache,
                 (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out, out_stride, seg_start, seg_len, seg_kv_len,
-                block_tables, table_stride, num_segs, heads, kv_heads, page_size, page_shift, window, scale * LOG2E,
-                error_word);
+                block_tables, table_stride, num_segs, heads, kv_heads, page_size, page_shift, (int)cache_pages, window,
+                scale * LOG2E, error_word);
     return jllm_check_launch("attention_prefill_pair");
 }

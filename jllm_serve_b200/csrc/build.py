@@ -24,6 +24,7 @@ from pathlib import Path
 
 CSRC = Path(__file__).resolve().parent
 LIB_NAME = "libjllm_b200.so"
+CHECKED_LIB_NAME = "libjllm_b200_checked.so"      # the same sources with -DJLLM_CHECK_BOUNDS
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
               "--expt-relaxed-constexpr"]
@@ -50,9 +51,15 @@ def _headers() -> list:
     return sorted(list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")))
 
 
-def _fingerprint(nvcc: str) -> str:
+def checked_build_wanted() -> bool:
+    """JLLM_B200_CHECK_BOUNDS=1 chooses the library whose kernels check every table index, page id, cache slot and
+    token id before they use it (slower; for tests and for hunting a fault)."""
+    return os.environ.get("JLLM_B200_CHECK_BOUNDS", "0") not in ("", "0")
+
+
+def _fingerprint(nvcc: str, extra=()) -> str:
     h = hashlib.sha256()
-    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
+    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + list(extra)).encode())
     h.update(nvcc.encode())
     for p in sources() + _headers():
         h.update(p.name.encode())
@@ -82,8 +89,8 @@ def _say(msg: str) -> None:
     print(f"[jllm-b200 build] {msg}", file=sys.stderr, flush=True)
 
 
-def _compile_one(nvcc: str, src: Path, obj: Path, verbose: bool) -> str:
-    cmd = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+def _compile_one(nvcc: str, src: Path, obj: Path, verbose: bool, extra=()) -> str:
+    cmd = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, *extra, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
@@ -93,19 +100,23 @@ def _compile_one(nvcc: str, src: Path, obj: Path, verbose: bool) -> str:
     return proc.stderr
 
 
-def ensure_built(force: bool = False, verbose: bool = False) -> Path:
-    """Returns the path of an up-to-date library, compiling it first if need be."""
+def ensure_built(force: bool = False, verbose: bool = False, checked: bool | None = None) -> Path:
+    """Returns the path of an up-to-date library, compiling it first if need be. `checked` (default: what
+    JLLM_B200_CHECK_BOUNDS says) chooses the variant with bounds checks, which is built beside the ordinary one."""
+    checked = checked_build_wanted() if checked is None else checked
+    extra = ["-DJLLM_CHECK_BOUNDS"] if checked else []
+    tag = "checked_" if checked else ""
     with _lock:
         nvcc = None
         out_dir = build_dir()
-        lib, stamp = out_dir / LIB_NAME, out_dir / "stamp.json"
+        lib, stamp = out_dir / (CHECKED_LIB_NAME if checked else LIB_NAME), out_dir / f"{tag}stamp.json"
         try:
             nvcc = find_nvcc()
         except BuildError:
             if lib.is_file() and not force:
                 return lib  # a prebuilt library travels with the tree; without nvcc it cannot be checked
             raise
-        want = _fingerprint(nvcc)
+        want = _fingerprint(nvcc, extra)
         if not force and lib.is_file() and stamp.is_file():
             try:
                 if json.loads(stamp.read_text()).get("fingerprint") == want:
@@ -113,7 +124,8 @@ def ensure_built(force: bool = False, verbose: bool = False) -> Path:
             except (json.JSONDecodeError, OSError):
                 pass
         srcs = sources()
-        _say(f"compiling {len(srcs)} CUDA files for sm_100a into {out_dir} (first call, or a source changed)")
+        _say(f"compiling {len(srcs)} CUDA files for sm_100a into {out_dir} (first call, or a source changed)"
+             + (", with bounds checks" if checked else ""))
         t0 = time.time()
         done = []
         stop = threading.Event()
@@ -129,17 +141,17 @@ def ensure_built(force: bool = False, verbose: bool = False) -> Path:
             with ThreadPoolExecutor(max_workers=min(len(srcs), os.cpu_count() or 4)) as pool:
                 futures = {}
                 for s in srcs:
-                    obj = out_dir / (s.stem + ".o")
-                    futures[pool.submit(_compile_one, nvcc, s, obj, verbose)] = s
+                    obj = out_dir / (tag + s.stem + ".o")
+                    futures[pool.submit(_compile_one, nvcc, s, obj, verbose, extra)] = s
                 for fut, s in futures.items():
                     logs[s.name] = fut.result()
                     done.append(s)
                     _say(f"compiled {s.name} ({len(done)}/{len(srcs)}, {time.time() - t0:.0f} s)")
-            tmp = out_dir / (LIB_NAME + f".tmp{os.getpid()}")
-            link = [nvcc, *ARCH_FLAGS, "-shared", "-o", str(tmp)] + [str(out_dir / (s.stem + ".o")) for s in srcs]
+            tmp = out_dir / (lib.name + f".tmp{os.getpid()}")
+            link = [nvcc, *ARCH_FLAGS, "-shared", "-o", str(tmp)] + [str(out_dir / (tag + s.stem + ".o")) for s in srcs]
             proc = subprocess.run(link, capture_output=True, text=True)
             if proc.returncode != 0:
-                raise BuildError(f"linking {LIB_NAME} failed:\n{proc.stdout}\n{proc.stderr}")
+                raise BuildError(f"linking {lib.name} failed:\n{proc.stdout}\n{proc.stderr}")
             os.replace(tmp, lib)
             stamp.write_text(json.dumps({"fingerprint": want, "seconds": round(time.time() - t0, 1)}))
         finally:

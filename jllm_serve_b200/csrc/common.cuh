@@ -26,11 +26,70 @@ enum JllmError : int {
 int jllm_fail(int code, const char* fmt, ...);
 int jllm_check_launch(const char* what);
 int jllm_device_sm_count();      // SMs of the current device (asked once), 0 if unknown
+int jllm_pool_pages();           // pages of the cache pool in use, as the host declared them (0 = unknown)
 
 #define JLLM_REQUIRE(cond, ...)                                   \
     do {                                                          \
         if (!(cond)) return jllm_fail(JLLM_BAD_ARGUMENT, __VA_ARGS__); \
     } while (0)
+
+// ---- bounds checks of what the kernels read through tables (a build with -DJLLM_CHECK_BOUNDS) --------------------
+// The kernels follow page tables, slot lists and token ids that the host packed. In the ordinary build they trust
+// them. In the checked build (a second library, chosen with JLLM_B200_CHECK_BOUNDS=1) every table index, page id,
+// cache slot and token id is compared with its limit first; an access that would leave its array is SKIPPED (a key
+// then counts as absent, a write is dropped) and the first such case is recorded in a word of this translation unit:
+// {what, index, limit, how many}. Nothing traps and nothing hangs: the host reads the words after the step
+// (`jllm_bounds_error_<file>`) and raises. A limit of 0 or less means "not known to this caller": only negative
+// indices are caught then.
+enum : int { BOUNDS_TABLE_INDEX = 1, BOUNDS_PAGE = 2, BOUNDS_SLOT = 3, BOUNDS_TOKEN = 4, BOUNDS_ROW = 5 };
+#ifdef JLLM_CHECK_BOUNDS
+constexpr bool kCheckBounds = true;
+static __device__ int jllm_bounds_word[4];
+__device__ __noinline__ static void jllm_bounds_record(int what, long long index, long long limit) {
+    if (atomicAdd(&jllm_bounds_word[3], 1) == 0) {
+        jllm_bounds_word[0] = what;
+        jllm_bounds_word[1] = (int)max(-2147483647ll, min(2147483647ll, index));
+        jllm_bounds_word[2] = (int)max(-2147483647ll, min(2147483647ll, limit));
+    }
+}
+#define JLLM_BOUNDS_READER(file)                                                                   \
+    JLLM_EXPORT int jllm_bounds_error_##file(int* out4) {                                          \
+        int zero[4] = {0, 0, 0, 0};                                                                \
+        if (cudaMemcpyFromSymbol(out4, jllm_bounds_word, sizeof(zero)) != cudaSuccess) return JLLM_CUDA_ERROR; \
+        if (out4[3] && cudaMemcpyToSymbol(jllm_bounds_word, zero, sizeof(zero)) != cudaSuccess) return JLLM_CUDA_ERROR; \
+        return JLLM_OK;                                                                            \
+    }
+#else
+constexpr bool kCheckBounds = false;
+#define JLLM_BOUNDS_READER(file)                                  \
+    JLLM_EXPORT int jllm_bounds_error_##file(int* out4) {         \
+        out4[0] = out4[1] = out4[2] = out4[3] = 0;                \
+        return JLLM_OK;                                           \
+    }
+#endif
+
+// True if `index` may be used; always true in the ordinary build (the check compiles to nothing).
+__device__ __forceinline__ bool jllm_in_bounds(long long index, long long limit, int what) {
+#ifdef JLLM_CHECK_BOUNDS
+    if (index < 0 || (limit > 0 && index >= limit)) {
+        jllm_bounds_record(what, index, limit);
+        return false;
+    }
+#endif
+    return true;
+}
+
+// The page of block `b` of a request's table; in the checked build -1 if the block lies outside the table's row or the
+// page outside the pool (the caller then skips the access).
+__device__ __forceinline__ long long jllm_page_of(const int* __restrict__ table, int b, int table_len, int num_pages) {
+#ifdef JLLM_CHECK_BOUNDS
+    if (!jllm_in_bounds(b, table_len, BOUNDS_TABLE_INDEX)) return -1;
+    const int page = table[b];
+    return jllm_in_bounds(page, num_pages, BOUNDS_PAGE) ? page : -1;
+#else
+    return table[b];
+#endif
+}
 
 // ---- programmatic dependent launch ---------------------------------------------------------------------
 // A decode step is a chain of some hundreds of short kernels. Launched the ordinary way each one starts

@@ -48,7 +48,11 @@ template <typename Tout, int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, VecRef bias,
                     int has_bias, Tout* __restrict__ out, int ldo, int accumulate, int M, int N, int K, int swiglu,
-                    int stream, float* __restrict__ partials, int* __restrict__ counters, int* __restrict__ error_word) {
+                    int stream, float* __restrict__ partials, int* __restrict__ counters, int* __restrict__ error_word,
+                    int starve) {
+    // `starve` (a test of the bounded waits, never set otherwise): the first stage's barrier expects 16 bytes more than
+    // the copies bring, so it never completes, and every wait gives up after 1,024 tries instead of 4 million.
+    const uint32_t spin = starve ? 1024u : SPIN_LIMIT;
     constexpr int STAGES = stages_for(BN), B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
     constexpr uint32_t IDESC = idesc_for(BN);
     static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "tile width");
@@ -138,8 +142,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             while (ok && next_unit(walk, tile, lo, hi)) {
                 const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
                 for (int kb = lo; kb < hi; ++kb) {
-                    if (!mbar_wait(empty_bar(s), parity, abort_flag)) { ok = false; break; }
-                    mbar_expect_tx(full_bar(s), STAGE_BYTES);
+                    if (!mbar_wait(empty_bar(s), parity, abort_flag, spin)) { ok = false; break; }
+                    mbar_expect_tx(full_bar(s), STAGE_BYTES + ((starve && kb == lo) ? 16u : 0u));
                     tma_load_2d(dst, &map_a, kb * BK, m0, full_bar(s));
                     tma_load_2d(dst + A_BYTES, &map_w, kb * BK, n0, full_bar(s));
                     dst += STAGE_BYTES;
@@ -158,11 +162,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int tile, lo, hi;
             for (; ok && next_unit(walk, tile, lo, hi); ++local_tile) {
                 const uint32_t buf = local_tile & 1u;
-                if (!mbar_wait(acc_empty_bar(buf), ((local_tile >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(acc_empty_bar(buf), ((local_tile >> 1) & 1u) ^ 1u, abort_flag, spin)) { ok = false; break; }
                 tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + buf * BN;
                 for (int kb = lo; kb < hi; ++kb) {
-                    if (!mbar_wait(full_bar(s), parity, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(full_bar(s), parity, abort_flag, spin)) { ok = false; break; }
                     tcgen05_fence_after();
                     const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
@@ -189,7 +193,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (; ok && next_unit(walk, tile, k_lo, k_hi); ++local_tile) {
             const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
             const uint32_t buf = local_tile & 1u;
-            if (!mbar_wait(acc_full_bar(buf), (local_tile >> 1) & 1u, abort_flag)) { ok = false; break; }
+            if (!mbar_wait(acc_full_bar(buf), (local_tile >> 1) & 1u, abort_flag, spin)) { ok = false; break; }
             tcgen05_fence_after();
             const int row = m0 + quad * 32 + lane;
             const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quad * 32) << 16);
@@ -413,6 +417,14 @@ JLLM_EXPORT int jllm_gemm_tcgen05_error() {
     return v;
 }
 
+// A test of the bounded waits: the NEXT product launched through jllm_gemm_tcgen05 by this thread starves (its first
+// barrier expects more bytes than arrive and its waits give up after 1,024 tries): it must return, raise the error
+// word and leave the device usable. The test keeps that product to a single tile.
+namespace {
+thread_local int g_starve_next = 0;
+}
+JLLM_EXPORT void jllm_gemm_tcgen05_starve_next() { g_starve_next = 1; }
+
 JLLM_EXPORT int jllm_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, const void* bias, int bias_dtype,
                                   void* out, int out_dtype, int ldo, int accumulate, int M, int N, int K, int max_blocks,
                                   int swiglu, float* workspace, long long workspace_floats, int stream_mode,
@@ -472,6 +484,10 @@ JLLM_EXPORT int jllm_gemm_tcgen05(const void* a, int lda, const void* w, int ldw
     int* counters = reinterpret_cast<int*>(workspace);
     float* partials = workspace ? workspace + JLLM_TC_MAX_TILES : nullptr;
     const int splits = streamed ? 1 : 0;      // the kernel's `stream` argument
+    const int starve = g_starve_next;
+    g_starve_next = 0;
+    JLLM_REQUIRE(!starve || (tiles == 1 && k_blocks <= 2), "gemm_tcgen05: the starved product of the wait test is one "
+                 "tile of at most two k blocks (got %d tiles, %d k blocks)", tiles, k_blocks);
     const VecRef b{bias, bias_dtype};
 #define JLLM_TC_GO(T, W)                                                                                              \
     do {                                                                                                              \
@@ -479,7 +495,7 @@ JLLM_EXPORT int jllm_gemm_tcgen05(const void* a, int lda, const void* w, int ldw
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes_for(W));             \
         jllm_launch(kern, dim3(grid), dim3(THREADS), smem_bytes_for(W), stream, true, map_a, map_w, b,                \
                     (int)(bias != nullptr), (T*)out, ldo, accumulate, M, N, K, swiglu, splits, partials, counters,    \
-                    error_word);                                                                                      \
+                    error_word, starve);                                                                              \
     } while (0)
 #define JLLM_TC_WIDTHS(T)                                                                                             \
     switch (BN) {                                                                                                     \

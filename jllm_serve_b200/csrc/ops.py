@@ -118,6 +118,14 @@ class _Signatures:
     P, I, F = c_void_p, c_int, c_float
     jllm_check_device = []
     jllm_sm_count = []
+    jllm_checks_bounds = []
+    jllm_set_pool_pages = [I]
+    jllm_bounds_error_attention_plain = [P]
+    jllm_bounds_error_attention_decode = [P]
+    jllm_bounds_error_attention_prefill = [P]
+    jllm_bounds_error_attention_prefill_tc = [P]
+    jllm_bounds_error_attention_prefill_pair = [P]
+    jllm_bounds_error_rowwise = [P]
     jllm_set_pdl = [I]
     jllm_launch_plan = [ctypes.c_longlong, I]
     jllm_embed_rows = [P, P, I, P, I, I, I, P]
@@ -128,6 +136,7 @@ class _Signatures:
     jllm_gemm_small_m = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, I, I, P]
     jllm_gemm_tcgen05 = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, I, P, ctypes.c_longlong, I, I, P]
     jllm_gemm_tcgen05_error = []
+    jllm_gemm_tcgen05_starve_next = []
     jllm_attention_plain = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P]
     jllm_attention_decode = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
     jllm_attention_decode_flat = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
@@ -274,14 +283,58 @@ def gemm_tcgen05(a, w, out, bias=None, accumulate=False, max_blocks: int = 0, sw
           ws.numel() if ws is not None else 0, int(stream_mode), int(tile_width), _stream())
 
 
+BOUNDS_FILES = ("attention_plain", "attention_decode", "attention_prefill", "attention_prefill_tc",
+                "attention_prefill_pair", "rowwise")
+BOUNDS_WHAT = {1: "a block-table index", 2: "a page id", 3: "a cache slot", 4: "a token id", 5: "a row"}
+
+
+def checks_bounds() -> bool:
+    """Whether the loaded library is the one built with bounds checks (JLLM_B200_CHECK_BOUNDS=1)."""
+    return bool(library().jllm_checks_bounds())
+
+
+def set_pool_pages(pages: int) -> None:
+    """Tells the library how many pages the cache pool has that the next launches read and write. Only the library
+    with bounds checks uses it (page ids and cache slots are compared with it)."""
+    library().jllm_set_pool_pages(int(pages))
+
+
+def bounds_errors() -> dict:
+    """{file: (what, index, limit, how many)} for every file of kernels whose checks caught something since the last
+    call (only the library built with bounds checks ever reports any). Synchronises."""
+    out = {}
+    lib = library()
+    word = (c_int * 4)()
+    for name in BOUNDS_FILES:
+        code = getattr(lib, "jllm_bounds_error_" + name)(word)
+        if code:
+            raise KernelError(f"reading the bounds word of {name} failed ({code})")
+        if word[3]:
+            out[name] = (BOUNDS_WHAT.get(word[0], str(word[0])), word[1], word[2], word[3])
+    return out
+
+
 def check_kernel_errors() -> None:
     """Raises if a tcgen05 kernel gave up on one of its bounded waits since the last check (its results are then
-    not to be trusted). Reads three words from the device, so it synchronises."""
+    not to be trusted), or, in the build with bounds checks, if a kernel was handed a table index, page id, cache
+    slot or token id outside its array (the access was skipped). Reads a few words from the device, so it
+    synchronises."""
     lib = library()
     raised = {name: code for name, code in (("gemm_tcgen05", lib.jllm_gemm_tcgen05_error()),
                                             ("attention_prefill_tc", lib.jllm_attention_prefill_tc_error())) if code}
     if raised:
         raise KernelError("a bounded wait ran out inside " + ", ".join(f"{k} (code {v})" for k, v in raised.items()))
+    if checks_bounds():
+        caught = bounds_errors()
+        if caught:
+            raise KernelError("out of bounds (the accesses were skipped): " + "; ".join(
+                f"{name}: {what} {index} with limit {limit}, {n} in all" for name, (what, index, limit, n) in caught.items()))
+
+
+def gemm_tcgen05_starve_next() -> None:
+    """A test of the bounded waits: the next tcgen05 product (one tile) is given a barrier that never completes and
+    waits that give up after 1,024 tries; it returns and raises the error word that `check_kernel_errors` reads."""
+    library().jllm_gemm_tcgen05_starve_next()
 
 
 def gemm_tcgen05_error() -> int:

@@ -15,11 +15,14 @@ __global__ void embed_rows_kernel(const int* __restrict__ ids, const T* __restri
                                   int dim, int vocab) {
     const int r = blockIdx.x;
     int id = ids[r];
+    jllm_in_bounds(id, vocab, BOUNDS_TOKEN);           // checked build: recorded
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // ids are validated on the host; never read out of bounds
     const T* src = table + (size_t)id * dim;
     float* dst = x + (size_t)r * dim;
     for (int i = threadIdx.x; i < dim; i += blockDim.x) dst[i] = to_float(src[i]);
 }
+
+JLLM_BOUNDS_READER(rowwise)
 
 JLLM_EXPORT int jllm_embed_rows(const int* ids, const void* table, int table_dtype, float* x, int rows, int dim,
                                 int vocab, cudaStream_t stream) {
@@ -171,7 +174,7 @@ __global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, VecRef q_gain, Ve
                                           int rotary_dim, const int* __restrict__ positions,
                                           const int* __restrict__ slots, T* __restrict__ k_cache,
                                           T* __restrict__ v_cache, int heads, int kv_heads, int head_dim,
-                                          int page_size, int row_stride) {
+                                          int page_size, int num_slots, int row_stride) {
     extern __shared__ float vec[];  // head_dim floats + 33 scratch
     float* scratch = vec + head_dim;
     pdl_wait();
@@ -208,6 +211,7 @@ __global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, VecRef q_gain, Ve
     } else {
         const int kvh = is_k ? h - heads : h - heads - kv_heads;
         const int slot = slots[r];
+        if (!jllm_in_bounds(slot, num_slots, BOUNDS_SLOT)) return;      // checked build: the write is dropped
         const size_t page = slot / page_size, off = slot % page_size;
         T* dst = (is_k ? k_cache : v_cache) + ((page * kv_heads + kvh) * page_size + off) * head_dim;
         for (int i = threadIdx.x; i < head_dim; i += blockDim.x) dst[i] = from_float<T>(vec[i]);
@@ -222,7 +226,7 @@ __global__ void __launch_bounds__(256)
 qk_norm_rope_store_warp_kernel(T* __restrict__ qkv, VecRef q_gain, VecRef k_gain, int use_norm, float eps,
                                const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                const int* __restrict__ positions, const int* __restrict__ slots, T* __restrict__ k_cache,
-                               T* __restrict__ v_cache, int heads, int kv_heads, int page_size, int row_stride,
+                               T* __restrict__ v_cache, int heads, int kv_heads, int page_size, int num_slots, int row_stride,
                                int heads_total, long long items) {
     constexpr int HD = 64 * V, HALF = 32 * V;
     pdl_wait();
@@ -267,6 +271,7 @@ qk_norm_rope_store_warp_kernel(T* __restrict__ qkv, VecRef q_gain, VecRef k_gain
     if (!is_q) {
         const int kvh = is_k ? h - heads : h - heads - kv_heads;
         const int slot = slots[r];
+        if (!jllm_in_bounds(slot, num_slots, BOUNDS_SLOT)) return;      // checked build: the write is dropped
         const size_t page = slot / page_size, off = slot % page_size;
         dst = (is_k ? k_cache : v_cache) + ((page * kv_heads + kvh) * page_size + off) * HD;
     }
@@ -287,7 +292,7 @@ qk_norm_rope_store_vec_kernel(__nv_bfloat16* __restrict__ qkv, VecRef q_gain, Ve
                               const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                               const int* __restrict__ positions, const int* __restrict__ slots,
                               __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int heads,
-                              int kv_heads, int page_size, int row_stride, int heads_total, long long items) {
+                              int kv_heads, int page_size, int num_slots, int row_stride, int heads_total, long long items) {
     constexpr int HD = 64 * V, HALF = 32 * V, LANES = 4 * V, PER_WARP = 32 / LANES;
     pdl_wait();
     pdl_trigger();
@@ -344,6 +349,7 @@ qk_norm_rope_store_vec_kernel(__nv_bfloat16* __restrict__ qkv, VecRef q_gain, Ve
     if (!is_q) {
         const int kvh = is_k ? h - heads : h - heads - kv_heads;
         const int slot = slots[r];
+        if (!jllm_in_bounds(slot, num_slots, BOUNDS_SLOT)) return;      // checked build: the write is dropped
         const size_t page = slot / page_size, off = slot % page_size;
         dst = (is_k ? k_cache : v_cache) + ((page * kv_heads + kvh) * page_size + off) * HD;
     }
@@ -373,6 +379,7 @@ JLLM_EXPORT int jllm_qk_norm_rope_store(void* qkv, int dtype, const void* q_gain
                  "qk_norm_rope_store: row_stride=%d is too small", row_stride);
     JLLM_REQUIRE(head_dim <= 8192, "qk_norm_rope_store: head_dim=%d is above 8192", head_dim);
     if (rows == 0) return JLLM_OK;
+    const int num_slots = (int)min((long long)jllm_pool_pages() * page_size, 2147483647ll);   // 0 = not known
     const dim3 grid(rows, write_kv ? heads + 2 * kv_heads : heads);
     const int threads = head_dim <= 64 ? 32 : (head_dim <= 128 ? 64 : 128);
     const size_t smem = (head_dim + 33) * sizeof(float);
@@ -383,7 +390,7 @@ JLLM_EXPORT int jllm_qk_norm_rope_store(void* qkv, int dtype, const void* q_gain
         const dim3 wgrid((unsigned)((items + 7) / 8));
 #define JLLM_WARP_ROPE(T, V)                                                                                          \
     jllm_launch(qk_norm_rope_store_warp_kernel<T, V>, wgrid, dim3(256), 0, stream, true, (T*)qkv, qg, kg, use_norm, eps, \
-                cos_t, sin_t, positions, slots, (T*)k_cache, (T*)v_cache, heads, kv_heads, page_size, row_stride,      \
+                cos_t, sin_t, positions, slots, (T*)k_cache, (T*)v_cache, heads, kv_heads, page_size, num_slots, row_stride,      \
                 heads_total, items)
         const int v = head_dim / 64;
         // the 16-byte kernel from 32 rows on (fewer rows are too few warps for it; JLLM_B200_ROPE_VEC_MIN_ROWS moves that)
@@ -398,7 +405,7 @@ JLLM_EXPORT int jllm_qk_norm_rope_store(void* qkv, int dtype, const void* q_gain
 #define JLLM_VEC_ROPE(V)                                                                                              \
     jllm_launch(qk_norm_rope_store_vec_kernel<V>, vgrid, dim3(256), 0, stream, true, (__nv_bfloat16*)qkv, qg, kg,     \
                 use_norm, eps, cos_t, sin_t, positions, slots, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, heads, \
-                kv_heads, page_size, row_stride, heads_total, items)
+                kv_heads, page_size, num_slots, row_stride, heads_total, items)
             if (v == 1) JLLM_VEC_ROPE(1); else if (v == 2) JLLM_VEC_ROPE(2); else JLLM_VEC_ROPE(4);
 #undef JLLM_VEC_ROPE
             return jllm_check_launch("qk_norm_rope_store");
@@ -415,10 +422,10 @@ JLLM_EXPORT int jllm_qk_norm_rope_store(void* qkv, int dtype, const void* q_gain
     if (dtype == JLLM_F32)
         jllm_launch(qk_norm_rope_store_kernel<float>, grid, dim3(threads), smem, stream, true,
             (float*)qkv, qg, kg, use_norm, eps, cos_t, sin_t, rotary_dim, positions, slots, (float*)k_cache,
-            (float*)v_cache, heads, kv_heads, head_dim, page_size, row_stride);
+            (float*)v_cache, heads, kv_heads, head_dim, page_size, num_slots, row_stride);
     else
         jllm_launch(qk_norm_rope_store_kernel<__nv_bfloat16>, grid, dim3(threads), smem, stream, true,
             (__nv_bfloat16*)qkv, qg, kg, use_norm, eps, cos_t, sin_t, rotary_dim, positions, slots,
-            (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, heads, kv_heads, head_dim, page_size, row_stride);
+            (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, heads, kv_heads, head_dim, page_size, num_slots, row_stride);
     return jllm_check_launch("qk_norm_rope_store");
 }

@@ -85,6 +85,17 @@ int jllm_device_sm_count() {
     return counts[dev];
 }
 
+// Pages of the cache pool that the launches which follow read and write (0 = not known). Only the build with bounds
+// checks uses it: there every page id is compared with it and every cache slot with pages x page size.
+namespace {
+int g_pool_pages = 0;
+}
+int jllm_pool_pages() { return g_pool_pages; }
+JLLM_EXPORT void jllm_set_pool_pages(int pages) { g_pool_pages = pages > 0 ? pages : 0; }
+
+// 1 if this library was built with bounds checks (-DJLLM_CHECK_BOUNDS), else 0.
+JLLM_EXPORT int jllm_checks_bounds() { return kCheckBounds ? 1 : 0; }
+
 JLLM_EXPORT int jllm_sm_count() { return jllm_device_sm_count(); }
 
 JLLM_EXPORT int jllm_abi_version() { return 1; }

@@ -100,6 +100,7 @@ class ModelRunner:
         self.builder = BatchBuilder(self.device, self.max_rows, self.max_requests, max_blocks, len(self.cache.paged),
                                     self.page_size, ops.resident_blocks())
         self.steps = 0
+        self._checked = ops.checks_bounds()
         self.use_graphs = bool(cuda_graphs)
         self.graph_safe = bool(getattr(self.model, "graph_safe", False))    # a model that does not say is not replayed
         self._graphs, self._graph_seen, self._static_logits, self._graph_kernels = {}, set(), None, {}
@@ -202,6 +203,8 @@ class ModelRunner:
             for r in opened:
                 self.cache.close(r)
             raise
+        if self._checked:
+            ops.set_pool_pages(self.cache.num_pages)     # the library with bounds checks compares page ids with it
         try:
             logits = self._run_model(batch, logits_out)
         except Exception:

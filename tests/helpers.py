@@ -59,6 +59,8 @@ def replay(runner, steps) -> dict:
 
     out = collect(steps, run)
     runner.cache.check()
+    from jllm_serve_b200.csrc import ops
+    ops.check_kernel_errors()        # bounded waits that ran out; in the checked build also accesses out of bounds
     return out
 
 
@@ -143,3 +145,5 @@ def replay_checked(runner, steps, checker: RowChecker) -> None:
             runner.finish(rid)
             fed.pop(rid, None)
     runner.cache.check()
+    from jllm_serve_b200.csrc import ops
+    ops.check_kernel_errors()

@@ -220,3 +220,45 @@ def test_batch_tables_follow_the_requests_tables():
     for _ in range(8):
         reqs = rng.sample(["a", "b"], 2)
         step(reqs, {"a": rng.randint(1, 3), "b": 1})
+
+
+def test_pool_sized_from_free_memory():
+    """A share of what is free after a reserve, in whole pages over all groups, capped by what the requests can use
+    (the reference's context budget: src/main/java/org/robomiri/jllm/ContextBudget.java:30-40,143-186)."""
+    from jllm_serve_b200.cache import plan_pages
+    from jllm_serve_b200.cache.budget import group_page_bytes
+    GB = 1 << 30
+    # Qwen3-32B shape: 64 layer runs, 8 kv heads of 128, pages of 16 positions, bfloat16: 4 MiB a page
+    per_page = group_page_bytes(64, 8, 128, 16, 2)
+    assert per_page == 64 * 2 * 8 * 16 * 128 * 2 == 4 << 20
+    plan = plan_pages(free_bytes=110 * GB, total_bytes=180 * GB, page_bytes_by_group=[per_page], page_size=16, ctx=8192,
+                      max_requests=64, share=0.9, held_bytes=1 * GB)
+    reserve = 180 * GB // 32
+    assert plan.limited_by == "memory" and plan.pages == int(0.9 * (110 * GB - GB - reserve)) // per_page
+    assert plan.pool_bytes <= plan.budget < plan.pool_bytes + per_page
+    few = plan_pages(110 * GB, 180 * GB, [per_page], 16, 8192, max_requests=4, share=0.9)
+    assert few.limited_by == "requests" and few.pages == 4 * 512          # never more than the requests can use
+    two = plan_pages(10 * GB, 180 * GB, [per_page, per_page // 2], 16, 1 << 20, 64, 0.6)
+    assert two.bytes_per_page == per_page * 3 // 2 and two.pages == int(0.6 * (10 * GB - reserve)) // two.bytes_per_page
+    with pytest.raises(MemoryError):
+        plan_pages(5 * GB, 180 * GB, [per_page], 16, 8192, 4, 0.6)          # the reserve alone is 5.6 GB: nothing is left
+    with pytest.raises(ValueError):
+        plan_pages(110 * GB, 180 * GB, [per_page], 16, 8192, 4, share=1.5)
+    assert plan_pages(110 * GB, 180 * GB, [], 16, 8192, 4).pages == 1     # a model that keeps no keys and values
+    from jllm_serve_b200.cache import CacheManager, FixedState, PagedKeysValues
+    needs = [PagedKeysValues(2, 16), (PagedKeysValues(2, 16, window=8), FixedState((3,))), None, PagedKeysValues(2, 16)]
+    assert CacheManager.page_bytes(needs, 4, 2) == [2 * 2 * 2 * 4 * 16 * 2, 1 * 2 * 2 * 4 * 16 * 2]
+
+
+def test_a_run_may_keep_paged_keys_and_a_state():
+    from jllm_serve_b200.cache import CacheManager, FixedState, PagedKeysValues
+    needs = [(PagedKeysValues(2, 16), FixedState((5,))), FixedState((5,)), (FixedState((5,)), FixedState((5,)), FixedState((2,)))]
+    made = {}
+    m = CacheManager(needs, 4, 10, 3, allocate=lambda shape, kind: made.setdefault((shape, kind), object()))
+    assert [g.runs for g in m.paged] == [[0]] and [g.runs for g in m.fixed] == [[0, 1, 2], [2], [2]]
+    assert m.paged_of_run == {0: 0} and m.fixed_of_run == {0: [0], 1: [0], 2: [0, 1, 2]}
+    assert ((3, 3, 5), "float32") in made and ((1, 3, 5), "float32") in made and ((1, 3, 2), "float32") in made
+    with pytest.raises(TypeError, match="two needs of paged"):
+        CacheManager([(PagedKeysValues(2, 16), PagedKeysValues(2, 16, window=4))], 4, 10, 3)
+    with pytest.raises(KeyError):
+        m.state(0, 1)

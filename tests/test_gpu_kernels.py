@@ -238,8 +238,29 @@ def test_qk_norm_rope_store(ops, dtype, H, Hkv, hd, rot, norm):
     assert torch.isnan(rest).all()                                   # nothing else was touched
 
 
-def attention_case(ops, dtype, H, Hkv, hd, page, lens, window, scale, make_far_key=False, q_lens=None):
-    """Several requests of `lens` cached positions each; the last `q_len` positions of each are the step's rows."""
+def rows_close(got, want, what="", share=2 ** -7, floor=2e-4):
+    """Every row within `share` of ITS OWN largest |value| (plus a floor for rounding of values near zero): an absolute
+    tolerance sized for the largest row would let a damaged row of small values through. Returns the worst ratio."""
+    got, want = got.float().cpu(), want.float().cpu()
+    assert torch.isfinite(got).all(), f"{what}: non-finite values"
+    tol = share * want.abs().amax(dim=-1, keepdim=True) + floor
+    ratio = ((got - want).abs() / tol).amax(dim=-1)
+    worst = int(ratio.argmax())
+    assert float(ratio[worst]) <= 1.0, (f"{what}: row {worst} differs by {float((got[worst] - want[worst]).abs().max()):.3e}, "
+                                        f"its largest |value| is {float(want[worst].abs().max()):.3e}")
+    return float(ratio[worst])
+
+
+MODES = ("random", "far", "planted")
+
+
+def attention_case(ops, dtype, H, Hkv, hd, page, lens, window, scale, make_far_key=False, q_lens=None, planted=False):
+    """Several requests of `lens` cached positions each; the last `q_len` positions of each are the step's rows.
+    `make_far_key` (True or "far"): one early key that the last query matches strongly. `planted` (or the mode
+    "planted"): one key in every 64-key tile that EVERY query matches strongly, with a value that tells which tile
+    it came from, so every row's result is large and a tile that is dropped, doubled or misplaced changes it."""
+    planted = planted or make_far_key == "planted"
+    make_far_key = make_far_key is True or make_far_key == "far"
     torch.manual_seed(H * 1000 + hd + page)
     nseq = len(lens)
     q_lens = q_lens or [min(l, 1 + 3 * i) for i, l in enumerate(lens)]
@@ -261,6 +282,14 @@ def attention_case(ops, dtype, H, Hkv, hd, page, lens, window, scale, make_far_k
             q[L - 1, :, :] *= 0.05
             q[L - 1, :, 0] = hd ** 0.5
             v[far] = 7.0
+        if planted:
+            marks = torch.arange(17 if L > 17 else 0, L, 64)
+            k[:, :, 1] = 0                     # only the planted keys answer to the queries' large component
+            k[marks] = 0
+            k[marks, :, 1] = 1.0
+            v[marks] = (10.0 * (1 + torch.arange(len(marks), dtype=torch.float32)))[:, None, None] * (1 + 0.1 * torch.randn(len(marks), Hkv, hd))
+            q *= 0.3
+            q[:, :, 1] = 8.0 / scale
         k, v, q = k.to(dtype).float(), v.to(dtype).float(), q.to(dtype).float()
         for b in range(-(-L // page)):
             pg = perm.pop()
@@ -285,18 +314,19 @@ def attention_case(ops, dtype, H, Hkv, hd, page, lens, window, scale, make_far_k
                                                    (6, 3, 80, 8, 21), (4, 2, 256, 16, 0), (2, 1, 32, 1, 7)])
 def test_attention_plain(ops, dtype, H, Hkv, hd, page, window):
     lens, scale = [1, 17, 64, 131, 300], 1.0 / math.sqrt(hd)
-    for far in (False, True):
+    for far in MODES:
         q, kc, vc, out, rseg, rpos, tables, want, _ = attention_case(ops, dtype, H, Hkv, hd, page, lens, window, scale,
                                                                       far)
         ops.attention_plain(q, q.stride(0), kc, vc, out, rseg, rpos, tables, q.shape[0], H, Hkv, hd, page, window, scale)
-        tol = dict(rtol=1e-4, atol=2e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
-        assert torch.isfinite(out).all()
-        assert torch.allclose(out.float().cpu(), want, **tol), float((out.float().cpu() - want).abs().max())
+        if dtype == torch.float32:
+            rows_close(out, want, f"plain {far}", share=1e-5, floor=1e-6)
+        else:
+            rows_close(out, want, f"plain {far}")
 
 
 def check_attention_prefill(ops, H, Hkv, hd, page, window, lens, q_lens, kernel):
     scale = 1.0 / math.sqrt(hd)
-    for far in (False, True):
+    for far in MODES:
         q, kc, vc, out, rseg, rpos, tables, want, q_lens = attention_case(ops, torch.bfloat16, H, Hkv, hd, page, lens,
                                                                           window, scale, far, q_lens)
         out.fill_(float("nan"))
@@ -305,8 +335,7 @@ def check_attention_prefill(ops, H, Hkv, hd, page, window, lens, q_lens, kernel)
         ops.attention_prefill(q, kc, vc, out, i32(starts), i32(q_lens), i32(lens), tables, q.shape[0], H, Hkv, hd, page,
                               window, scale, kernel=kernel)
         assert ops.attention_prefill_tc_error() == 0
-        assert torch.isfinite(out).all()
-        assert torch.allclose(out.float().cpu(), want, rtol=2e-2, atol=2e-2), float((out.float().cpu() - want).abs().max())
+        rows_close(out, want, f"prefill {kernel} {far}")
 
 
 @pytest.mark.parametrize("kernel", ["mma", "tc", "pair"])
@@ -338,7 +367,7 @@ def test_attention_prefill_tcgen05_tiles(ops, H, Hkv, page, window, kernel):
 def test_attention_decode(ops, H, Hkv, hd, page, window, splits):
     """One query per request: rows of the decode kernel against the plain attention, also split over blocks."""
     lens, scale = [1, 17, 64, 131, 300, 1000], 1.0 / math.sqrt(hd)
-    for far in (False, True):
+    for far in MODES:
         q, kc, vc, out, rseg, rpos, tables, want, q_lens = attention_case(ops, torch.bfloat16, H, Hkv, hd, page, lens,
                                                                           window, scale, far)
         # keep the last row of every request only: one query position per row
@@ -349,8 +378,7 @@ def test_attention_decode(ops, H, Hkv, hd, page, window, splits):
                              device=DEV)
         ops.attention_decode(q1, kc, vc, out1, rseg1, rpos1, tables, len(lens), H, Hkv, hd, page, window, scale, splits,
                              scratch)
-        assert torch.isfinite(out1).all()
-        assert torch.allclose(out1.float().cpu(), want1, rtol=2e-2, atol=2e-2), float((out1.float().cpu() - want1).abs().max())
+        rows_close(out1, want1, f"decode splits {splits} {far}")
 
 
 @pytest.mark.parametrize("blocks", [1, 7, 40, 296])
@@ -361,7 +389,7 @@ def test_attention_decode_dealt_out_evenly(ops, H, Hkv, hd, page, window, blocks
     pairs that spread over many blocks, blocks with nothing to do."""
     lens, scale = [1, 17, 64, 131, 300, 1000, 65, 2], 1.0 / math.sqrt(hd)
     blocks = min(blocks, 62 * Hkv)
-    for far in (False, True):
+    for far in MODES:
         q, kc, vc, out, rseg, rpos, tables, want, q_lens = attention_case(ops, torch.bfloat16, H, Hkv, hd, page, lens,
                                                                           window, scale, far)
         last = torch.tensor([sum(q_lens[:i + 1]) - 1 for i in range(len(lens))], device=DEV)
@@ -371,8 +399,7 @@ def test_attention_decode_dealt_out_evenly(ops, H, Hkv, hd, page, window, blocks
                              device=DEV)
         ops.attention_decode_flat(q1, kc, vc, out1, rseg1, rpos1, tables, len(lens), H, Hkv, hd, page, window, scale,
                                   blocks, scratch)
-        assert torch.isfinite(out1).all()
-        assert torch.allclose(out1.float().cpu(), want1, rtol=2e-2, atol=2e-2), float((out1.float().cpu() - want1).abs().max())
+        rows_close(out1, want1, f"decode dealt out over {blocks} blocks {far}")
 
 
 def test_attention_decode_dealt_out_evenly_random_shapes(ops):
@@ -390,9 +417,8 @@ def test_attention_decode_dealt_out_evenly_random_shapes(ops):
                              device=DEV)
         ops.attention_decode_flat(q, kc, vc, a, rseg, rpos, tables, len(lens), H, Hkv, hd, page, 0, scale, blocks, scratch)
         ops.attention_decode(q, kc, vc, b, rseg, rpos, tables, len(lens), H, Hkv, hd, page, 0, scale)
-        assert torch.isfinite(a).all(), (trial, lens, blocks)
-        assert torch.allclose(a.float(), b.float(), rtol=2e-2, atol=1e-2), (trial, lens, blocks)
-        assert torch.allclose(a.float().cpu(), want, rtol=2e-2, atol=2e-2), (trial, lens, blocks)
+        rows_close(a, want, f"trial {trial}: dealt out, lens {lens}, {blocks} blocks")
+        rows_close(b, want, f"trial {trial}: one block per pair, lens {lens}")
 
 
 # ---- choosing tokens -----------------------------------------------------------------------------------------

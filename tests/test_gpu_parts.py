@@ -84,6 +84,7 @@ def test_attention_part_and_block(dtype, window, bias, hd):
     then the rest), over a real cache manager and batch builder."""
     from jllm_serve_b200.cache import CacheManager
     from jllm_serve_b200.config import DenseGluSpec, GqaAttentionSpec, LayerSpec, NormSpec, RopeTableSpec
+    from jllm_serve_b200.csrc import ops
     from jllm_serve_b200.engine.batch import BatchBuilder, Segment
     from jllm_serve_b200.parts import PreNormBlock, RotaryTable, RunCache
     dim, H, Hkv, page = 72, 6, 2, 4
@@ -176,22 +177,22 @@ def toy_pieces():
 
         def __init__(self, spec, dim, tensors, prefix, runtime):
             self.dim = dim
-            self.w = tensors.pop(prefix + "mix.weight").float()
+            self.w = tensors.pop(prefix + "mix.weight")
+            assert self.w.dtype == torch.float32      # wanted as matrix_fp32: 32-bit whatever the compute dtype
 
         @classmethod
         def wants(cls, spec, dim, prefix):
-            return {prefix + "mix.weight": TensorWant((dim, dim))}
+            return {prefix + "mix.weight": TensorWant((dim, dim), "matrix_fp32")}
 
         @classmethod
         def cache_need(cls, spec):
             return FixedState((spec.width + 1,), "float32")
 
-        def forward(self, xb, x, batch, cache):
+        def forward(self, xb, x, batch, cache, state=None):
+            state_of = cache.state if state is None else state
             for seg, start, slot in zip(batch.segments, batch.host_seg_start, batch.host_state_slots):
                 n = len(seg.tokens)
-                state = cache.state[slot]
-                if seg.start == 0:
-                    state.zero_()
+                state = state_of[slot]            # the manager hands a slot out zeroed: no clearing here
                 rows = xb[start:start + n].float()
                 sums = state[:self.dim] + torch.cumsum(rows, dim=0)
                 counts = state[self.dim] + torch.arange(1, n + 1, device=rows.device, dtype=torch.float32)
@@ -201,13 +202,47 @@ def toy_pieces():
 
     register_mixer("toy_running_mean", RunningMean, replace=True)
 
+    @dataclass(frozen=True)
+    class HybridSpec(MixerSpec):
+        kind: str = field(default="toy_attention_and_mean", init=False)
+        attention: GqaAttentionSpec = None
+        width: int = 0
+        rope_table: int = 0
+
+    class AttentionAndMean(Mixer):
+        """Attention over paged keys and values AND a running mean with a state of fixed size: a mixer that names
+        two needs and gets both in its RunCache."""
+        graph_safe = False
+
+        def __init__(self, spec, dim, tensors, prefix, runtime, rope=None):
+            from jllm_serve_b200.parts import GqaAttention
+            self.attention = GqaAttention(spec.attention, dim, tensors, prefix, runtime, rope=rope)
+            self.mean = RunningMean(spec, dim, tensors, prefix, runtime)
+
+        @classmethod
+        def wants(cls, spec, dim, prefix):
+            from jllm_serve_b200.parts import GqaAttention
+            return {**GqaAttention.wants(spec.attention, dim, prefix), **RunningMean.wants(spec, dim, prefix)}
+
+        @classmethod
+        def cache_need(cls, spec):
+            from jllm_serve_b200.parts import GqaAttention
+            return (GqaAttention.cache_need(spec.attention), RunningMean.cache_need(spec))
+
+        def forward(self, xb, x, batch, cache):
+            assert cache.keys is not None and len(cache.states) == 1 and cache.state is cache.states[0]
+            self.attention.forward(xb, x, batch, cache)
+            self.mean.forward(xb, x, batch, cache)
+
+    register_mixer("toy_attention_and_mean", AttentionAndMean, replace=True)
+
     def parse(values):
         dim, layers = values["width"], values["depth"]
         norm = NormSpec("rmsnorm", values["eps"])
         attn = GqaAttentionSpec(heads=4, kv_heads=2, head_dim=16, rope_table=0, qk_norm=True, qk_norm_eps=values["eps"],
                                 scale=0.25)
-        specs = tuple(LayerSpec(attn if l % 2 else RunningMeanSpec(width=dim), DenseGluSpec(hidden=values["ffn"]), norm)
-                      for l in range(layers))
+        mixers = [RunningMeanSpec(width=dim), attn, HybridSpec(attention=attn, width=dim)]     # layer 2 keeps both
+        specs = tuple(LayerSpec(mixers[l % 3], DenseGluSpec(hidden=values["ffn"]), norm) for l in range(layers))
         core = Core("ToyForCausalLM", "toy_mean", dim, layers, values["vocab"], values["eps"], True, -1, (), 512, "toy")
         return Decoder(core, specs, (RopeTableSpec(16, 10000.0),), norm)
 
@@ -223,11 +258,12 @@ def toy_pieces():
         for l in range(3):
             p = f"model.layers.{l}."
             xb = P.rmsnorm(x, w[p + "input_layernorm.weight"], 1e-5)
-            if l % 2:
-                y, _ = P.attention_block(xb, w, p + "self_attn.", cfg, 0, cos, sin)
-            else:
+            y = torch.zeros_like(x)
+            if l % 3 in (1, 2):
+                y = y + P.attention_block(xb, w, p + "self_attn.", cfg, 0, cos, sin)[0]
+            if l % 3 in (0, 2):
                 mean = torch.cumsum(xb, dim=0) / torch.arange(1, T + 1, dtype=xb.dtype)[:, None]
-                y = mean @ w[p + "self_attn.mix.weight"].t()
+                y = y + mean @ w[p + "self_attn.mix.weight"].t()
             x = x + y
             xb = P.rmsnorm(x, w[p + "post_attention_layernorm.weight"], 1e-5)
             x = x + P.swiglu_feed_forward(xb, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
@@ -251,6 +287,7 @@ def test_toy_mixer_with_state_registers_builds_and_steps(dtype, tmp_path):
             runner = ModelRunner(folder, dtype=dtype, page_size=4, num_pages=60, max_batch_tokens=128, max_requests=3,
                                  ctx=128, poison_freed_pages=True)
             assert len(runner.cache.fixed) == 1 and runner.cache.fixed[0].runs == [0, 2] and not runner.graph_safe
+            assert len(runner.cache.paged) == 1 and runner.cache.paged[0].runs == [1, 2]     # run 2 is in both
             got = replay(runner, steps)
             scale = 0.0
             for rid, toks in reqs.items():

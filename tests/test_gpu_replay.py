@@ -98,6 +98,28 @@ def test_float32_cuts_agree_bit_for_bit(name):
             assert torch.equal(row, got[key]), f"{name}: row {key} differs between cuts"
 
 
+def test_captured_decode_steps_are_evicted_and_captured_again():
+    """More decode shapes than the runner keeps graphs for: the oldest capture makes room, and a shape that comes back
+    is captured anew; every step's logits are right whether it ran launch by launch, was captured, or replayed."""
+    reqs = requests_for("B", (40, 40, 40), seed=9)
+    ids = list(reqs)
+    steps = [{"step": 0, "entries": [{"id": r, "tokens": reqs[r][:10], "want": list(range(10))} for r in ids], "end": []}]
+    at = {r: 10 for r in ids}
+    for group in ([ids[0]], ids[:2], ids, [ids[0]], ids[1:], ids[:2], ids):
+        for _ in range(4):
+            steps.append({"step": len(steps), "entries": [{"id": r, "tokens": reqs[r][at[r]:at[r] + 1], "want": [0]}
+                                                           for r in group], "end": []})
+            for r in group:
+                at[r] += 1
+    steps.append({"step": len(steps), "entries": [{"id": r, "tokens": reqs[r][at[r]:], "want": list(range(40 - at[r]))}
+                                                   for r in ids], "end": ids})
+    runner = make_runner("B", "bfloat16", steps)
+    runner.max_graphs = 2
+    got = replay(runner, steps)
+    compare_with_plain(got, model_folder("B"), reqs, "bfloat16", what="B graphs evicted")
+    assert len(runner._graphs) == 2 and len(runner._graph_seen) == 3     # three shapes were met, two are kept
+
+
 def test_long_decoding():
     """300 tokens one by one after a short prompt: every page edge and the window's edge are crossed."""
     for name, dtype in (("B", "float32"), ("C", "float32"), ("C", "bfloat16")):
@@ -117,20 +139,66 @@ def test_first_tokens_of_a_sequence():
             compare_with_plain(got, model_folder(name), reqs, dtype, what=f"{name} first tokens")
 
 
-def test_step_larger_than_a_batch_is_split():
-    reqs = requests_for("B", (129, 64), seed=3)
+@pytest.mark.parametrize("name, dtype, lengths, rows", [("B", "float32", (129, 64), 50), ("E", "bfloat16", (300, 170), 130),
+                                                        ("C", "bfloat16", (130, 97), 48)])
+def test_step_larger_than_a_batch_is_split(name, dtype, lengths, rows):
+    """A step of more rows than a batch holds runs as several batches (also over a windowed group, which gives pages
+    back between the parts); the logits come back in the order that was asked for."""
+    from jllm_serve_b200.engine import Segment
+    from tests.helpers import RowChecker
+    reqs = requests_for(name, lengths, seed=3)
     steps = [{"step": 0, "entries": [{"id": r, "tokens": t, "want": list(range(len(t)))[::-1]}
                                      for r, t in reqs.items()], "end": list(reqs)}]
-    runner = make_runner("B", "float32", steps, max_batch_tokens=50)
-    rows = runner.step([__import__("jllm_serve_b200").engine.Segment(e["id"], e["tokens"], 0, e["want"])
-                        for e in steps[0]["entries"]]).cpu()
-    from tests.helpers import plain_logits
+    runner = make_runner(name, dtype, steps, max_batch_tokens=rows)
+    got = runner.step([Segment(e["id"], e["tokens"], 0, e["want"]) for e in steps[0]["entries"]]).float().cpu()
+    checker = RowChecker(model_folder(name), reqs, dtype, what=f"{name} step in parts")
     r = 0
     for rid, toks in reqs.items():
-        want = plain_logits(model_folder("B"), tuple(toks))
         for p in reversed(range(len(toks))):
-            assert float((rows[r] - want[p]).abs().max()) < 2e-5 * float(want.abs().max())
+            checker.row(rid, p, got[r])
             r += 1
+    checker.finish()
+    assert runner.steps >= 3
+    for rid in reqs:
+        runner.finish(rid)
+    runner.cache.check()
+
+
+def test_step_in_parts_takes_all_its_pages_or_none():
+    """The pages of every part are reserved before the first part runs: a pool that cannot hold the step refuses it
+    with nothing run, nothing committed and nothing held."""
+    from jllm_serve_b200.cache import PoolExhausted
+    from jllm_serve_b200.engine import ModelRunner, Segment
+    reqs = requests_for("B", (129, 64), seed=3)
+    runner = ModelRunner(model_folder("B"), dtype="float32", page_size=8, num_pages=20, max_batch_tokens=50, max_requests=4,
+                         ctx=512)                               # 20 pages hold 160 tokens; the step brings 193
+    with pytest.raises(PoolExhausted):
+        runner.step([Segment(r, t, 0, [len(t) - 1]) for r, t in reqs.items()])
+    assert runner.steps == 0 and not runner.cache.requests and runner.cache.free_pages() == [20]
+    runner.cache.check()
+    small = {"r0": reqs["r0"]}                                 # what fits still runs afterwards
+    got = replay(runner, traces.whole(small))
+    compare_with_plain(got, model_folder("B"), small, "float32", what="after a refused step")
+
+
+def test_a_step_that_fails_while_running_gives_its_pages_back(monkeypatch):
+    """If the forward pass raises, the pages reserved for the step go back and requests opened for it are closed, so
+    the cache's books still say what the caller believes."""
+    from jllm_serve_b200.engine import ModelRunner, Segment
+    reqs = requests_for("A", (20, 9), seed=3)
+    runner = ModelRunner(model_folder("A"), dtype="float32", page_size=4, num_pages=30, max_batch_tokens=64, max_requests=4,
+                         ctx=128)
+    runner.step([Segment("r0", reqs["r0"][:8], 0, [])])
+    free = runner.cache.free_pages()
+
+    def broken(batch, cache, logits_out=None):
+        raise RuntimeError("a kernel failed")
+
+    monkeypatch.setattr(runner.model, "forward", broken)
+    with pytest.raises(RuntimeError, match="a kernel failed"):
+        runner.step([Segment("r0", reqs["r0"][8:], 8, [11]), Segment("r1", reqs["r1"], 0, [8])])
+    assert runner.cache.length("r0") == 8 and not runner.cache.is_open("r1") and runner.cache.free_pages() == free
+    runner.cache.check()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -228,3 +228,20 @@ def test_sampling_params_validation():
     d = SamplingParams()
     assert (d.temperature, d.top_k, d.top_p, d.min_p, d.seed, d.max_tokens) == (0.6, 20, 0.95, 0.0, -1, 1024)
     assert SamplingParams(temperature=0).greedy and SamplingParams(top_k=1).greedy and not d.greedy
+
+
+def test_requests_the_planner_ends_itself_are_handed_to_the_caller():
+    """A request that can never fit the pool ends inside `plan` with `kv_exhausted`; `take_ended` hands it over once,
+    so whoever drives the steps by hand learns of it although it never reaches `complete`."""
+    from jllm_serve_b200.cache import CacheManager, PagedKeysValues
+    from jllm_serve_b200.engine.scheduler import Request, Scheduler
+    from jllm_serve_b200.sampling.params import SamplingParams
+    cache = CacheManager([PagedKeysValues(1, 8)], page_size=4, num_pages=3, max_requests=2)      # room for 12 tokens
+    s = Scheduler(cache, ctx=64, max_batch_tokens=32, chunk=32, min_chunk=1, max_running=2)
+    s.add(Request("big", list(range(1, 31)), SamplingParams.greedy_params(4)))
+    s.add(Request("small", [1, 2, 3], SamplingParams.greedy_params(2)))
+    plan = s.plan()
+    ended = s.take_ended()
+    assert [r.id for r in ended] == ["big"] and ended[0].finish_reason == "kv_exhausted"
+    assert s.take_ended() == []                                    # handed over once
+    assert [p.request.id for p in plan] == ["small"]               # the next request in line runs in the same step
