@@ -7,11 +7,16 @@
 // bytes of a weight row straight from global memory into the registers of the A fragment; the k index
 // inside one 32-wide chunk is permuted (thread t owns k = 8t .. 8t+7), and the activation fragment is
 // loaded with the same permutation, which a sum over k does not notice. The 8 warps of a block take
-// interleaved 32-wide chunks of K (so the block reads 512 contiguous bytes of every row at a time),
-// and their partial sums are added in shared memory in a fixed order: results are deterministic.
+// interleaved 64-wide k blocks, and their partial sums are added in shared memory in a fixed order:
+// results are deterministic.
+//
+// The weights are read in the PACKED layout all bfloat16 products share (ops.pack_weight: tiles of 128 rows x 64 k,
+// a row of a tile 128 bytes, its 16-byte chunk c at chunk position c ^ (row & 7), tile (t, kb) at
+// (t * k_blocks + kb) * 16 KB; padded with zeros). A warp's load of 8 rows x 64 bytes then comes from one 1 KB
+// stretch of memory instead of 8 rows that lie a whole row apart.
 //
 // Requirements (else the caller uses the CUDA-core kernel): bfloat16 inputs, K a multiple of 8,
-// 16-byte aligned rows (lda, ldw multiples of 8; aligned base pointers), 1 <= M <= 64.
+// 16-byte aligned rows (lda a multiple of 8; aligned base pointers), 1 <= M <= 64.
 #include "common.cuh"
 
 namespace {
@@ -42,9 +47,9 @@ __device__ __forceinline__ uint4 load_16_stream(const __nv_bfloat16* p) {
 
 template <int NT, int RT, int UNROLL, typename Tout>
 __global__ void __launch_bounds__(WARPS * 32, 2)
-gemm_small_m_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w, int ldw,
+gemm_small_m_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w, int k_blocks,
                     VecRef bias, int has_bias, Tout* __restrict__ out, int ldo, int accumulate, int M, int N, int K,
-                    int swiglu, int prefetch_bytes) {
+                    int swiglu) {
     extern __shared__ float red[];  // [WARPS][RT * 16][NT * 8]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -57,15 +62,19 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfl
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[r][j][i] = 0.f;
 
+    // where this thread's weight rows start in the packed layout (rows beyond N are zeros there; beyond the padded
+    // rows there is nothing: those are not read)
     const __nv_bfloat16* wrow[RT][2];
     bool wok[RT][2];
+    const int padded_rows = (N + 127) & ~127;
 #pragma unroll
     for (int r = 0; r < RT; ++r)
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int n = n0 + r * 16 + h * 8 + g;
-            wok[r][h] = n < N;
-            wrow[r][h] = w + (size_t)(wok[r][h] ? n : 0) * ldw;
+            wok[r][h] = n < padded_rows;
+            const int nn = wok[r][h] ? n : 0;
+            wrow[r][h] = w + (size_t)(nn >> 7) * k_blocks * 8192 + (size_t)(nn & 127) * 64;
         }
     const __nv_bfloat16* arow[NT];
     bool aok[NT];
@@ -78,37 +87,41 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfl
     const uint4 zero = make_uint4(0, 0, 0, 0);
     const int chunks = (K + KCHUNK - 1) / KCHUNK;
     uint4 wv[UNROLL][RT][2];
+    static_assert(UNROLL % 2 == 0, "a warp takes the two halves of a k block together");
+    // the u-th 32-wide chunk of the batch that starts at k block c0: k blocks c0, c0 + WARPS, ..., two chunks each
+    auto chunk_of = [&](int c0, int u) { return 2 * (c0 + (u >> 1) * WARPS) + (u & 1); };
     auto load_weights = [&](int c0) {
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-            const int k = (c0 + u * WARPS) * KCHUNK + 8 * t;
-            const bool kin = (c0 + u * WARPS) < chunks && k < K;
+            // 32-wide chunk cc of k: k block cc / 2, 16-byte chunks (cc % 2) * 4 + t of the row's 128 bytes, which lie
+            // at chunk position (that) ^ (row & 7); row & 7 = g for all of this thread's rows. A warp takes BOTH
+            // halves of a k block one after the other, so that it reads whole 128-byte lines: its 16 rows of a k block
+            // are one contiguous 2 KB piece of the packed weight.
+            const int cc = chunk_of(c0, u);
+            const bool kin = cc < chunks;
+            const size_t at = (size_t)(cc >> 1) * 8192 + (size_t)(((((cc & 1) << 2) + t) ^ g) << 3);
 #pragma unroll
             for (int r = 0; r < RT; ++r)
 #pragma unroll
-                for (int h = 0; h < 2; ++h) wv[u][r][h] = (kin && wok[r][h]) ? load_16_stream(wrow[r][h] + k) : zero;
+                for (int h = 0; h < 2; ++h) wv[u][r][h] = (kin && wok[r][h]) ? load_16_stream(wrow[r][h] + at) : zero;
         }
     };
     // The weights do not depend on the kernel before this one: the first batch is requested while that kernel
-    // is still running, and the head of every row of the block's slice (prefetch_bytes, bounded by the host so
-    // that one product never asks for more than a fraction of L2) is pulled towards L2. The kernels between two
-    // products (norms, RoPE, the attention combine) are tiny: the weight stream would otherwise pause for them.
-    if (prefetch_bytes > 0 && threadIdx.x < RT * 16) {
-        const int n = n0 + threadIdx.x;
-        if (n < N)
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(w + (size_t)n * ldw), "r"(prefetch_bytes) : "memory");
-    }
+    // is still running. The kernels between two products (norms, RoPE, the attention combine) are tiny: the weight
+    // stream would otherwise pause for them.
     load_weights(warp);
     pdl_wait();
     pdl_trigger();
-    for (int c0 = warp; c0 < chunks; c0 += WARPS * UNROLL) {
+    const int k_blocks_here = (chunks + 1) >> 1;
+    for (int c0 = warp; c0 < k_blocks_here; c0 += WARPS * (UNROLL / 2)) {
         // the activations of these chunks: issued before any of the weights is waited for, so that their
         // (L2) latency overlaps the weights' (HBM) latency instead of following it
         uint4 xv[UNROLL][NT];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-            const int k = (c0 + u * WARPS) * KCHUNK + 8 * t;
-            const bool kin = (c0 + u * WARPS) < chunks && k < K;
+            const int cc = chunk_of(c0, u);
+            const int k = cc * KCHUNK + 8 * t;
+            const bool kin = cc < chunks && k < K;
 #pragma unroll
             for (int j = 0; j < NT; ++j) xv[u][j] = (kin && aok[j]) ? load_16(arow[j] + k) : zero;
         }
@@ -125,7 +138,7 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfl
                 }
             }
         }
-        if (c0 + WARPS * UNROLL < chunks) load_weights(c0 + WARPS * UNROLL);
+        if (c0 + WARPS * (UNROLL / 2) < k_blocks_here) load_weights(c0 + WARPS * (UNROLL / 2));
     }
     // partial sums of the 8 warps -> shared memory, laid out [warp][token][row] so the final pass writes
     // consecutive output features from consecutive threads
@@ -166,20 +179,20 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfl
 }
 
 template <int NT, int RT, int UNROLL>
-int launch(const void* a, int lda, const void* w, int ldw, VecRef bias, int has_bias, void* out, int out_dtype, int ldo,
-           int accumulate, int M, int N, int K, int swiglu, int prefetch_bytes, cudaStream_t stream) {
+int launch(const void* a, int lda, const void* w, int k_blocks, VecRef bias, int has_bias, void* out, int out_dtype, int ldo,
+           int accumulate, int M, int N, int K, int swiglu, cudaStream_t stream) {
     const int grid = (N + 16 * RT - 1) / (16 * RT);
     const size_t smem = (size_t)WARPS * RT * 16 * NT * 8 * sizeof(float);
     if (out_dtype == JLLM_F32) {
         auto kern = gemm_small_m_kernel<NT, RT, UNROLL, float>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         jllm_launch(kern, dim3(grid), dim3(WARPS * 32), smem, stream, LAUNCH_DEPENDENT_WANTS_L1, (const __nv_bfloat16*)a, lda,
-                    (const __nv_bfloat16*)w, ldw, bias, has_bias, (float*)out, ldo, accumulate, M, N, K, swiglu, prefetch_bytes);
+                    (const __nv_bfloat16*)w, k_blocks, bias, has_bias, (float*)out, ldo, accumulate, M, N, K, swiglu);
     } else {
         auto kern = gemm_small_m_kernel<NT, RT, UNROLL, __nv_bfloat16>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         jllm_launch(kern, dim3(grid), dim3(WARPS * 32), smem, stream, LAUNCH_DEPENDENT_WANTS_L1, (const __nv_bfloat16*)a, lda,
-                    (const __nv_bfloat16*)w, ldw, bias, has_bias, (__nv_bfloat16*)out, ldo, accumulate, M, N, K, swiglu, prefetch_bytes);
+                    (const __nv_bfloat16*)w, k_blocks, bias, has_bias, (__nv_bfloat16*)out, ldo, accumulate, M, N, K, swiglu);
     }
     return jllm_check_launch("gemm_small_m");
 }
@@ -187,17 +200,20 @@ int launch(const void* a, int lda, const void* w, int ldw, VecRef bias, int has_
 }  // namespace
 
 // Returns 1 if jllm_gemm_small_m takes this product.
-JLLM_EXPORT int jllm_gemm_small_m_fits(const void* a, int lda, const void* w, int ldw, int M, int N, int K) {
-    return M >= 1 && M <= 64 && N >= 1 && K >= 8 && K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 &&
-           ((uintptr_t)a % 16) == 0 && ((uintptr_t)w % 16) == 0;
+JLLM_EXPORT int jllm_gemm_small_m_fits(const void* a, int lda, const void* w_packed, int M, int N, int K) {
+    return M >= 1 && M <= 64 && N >= 1 && K >= 8 && K % 8 == 0 && lda % 8 == 0 && ((uintptr_t)a % 16) == 0 &&
+           ((uintptr_t)w_packed % 16) == 0;
 }
 
-JLLM_EXPORT int jllm_gemm_small_m(const void* a, int lda, const void* w, int ldw, const void* bias, int bias_dtype,
+// w_packed: ops.pack_weight of the [N, K] weight, k_blocks = ceil(K / 64) its k blocks.
+JLLM_EXPORT int jllm_gemm_small_m(const void* a, int lda, const void* w, int k_blocks, const void* bias, int bias_dtype,
                                   void* out, int out_dtype, int ldo, int accumulate, int M, int N, int K,
-                                  int tuning, int swiglu, int prefetch_mb, cudaStream_t stream) {
-    JLLM_REQUIRE(jllm_gemm_small_m_fits(a, lda, w, ldw, M, N, K),
-                 "gemm_small_m: needs 1 <= M <= 64, K %% 8 == 0 and 16-byte aligned rows (M=%d N=%d K=%d lda=%d ldw=%d)",
-                 M, N, K, lda, ldw);
+                                  int swiglu, cudaStream_t stream) {
+    JLLM_REQUIRE(jllm_gemm_small_m_fits(a, lda, w, M, N, K),
+                 "gemm_small_m: needs 1 <= M <= 64, K %% 8 == 0 and 16-byte aligned rows (M=%d N=%d K=%d lda=%d)",
+                 M, N, K, lda);
+    JLLM_REQUIRE(k_blocks == (K + 63) / 64, "gemm_small_m: the packed weight has %d k blocks, K=%d needs %d", k_blocks, K,
+                 (K + 63) / 64);
     JLLM_REQUIRE(ldo >= (swiglu ? N / 2 : N), "gemm_small_m: ldo=%d < N=%d", ldo, N);
     JLLM_REQUIRE(!swiglu || (N % 16 == 0 && !bias && !accumulate),
                  "gemm_small_m: the SwiGLU epilogue needs N %% 16 == 0, no bias and no accumulation (N=%d)", N);
@@ -207,26 +223,14 @@ JLLM_EXPORT int jllm_gemm_small_m(const void* a, int lda, const void* w, int ldw
     // on the layer shapes of an 8B model. What counts is that every SM has two resident blocks with enough bytes on
     // their way: a matrix with few rows (at most one 32-row block per SM) is cut into 16-row blocks; up to 8 tokens
     // the blocks are 16 rows with the deeper unroll, except where 32-row blocks make between one and two rounds.
-    // tuning (experiments): bit 0 = 32 rows, bit 1 = deeper unroll, value 8 = 16 rows
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    }
+    const int sms = jllm_device_sm_count() > 0 ? jllm_device_sm_count() : 1;
     const int blocks32 = (N + 31) / 32;
     bool wide = blocks32 > sms;
     int deep = 0;
-    if (M <= 8) {
-        wide = blocks32 > sms && blocks32 <= 2 * sms;
-        deep = !wide;
-    }
-    if (tuning > 0) { wide = (tuning & 1) != 0; deep = (tuning >> 1) & 1; }
-    // at most prefetch_mb MB of this matrix are prefetched into L2, the same number of bytes from every row
-    long long per_row = prefetch_mb > 0 ? ((long long)prefetch_mb << 20) / N : 0;
-    if (per_row > (long long)K * 2) per_row = (long long)K * 2;
-    const int prefetch_bytes = (int)(per_row & ~15LL);
-#define JLLM_GO(NT, RT, UN) return launch<NT, RT, UN>(a, lda, w, ldw, b, hb, out, out_dtype, ldo, accumulate, M, N, K, swiglu, prefetch_bytes, stream)
+    if (M <= 8) wide = blocks32 > sms && blocks32 <= 2 * sms;
+    // (with the packed weight a warp's batch of four k blocks is four contiguous 2 KB pieces: twice as deep an unroll,
+    // which paid on row-major weights, is slower here: gate_up at 8 rows 37.7 us against 34.8)
+#define JLLM_GO(NT, RT, UN) return launch<NT, RT, UN>(a, lda, w, k_blocks, b, hb, out, out_dtype, ldo, accumulate, M, N, K, swiglu, stream)
     if (M <= 8) { if (wide) { if (deep) JLLM_GO(1, 2, 8); JLLM_GO(1, 2, 4); } if (deep) JLLM_GO(1, 1, 8); JLLM_GO(1, 1, 4); }
     if (M <= 16) { if (wide) JLLM_GO(2, 2, 4); if (deep) JLLM_GO(2, 1, 8); JLLM_GO(2, 1, 4); }
     if (M <= 32) { if (wide) JLLM_GO(4, 2, 2); JLLM_GO(4, 1, 4); }

@@ -2,9 +2,11 @@
 //
 // The prefill product. A persistent kernel, one block per SM, walks 128 x BN output tiles (BN = 256 for big
 // products, narrower when the rows are few):
-//   * warp 0 (one lane) is the TMA producer: for every 64-wide k block it waits for a free stage and
-//     issues two tiled bulk copies (a 128 x 64 tile of A, a 256 x 64 tile of W) into 128-byte-swizzled
-//     shared memory, completing on the stage's "full" mbarrier (every block loads its own copy);
+//   * warp 0 (one lane) is the producer: for every 64-wide k block it waits for a free stage and brings a
+//     128 x 64 tile of A (a tiled TMA copy into 128-byte-swizzled shared memory) and a BN x 64 tile of W, which
+//     is kept PACKED in exactly that shared-memory image (ops.pack_weight), so its tile is one or two plain
+//     contiguous bulk copies of up to 16 KB; all complete on the stage's "full" mbarrier (no multicast: every
+//     block loads its own copy);
 //   * warp 1 (one lane) issues the MMAs: 4 x tcgen05.mma (M 128, N 256, K 16) per k block, operands
 //     described by shared-memory descriptors, the float32 accumulator in tensor memory (TMEM);
 //     tcgen05.commit frees the stage, and after the last k block signals "accumulator full";
@@ -46,7 +48,7 @@ __host__ __device__ constexpr uint32_t idesc_for(int bn) {
 
 template <typename Tout, int BN>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, VecRef bias,
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __nv_bfloat16* __restrict__ w_packed, VecRef bias,
                     int has_bias, Tout* __restrict__ out, int ldo, int accumulate, int M, int N, int K, int swiglu,
                     int stream, float* __restrict__ partials, int* __restrict__ counters, int* __restrict__ error_word,
                     int starve) {
@@ -72,6 +74,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN, tiles = tiles_m * tiles_n;
     const int k_blocks = (K + BK - 1) / BK;
+    const int padded_rows = (N + 127) & ~127;       // rows of the packed weight
     // The work of a block: whole tiles, tile = block, block + grid, ... as long as full rounds of tiles last. The
     // tiles of a last, partly filled round are streamed instead (stream-K): their (tile, k block) pairs, in tile
     // order, are cut into one equal run per block, so that no SM idles through that round; a tile whose k blocks
@@ -143,9 +146,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
                 for (int kb = lo; kb < hi; ++kb) {
                     if (!mbar_wait(empty_bar(s), parity, abort_flag, spin)) { ok = false; break; }
-                    mbar_expect_tx(full_bar(s), STAGE_BYTES + ((starve && kb == lo) ? 16u : 0u));
+                    // the W tile: rows [n0, n0 + BN) of k block kb, contiguous pieces of the packed layout (a piece ends
+                    // where a packed tile of 128 rows ends; rows beyond the padded matrix do not exist: their part of
+                    // the stage keeps what it held, and the columns they would give are never stored)
+                    const int w_rows = min(BN, padded_rows - n0);
+                    mbar_expect_tx(full_bar(s), A_BYTES + (uint32_t)w_rows * 128u + ((starve && kb == lo) ? 16u : 0u));
                     tma_load_2d(dst, &map_a, kb * BK, m0, full_bar(s));
-                    tma_load_2d(dst + A_BYTES, &map_w, kb * BK, n0, full_bar(s));
+                    for (int r = 0; r < w_rows;) {
+                        const int n = n0 + r, in_tile = n & 127, cnt = min(128 - in_tile, w_rows - r);
+                        bulk_copy(dst + A_BYTES + (uint32_t)r * 128u,
+                                  w_packed + ((size_t)(n >> 7) * k_blocks + kb) * 8192 + (size_t)in_tile * 64,
+                                  (uint32_t)cnt * 128u, full_bar(s));
+                        r += cnt;
+                    }
                     dst += STAGE_BYTES;
                     if (++s == STAGES) { s = 0; parity ^= 1u; dst = base; }
                 }
@@ -402,9 +415,11 @@ int* error_word_for_device() {
 
 }  // namespace
 
-JLLM_EXPORT int jllm_gemm_tcgen05_fits(const void* a, int lda, const void* w, int ldw, int M, int N, int K) {
-    return M >= 1 && N >= 1 && K >= 8 && K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && ((uintptr_t)a % 16) == 0 &&
-           ((uintptr_t)w % 16) == 0;
+int* jllm_gemm_error_word() { return error_word_for_device(); }      // shared with the weight-stream product
+
+JLLM_EXPORT int jllm_gemm_tcgen05_fits(const void* a, int lda, const void* w_packed, int M, int N, int K) {
+    return M >= 1 && N >= 1 && K >= 8 && K % 8 == 0 && lda % 8 == 0 && ((uintptr_t)a % 16) == 0 &&
+           ((uintptr_t)w_packed % 16) == 0;
 }
 
 // Reads and clears the error word that a kernel whose wait ran out has raised (0 = none). Synchronises the device.
@@ -425,22 +440,19 @@ thread_local int g_starve_next = 0;
 }
 JLLM_EXPORT void jllm_gemm_tcgen05_starve_next() { g_starve_next = 1; }
 
-JLLM_EXPORT int jllm_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, const void* bias, int bias_dtype,
+// w: ops.pack_weight of the [N, K] weight (k_blocks_packed = ceil(K / 64) its k blocks).
+JLLM_EXPORT int jllm_gemm_tcgen05(const void* a, int lda, const void* w, int k_blocks_packed, const void* bias, int bias_dtype,
                                   void* out, int out_dtype, int ldo, int accumulate, int M, int N, int K, int max_blocks,
                                   int swiglu, float* workspace, long long workspace_floats, int stream_mode,
                                   int tile_width, cudaStream_t stream) {
-    JLLM_REQUIRE(jllm_gemm_tcgen05_fits(a, lda, w, ldw, M, N, K),
-                 "gemm_tcgen05: needs K %% 8 == 0 and 16-byte aligned rows (M=%d N=%d K=%d lda=%d ldw=%d)", M, N, K, lda,
-                 ldw);
+    JLLM_REQUIRE(jllm_gemm_tcgen05_fits(a, lda, w, M, N, K),
+                 "gemm_tcgen05: needs K %% 8 == 0 and 16-byte aligned rows (M=%d N=%d K=%d lda=%d)", M, N, K, lda);
+    JLLM_REQUIRE(k_blocks_packed == (K + BK - 1) / BK, "gemm_tcgen05: the packed weight has %d k blocks, K=%d needs %d",
+                 k_blocks_packed, K, (K + BK - 1) / BK);
     JLLM_REQUIRE(ldo >= (swiglu ? N / 2 : N), "gemm_tcgen05: ldo=%d < N=%d", ldo, N);
     JLLM_REQUIRE(!swiglu || (N % 16 == 0 && !bias && !accumulate),
                  "gemm_tcgen05: the SwiGLU epilogue needs N %% 16 == 0, no bias and no accumulation (N=%d)", N);
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    }
+    const int sms = jllm_device_sm_count() > 0 ? jllm_device_sm_count() : 1;
     // The tile width: a block's time for a tile grows with the bytes it pulls in (its rows of A and BN rows of W
     // per k block), and the product takes as many rounds as the tiles need on the SMs there are.
     const int widths[5] = {256, 192, 128, 64, 32};
@@ -458,10 +470,8 @@ JLLM_EXPORT int jllm_gemm_tcgen05(const void* a, int lda, const void* w, int ldw
     bool streamed = false;
     if (tile_width > 0) BN = tile_width;
     JLLM_REQUIRE(BN == 256 || BN == 192 || BN == 128 || BN == 64 || BN == 32, "gemm_tcgen05: tile width %d", BN);
-    CUtensorMap map_a, map_w;
+    CUtensorMap map_a;
     int rc = tensor_map_for(a, M, K, lda, BM, &map_a);
-    if (rc != JLLM_OK) return rc;
-    rc = tensor_map_for(w, N, K, ldw, BN, &map_w);
     if (rc != JLLM_OK) return rc;
     int* error_word = error_word_for_device();
     if (!error_word) return jllm_fail(JLLM_CUDA_ERROR, "gemm_tcgen05: no error word");
@@ -493,7 +503,7 @@ JLLM_EXPORT int jllm_gemm_tcgen05(const void* a, int lda, const void* w, int ldw
     do {                                                                                                              \
         auto kern = gemm_tcgen05_kernel<T, W>;                                                                        \
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes_for(W));             \
-        jllm_launch(kern, dim3(grid), dim3(THREADS), smem_bytes_for(W), stream, true, map_a, map_w, b,                \
+        jllm_launch(kern, dim3(grid), dim3(THREADS), smem_bytes_for(W), stream, true, map_a, (const __nv_bfloat16*)w, b, \
                     (int)(bias != nullptr), (T*)out, ldo, accumulate, M, N, K, swiglu, splits, partials, counters,    \
                     error_word, starve);                                                                              \
     } while (0)

@@ -133,8 +133,9 @@ class _Signatures:
     jllm_swiglu = [P, P, I, I, I, P]
     jllm_qk_norm_rope_store = [P, I, P, P, I, I, F, P, P, I, P, P, P, P, I, I, I, I, I, I, I, P]
     jllm_gemm_plain = [P, I, I, P, I, P, I, P, I, I, I, I, I, I, P]
-    jllm_gemm_small_m = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, I, I, P]
+    jllm_gemm_small_m = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, P]
     jllm_gemm_tcgen05 = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, I, P, ctypes.c_longlong, I, I, P]
+    jllm_gemm_stream = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, P, ctypes.c_longlong, I, I, P]
     jllm_gemm_tcgen05_error = []
     jllm_gemm_tcgen05_starve_next = []
     jllm_attention_plain = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P]
@@ -210,29 +211,41 @@ def sample(logits, temperature, top_k, top_p, min_p, uniform, out, vocab: int | 
           out.data_ptr(), _stream())
 
 
-def _small_m_fits(a, w) -> bool:
+def _packed(w) -> "PackedWeight":
+    """The weight in the packed layout: as given, or packed now (tests and one-off calls hand in plain matrices; a
+    model packs its weights once at load)."""
+    return w if isinstance(w, PackedWeight) else pack_weight(w)
+
+
+def _rows_fit(a, w) -> bool:
+    """Whether the weight-row kernel (`gemm_small_m`) takes this product."""
     M, K = a.shape
-    return (1 <= M <= 64 and K >= 8 and K % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
-            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+    return (1 <= M <= 64 and K >= 8 and K % 8 == 0 and a.stride(0) % 8 == 0 and a.stride(1) == 1
+            and a.data_ptr() % 16 == 0)
 
 
 def _tcgen05_fits(a, w) -> bool:
     M, K = a.shape
-    return (M >= 1 and K >= 8 and K % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
-            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+    return M >= 1 and K >= 8 and K % 8 == 0 and a.stride(0) % 8 == 0 and a.stride(1) == 1 and a.data_ptr() % 16 == 0
 
 
 def gemm_bf16_fits(a, w, out) -> bool:
     """Whether the tensor-core kernels take this product; otherwise the CUDA-core kernel runs it."""
-    return a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and _tcgen05_fits(a, w)
+    return a.dtype == torch.bfloat16 and (isinstance(w, PackedWeight) or w.dtype == torch.bfloat16) and _tcgen05_fits(a, w)
 
 
-# Which kernel takes a product of M rows (measured on the layer shapes of an 8B model): up to SMALL_M_ROWS the
-# mma.sync weight stream (a decode step at batch 40: 9.5 ms with it, 10.0 ms with tcgen05 tiles above 32 rows; at
-# 64 rows the two meet); above, the tcgen05 tiles (128 x 256, narrower when the rows are few).
+# Which kernel takes a bfloat16 product of M rows (measured on the layer shapes of an 8B model; the figures are in the
+# design notes):
+#   "rows"   gemm_small_m: weight rows as the M side of mma.sync, tokens register-blocked; the fastest up to 16 rows
+#            and for small matrices up to 64 rows;
+#   "swap"   gemm_stream: tcgen05 with the weight rows as the M side, one 16 KB bulk copy per tile, the k blocks dealt
+#            out evenly over the SMs; from 17 to 128 rows for matrices of 40 MB or more whose rows do not fill the SMs
+#            with whole tiles (QKV, down), where the row kernel's time grows with the rows;
+#   "tiles"  gemm_tcgen05: tokens as the M side, 128 x BN tiles; above that, and from 16 rows for very wide matrices.
 TILE_ROWS = 128          # rows of a tcgen05 product tile (BM in gemm_tcgen05.cu): a step of 129 rows pays for 256
 SMALL_M_ROWS = int(os.environ.get("JLLM_B200_SMALL_M_ROWS", "64"))
 WIDE_ROWS = int(os.environ.get("JLLM_B200_WIDE_ROWS", "16384"))
+SWAP_MIN_BYTES = int(os.environ.get("JLLM_B200_SWAP_MIN_BYTES", str(40_000_000)))
 _workspaces = {}
 # counters of up to 65,536 tiles, then two parked 128 x 256 partial tiles for each of up to 160 blocks
 STREAM_WORKSPACE_FLOATS = 65536 + 160 * 2 * 128 * 256
@@ -247,23 +260,31 @@ def gemm_workspace(device, floats: int = 8 << 20) -> torch.Tensor:
     return held[-1]
 
 
-def gemm_kernel_for(rows: int, out_features: int, stream_fits: bool = True, tiles_fit: bool = True) -> str:
-    """"stream" (the mma.sync weight stream), "tiles" (tcgen05) or "" for a bfloat16 product of `rows` rows against
-    `out_features` weight rows, given which kernels take its strides and alignment."""
+def gemm_kernel_for(rows: int, out_features: int, in_features: int = 4096, rows_fit: bool = True,
+                    tiles_fit: bool = True) -> str:
+    """"rows", "swap", "tiles" or "" for a bfloat16 product of `rows` rows against a [out_features, in_features]
+    weight, given which kernels take its strides and alignment."""
     # 16 or more rows against a wide matrix (gate_up): 128 or more 192-wide tcgen05 tiles stream it faster than the
-    # weight-stream kernel, whose blocks have half their loads in flight once they hold more than two token tiles
+    # weight-row kernel, whose blocks have half their loads in flight once they hold more than two token tiles
     wide = rows >= 16 and out_features >= WIDE_ROWS and tiles_fit
-    if rows <= min(SMALL_M_ROWS, 64) and stream_fits and not wide:
-        return "stream"
+    if tiles_fit and not wide and 16 < rows <= 128 and out_features * in_features * 2 >= SWAP_MIN_BYTES \
+            and (rows <= 96 or in_features >= 8192):
+        return "swap"
+    if rows <= min(SMALL_M_ROWS, 64) and rows_fit and not wide:
+        return "rows"
     return "tiles" if tiles_fit else ""
 
 
 def gemm_bf16(a, w, out, bias=None, accumulate=False, swiglu=False) -> None:
-    """out (+)= a @ w.T (+ bias) on the tensor cores: bfloat16 operands, float32 accumulation. With `swiglu`
-    the rows of w are blocks of 8 gate rows followed by their 8 up rows and out[m, j] = silu(gate_j) * up_j."""
-    kernel = gemm_kernel_for(a.shape[0], w.shape[0], _small_m_fits(a, w), _tcgen05_fits(a, w))
-    if kernel == "stream":
+    """out (+)= a @ w.T (+ bias) on the tensor cores: bfloat16 operands, float32 accumulation; `w` a PackedWeight (a
+    plain [out, in] matrix is packed on the spot). With `swiglu` the rows of w are blocks of 8 gate rows followed by
+    their 8 up rows and out[m, j] = silu(gate_j) * up_j."""
+    w = _packed(w)
+    kernel = gemm_kernel_for(a.shape[0], w.rows, w.cols, _rows_fit(a, w), _tcgen05_fits(a, w))
+    if kernel == "rows":
         return gemm_small_m(a, w, out, bias, accumulate, swiglu=swiglu)
+    if kernel == "swap":
+        return gemm_stream(a, w, out, bias, accumulate, swiglu=swiglu, ordered=True)
     if kernel == "tiles":
         return gemm_tcgen05(a, w, out, bias, accumulate, swiglu=swiglu)
     raise KernelError("the tensor-core matrix product is not built for this shape")
@@ -271,16 +292,89 @@ def gemm_bf16(a, w, out, bias=None, accumulate=False, swiglu=False) -> None:
 
 def gemm_tcgen05(a, w, out, bias=None, accumulate=False, max_blocks: int = 0, swiglu=False, stream_mode: int = 0,
                  tile_width: int = 0) -> None:
-    """The prefill product: TMA-fed tcgen05.mma tiles of 128 x `tile_width` (0: chosen from the shape, 256 for big
-    products, down to 32 when the rows are few) with the accumulator in tensor memory. `stream_mode` 1: the tiles
-    of a last, partly filled round are streamed (stream-K: equal runs of (tile, k block) pairs per block, partial
-    tiles meeting in a workspace); off by default (measured slower on 8B layer shapes)."""
-    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.stride(-1) == 1
+    """The prefill product: tcgen05.mma tiles of 128 x `tile_width` (0: chosen from the shape, 256 for big products,
+    down to 32 when the rows are few) with the accumulator in tensor memory; the activations' tiles come by TMA, the
+    packed weight's by contiguous bulk copies. `stream_mode` 1: the tiles of a last, partly filled round are
+    streamed (stream-K: equal runs of (tile, k block) pairs per block, partial tiles meeting in a workspace); off by
+    default (measured slower on 8B layer shapes)."""
+    w = _packed(w)
+    assert a.dtype == torch.bfloat16 and out.stride(-1) == 1 and a.shape[1] == w.cols
     ws = gemm_workspace(a.device, STREAM_WORKSPACE_FLOATS) if stream_mode > 0 else None
-    _call("jllm_gemm_tcgen05", a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), _p(bias),
+    _call("jllm_gemm_tcgen05", a.data_ptr(), a.stride(0), w.data.data_ptr(), w.k_blocks, _p(bias),
           _DT[bias.dtype] if bias is not None else F32, out.data_ptr(), _DT[out.dtype], out.stride(0),
-          int(accumulate), a.shape[0], w.shape[0], a.shape[1], int(max_blocks), int(swiglu), _p(ws),
+          int(accumulate), a.shape[0], w.rows, w.cols, int(max_blocks), int(swiglu), _p(ws),
           ws.numel() if ws is not None else 0, int(stream_mode), int(tile_width), _stream())
+
+
+class PackedWeight:
+    """A [rows, cols] bfloat16 weight in the layout the tensor cores stream: tiles of 128 rows x 64 k, each tile the
+    16 KB image of its 128-byte-swizzled shared-memory form (row r of a tile is 128 bytes; its 16-byte chunk c lies at
+    chunk position c ^ (r & 7)), tile (t, kb) at (t * k_blocks + kb) * 16 KB. Rows are padded to a multiple of 128 and
+    k to a multiple of 64 with zeros. One tile is one contiguous bulk copy."""
+
+    def __init__(self, data: torch.Tensor, rows: int, cols: int):
+        self.data, self.rows, self.cols = data, rows, cols
+        self.tiles, self.k_blocks = data.shape[0], data.shape[1]
+
+    @property
+    def shape(self):
+        return (self.rows, self.cols)
+
+    def unpack(self) -> torch.Tensor:
+        """The [rows, cols] matrix again (tests)."""
+        T, KB = self.tiles, self.k_blocks
+        idx = _swizzle_index(self.data.device).expand(T, KB, 128, 8, 8)
+        plain = self.data.view(T, KB, 128, 8, 8).gather(3, idx).permute(0, 2, 1, 3, 4).reshape(T * 128, KB * 64)
+        return plain[:self.rows, :self.cols].contiguous()
+
+
+_swizzle = {}
+
+
+def _swizzle_index(device) -> torch.Tensor:
+    idx = _swizzle.get(device)
+    if idx is None:
+        r, c = torch.arange(128, device=device), torch.arange(8, device=device)
+        idx = (c[None, :] ^ (r[:, None] & 7))[None, None, :, :, None]          # [1, 1, 128, 8, 1]
+        _swizzle[device] = idx
+    return idx
+
+
+def pack_weight(w: torch.Tensor) -> PackedWeight:
+    """Packs a [rows, cols] bfloat16 weight for `gemm_stream` (done once, at load)."""
+    assert w.dim() == 2 and w.dtype == torch.bfloat16
+    N, K = w.shape
+    T, KB = -(-N // 128), -(-K // 64)
+    if T * 128 != N or KB * 64 != K:
+        padded = torch.zeros((T * 128, KB * 64), dtype=w.dtype, device=w.device)
+        padded[:N, :K] = w
+    else:
+        padded = w
+    tiles = padded.view(T, 128, KB, 8, 8).permute(0, 2, 1, 3, 4)                   # [T, KB, 128 rows, 8 chunks, 8]
+    data = tiles.gather(3, _swizzle_index(w.device).expand(T, KB, 128, 8, 8)).contiguous().view(T, KB, 128, 64)
+    return PackedWeight(data, N, K)
+
+
+def gemm_stream_fits(a, packed: PackedWeight) -> bool:
+    M, K = a.shape
+    return (1 <= M <= 128 and K == packed.cols and K >= 8 and K % 8 == 0 and a.stride(0) % 8 == 0 and a.stride(1) == 1
+            and a.data_ptr() % 16 == 0)
+
+
+def gemm_stream(a, packed: PackedWeight, out, bias=None, accumulate=False, swiglu=False, max_blocks: int = 0,
+                ordered: bool = False) -> None:
+    """out (+)= a @ W^T (+ bias) for at most 128 rows: the packed weight streamed once through tcgen05.mma with the
+    weight rows as the M side (see gemm_stream.cu). With `swiglu` the rows of W are blocks of 8 gate rows followed by
+    their 8 up rows and out[m, j] = silu(gate_j) * up_j. A tile's parts (its k blocks may fall to several blocks) are
+    added in k order, except where the product is added into float32 memory: there each part is added as it comes,
+    unless `ordered`."""
+    packed = _packed(packed)
+    assert a.dtype == torch.bfloat16 and out.stride(-1) == 1 and a.shape[1] == packed.cols
+    ws = gemm_workspace(a.device, STREAM_WORKSPACE_FLOATS)
+    _call("jllm_gemm_stream", a.data_ptr(), a.stride(0), packed.data.data_ptr(), packed.k_blocks, _p(bias),
+          _DT[bias.dtype] if bias is not None else F32, out.data_ptr(), _DT[out.dtype], out.stride(0), int(accumulate),
+          a.shape[0], packed.rows, packed.cols, int(swiglu), ws.data_ptr(), ws.numel(), int(max_blocks), int(ordered),
+          _stream())
 
 
 BOUNDS_FILES = ("attention_plain", "attention_decode", "attention_prefill", "attention_prefill_tc",
@@ -342,20 +436,13 @@ def gemm_tcgen05_error() -> int:
     return library().jllm_gemm_tcgen05_error()
 
 
-# MB of each small-M product's weights pulled towards L2 before the product waits for its predecessor. Off: with
-# 16-row blocks and the deep unroll (two resident blocks per SM on every layer shape) the prefetch only got in
-# the way of the loads themselves (8B decode step, batch 8: 4.54 ms without, 4.56 with 8 MB, 4.70 with 16 MB).
-PREFETCH_MB = int(os.environ.get("JLLM_B200_PREFETCH_MB", "0"))
-_SMALL_M_TUNING = int(os.environ.get("JLLM_B200_SMALL_M_TUNING", "0"))   # experiments only
-
-
-def gemm_small_m(a, w, out, bias=None, accumulate=False, tuning: int = 0, swiglu=False) -> None:
-    """The decode-step product (at most 64 rows): a weight stream through mma.sync with swapped operands."""
-    tuning = tuning or _SMALL_M_TUNING
-    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.stride(-1) == 1
-    _call("jllm_gemm_small_m", a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), _p(bias),
+def gemm_small_m(a, w, out, bias=None, accumulate=False, swiglu=False) -> None:
+    """The decode-step product (at most 64 rows): the packed weight's rows as the M side of mma.sync, tokens as N."""
+    w = _packed(w)
+    assert a.dtype == torch.bfloat16 and out.stride(-1) == 1 and a.shape[1] == w.cols
+    _call("jllm_gemm_small_m", a.data_ptr(), a.stride(0), w.data.data_ptr(), w.k_blocks, _p(bias),
           _DT[bias.dtype] if bias is not None else F32, out.data_ptr(), _DT[out.dtype], out.stride(0),
-          int(accumulate), a.shape[0], w.shape[0], a.shape[1], int(tuning), int(swiglu), PREFETCH_MB, _stream())
+          int(accumulate), a.shape[0], w.rows, w.cols, int(swiglu), _stream())
 
 
 def attention_decode_fits(dtype, heads, kv_heads, head_dim) -> bool:

@@ -29,7 +29,7 @@ class DecoderModel:
         head = None if core.tied else tensors.pop(names.head, None)
         if head is None and not core.tied:
             runtime.notes.append(f"{names.head} is not in the checkpoint: the embedding serves as the head")
-        self.head = Linear(self.embedding if head is None else head)
+        self.head = Linear(self.embedding, keep_plain=True) if head is None else Linear(head)
         self.position_encodings = []
         for t in spec.rope_tables:
             cls = part_class("position", t.kind)

@@ -37,7 +37,7 @@ def main() -> int:
 
     def weights(n, k):
         copies = max(2, int(300e6 // (n * k * 2)) + 1) if args.repeat > 1 else 1
-        return [(torch.randn(n, k, device=dev) * 0.02).to(bf) for _ in range(copies)]
+        return [ops.pack_weight((torch.randn(n, k, device=dev) * 0.02).to(bf)) for _ in range(copies)]
 
     def interleaved(n_hidden, k):
         return weights(2 * n_hidden, k)      # the SwiGLU epilogue only needs the row count to be a multiple of 16
@@ -53,12 +53,12 @@ def main() -> int:
     x = torch.randn(M, D, device=dev)
     qkv_d, h_d = torch.empty(M, (H + 2 * Hkv) * hd, device=dev, dtype=bf), torch.empty(M, F, device=dev, dtype=bf)
     w_qkv, w_o, w_gu, w_down = weights((H + 2 * Hkv) * hd, D), weights(D, H * hd), interleaved(F, D), weights(D, F)
-    case("decode gemm qkv", lambda i: ops.gemm_bf16(a_d, w_qkv[i], qkv_d), len(w_qkv), w_qkv[0].numel() * 2)
-    case("decode gemm o (+= residual)", lambda i: ops.gemm_bf16(a_d, w_o[i], x, None, True), len(w_o), w_o[0].numel() * 2)
+    case("decode gemm qkv", lambda i: ops.gemm_bf16(a_d, w_qkv[i], qkv_d), len(w_qkv), w_qkv[0].rows * w_qkv[0].cols * 2)
+    case("decode gemm o (+= residual)", lambda i: ops.gemm_bf16(a_d, w_o[i], x, None, True), len(w_o), w_o[0].rows * w_o[0].cols * 2)
     case("decode gemm gate_up + swiglu", lambda i: ops.gemm_bf16(a_d, w_gu[i], h_d, swiglu=True), len(w_gu),
-         w_gu[0].numel() * 2)
+         w_gu[0].rows * w_gu[0].cols * 2)
     case("decode gemm down (+= residual)", lambda i: ops.gemm_bf16(a_f, w_down[i], x, None, True), len(w_down),
-         w_down[0].numel() * 2)
+         w_down[0].rows * w_down[0].cols * 2)
     pages = M * (ctx // page + 1)
     n_caches = max(2, int(300e6 // (pages * Hkv * page * hd * 4)) + 1) if args.repeat > 1 else 1
     caches = [(torch.randn(pages, Hkv, page, hd, device=dev).to(bf), torch.randn(pages, Hkv, page, hd, device=dev).to(bf))

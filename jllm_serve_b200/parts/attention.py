@@ -29,7 +29,7 @@ class GqaAttention(Mixer):
         w = [tensors.pop(prefix + n + ".weight") for n in names]
         b = [tensors.pop(prefix + n + ".bias") for n in names] if spec.bias else None
         self.qkv = Linear(torch.cat(w, dim=0).contiguous(), torch.cat(b).contiguous() if b else None)
-        self.q_only = Linear(self.qkv.weight[:self.q_width], self.qkv.bias[:self.q_width] if b else None)
+        self._q_only = None          # the query rows alone, made when a run first reads another run's cache
         del w, b
         self.out = Linear(tensors.pop(prefix + "o_proj.weight"),
                           tensors.pop(prefix + "o_proj.bias") if spec.out_bias else None)
@@ -67,7 +67,9 @@ class GqaAttention(Mixer):
             self.qkv.forward(xb, qkv)
         else:
             qkv = self.rt.buffer("q_only", self.q_width)[:rows]
-            self.q_only.forward(xb, qkv)
+            if self._q_only is None:
+                self._q_only = self.qkv.rows(0, self.q_width)
+            self._q_only.forward(xb, qkv)
         rope = self.rope
         ops.qk_norm_rope_store(qkv, self.q_gain, self.k_gain, s.qk_norm_eps,
                                rope.cos if rope else None, rope.sin if rope else None,

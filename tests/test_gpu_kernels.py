@@ -113,6 +113,50 @@ def test_gemm_small_m(ops, M, N, K):
     assert torch.allclose(out16.float().cpu(), gemm_want(a, w), rtol=2 ** -7, atol=2e-3)
 
 
+@pytest.mark.parametrize("M", [1, 5, 8, 16, 17, 33, 64, 100, 128])
+@pytest.mark.parametrize("N,K", [(40, 64), (517, 72), (6144, 4096), (4096, 12288), (4736, 1000), (128, 8)])
+def test_gemm_stream(ops, M, N, K):
+    """The weight-stream product over a packed weight: whole tiles and tiles whose k blocks fall to several blocks,
+    bias, the residual add, bfloat16 output, few blocks (every block walks many tiles), and the same bits twice."""
+    a, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=1, scale=0.05)
+    packed = ops.pack_weight(w)
+    assert torch.equal(packed.unpack(), w)
+    bias = rnd(N, dtype=torch.bfloat16, seed=2)
+    want = gemm_want(a, w, bias)
+    out = torch.full((M, N), float("nan"), device=DEV)
+    ops.gemm_stream(a, packed, out, bias)
+    assert ops.gemm_tcgen05_error() == 0
+    tol = 1e-4 * math.sqrt(K) * 0.05
+    assert torch.allclose(out.cpu(), want, rtol=1e-4, atol=tol), float((out.cpu() - want).abs().max())
+    base = rnd(M, N, seed=3)
+    for blocks in (0, 3, 7):
+        acc, again, free = base.clone(), base.clone(), base.clone()
+        ops.gemm_stream(a, packed, acc, bias, accumulate=True, max_blocks=blocks, ordered=True)
+        ops.gemm_stream(a, packed, again, bias, accumulate=True, max_blocks=blocks, ordered=True)
+        assert torch.allclose(acc.cpu(), gemm_want(a, w, bias, base), rtol=1e-4, atol=tol), blocks
+        assert torch.equal(acc, again), "the parts of a tile are added in k order: two runs give the same bits"
+        ops.gemm_stream(a, packed, free, bias, accumulate=True, max_blocks=blocks)      # parts added as they come
+        assert torch.allclose(free.cpu(), gemm_want(a, w, bias, base), rtol=1e-4, atol=tol), blocks
+    out16 = torch.zeros(M, N + 8, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_stream(a, packed, out16[:, :N])
+    assert torch.allclose(out16[:, :N].float().cpu(), gemm_want(a, w), rtol=2 ** -7, atol=2e-3)
+    assert float(out16[:, N:].abs().max()) == 0 and ops.gemm_tcgen05_error() == 0
+
+
+@pytest.mark.parametrize("M", [1, 8, 20, 64, 128])
+@pytest.mark.parametrize("hidden,K", [(8, 8), (200, 72), (12288, 4096), (1000, 136)])
+def test_gemm_stream_with_swiglu_epilogue(ops, M, hidden, K):
+    a = rnd(M, K, dtype=torch.bfloat16)
+    gate, up = rnd(hidden, K, dtype=torch.bfloat16, seed=1, scale=0.05), rnd(hidden, K, dtype=torch.bfloat16, seed=2, scale=0.05)
+    w = torch.stack([gate.view(hidden // 8, 8, K), up.view(hidden // 8, 8, K)], dim=1).reshape(2 * hidden, K).contiguous()
+    want = P.silu(gemm_want(a, gate)) * gemm_want(a, up)
+    for blocks in (0, 5):
+        out = torch.full((M, hidden), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.gemm_stream(a, ops.pack_weight(w), out, swiglu=True, max_blocks=blocks)
+        assert ops.gemm_tcgen05_error() == 0
+        assert torch.allclose(out.float().cpu(), want, rtol=2 ** -7, atol=1e-3), float((out.float().cpu() - want).abs().max())
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (1, 8, 8), (100, 517, 72), (300, 1000, 200), (2048, 6144, 4096),
                                    (257, 4096, 12288), (64, 300, 4096), (129, 257, 136)])
 def test_gemm_tcgen05(ops, M, N, K):

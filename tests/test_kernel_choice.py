@@ -4,17 +4,20 @@ import torch
 from jllm_serve_b200.csrc import ops
 
 
-def test_product_kernel_by_rows_and_width():
-    assert ops.gemm_kernel_for(1, 4096) == "stream"
-    assert ops.gemm_kernel_for(8, 24576) == "stream"               # few rows: even the widest matrix is a stream
-    assert ops.gemm_kernel_for(16, 24576) == "tiles"               # 16 rows against gate_up: tcgen05 tiles
-    assert ops.gemm_kernel_for(16, 4096) == "stream"
-    assert ops.gemm_kernel_for(64, 6144) == "stream"
-    assert ops.gemm_kernel_for(65, 6144) == "tiles"
-    assert ops.gemm_kernel_for(2048, 4096) == "tiles"
-    assert ops.gemm_kernel_for(16, 24576, tiles_fit=False) == "stream"
-    assert ops.gemm_kernel_for(8, 4096, stream_fits=False) == "tiles"
-    assert ops.gemm_kernel_for(8, 4096, stream_fits=False, tiles_fit=False) == ""
+def test_product_kernel_by_rows_and_shape():
+    k = ops.gemm_kernel_for
+    assert k(1, 4096, 4096) == "rows"
+    assert k(8, 24576, 4096) == "rows"                     # few rows: even the widest matrix goes row by row
+    assert k(16, 24576, 4096) == "tiles"                   # 16 rows against gate_up: tcgen05 tiles
+    assert k(16, 6144, 4096) == "rows"
+    assert k(17, 6144, 4096) == "swap"                     # QKV (50 MB) from 17 rows: weight rows as the MMA's M side
+    assert k(64, 6144, 4096) == "swap" and k(96, 6144, 4096) == "swap" and k(128, 6144, 4096) == "tiles"
+    assert k(64, 4096, 12288) == "swap" and k(128, 4096, 12288) == "swap" and k(129, 4096, 12288) == "tiles"
+    assert k(64, 4096, 4096) == "rows" and k(65, 4096, 4096) == "tiles"        # O (34 MB): too small for it
+    assert k(2048, 4096, 4096) == "tiles"
+    assert k(16, 24576, 4096, tiles_fit=False) == "rows"
+    assert k(8, 4096, 4096, rows_fit=False) == "tiles"
+    assert k(8, 4096, 4096, rows_fit=False, tiles_fit=False) == ""
 
 
 def test_decode_attention_splits_fill_the_gpu_once():
