@@ -108,6 +108,8 @@ def main() -> int:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--rounds", type=int, default=5,
+                    help="the K steps are timed this many times, one after the other; the median round is reported")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0,
@@ -116,6 +118,9 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length at which the decode steps are timed")
     ap.add_argument("--mixed-chunk", type=int, default=0,
                     help="rows of a prompt portion that rides in every timed step beside the decoding requests")
+    ap.add_argument("--kv-share", type=float, default=0.0,
+                    help="size the cache pool as this share of the device memory left after the weights (else: the "
+                         "pages the run needs)")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true")
@@ -160,10 +165,13 @@ def main() -> int:
                  "rows": got["rows"], "max_rel": round(got["max_rel"], 5), "rms_rel": round(got["rms_rel"], 5),
                  "argmax_agree": round(got["argmax_agree"], 4), "choice_gap_rel": round(got["worst_choice_gap_rel"], 5)}
     t0 = time.time()
-    engine = Engine(config=cfg, seed=0, dtype="bfloat16", ctx=ctx, page_size=PAGE, num_pages=pool_tokens // PAGE,
+    engine = Engine(config=cfg, seed=0, dtype="bfloat16", ctx=ctx, page_size=PAGE,
+                    num_pages="auto" if args.kv_share > 0 else pool_tokens // PAGE, kv_share=args.kv_share or 0.6,
                     max_batch_tokens=PREFILL_TOKENS + 64, chunk=PREFILL_TOKENS, max_running=biggest + 1)
     runner = engine.runner
     print(f"bench: {runner.describe()} (built in {time.time() - t0:.0f} s)", file=sys.stderr, flush=True)
+    for note in runner.notes:
+        print(f"bench: {note}", file=sys.stderr, flush=True)
     for g in runner.cache.paged:      # any cached values do for timing; zeros would be kinder to the memory system
         g.storage.normal_()
     out_tok = torch.empty(64, dtype=torch.int32, device=dev)
@@ -171,13 +179,15 @@ def main() -> int:
     def events():
         return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
-    def decode_device_timed(batch: int, steps: int, warmup: int):
-        """`batch` requests whose contexts END at the context length after warmup + steps decoded tokens; the
-        cache content is synthetic. With --mixed-chunk a portion of a prompt (rows 1,024 onwards of a request that
-        is given back after the step) runs in every step before them.
-        Returns (ms per step, mean context during the timed steps, kernels launched)."""
+    def decode_device_timed(batch: int, steps: int, warmup: int, rounds: int = 1):
+        """`batch` requests whose contexts END at the context length after warmup + rounds x steps decoded tokens;
+        the cache content is synthetic. With --mixed-chunk a portion of a prompt (rows 1,024 onwards of a request
+        that is given back after the step) runs in every step before them. Each round times exactly `steps` steps
+        between two events with a synchronize on both sides; the median round is reported.
+        Returns (ms per step of the median round, mean context during that round, kernels launched in it, ms per
+        step of every round)."""
         ids = [f"d{batch}-{i}" for i in range(batch)]
-        start = ctx - warmup - steps
+        start = ctx - warmup - rounds * steps
         portions = [0]
         for i in ids:
             runner.cache.open(i)
@@ -200,19 +210,25 @@ def main() -> int:
 
         for _ in range(warmup):
             one_step()
-        torch.cuda.synchronize()
-        before = ops.launch_count
-        s, e = events()
-        s.record()
-        for _ in range(steps):
-            one_step()
-        e.record()
-        torch.cuda.synchronize()
-        ms = s.elapsed_time(e) / steps
-        launched = ops.launch_count - before
+        times, launched = [], 0
+        for _ in range(rounds):
+            torch.cuda.synchronize()
+            before = ops.launch_count
+            s, e = events()
+            s.record()
+            for _ in range(steps):
+                one_step()
+            e.record()
+            torch.cuda.synchronize()
+            times.append(s.elapsed_time(e) / steps)
+            launched = ops.launch_count - before
         for i in ids:
             runner.finish(i)
-        return ms, ctx - steps / 2.0, launched
+        order = sorted(range(rounds), key=lambda r: times[r])
+        mid = order[rounds // 2]
+        # the median round ran steps [mid * steps, (mid + 1) * steps) of the timed ones: its mean context
+        mean_ctx = ctx - (rounds - mid) * steps + steps / 2.0
+        return times[mid], mean_ctx, launched, times
 
     def decode_bytes(batch: int, context: float) -> float:
         return nums["weight_bytes"] + batch * context * nums["kv_bytes_per_token"]
@@ -233,12 +249,14 @@ def main() -> int:
     # ---- the headline: decode at the default batch, clocks sampled meanwhile -------------------------------
     clocks = ClockSampler()
     clocks.start()
-    ms_step, mean_ctx, launches = decode_device_timed(args.batch, args.steps, args.warmup)
+    ms_step, mean_ctx, launches, round_ms = decode_device_timed(args.batch, args.steps, args.warmup, max(1, args.rounds))
     clock_record = clocks.stop()
+    clock_record["rounds_ms_per_step"] = [round(t, 4) for t in round_ms]
     value = args.batch * 1000.0 / ms_step
     achieved = decode_bytes(args.batch, mean_ctx) / (ms_step * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                "frac": round(achieved / pk["hbm_gbs"], 4), "peak_source": pk["source"]}
+                "frac": round(achieved / pk["hbm_gbs"], 4), "peak_source": pk["source"],
+                "bytes": int(decode_bytes(args.batch, mean_ctx))}
 
     # ---- prefill of one 2,048-token prompt ---------------------------------------------------------------------
     g = torch.Generator().manual_seed(1)
@@ -259,19 +277,29 @@ def main() -> int:
     flops = 2.0 * nums["layer_params"] * args.layers * PREFILL_TOKENS + nums["attn_flops_per_layer"](PREFILL_TOKENS) \
         * args.layers + 2.0 * nums["head_params"]
     prefill = {"value": round(PREFILL_TOKENS / pre_ms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
-               "frac": round(flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "tflops": round(flops / pre_ms / 1e9, 1)}
+               "frac": round(flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "tflops": round(flops / pre_ms / 1e9, 1),
+               "peak_tflops": pk["bf16_tflops"], "peak_source": pk["source"]}
+    if "bf16_tflops_sustained" in pk:       # the same against what the GEMM library sustains under the power cap
+        prefill["frac_of_sustained"] = round(flops / (pre_ms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)
 
     # ---- decode at batch 1 and 64 --------------------------------------------------------------------------------
     points = {}
     if not args.skip_points:
         for b in (1, 64):
-            ms_b, _, _ = decode_device_timed(b, max(8, args.steps // 2), 3)
+            ms_b, ctx_b, _, _ = decode_device_timed(b, max(8, args.steps // 2), 3, 3)
+            gbs = decode_bytes(b, ctx_b) / (ms_b * 1e-3) / 1e9
             points[f"decode_b{b}"] = round(b * 1000.0 / ms_b, 1)
+            points[f"decode_b{b}_ms"] = round(ms_b, 4)
+            points[f"decode_b{b}_hbm_frac"] = round(gbs / pk["hbm_gbs"], 4)
 
     # ---- end to end through the public entry point --------------------------------------------------------------
     e2e = None
     if not args.skip_e2e:
         e2e = end_to_end(engine, args.batch, args.steps, args.warmup, cfg["vocab_size"])
+        if not args.skip_points:
+            for b in (1, 64):
+                other = end_to_end(engine, b, max(8, args.steps // 2), 3, cfg["vocab_size"])
+                points[f"e2e_b{b}"] = other["value"]
 
     record = {
         "metric": (f"decode tok/s @ batch {args.batch}, context {ctx} (Qwen3-{args.shape.upper()} shape, bf16, random weights"
@@ -299,7 +327,11 @@ def end_to_end(engine, batch: int, steps: int, warmup: int, vocab: int):
     import torch
 
     from jllm_serve_b200.sampling import SamplingParams
-    new_tokens = warmup + steps + 1
+    # the prompts are prefilled one after the other (two portions each): a request that is ready early decodes while the
+    # others' prompts still run, so every request may generate that many tokens more than the timed steps need and none
+    # ends inside the timed region
+    slack = 2 * batch + 2
+    new_tokens = warmup + steps + 1 + slack
     prompt_len = CONTEXT - new_tokens
     g = torch.Generator().manual_seed(2)
     params = SamplingParams.greedy_params(max_tokens=new_tokens, ignore_eos=True)
@@ -312,18 +344,27 @@ def end_to_end(engine, batch: int, steps: int, warmup: int, vocab: int):
         engine.step_once()
     torch.cuda.synchronize()
     h2d = engine.runner.builder.bytes_per_step(batch)
+    mine = [r for r in sched.running + sched.waiting]
+
+    def generated():
+        return sum(len(r.output) for r in mine)
+
+    before = generated()
     t0 = time.perf_counter()
-    done = 0
     for _ in range(steps):
         engine.step_once()
-        done += batch
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
+    done = generated() - before          # tokens that were really sampled (a preempted request decodes nothing)
+    if done != steps * batch:
+        print(f"bench: end to end at batch {batch}: {done} tokens in {steps} steps, expected {steps * batch}",
+              file=sys.stderr, flush=True)
     engine.run_until_done()
     for i in ids:
         engine.scheduler.finished.pop(i, None)
     return {"value": round(done / dt, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * engine.sampler.max_rows,
-            "ms_per_step": round(dt / steps * 1e3, 4)}
+            "ms_per_step": round(dt / steps * 1e3, 4), "tokens_per_step": round(done / steps, 2),
+            "preemptions": sched.preemptions}
 
 
 if __name__ == "__main__":
