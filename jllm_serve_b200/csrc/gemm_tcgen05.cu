@@ -144,21 +144,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __nv_bfloat
             int tile, lo, hi;
             while (ok && next_unit(walk, tile, lo, hi)) {
                 const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
-                for (int kb = lo; kb < hi; ++kb) {
+                // The W tile: rows [n0, n0 + BN) of every k block, as one or two contiguous pieces of the packed layout
+                // (a piece ends where a packed tile of 128 rows ends; a BN-row tile meets at most two of them). Rows
+                // beyond the padded matrix do not exist: their part of a stage keeps what it held, and the columns they
+                // would give are never stored. Everything that does not change with the k block is worked out here:
+                // this one thread's instructions per k block are what a product of narrow tiles waits for.
+                const int w_rows = min(BN, padded_rows - n0);
+                const int in_tile = n0 & 127;
+                const uint32_t bytes0 = (uint32_t)min(128 - in_tile, w_rows) * 128u;
+                const uint32_t bytes1 = (uint32_t)w_rows * 128u - bytes0;
+                const __nv_bfloat16* src = w_packed + ((size_t)(n0 >> 7) * k_blocks + lo) * 8192 + (size_t)in_tile * 64;
+                const size_t next_tile = (size_t)k_blocks * 8192 - (size_t)in_tile * 64;      // to the tile below, row 0
+                const uint32_t tx = A_BYTES + bytes0 + bytes1;
+                uint32_t extra = starve ? 16u : 0u;         // the wait test: the first barrier expects too much
+                for (int kb = lo; kb < hi; ++kb, src += 8192) {
                     if (!mbar_wait(empty_bar(s), parity, abort_flag, spin)) { ok = false; break; }
-                    // the W tile: rows [n0, n0 + BN) of k block kb, contiguous pieces of the packed layout (a piece ends
-                    // where a packed tile of 128 rows ends; rows beyond the padded matrix do not exist: their part of
-                    // the stage keeps what it held, and the columns they would give are never stored)
-                    const int w_rows = min(BN, padded_rows - n0);
-                    mbar_expect_tx(full_bar(s), A_BYTES + (uint32_t)w_rows * 128u + ((starve && kb == lo) ? 16u : 0u));
+                    mbar_expect_tx(full_bar(s), tx + extra);
+                    extra = 0;
                     tma_load_2d(dst, &map_a, kb * BK, m0, full_bar(s));
-                    for (int r = 0; r < w_rows;) {
-                        const int n = n0 + r, in_tile = n & 127, cnt = min(128 - in_tile, w_rows - r);
-                        bulk_copy(dst + A_BYTES + (uint32_t)r * 128u,
-                                  w_packed + ((size_t)(n >> 7) * k_blocks + kb) * 8192 + (size_t)in_tile * 64,
-                                  (uint32_t)cnt * 128u, full_bar(s));
-                        r += cnt;
-                    }
+                    bulk_copy(dst + A_BYTES, src, bytes0, full_bar(s));
+                    if (bytes1) bulk_copy(dst + A_BYTES + bytes0, src + next_tile, bytes1, full_bar(s));
                     dst += STAGE_BYTES;
                     if (++s == STAGES) { s = 0; parity ^= 1u; dst = base; }
                 }
