@@ -36,8 +36,11 @@ __host__ __device__ constexpr int stages_for(int bn) { return bn >= 256 ? 4 : bn
 constexpr int JLLM_TC_MAX_TILES = 65536;  // counter words at the head of the workspace of streamed products
 constexpr int THREADS = 192;           // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
 constexpr int TMEM_COLS = 512;
+constexpr int STAGING_ROW = 36;        // floats of a staged row of 32 values: 16-byte aligned, and rows fall in other banks
+constexpr int STAGING_BYTES = 4 * 32 * STAGING_ROW * 4;      // 32 rows for each of the four epilogue warps
 __host__ __device__ constexpr size_t smem_bytes_for(int bn) {
-    return (size_t)stages_for(bn) * (A_BYTES + bn * BK * 2) + 1024 /* alignment slack */ + 256 /* barriers */;
+    return (size_t)stages_for(bn) * (A_BYTES + bn * BK * 2) + 1024 /* alignment slack */ + 256 /* barriers */ +
+           STAGING_BYTES;
 }
 
 // Instruction descriptor of kind::f16: float32 accumulate (1 at [4,6)), A and B bfloat16 (1 at [7,10) and
@@ -70,6 +73,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __nv_bfloat
     uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(aligned + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 4));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
     volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 2);
+    float* staging = reinterpret_cast<float*>(aligned + STAGES * STAGE_BYTES + 256);     // behind the barriers
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN, tiles = tiles_m * tiles_n;
@@ -216,8 +220,45 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __nv_bfloat
             const int row = m0 + quad * 32 + lane;
             const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quad * 32) << 16);
             // bias / residual / SwiGLU and the store of 32 columns of this thread's row
+            // all 32 rows of this warp lie inside the matrix, and float32 rows can be accessed 16 bytes at a time
+            const bool rows_whole = !swiglu && m0 + quad * 32 + 32 <= M && sizeof(Tout) == 4 && (ldo & 3) == 0 &&
+                                    (((uintptr_t)out) & 15u) == 0;
+            // Through shared memory, so that a warp's accesses are whole lines: a thread holds 32 values of ONE row, and
+            // written (or added) from there a warp's instruction would touch 32 rows with 16 bytes each. The warp parks
+            // its 32 x 32 block and takes it back four rows at a time, eight threads to a row: four full 128-byte lines
+            // per instruction, and all eight loads of a residual add are on their way before the first store.
+            auto staged_rows = [&](uint32_t (&v)[32], int c0) {
+                const int n_base = n0 + c0;
+                float* mine = staging + quad * (32 * STAGING_ROW);
+                float4* srow = reinterpret_cast<float4*>(mine + lane * STAGING_ROW);
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    srow[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                          __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                __syncwarp();
+                const int sub = lane >> 3, c4 = (lane & 7) * 4;
+                float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (has_bias)
+                    bv = make_float4(bias[n_base + c4], bias[n_base + c4 + 1], bias[n_base + c4 + 2], bias[n_base + c4 + 3]);
+                float* d0 = reinterpret_cast<float*>(out) + (size_t)(m0 + quad * 32 + sub) * ldo + n_base + c4;
+                float4 old[8];
+                if (accumulate) {
+#pragma unroll
+                    for (int p = 0; p < 8; ++p) old[p] = *reinterpret_cast<const float4*>(d0 + (size_t)(4 * p) * ldo);
+                }
+#pragma unroll
+                for (int p = 0; p < 8; ++p) {
+                    float4 x = *reinterpret_cast<const float4*>(mine + (4 * p + sub) * STAGING_ROW + c4);
+                    x.x += bv.x; x.y += bv.y; x.z += bv.z; x.w += bv.w;
+                    if (accumulate) { x.x += old[p].x; x.y += old[p].y; x.z += old[p].z; x.w += old[p].w; }
+                    *reinterpret_cast<float4*>(d0 + (size_t)(4 * p) * ldo) = x;
+                }
+                __syncwarp();
+            };
             auto finalize = [&](uint32_t (&v)[32], int c0) {
-                if (row < M && swiglu) {
+                if (rows_whole && n0 + c0 + 32 <= N) {
+                    staged_rows(v, c0);
+                } else if (row < M && swiglu) {
                     // columns come in blocks of 16: 8 gate columns, then the 8 up columns of the same hidden units
                     const int n_base = n0 + c0;
                     Tout* dst = out + (size_t)row * ldo + (n_base >> 1);
