@@ -55,7 +55,13 @@ __device__ __forceinline__ void attend(uint8_t* smem_raw, const __nv_bfloat16* _
                                        int table_len, int num_pages, int heads, int kv_heads, int page_size,
                                        float scale_log2, int r, int kvh, int P,
                                        int first, int tile_lo, int n_tiles, bool whole, float* __restrict__ part_o,
-                                       size_t o_stride, float* __restrict__ part_ml, size_t ml_stride) {
+                                       size_t o_stride, float* __restrict__ part_ml, size_t ml_stride,
+                                       bool early = false) {
+    // `early`: the block has not yet waited for the kernel in front of it (programmatic dependent launch). That kernel
+    // wrote the queries and the key and value of position P; the block tables and the positions came from the host
+    // before the step, and the keys and values of earlier positions were written by earlier steps. So the rows of
+    // the first two tiles are looked up, and those tiles requested if they end before P, while that kernel still
+    // runs; the wait comes before anything of position P or of the queries is touched.
     constexpr int CHUNKS = HD / 8, TILE_BYTES = TILE * HD * 2, STAGE_BYTES = 2 * TILE_BYTES;
     const uint32_t s_q = (uint32_t)__cvta_generic_to_shared(smem_raw);
     const uint32_t s_kv = s_q + 16 * HD * 2;
@@ -65,11 +71,13 @@ __device__ __forceinline__ void attend(uint8_t* smem_raw, const __nv_bfloat16* _
     const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
 
     // Q: the G heads of this kv head as rows 0 .. G-1 of a 16-row tile (the rest zero)
-    for (int i = threadIdx.x; i < 16 * CHUNKS; i += THREADS) {
-        const int row = i / CHUNKS, c = i % CHUNKS;
-        const __nv_bfloat16* src = q + (size_t)r * q_stride + (size_t)(kvh * G + min(row, G - 1)) * HD + c * 8;
-        cp16(s_q + off<HD>(row, c), src, row < G ? 16 : 0);
-    }
+    auto load_q = [&]() {
+        for (int i = threadIdx.x; i < 16 * CHUNKS; i += THREADS) {
+            const int row = i / CHUNKS, c = i % CHUNKS;
+            const __nv_bfloat16* src = q + (size_t)r * q_stride + (size_t)(kvh * G + min(row, G - 1)) * HD + c * 8;
+            cp16(s_q + off<HD>(row, c), src, row < G ? 16 : 0);
+        }
+    };
     // Where the rows of a tile lie in the cache (element offset of the key's first value, -1 past the end): looked
     // up by one thread per row a tile ahead of the copies, so that no copy waits for a page-table load.
     __shared__ long long s_row_base[2][TILE];
@@ -107,8 +115,19 @@ __device__ __forceinline__ void attend(uint8_t* smem_raw, const __nv_bfloat16* _
     find_rows(0);
     find_rows(1);
     __syncthreads();
-    load_tile(0);           // group 0 also carries Q
-    load_tile(1);
+    // a tile may be requested before the wait if all its keys lie before position P
+    const int last_of_0 = first + (tile_lo + 1) * TILE - 1, last_of_1 = last_of_0 + TILE;
+    const bool pre0 = early && last_of_0 < P, pre1 = early && last_of_1 < P;
+    if (pre0) load_tile(0);
+    if (pre1) load_tile(1);
+    if (early) {
+        pdl_wait();
+        pdl_trigger();
+    }
+    load_q();
+    if (!pre0) load_tile(0); else if (!pre1) load_tile(1);     // (each load_tile commits a group; Q rides in this one)
+    if (!pre0 && !pre1) load_tile(1);
+    if (pre0 && pre1) commit();                                 // Q alone
     __syncthreads();        // everyone has read the rows of tile 0: its slot takes those of tile 2
     find_rows(2);
 
@@ -121,7 +140,9 @@ __device__ __forceinline__ void attend(uint8_t* smem_raw, const __nv_bfloat16* _
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
     for (int i = 0; i < n_tiles; ++i) {
-        wait_group<STAGES - 2>();   // tile i has landed (the groups of later tiles may still be in flight)
+        // tile i has landed (the groups of later tiles may still be in flight); before the first tile everything that
+        // was asked for so far, because Q may have been asked for after tile 1
+        if (i == 0) wait_group<0>(); else wait_group<STAGES - 2>();
         __syncthreads();            // ... for every thread's part of it; and everyone is done with tile i - 1
         load_tile(i + STAGES - 1);  // refills the stage that tile i - 1 used
         find_rows(i + STAGES);      // into the slot that tile i + 1's copies (issued an iteration ago) have left
@@ -251,8 +272,8 @@ attention_decode_staged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const int r = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int G = heads / kv_heads;
-    pdl_wait();      // the newest key and value of every row were written by the kernel before this one
-    pdl_trigger();
+    // (the wait for the kernel in front, which wrote the newest key and value of every row and the queries, is inside
+    // `attend`, behind the look-ups and the first requests that do not depend on it)
     const int P = row_pos[r];
     const int first = window > 0 ? max(0, P + 1 - window) : 0;
     const int tiles_total = (P + 1 - first + TILE - 1) / TILE;
@@ -262,8 +283,8 @@ attention_decode_staged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
     // partials: (row, head, split) -> head_dim sums in part_o, (maximum, weight) in part_ml
     const size_t slot = ((size_t)r * heads + kvh * G) * splits + split;
     attend<HD>(smem_raw, q, q_stride, k_cache, v_cache, out, out_stride, table, table_stride, num_pages, heads, kv_heads,
-               page_size, scale_log2, r, kvh, P, first, tile_lo, max(0, tile_hi - tile_lo), splits == 1, part_o + slot * HD, (size_t)splits * HD,
-               part_ml + slot * 2, (size_t)splits * 2);
+               page_size, scale_log2, r, kvh, P, first, tile_lo, max(0, tile_hi - tile_lo), splits == 1, part_o + slot * HD,
+               (size_t)splits * HD, part_ml + slot * 2, (size_t)splits * 2, true);
 }
 
 // ---- the same attention with the key tiles of all (row, kv head) pairs dealt out evenly ----------------------------------
