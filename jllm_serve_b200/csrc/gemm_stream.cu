@@ -11,11 +11,9 @@
 //     x tokens] lives in tensor memory, two of them so that an epilogue overlaps the next tile's stream;
 //   * the k blocks of ALL tiles, in tile order, are dealt out in equal runs over one block per SM, so every SM
 //     streams the same number of bytes whatever the matrix's height; a tile whose k blocks fall to several blocks
-//     is finished by whichever of them comes last, which adds the parked parts in k order (the result does not
-//     depend on which block that was). Where the product is ADDED into float32 memory (the residual stream), the
-//     parts are instead added straight into it (float atomics: no parking, no waiting for the other parts, which
-//     takes some microseconds off every such product); the order of those few additions is then not fixed, so two
-//     runs may differ in the last bit (`ordered` asks for the parked, fixed-order way there too);
+//     is finished by those blocks together: each parks its part, and when all have, those that end their run in the
+//     tile each add up a share of the token columns over the parts in k order (the result does not depend on who
+//     came when);
 //   * the activations' tile of a k block (tokens x 64) comes by TMA from the [rows, K] matrix (L2 resident);
 //   * the producer requests its first weights BEFORE it waits for the kernel in front of it (programmatic dependent
 //     launch): weights do not depend on it.
@@ -43,22 +41,11 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
         : "memory");
 }
 
-#ifdef JLLM_STREAM_TIMING
-__device__ unsigned long long g_stamp[160][8];
-__device__ __forceinline__ void stamp(int i) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_stamp[blockIdx.x][i] = t;
-}
-#else
-__device__ __forceinline__ void stamp(int) {}
-#endif
-
 template <typename Tout>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __nv_bfloat16* __restrict__ w_packed, VecRef bias,
                    int has_bias, Tout* __restrict__ out, int ldo, int accumulate, int M, int N, int k_blocks, int swiglu,
-                   int ntok, int stages, uint32_t tmem_cols, int ordered, float* __restrict__ partials,
+                   int ntok, int stages, uint32_t tmem_cols, float* __restrict__ partials,
                    int* __restrict__ counters, int* __restrict__ error_word) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -74,7 +61,6 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __nv_bfloat1
     volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x == 0) stamp(0);
     const int tiles = (N + WM - 1) / WM;
     // the work: (tile, k block) pairs in tile order, one equal run per block
     const long long total = (long long)tiles * k_blocks;
@@ -116,10 +102,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __nv_bfloat1
                 mbar_expect_tx(full_bar(i), stage_bytes);
                 bulk_copy(base + (uint32_t)i * stage_bytes, w_packed + (size_t)g * (WM * BK), W_TILE_BYTES, full_bar(i));
             }
-            stamp(1);
             pdl_wait();
             pdl_trigger();
-            stamp(2);
             for (int i = 0; i < early; ++i) {
                 const int kb = (int)((run_lo + i) % k_blocks);
                 tma_load_2d(base + (uint32_t)i * stage_bytes + W_TILE_BYTES, &map_a, kb * BK, 0, full_bar(i));
@@ -156,7 +140,6 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __nv_bfloat1
                 const uint32_t tmem_d = tmem_base + buf * acc_cols;
                 for (bool first = true; g < seg_end; ++g, first = false) {
                     if (!mbar_wait(full_bar(s), parity, abort_flag)) { ok = false; break; }
-                    if (g == run_lo) stamp(3);
                     tcgen05_fence_after();
                     const uint32_t w_addr = base + (uint32_t)s * stage_bytes, b_addr = w_addr + W_TILE_BYTES;
 #pragma unroll
@@ -169,7 +152,6 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __nv_bfloat1
                 if (ok) tcgen05_commit(acc_full_bar(buf));
                 ++segment;
             }
-            stamp(4);
             if (!ok) { *abort_flag = 1; atomicExch(error_word, 12); }
         }
     } else {
@@ -190,25 +172,12 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __nv_bfloat1
             const uint32_t buf = segment & 1u;
             if (!mbar_wait(acc_full_bar(buf), (segment >> 1) & 1u, abort_flag)) { ok = false; break; }
             tcgen05_fence_after();
-            if (warp == 2 && lane == 0) stamp(7);
             const int row_in_tile = quad * 32 + lane;
             const int n = tile * WM + row_in_tile;                 // this thread's weight row = output column
             const uint32_t taddr = tmem_base + buf * acc_cols + ((uint32_t)(quad * 32) << 16);
             // value of (token m, weight row n): bias / residual / SwiGLU and the store
-            auto finalize16 = [&](const float (&v)[16], int m0, bool part = false) {
-                if (part) {
-                    // a part of a tile that is added into float32 memory: straight into it, whoever comes first (the
-                    // bias rides with the part that holds the tile's first k block)
-                    if constexpr (sizeof(Tout) == 4) {
-                        if (n < N) {
-                            const float b = (has_bias && kb0 == 0) ? bias[n] : 0.f;
-                            float* dst = reinterpret_cast<float*>(out) + (size_t)m0 * ldo + n;
-#pragma unroll
-                            for (int j = 0; j < 16; ++j)
-                                if (m0 + j < M) atomicAdd(dst + (size_t)j * ldo, v[j] + b);
-                        }
-                    }
-                } else if (swiglu) {
+            auto finalize16 = [&](const float (&v)[16], int m0) {
+                if (swiglu) {
                     // rows come in blocks of 16: 8 gate rows, then the 8 up rows of the same hidden units
                     const int unit = (n >> 4) * 8 + (n & 7);
 #pragma unroll
@@ -232,9 +201,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __nv_bfloat1
                         if (m0 + j < M) dst[(size_t)j * ldo] = from_float<Tout>((v[j] + b) + old[j]);
                 }
             };
-            const bool whole = kb0 == 0 && kb1 == k_blocks;         // the whole tile is this block's
-            const bool adds_part = !whole && accumulate && sizeof(Tout) == 4 && !ordered;
-            if (whole || adds_part) {
+            if (kb0 == 0 && kb1 == k_blocks) {                      // the whole tile is this block's
 #pragma unroll 1
                 for (int c0 = 0; c0 < ntok; c0 += 16) {
                     uint32_t raw[16];
@@ -243,7 +210,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __nv_bfloat1
                     float v[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(raw[j]);
-                    finalize16(v, c0, adds_part);
+                    finalize16(v, c0);
                 }
                 tcgen05_fence_before();
                 __syncwarp();
@@ -270,20 +237,37 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __nv_bfloat1
                 __syncwarp();
                 if (lane == 0) mbar_arrive(acc_empty_bar(buf));
                 asm volatile("bar.sync 1, 128;" ::: "memory");       // the four epilogue warps have written
+                // The parts of a tile are added up by the blocks that hold one and END their run in it: number p of them takes
+                // the 16-token chunks p, p + np, ... (a block may have none), so that each has one batch of loads to wait
+                // for instead of one block having them all. They finish their runs at about the same time, so waiting for
+                // one another costs little, and nothing is behind that wait in their runs. The block that only BEGINS its
+                // run in this tile (the tile's last holder, if its run goes on into other tiles) parks its part long
+                // before and waits for nobody: a wait there would hold up its later tiles, and through them the blocks
+                // that wait for those. Every holder counts itself in; the wait is a bounded one on that counter (all
+                // blocks of the grid are resident, one per SM).
+                const int p_me = (int)blockIdx.x - c_first, chunks = ntok >> 4;
+                const bool tail_goes_on = run_start(c_first + parts) > tile_g0 + k_blocks;
+                const int np = parts - (tail_goes_on ? 1 : 0);              // holders that take part in the adding
+                const bool takes_part = seg_end == run_hi;                   // (p_me < np says the same)
+                const bool has_share = takes_part && p_me < chunks;
                 if (warp == 2 && lane == 0) {
                     __threadfence();
-                    const int seen = atomicAdd(&counters[tile], 1);
-                    *last_flag = seen == parts - 1;
-                    if (seen == parts - 1) {
-                        counters[tile] = 0;                            // back to zero for the next product
-                        __threadfence();
+                    atomicAdd(&counters[tile], 1);
+                    int seen = has_share ? 0 : parts;
+                    for (uint32_t spin = 0; seen < parts && spin < SPIN_LIMIT; ++spin) {
+                        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(counters + tile) : "memory");
+                        if (seen < parts) {
+                            if ((spin & 255u) == 255u && *abort_flag) break;
+                            __nanosleep(32);
+                        }
                     }
+                    *last_flag = seen >= parts;
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (*last_flag) {
-                    // ---- the block that came last adds the parts in k order and finishes the tile ----
+                if (!*last_flag) { ok = false; break; }
+                if (has_share) {
 #pragma unroll 1
-                    for (int c0 = 0; c0 < ntok; c0 += 16) {
+                    for (int c0 = p_me * 16; c0 < ntok; c0 += np * 16) {
                         float acc[16];
 #pragma unroll
                         for (int j = 0; j < 16; ++j) acc[j] = 0.f;
@@ -305,13 +289,20 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __nv_bfloat1
                         finalize16(acc, c0);
                     }
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory");       // last_flag is read before the next segment sets it
+                // of those that take part, the one that is done last puts the tile's two counters back to zero for the next
+                // product (all have read the first counter by then, and the early holder never reads it)
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (takes_part && warp == 2 && lane == 0) {
+                    if (atomicAdd(&counters[MAX_TILES + tile], 1) == np - 1) {
+                        counters[tile] = 0;
+                        counters[MAX_TILES + tile] = 0;
+                        __threadfence();
+                    }
+                }
             }
             g = seg_end;
             ++segment;
-            if (warp == 2 && lane == 0) stamp(5);
         }
-        if (warp == 2 && lane == 0) stamp(6);
         if (!ok && lane == 0) { *abort_flag = 1; atomicExch(error_word, 13); }
     }
     tcgen05_fence_before();
@@ -324,23 +315,17 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __nv_bfloat1
 
 }  // namespace
 
-#ifdef JLLM_STREAM_TIMING
-JLLM_EXPORT int jllm_gemm_stream_stamps(unsigned long long* out) {
-    return cudaMemcpyFromSymbol(out, g_stamp, sizeof(g_stamp)) == cudaSuccess ? 0 : 2;
-}
-#endif
-
 // The error word is gemm_tcgen05's (one word for the tcgen05 products).
 int* jllm_gemm_error_word();
 
-JLLM_EXPORT long long jllm_gemm_stream_workspace_floats() { return MAX_TILES + 2LL * 160 * MAX_TOKENS * WM; }
+JLLM_EXPORT long long jllm_gemm_stream_workspace_floats() { return 2LL * MAX_TILES + 2LL * 160 * MAX_TOKENS * WM; }
 
 // a [M, K] bfloat16 (row stride lda), w_packed: ops.pack_weight of the [N, K] weight (k padded to k_blocks * 64, rows
 // to a multiple of 128, zeros), out [M, N] (or [M, N / 2] with swiglu) float32 or bfloat16. `workspace`: zeroed floats
 // (counters, then parked parts), at least jllm_gemm_stream_workspace_floats().
 JLLM_EXPORT int jllm_gemm_stream(const void* a, int lda, const void* w_packed, int k_blocks, const void* bias,
                                  int bias_dtype, void* out, int out_dtype, int ldo, int accumulate, int M, int N, int K,
-                                 int swiglu, float* workspace, long long workspace_floats, int max_blocks, int ordered,
+                                 int swiglu, float* workspace, long long workspace_floats, int max_blocks,
                                  cudaStream_t stream) {
     JLLM_REQUIRE(M >= 1 && M <= MAX_TOKENS && N >= 1 && K >= 8 && K % 8 == 0 && lda % 8 == 0 && ((uintptr_t)a % 16) == 0 &&
                      ((uintptr_t)w_packed % 16) == 0,
@@ -375,7 +360,7 @@ JLLM_EXPORT int jllm_gemm_stream(const void* a, int lda, const void* w_packed, i
     if (grid > 160) grid = 160;
     if (max_blocks > 0 && grid > max_blocks) grid = max_blocks;
     int* counters = reinterpret_cast<int*>(workspace);
-    float* partials = workspace + MAX_TILES;
+    float* partials = workspace + 2 * MAX_TILES;      // two counters per tile (counted in, done), then the parked parts
     const VecRef b{bias, bias_dtype};
 #define JLLM_STREAM_GO(T)                                                                                           \
     do {                                                                                                            \
@@ -383,7 +368,7 @@ JLLM_EXPORT int jllm_gemm_stream(const void* a, int lda, const void* w_packed, i
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                         \
         jllm_launch(kern, dim3(grid), dim3(THREADS), smem, stream, LAUNCH_DEPENDENT, map_a,                          \
                     (const __nv_bfloat16*)w_packed, b, (int)(bias != nullptr), (T*)out, ldo, accumulate, M, N, k_blocks, \
-                    swiglu, ntok, stages, tmem_cols, ordered, partials, counters, error_word);                      \
+                    swiglu, ntok, stages, tmem_cols, partials, counters, error_word);                               \
     } while (0)
     if (out_dtype == JLLM_F32) JLLM_STREAM_GO(float); else JLLM_STREAM_GO(__nv_bfloat16);
 #undef JLLM_STREAM_GO

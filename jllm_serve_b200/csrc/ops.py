@@ -135,7 +135,7 @@ class _Signatures:
     jllm_gemm_plain = [P, I, I, P, I, P, I, P, I, I, I, I, I, I, P]
     jllm_gemm_small_m = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, P]
     jllm_gemm_tcgen05 = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, I, P, ctypes.c_longlong, I, I, P]
-    jllm_gemm_stream = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, P, ctypes.c_longlong, I, I, P]
+    jllm_gemm_stream = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, P, ctypes.c_longlong, I, P]
     jllm_gemm_tcgen05_error = []
     jllm_gemm_tcgen05_starve_next = []
     jllm_attention_plain = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P]
@@ -239,8 +239,9 @@ def gemm_bf16_fits(a, w, out) -> bool:
 #   "rows"   gemm_small_m: weight rows as the M side of mma.sync, tokens register-blocked; the fastest up to 16 rows
 #            and for small matrices up to 64 rows;
 #   "swap"   gemm_stream: tcgen05 with the weight rows as the M side, one 16 KB bulk copy per tile, the k blocks dealt
-#            out evenly over the SMs; from 17 to 128 rows for matrices of 40 MB or more whose rows do not fill the SMs
-#            with whole tiles (QKV, down), where the row kernel's time grows with the rows;
+#            out evenly over the SMs; from 17 to 128 rows for matrices of 40 MB or more (QKV, down), from 41 rows for
+#            smaller ones (O), where the row kernel's time grows with the rows; not for very wide matrices (gate_up),
+#            which whole tiles of the tiles kernel fill the SMs with;
 #   "tiles"  gemm_tcgen05: tokens as the M side, 128 x BN tiles; above that, and from 16 rows for very wide matrices.
 TILE_ROWS = 128          # rows of a tcgen05 product tile (BM in gemm_tcgen05.cu): a step of 129 rows pays for 256
 SMALL_M_ROWS = int(os.environ.get("JLLM_B200_SMALL_M_ROWS", "64"))
@@ -249,13 +250,16 @@ SWAP_MIN_BYTES = int(os.environ.get("JLLM_B200_SWAP_MIN_BYTES", str(40_000_000))
 _workspaces = {}
 # counters of up to 65,536 tiles, then two parked 128 x 256 partial tiles for each of up to 160 blocks
 STREAM_WORKSPACE_FLOATS = 65536 + 160 * 2 * 128 * 256
+SWAP_WORKSPACE_FLOATS = 2 * 65536 + 160 * 2 * 128 * 128       # gemm_stream: two counters per tile, then the parts
 
 
-def gemm_workspace(device, floats: int = 8 << 20) -> torch.Tensor:
-    """Zero-initialised workspace of a streamed product (tile counters, then parked partial tiles), one per device,
-    grown when a product needs more; earlier ones stay alive because captured graphs may point at them."""
-    held = _workspaces.setdefault(device, [])
+def gemm_workspace(key, floats: int = 8 << 20) -> torch.Tensor:
+    """Zero-initialised workspace of a streamed product (tile counters, then parked partial tiles), one per `key` (a
+    device, or (device, kernel) for a kernel that keeps its own), grown when a product needs more; earlier ones stay
+    alive because captured graphs may point at them."""
+    held = _workspaces.setdefault(key, [])
     if not held or held[-1].numel() < floats:
+        device = key[0] if isinstance(key, tuple) else key
         held.append(torch.zeros(max(floats, 8 << 20), dtype=torch.float32, device=device))
     return held[-1]
 
@@ -267,8 +271,7 @@ def gemm_kernel_for(rows: int, out_features: int, in_features: int = 4096, rows_
     # 16 or more rows against a wide matrix (gate_up): 128 or more 192-wide tcgen05 tiles stream it faster than the
     # weight-row kernel, whose blocks have half their loads in flight once they hold more than two token tiles
     wide = rows >= 16 and out_features >= WIDE_ROWS and tiles_fit
-    if tiles_fit and not wide and 16 < rows <= 128 and out_features * in_features * 2 >= SWAP_MIN_BYTES \
-            and (rows <= 96 or in_features >= 8192):
+    if tiles_fit and not wide and 16 < rows <= 128 and (out_features * in_features * 2 >= SWAP_MIN_BYTES or rows > 40):
         return "swap"
     if rows <= min(SMALL_M_ROWS, 64) and rows_fit and not wide:
         return "rows"
@@ -284,7 +287,7 @@ def gemm_bf16(a, w, out, bias=None, accumulate=False, swiglu=False) -> None:
     if kernel == "rows":
         return gemm_small_m(a, w, out, bias, accumulate, swiglu=swiglu)
     if kernel == "swap":
-        return gemm_stream(a, w, out, bias, accumulate, swiglu=swiglu, ordered=True)
+        return gemm_stream(a, w, out, bias, accumulate, swiglu=swiglu)
     if kernel == "tiles":
         return gemm_tcgen05(a, w, out, bias, accumulate, swiglu=swiglu)
     raise KernelError("the tensor-core matrix product is not built for this shape")
@@ -361,20 +364,17 @@ def gemm_stream_fits(a, packed: PackedWeight) -> bool:
             and a.data_ptr() % 16 == 0)
 
 
-def gemm_stream(a, packed: PackedWeight, out, bias=None, accumulate=False, swiglu=False, max_blocks: int = 0,
-                ordered: bool = False) -> None:
+def gemm_stream(a, packed: PackedWeight, out, bias=None, accumulate=False, swiglu=False, max_blocks: int = 0) -> None:
     """out (+)= a @ W^T (+ bias) for at most 128 rows: the packed weight streamed once through tcgen05.mma with the
     weight rows as the M side (see gemm_stream.cu). With `swiglu` the rows of W are blocks of 8 gate rows followed by
     their 8 up rows and out[m, j] = silu(gate_j) * up_j. A tile's parts (its k blocks may fall to several blocks) are
-    added in k order, except where the product is added into float32 memory: there each part is added as it comes,
-    unless `ordered`."""
+    added in k order: two runs give the same bits."""
     packed = _packed(packed)
     assert a.dtype == torch.bfloat16 and out.stride(-1) == 1 and a.shape[1] == packed.cols
-    ws = gemm_workspace(a.device, STREAM_WORKSPACE_FLOATS)
+    ws = gemm_workspace((a.device, "stream"), SWAP_WORKSPACE_FLOATS)     # its own: it keeps counters of its own there
     _call("jllm_gemm_stream", a.data_ptr(), a.stride(0), packed.data.data_ptr(), packed.k_blocks, _p(bias),
           _DT[bias.dtype] if bias is not None else F32, out.data_ptr(), _DT[out.dtype], out.stride(0), int(accumulate),
-          a.shape[0], packed.rows, packed.cols, int(swiglu), ws.data_ptr(), ws.numel(), int(max_blocks), int(ordered),
-          _stream())
+          a.shape[0], packed.rows, packed.cols, int(swiglu), ws.data_ptr(), ws.numel(), int(max_blocks), _stream())
 
 
 BOUNDS_FILES = ("attention_plain", "attention_decode", "attention_prefill", "attention_prefill_tc",

@@ -11,9 +11,10 @@ def test_product_kernel_by_rows_and_shape():
     assert k(16, 24576, 4096) == "tiles"                   # 16 rows against gate_up: tcgen05 tiles
     assert k(16, 6144, 4096) == "rows"
     assert k(17, 6144, 4096) == "swap"                     # QKV (50 MB) from 17 rows: weight rows as the MMA's M side
-    assert k(64, 6144, 4096) == "swap" and k(96, 6144, 4096) == "swap" and k(128, 6144, 4096) == "tiles"
+    assert k(64, 6144, 4096) == "swap" and k(128, 6144, 4096) == "swap" and k(129, 6144, 4096) == "tiles"
     assert k(64, 4096, 12288) == "swap" and k(128, 4096, 12288) == "swap" and k(129, 4096, 12288) == "tiles"
-    assert k(64, 4096, 4096) == "rows" and k(65, 4096, 4096) == "tiles"        # O (34 MB): too small for it
+    assert k(40, 4096, 4096) == "rows" and k(41, 4096, 4096) == "swap"         # O (34 MB): from 41 rows
+    assert k(64, 24576, 4096) == "tiles"                                       # gate_up: whole tiles fill the SMs
     assert k(2048, 4096, 4096) == "tiles"
     assert k(16, 24576, 4096, tiles_fit=False) == "rows"
     assert k(8, 4096, 4096, rows_fit=False) == "tiles"
