@@ -105,10 +105,9 @@ __device__ __forceinline__ long long jllm_page_of(const int* __restrict__ table,
 // are resident on it. A kernel whose blocks arrive while a predecessor with a large shared-memory allocation (the
 // staged decode attention, the tcgen05 kernels) still holds the SM runs with that predecessor's split, that is
 // with little L1, and so does every kernel that overlaps it in turn, until one launch waits for the SMs to drain.
-// The decode products re-read their activations through L1 (every block reads all of them): behind a tcgen05
-// product a 16 x 4096 x 12288 product took 47 us as a dependent launch and 22 us launched plainly, and a decode
-// step at batch 16 6.8 ms instead of 5.6. A launch that says it wants L1 (LAUNCH_DEPENDENT_WANTS_L1) is
-// therefore made plainly when a large-shared-memory kernel has been launched since the last plain launch.
+// The row kernel of the decode products re-reads its activations through L1 (every block reads all of them) and
+// runs at half its speed that way. A launch that says it wants L1 (LAUNCH_DEPENDENT_WANTS_L1) is therefore made
+// plainly when a large-shared-memory kernel has been launched since the last plain launch.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

@@ -490,8 +490,8 @@ def decode_plan(rows, kv_heads, kv_bucket, heads, head_dim, scratch, places: int
     when there are more (row, kv head) pairs than places for blocks (`places`, by default two per SM of the device)
     and they would fill the last round of places
     badly (by less than 93 %), the key tiles of all pairs dealt out evenly over as many blocks as there are places
-    (measured at context 4,096: 188 against 195 us at batch 64; with fewer pairs than places the even deal was the
-    slower one, 34.5 against 32.4 us at batch 8). `kv_bucket` = the longest request's keys in units of 256."""
+    (with fewer pairs than places the even deal is the slower one). `kv_bucket` = the longest request's keys in
+    units of 256."""
     places = places or resident_blocks()
     splits = decode_splits(rows, kv_heads, kv_bucket, heads, head_dim, scratch, places)
     uniform = rows * kv_heads * splits

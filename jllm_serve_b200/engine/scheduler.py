@@ -1,7 +1,9 @@
 """The scheduler: admits requests, forms each step's batch under a token budget, finishes and frees.
 
-The pass-forming rule is the reference's (docs/25-scheduler.md;
-src/main/java/org/robomiri/jllm/engine/PassPlanner.java:74-112): every decoding request
+`plan_pass` is a port of the reference's pass-forming rule, function for function (docs/25-scheduler.md;
+src/main/java/org/robomiri/jllm/engine/PassPlanner.java:74-112, without its classes, aging and background cap, and
+with the row quantum added): the rule is the contract, and the reference's own test vectors are this module's
+tests. Every decoding request
 rides along with its one token, in order of arrival, while it fits the budget; then ONE
 prompt portion, the head of the prefill line, takes what is left, trimmed to the room, but
 only if that is at least `min_chunk` rows (or all the portion needs); if nothing fits, the
@@ -91,8 +93,7 @@ def plan_pass(pending: Sequence[Item], budget: int, min_chunk: int, row_quantum:
     `pending` chunks in the order given, trimmed to the room left, and waits if the room is smaller
     than min(min_chunk, its rows). With `row_quantum` (the rows of a matrix-product tile) a chunk that is cut
     anyway, because its prompt goes on after it, is cut so that the pass has a whole number of tiles: the rows
-    beyond the last full tile would cost a tile of their own (measured, 8B shape, 32 riders: 544 rows 15.7 ms,
-    512 rows 14.4 ms)."""
+    beyond the last full tile would cost a tile of their own."""
     if budget < 1:
         raise ValueError("a pass needs a budget of at least one row")
     riders = sorted((i for i in pending if i.kind != "chunk"), key=lambda i: i.enqueued)
