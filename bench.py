@@ -6,8 +6,9 @@ A step is one decode step of a batch of 8 requests whose contexts end at 4,096 t
 decoded tokens per second timed on the device with CUDA events around exactly K steps (each step:
 the batch tables copied to the device, the captured decode graph replayed, argmax on the device);
 `e2e` is the same through the public entry point (`Engine.add_request` / `Engine.step_once`): host
-token lists in, sampled tokens read back on the host every step, prompts prefilled by the engine
-itself. `prefill` times one 2,048-token prompt; `roofline` compares the bytes a decode step has to
+token lists in, sampled tokens read back on the host every step (the engine plans and launches a step
+while the one before runs, so the tokens it reads are those of the step before), prompts prefilled by
+the engine itself. `prefill` times one 2,048-token prompt; `roofline` compares the bytes a decode step has to
 read (every weight once plus the cache of the live requests) with the measured copy bandwidth;
 `points` holds decode at batch 1 and 64; `check` compares the bfloat16 logits with the 32-bit path's at these
 layer sizes (two layers, untimed). Peaks come from MEASURED_PEAKS.json when it exists.
@@ -298,7 +299,7 @@ def main() -> int:
         e2e = end_to_end(engine, args.batch, args.steps, args.warmup, cfg["vocab_size"])
         if not args.skip_points:
             for b in (1, 64):
-                other = end_to_end(engine, b, max(8, args.steps // 2), 3, cfg["vocab_size"])
+                other = end_to_end(engine, b, args.steps, args.warmup, cfg["vocab_size"])
                 points[f"e2e_b{b}"] = other["value"]
 
     record = {

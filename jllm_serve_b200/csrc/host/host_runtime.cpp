@@ -467,8 +467,11 @@ JH_EXPORT int jh_builder_build(void* bv, void* cv, int segments, const long long
         Request* rq = c->find(id);
         if (!rq) return fail(JH_KEY, "request #%lld is not open", id);
         for (int i = 0; i < n; ++i) {
+            // a token id t < 0 says: row -t - 1 of the tokens that the step before this one sampled, which are still on
+            // the device (`jllm_feed_tokens` puts it in place before the step runs); only a decoded token can be that
             const int t = tokens[t_at + i];
-            if (t < 0 || t >= vocab) return fail(JH_VALUE, "request #%lld: token id outside [0, %d)", id, vocab);
+            if (t >= vocab || t < -S || (t < 0 && n != 1))
+                return fail(JH_VALUE, "request #%lld: token id outside [0, %d)", id, vocab);
             tok[r + i] = t;
             pos[r + i] = start + i;
             rseg[r + i] = si;

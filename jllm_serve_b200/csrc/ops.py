@@ -129,6 +129,7 @@ class _Signatures:
     jllm_set_pdl = [I]
     jllm_launch_plan = [ctypes.c_longlong, I]
     jllm_embed_rows = [P, P, I, P, I, I, I, P]
+    jllm_feed_tokens = [P, P, I, I, P]
     jllm_rmsnorm = [P, P, I, P, I, P, I, I, F, P]
     jllm_swiglu = [P, P, I, I, I, P]
     jllm_qk_norm_rope_store = [P, I, P, P, I, I, F, P, P, I, P, P, P, P, I, I, I, I, I, I, I, P]
@@ -156,6 +157,13 @@ def embed_rows(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> Non
     assert ids.dtype == torch.int32 and out.dtype == torch.float32 and table.dim() == 2
     _call("jllm_embed_rows", ids.data_ptr(), table.data_ptr(), _DT[table.dtype], out.data_ptr(), ids.numel(),
           table.shape[1], table.shape[0], _stream())
+
+
+def feed_tokens(ids: torch.Tensor, sampled: torch.Tensor) -> None:
+    """ids[r] < 0 becomes sampled[-ids[r] - 1]: tokens that the step before sampled go into this step's rows on the
+    device, before the host has read them."""
+    assert ids.dtype == torch.int32 and sampled.dtype == torch.int32
+    _call("jllm_feed_tokens", ids.data_ptr(), sampled.data_ptr(), ids.numel(), sampled.numel(), _stream())
 
 
 def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor, row_index: torch.Tensor | None = None,

@@ -36,6 +36,27 @@ JLLM_EXPORT int jllm_embed_rows(const int* ids, const void* table, int table_dty
 }
 
 // ---------------------------------------------------------------------------------------------------
+// ids[r] < 0 stands for "row -ids[r] - 1 of the tokens the step before sampled" (still on the device, the host has not
+// read them yet): put them in place. One block; a step has at most some hundreds of rows.
+// ---------------------------------------------------------------------------------------------------
+__global__ void feed_tokens_kernel(int* __restrict__ ids, const int* __restrict__ sampled, int rows, int sampled_rows) {
+    for (int r = threadIdx.x; r < rows; r += blockDim.x) {
+        const int t = ids[r];
+        if (t < 0) {
+            const int j = -t - 1;
+            ids[r] = j < sampled_rows ? sampled[j] : 0;
+        }
+    }
+}
+
+JLLM_EXPORT int jllm_feed_tokens(int* ids, const int* sampled, int rows, int sampled_rows, cudaStream_t stream) {
+    JLLM_REQUIRE(rows >= 0 && sampled_rows >= 0, "feed_tokens: rows=%d sampled=%d", rows, sampled_rows);
+    if (rows == 0) return JLLM_OK;
+    feed_tokens_kernel<<<1, 256, 0, stream>>>(ids, sampled, rows, sampled_rows);
+    return jllm_check_launch("feed_tokens");
+}
+
+// ---------------------------------------------------------------------------------------------------
 // RMSNorm: out[r] = (x[src(r)] * (1 / sqrt(mean(x^2) + eps))) * gain, src(r) = row_index ? row_index[r] : r
 // The scale is taken in double from a float mean, as the reference does.
 // ---------------------------------------------------------------------------------------------------

@@ -55,10 +55,13 @@ class Engine:
                  dtype="bfloat16", device="cuda:0", ctx: Optional[int] = None, page_size: int = 16,
                  num_pages=None, max_tokens_cached: Optional[int] = None,
                  max_batch_tokens: int = 2048, chunk: int = 512, min_chunk: int = 16, max_running: int = 64,
-                 sample_vocab: Optional[int] = None, cuda_graphs: bool = True, kv_share: float = 0.6):
+                 sample_vocab: Optional[int] = None, cuda_graphs: bool = True, kv_share: float = 0.6,
+                 overlap: bool = True):
         """`num_pages`: pages of the cache pool, or "auto" for the share `kv_share` of the device memory that is
         free once the weights are loaded; without it the pool holds `max_tokens_cached` tokens (default: four
-        full contexts)."""
+        full contexts). `overlap`: a step is planned and launched while the step before it still runs, its sampled
+        tokens going from one step into the next on the device; the host reads them one step later (what `step_once`
+        returns lags by a step; `run_until_done` and `generate` do not care)."""
         self.runner = ModelRunner(model_dir, config=config, seed=seed, dtype=dtype, device=device,
                                   page_size=page_size, num_pages=num_pages, max_tokens=max_tokens_cached,
                                   max_batch_tokens=max_batch_tokens, max_requests=max_running, ctx=ctx,
@@ -71,6 +74,8 @@ class Engine:
         self._rngs = {}
         self._times = {}
         self._ids = 0
+        self.overlap = bool(overlap)
+        self._inflight = None              # (the planned segments, the ticket of their sampling) of a launched step
 
     # ---- requests ------------------------------------------------------------------------------------------
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
@@ -88,36 +93,62 @@ class Engine:
         return rid
 
     def step_once(self) -> List[Request]:
-        """One scheduler step: plan, run, sample, complete. Returns the requests that finished, those included
-        that the scheduler ended while planning because the pool can never hold them (`kv_exhausted`)."""
-        plan = self.scheduler.plan()
+        """One scheduler step: plan, launch, and read the tokens of the step before (without `overlap`: of this
+        step). Returns the requests that finished, those included that the scheduler ended while planning because
+        the pool can never hold them (`kv_exhausted`)."""
+        finished: List[Request] = []
+        plan = None
+        if self._inflight is not None:
+            plan = self.scheduler.plan(inflight=self._inflight[0])
+            if plan is None:               # the pool is short: no planning ahead of the tokens that are on their way
+                finished += self._read_inflight()
+        if plan is None:
+            plan = self.scheduler.plan()
         ended = self.scheduler.take_ended()
         now = time.perf_counter()
         for r in ended:
             self._times[r.id]["end"] = now
             self._rngs.pop(r.id, None)
-        if not plan:
-            return ended
+        finished += ended
+        launched = self._launch(plan) if plan else None
+        finished += self._read_inflight()          # the step before this one (it ran while this one was prepared)
+        self._inflight = launched
+        if launched is not None and not self.overlap:
+            finished += self._read_inflight()
+        return finished
+
+    def _launch(self, plan):
+        """Hands the planned segments to the step function and starts the choice of their tokens; waits for nothing."""
         segments = [Segment(p.request.id, p.tokens, p.start, [len(p.tokens) - 1] if p.wants_logits else [])
                     for p in plan]
-        logits = self.runner.step(segments)
+        fed = any(len(p.tokens) == 1 and p.tokens[0] < 0 for p in plan)
+        logits = self.runner.step(segments, fed_from=self._inflight[1].device_tokens if fed else None)
         wanting = [p.request for p in plan if p.wants_logits]
-        sampled = self.sampler.sample(logits, [r.params for r in wanting],
-                                      [0.0 if r.params.greedy else self._rngs[r.id].next() for r in wanting])
+        ticket = self.sampler.launch(logits, [r.params for r in wanting],
+                                     [0.0 if r.params.greedy else self._rngs[r.id].next() for r in wanting])
+        return plan, ticket
+
+    def _read_inflight(self) -> List[Request]:
+        """Waits for the tokens of the step in flight, hands them to the scheduler; the requests they finished."""
+        if self._inflight is None:
+            return []
+        plan, ticket = self._inflight
+        self._inflight = None
+        sampled = self.sampler.fetch(ticket)
         now = time.perf_counter()
-        for r in wanting:
-            if self._times[r.id]["first"] is None:
-                self._times[r.id]["first"] = now
+        for p in plan:
+            if p.wants_logits and self._times[p.request.id]["first"] is None:
+                self._times[p.request.id]["first"] = now
         done = self.scheduler.complete(plan, sampled)
         for r in done:
             self._times[r.id]["end"] = now
             self._rngs.pop(r.id, None)
-        return ended + done
+        return done
 
     def run_until_done(self) -> List[Request]:
         finished = []
         steps = 0
-        while self.scheduler.has_work():
+        while self.scheduler.has_work() or self._inflight is not None:
             finished.extend(self.step_once())
             steps += 1
             if steps % 256 == 0:

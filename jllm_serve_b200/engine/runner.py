@@ -114,13 +114,18 @@ class ModelRunner:
         return torch.zeros(shape, dtype=getattr(torch, kind), device=self.device)
 
     # ---- the step -----------------------------------------------------------------------------------------
-    def step(self, segments: Sequence[Segment], logits_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def step(self, segments: Sequence[Segment], logits_out: Optional[torch.Tensor] = None,
+             fed_from: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Runs the segments as one batch; returns float32 logits [wanted places, vocab] on the device, in
-        the order of the segments and of each segment's `want`."""
+        the order of the segments and of each segment's `want`. A single-token segment may give the token -(j + 1)
+        instead of an id: row j of `fed_from`, an int32 tensor of tokens on the device that the step before sampled
+        and the host has not read yet."""
         segments = list(segments)
         if sum(len(s.tokens) for s in segments) > self.max_rows:
+            if fed_from is not None:
+                raise ValueError("a step that is split over several batches takes its tokens from the host")
             return self._step_in_parts(segments, logits_out)
-        return self._step_once(segments, logits_out)
+        return self._step_once(segments, logits_out, fed_from=fed_from)
 
     def _step_in_parts(self, segments, logits_out):
         """More rows than one batch holds: the same tokens as several batches, one after the other. The
@@ -195,7 +200,7 @@ class ModelRunner:
             elif self.cache.is_open(seg.request):
                 self.cache.trim(seg.request)
 
-    def _step_once(self, segments, logits_out, reserve: bool = True):
+    def _step_once(self, segments, logits_out, reserve: bool = True, fed_from=None):
         opened = self._open(segments)
         try:
             batch = self.builder.build(segments, self.cache, self.vocab, reserve=reserve)   # all pages or none
@@ -206,6 +211,8 @@ class ModelRunner:
         if self._checked:
             ops.set_pool_pages(self.cache.num_pages)     # the library with bounds checks compares page ids with it
         try:
+            if fed_from is not None:
+                ops.feed_tokens(batch.token_ids, fed_from)
             logits = self._run_model(batch, logits_out)
         except Exception:
             # the step did not run to its end: its pages go back and the books say what they said before it, so

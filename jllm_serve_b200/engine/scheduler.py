@@ -22,6 +22,14 @@ and recomputes what could not be kept: engine/Admission.java:288-301, engine/Eng
 657-666). The oldest request is never preempted, so it always finishes; a request that
 cannot fit in the empty pool ends with the reason "kv_exhausted".
 
+One step ahead. `plan` may be called while the step before is still running on the device and its
+sampled tokens have not been read (`plan(inflight=that step's segments)`): a request whose next token is
+among them is planned with a marker in place of the token (the runner takes the token from the device),
+on the guess that the token is no stop token; a request that those tokens complete by length is left out.
+`complete` of the earlier step comes afterwards; if it ends a request by a stop token, the rows that were
+planned for it on the guess are wasted and their token ignored. Planning ahead never preempts: if the pool
+is short it returns None and the caller completes the step in flight first.
+
 The scheduler is host logic only: it asks the cache manager for pages and tells the caller
 which segments to run; it never touches a tensor.
 """
@@ -44,7 +52,9 @@ class Request:
     params: SamplingParams
     output: List[int] = field(default_factory=list)
     state: str = WAITING
-    computed: int = 0                      # tokens whose keys and values are in the cache
+    computed: int = 0                      # tokens whose keys and values are in the cache (steps that were completed)
+    launched: int = 0                      # tokens whose rows were handed to a step; ahead of `computed` by a step in flight
+    unknown: int = 0                       # tokens that steps in flight will sample: part of the sequence, not yet read
     finish_reason: Optional[str] = None
     arrival: int = 0
     admitted: int = -1                     # order of (re)admission, for choosing whom to preempt
@@ -66,7 +76,18 @@ class Request:
 
     @property
     def remaining(self) -> int:
-        return len(self.prompt) + len(self.output) - self.computed
+        """Tokens of the sequence (those still to be read from a step in flight included) not yet handed to a step."""
+        return len(self.prompt) + len(self.output) + self.unknown - self.launched
+
+    @property
+    def ends_by_length(self) -> bool:
+        """The tokens it has, with those on their way, are all it may have: it is not scheduled again."""
+        n_out = len(self.output) + self.unknown
+        return n_out >= self.max_new
+
+    def feed_marker(self, index: int) -> int:
+        """What stands for a token that is still on the device: row `index` of the step before's samples."""
+        return -(index + 1)
 
 
 @dataclass(frozen=True)
@@ -186,19 +207,26 @@ class Scheduler:
                 self.prefill_line.append(r)
 
     def _fits_now(self, r: Request, rows: int) -> bool:
-        rows = min(rows, self.ctx - r.computed)
+        rows = min(rows, self.ctx - r.launched)
         if self.cache.is_open(r.id):
-            return self.cache.can_reserve(r.id, r.computed, rows)
-        missing = -(-(r.computed + rows) // self.cache.page_size)
+            return self.cache.can_reserve(r.id, r.launched, rows)
+        missing = -(-(r.launched + rows) // self.cache.page_size)
         return all(missing <= free for free in self.cache.free_pages())
 
-    def plan(self) -> List[PlannedSegment]:
-        """Admits, picks the step's segments and reserves their pages (preempting if the pool is short)."""
+    def plan(self, inflight: Optional[Sequence["PlannedSegment"]] = None) -> Optional[List[PlannedSegment]]:
+        """Admits, picks the step's segments and reserves their pages (preempting if the pool is short). With
+        `inflight` (the segments of a step whose tokens have not been read yet) it plans one step ahead and never
+        preempts: None means that the step in flight has to be completed first."""
+        ahead = inflight is not None
+        fed = {}
+        if ahead:
+            wanting = [seg.request for seg in inflight if seg.wants_logits]
+            fed = {r.id: j for j, r in enumerate(wanting)}
         self._admit()
         while True:
             items = []
             for r in sorted(self.running, key=lambda q: q.arrival):
-                if r.remaining == 1:
+                if r.remaining == 1 and r not in self.prefill_line and not self._full(r):
                     items.append(Item(r, "rider", 1, r.arrival))
             for r in self.prefill_line:
                 items.append(Item(r, "chunk", min(r.remaining, self.chunk), r.arrival, r.remaining > self.chunk + 1))
@@ -206,9 +234,11 @@ class Scheduler:
                 return []
             picks = plan_pass(items, self.budget, self.min_chunk, self.row_quantum)
             try:      # pages for every pick, or for none
-                self.cache.reserve_all([p.ref.id for p in picks], [p.ref.computed for p in picks],
+                self.cache.reserve_all([p.ref.id for p in picks], [p.ref.launched for p in picks],
                                        [p.rows for p in picks])
             except PoolExhausted:
+                if ahead:
+                    return None
                 if not self._preempt_one():
                     # a single running request that cannot grow: it ends here
                     r = self.running[0]
@@ -221,13 +251,26 @@ class Scheduler:
             segments = []
             for p in picks:
                 r = p.ref
-                toks = r.tokens_between(r.computed, r.computed + p.rows)
-                segments.append(PlannedSegment(r, r.computed, toks, r.computed + p.rows == len(r.prompt) + len(r.output)))
+                known = len(r.prompt) + len(r.output)
+                if r.launched + p.rows > known:
+                    # its next token is among those the step in flight samples: the runner takes it from the device
+                    toks = [r.feed_marker(fed[r.id])]
+                else:
+                    toks = r.tokens_between(r.launched, r.launched + p.rows)
+                wants = r.launched + p.rows == known + r.unknown
+                segments.append(PlannedSegment(r, r.launched, toks, wants))
                 if p.kind == "chunk":
                     self.prefill_line.remove(r)
                     if r.remaining - p.rows > 1:
                         self.prefill_line.append(r)   # to the back: prompts alternate
+            for seg in segments:
+                seg.request.launched += len(seg.tokens)
+                seg.request.unknown += 1 if seg.wants_logits else 0
             return segments
+
+    def _full(self, r: Request) -> bool:
+        """With the tokens it has and those on their way the request has all it may have."""
+        return r.ends_by_length or len(r.prompt) + len(r.output) + r.unknown >= self.ctx
 
     def _preempt_one(self) -> bool:
         """The most recently admitted running request gives everything back and waits again, in front."""
@@ -235,7 +278,7 @@ class Scheduler:
             return False
         victim = max(self.running, key=lambda q: q.admitted)
         self._release(victim)
-        victim.state, victim.computed = WAITING, 0
+        victim.state, victim.computed, victim.launched = WAITING, 0, 0
         victim.preemptions += 1
         self.preemptions += 1
         self.waiting.insert(0, victim)
@@ -259,17 +302,22 @@ class Scheduler:
 
     def complete(self, segments: Sequence[PlannedSegment], sampled: Sequence[int]) -> List[Request]:
         """After the step ran: lengths are committed, the sampled tokens (one per segment that wanted
-        logits, in order) are appended, and requests that are done are finished and freed."""
+        logits, in order) are appended, and requests that are done are finished and freed. Rows of a request that an
+        earlier step's token has ended meanwhile (they were planned ahead, on the guess that it goes on) are passed
+        over."""
         done = []
         it = iter(sampled)
         for seg in segments:
             r = seg.request
+            tok = next(it) if seg.wants_logits else None
+            if r.state == FINISHED:
+                continue
             r.computed = seg.start + len(seg.tokens)
             if self.commits:
                 self.cache.commit(r.id, r.computed)
             if not seg.wants_logits:
                 continue
-            tok = next(it)
+            r.unknown -= 1
             if not r.params.ignore_eos and (tok in self.eos or tok in r.params.stop_token_ids):
                 reason = "stop"            # the stop token is not part of the output
             else:

@@ -29,40 +29,68 @@ class RequestRng:
         return self._rng.random()
 
 
+class Ticket:
+    """A launched sampling whose tokens the host has not read yet."""
+
+    def __init__(self, slot: int, rows: int, device_tokens: torch.Tensor, done):
+        self.slot, self.rows, self.device_tokens, self.done = slot, rows, device_tokens, done
+
+
 class Sampler:
+    """`launch` starts the choice of a step's tokens on the device and their copy to pinned host memory and returns at
+    once; `fetch` waits for that copy and gives the tokens. Two sets of buffers take turns, so the tokens of one step
+    can be on their way (and be fed into the next step on the device, `Ticket.device_tokens`) while the next step's
+    sampling is launched. `sample` is the two in one."""
+
     def __init__(self, device, max_rows: int, vocab: int, sample_vocab: int | None = None):
         self.device, self.max_rows, self.vocab = device, max_rows, vocab
         self.sample_vocab = min(vocab, sample_vocab or vocab)  # ids at or above it are never drawn (padding rows)
         pin = torch.cuda.is_available()
-        self._host_f = torch.empty((3, max_rows), dtype=torch.float32, pin_memory=pin)   # temperature, top_p, min_p
-        self._host_k = torch.empty(max_rows, dtype=torch.int32, pin_memory=pin)
-        self._host_u = torch.empty(max_rows, dtype=torch.float64, pin_memory=pin)
-        self._f = torch.empty((3, max_rows), dtype=torch.float32, device=device)
-        self._k = torch.empty(max_rows, dtype=torch.int32, device=device)
-        self._u = torch.empty(max_rows, dtype=torch.float64, device=device)
-        self._out = torch.empty(max_rows, dtype=torch.int32, device=device)
-        self._out_host = torch.empty(max_rows, dtype=torch.int32).pin_memory()
-        self._out_host_np = self._out_host.numpy()
+        self._sets = []
+        for _ in range(2):
+            host_out = torch.empty(max_rows, dtype=torch.int32, pin_memory=pin)
+            self._sets.append(dict(
+                host_f=torch.empty((3, max_rows), dtype=torch.float32, pin_memory=pin),   # temperature, top_p, min_p
+                host_k=torch.empty(max_rows, dtype=torch.int32, pin_memory=pin),
+                host_u=torch.empty(max_rows, dtype=torch.float64, pin_memory=pin),
+                f=torch.empty((3, max_rows), dtype=torch.float32, device=device),
+                k=torch.empty(max_rows, dtype=torch.int32, device=device),
+                u=torch.empty(max_rows, dtype=torch.float64, device=device),
+                out=torch.zeros(max_rows, dtype=torch.int32, device=device),
+                host_out=host_out, host_out_np=host_out.numpy(),
+                done=torch.cuda.Event() if pin else None))
+        self._next = 0
+
+    def launch(self, logits: torch.Tensor, params: Sequence[SamplingParams], uniforms: Sequence[float]) -> Ticket:
+        """logits float32 [n, vocab] on the device; nothing is waited for."""
+        n = logits.shape[0]
+        assert n <= self.max_rows and len(params) == n
+        b = self._sets[self._next]
+        slot, self._next = self._next, self._next ^ 1
+        if n > 0:
+            out = b["out"][:n]
+            if all(p.greedy for p in params):
+                ops.argmax(logits, out, self.sample_vocab)
+            else:
+                hf, hk, hu = b["host_f"], b["host_k"], b["host_u"]
+                for i, p in enumerate(params):
+                    hf[0, i], hf[1, i], hf[2, i] = p.temperature, p.top_p, p.min_p
+                    hk[i] = p.top_k
+                    hu[i] = uniforms[i]
+                b["f"].copy_(hf, non_blocking=True)
+                b["k"].copy_(hk, non_blocking=True)
+                b["u"].copy_(hu, non_blocking=True)
+                ops.sample(logits, b["f"][0, :n], b["k"][:n], b["f"][1, :n], b["f"][2, :n], b["u"][:n], out, self.sample_vocab)
+            b["host_out"].copy_(b["out"], non_blocking=True)     # all of the small buffer: no views to make
+            b["done"].record()
+        return Ticket(slot, n, b["out"], b["done"])
+
+    def fetch(self, ticket: Ticket) -> List[int]:
+        if ticket.rows == 0:
+            return []
+        ticket.done.synchronize()
+        return self._sets[ticket.slot]["host_out_np"][:ticket.rows].tolist()
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], uniforms: Sequence[float]) -> List[int]:
         """logits float32 [n, vocab] on the device -> n token ids on the host."""
-        n = logits.shape[0]
-        if n == 0:
-            return []
-        assert n <= self.max_rows and len(params) == n
-        out = self._out[:n]
-        if all(p.greedy for p in params):
-            ops.argmax(logits, out, self.sample_vocab)
-        else:
-            for i, p in enumerate(params):
-                self._host_f[0, i], self._host_f[1, i], self._host_f[2, i] = p.temperature, p.top_p, p.min_p
-                self._host_k[i] = p.top_k
-                self._host_u[i] = uniforms[i]
-            self._f.copy_(self._host_f, non_blocking=True)
-            self._k.copy_(self._host_k, non_blocking=True)
-            self._u.copy_(self._host_u, non_blocking=True)
-            ops.sample(logits, self._f[0, :n], self._k[:n], self._f[1, :n], self._f[2, :n], self._u[:n], out,
-                       self.sample_vocab)
-        self._out_host.copy_(self._out, non_blocking=True)     # all of the small buffer: no views to make
-        torch.cuda.current_stream().synchronize()
-        return self._out_host_np[:n].tolist()
+        return self.fetch(self.launch(logits, params, uniforms))

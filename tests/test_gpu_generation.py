@@ -136,3 +136,35 @@ def test_command_line_run_and_bench(tmp_path):
                            "--bench.rounds", "2"], capture_output=True, text=True, timeout=600)
     assert proc.returncode == 0, proc.stderr[-2000:]
     assert proc.stdout.startswith("prefill 50 tok in") and "decode 8 tok in" in proc.stdout
+
+
+@pytest.mark.parametrize("overlap", [False, True])
+def test_stop_tokens_with_and_without_planning_ahead(tmp_path, overlap):
+    """Planned one step ahead, a request whose token turns out to be a stop token has a row in the step after: the row
+    is wasted, its token ignored, and every request's output is what it is without planning ahead."""
+    from jllm_serve_b200.engine import Engine
+    from jllm_serve_b200.sampling import SamplingParams
+    base = CONFIGS["A"]
+    prompts = [random_tokens(n, base["vocab_size"], 300 + n) for n in (11, 5, 23, 8)]
+    kw = dict(dtype="float32", ctx=96, max_batch_tokens=32, chunk=16, max_running=3, page_size=4, max_tokens_cached=384)
+    free = Engine(make_model_folder(base, 7, tmp_path / "free"), overlap=False, **kw)
+    outs = [r.tokens for r in free.generate(prompts, SamplingParams.greedy_params(20, ignore_eos=True))]
+    stops = sorted({outs[0][6], outs[1][3], outs[2][12]})
+    want = []
+    for o in outs:
+        cut = min([o.index(t) for t in stops if t in o] + [len(o)])
+        want.append((o[:cut], "stop" if cut < len(o) else "length"))
+    eng = Engine(make_model_folder(dict(base, eos_token_id=stops), 7, tmp_path / "stop"), overlap=overlap, **kw)
+    got = eng.generate(prompts, SamplingParams.greedy_params(20))
+    assert [(r.tokens, r.finish_reason) for r in got] == want
+    assert not eng.runner.cache.requests and eng._inflight is None
+    eng.runner.cache.check()
+
+
+def test_seeded_sampling_is_the_same_with_and_without_planning_ahead():
+    from jllm_serve_b200.sampling import SamplingParams
+    prompts = prompts_for("B", (9, 40, 70, 3), seed=41)
+    params = [SamplingParams(temperature=0.9, top_k=30, top_p=0.9, seed=7 + i, max_tokens=20, ignore_eos=True) for i in range(4)]
+    a = engine_for("B", "float32", overlap=False).generate(prompts, params)
+    b = engine_for("B", "float32", overlap=True).generate(prompts, params)
+    assert [r.tokens for r in a] == [r.tokens for r in b]
