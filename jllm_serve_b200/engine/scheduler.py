@@ -151,8 +151,8 @@ class PlannedSegment:
 class Scheduler:
     def __init__(self, cache, ctx: int, max_batch_tokens: int, chunk: int = 512, min_chunk: int = 16,
                  max_running: int = 64, eos_ids: Sequence[int] = (), commits: bool = True, row_quantum: int = 0):
-        """`commits`: whether `complete` records the new lengths in the cache (False when whoever runs the steps
-        does that itself, as the model runner does). `row_quantum`: see `plan_pass`."""
+        """`commits`: whether `plan` records the new lengths in the cache when it hands a step out (False when whoever
+        runs the steps does that itself, as the model runner does at launch). `row_quantum`: see `plan_pass`."""
         self.cache, self.ctx, self.commits, self.row_quantum = cache, ctx, commits, row_quantum
         self.budget, self.chunk, self.min_chunk, self.max_running = max_batch_tokens, chunk, min_chunk, max_running
         self.eos = set(eos_ids)
@@ -266,6 +266,8 @@ class Scheduler:
             for seg in segments:
                 seg.request.launched += len(seg.tokens)
                 seg.request.unknown += 1 if seg.wants_logits else 0
+                if self.commits:       # as the model runner does when it launches a step: the rows count as written
+                    self.cache.commit(seg.request.id, seg.request.launched)
             return segments
 
     def _full(self, r: Request) -> bool:
@@ -313,8 +315,6 @@ class Scheduler:
             if r.state == FINISHED:
                 continue
             r.computed = seg.start + len(seg.tokens)
-            if self.commits:
-                self.cache.commit(r.id, r.computed)
             if not seg.wants_logits:
                 continue
             r.unknown -= 1

@@ -245,3 +245,71 @@ def test_requests_the_planner_ends_itself_are_handed_to_the_caller():
     assert [r.id for r in ended] == ["big"] and ended[0].finish_reason == "kv_exhausted"
     assert s.take_ended() == []                                    # handed over once
     assert [p.request.id for p in plan] == ["small"]               # the next request in line runs in the same step
+
+
+def drive_ahead(scheduler, token_of, ahead: bool, max_steps=500):
+    """Runs the scheduler against a fake model (`token_of(request, position)` is what a step samples for the token
+    that follows `position`), either completing every step before the next is planned or planning one step ahead.
+    Returns {request id: (output, finish reason)} and the steps as lists of (id, start, tokens, wants)."""
+    steps, inflight = [], None
+
+    def result_of(plan):
+        return [token_of(p.request, p.start + len(p.tokens) - 1) for p in plan if p.wants_logits]
+
+    for _ in range(max_steps):
+        if not scheduler.has_work() and inflight is None:
+            break
+        plan = None
+        if inflight is not None and ahead:
+            plan = scheduler.plan(inflight=inflight)
+        if plan is None:
+            if inflight is not None:
+                scheduler.complete(inflight, result_of(inflight))
+                inflight = None
+            plan = scheduler.plan()
+        scheduler.take_ended()
+        if plan:
+            steps.append([(p.request.id, p.start, list(p.tokens), p.wants_logits) for p in plan])
+        if inflight is not None:
+            scheduler.complete(inflight, result_of(inflight))
+        inflight = plan or None
+        if not ahead and inflight is not None:
+            scheduler.complete(inflight, result_of(inflight))
+            inflight = None
+    return {rid: (r.output, r.finish_reason) for rid, r in scheduler.finished.items()}, steps
+
+
+def test_planning_one_step_ahead_gives_the_same_outputs():
+    """With a step planned while the one before is unread: the next token of a decoding request is a marker for "row j
+    of the step before's samples", a request that ends by length is not planned again, one that ends by a stop token
+    has had one row too many (wasted), and all outputs and reasons are those of the step-by-step order; a pool that
+    is short makes the planner wait for the step in flight (None) instead of preempting blindly."""
+    def token_of(r, position):       # a fake model: the token after `position` of request r
+        return (7 * position + 3 * len(r.prompt)) % 50
+
+    def make(pages):
+        cache = CacheManager([PagedKeysValues(1, 8)], page_size=4, num_pages=pages, max_requests=4)
+        s = Scheduler(cache, ctx=64, max_batch_tokens=24, chunk=16, min_chunk=2, max_running=3, eos_ids=[11, 17])
+        for i, (n, new) in enumerate([(5, 12), (30, 6), (9, 40), (3, 1), (14, 9)]):
+            s.add(Request(f"q{i}", [(i + t) % 50 for t in range(n)], SamplingParams.greedy_params(new)))
+        return s, cache
+
+    for pages in (64, 14):           # roomy, and so tight that requests are preempted and recomputed
+        a, _ = make(pages)
+        want, sync_steps = drive_ahead(a, token_of, ahead=False)
+        b, cache = make(pages)
+        got, ahead_steps = drive_ahead(b, token_of, ahead=True)
+        assert got == want and set(want) == {f"q{i}" for i in range(5)}
+        assert any(reason == "stop" for _, reason in want.values()) and any(reason == "length" for _, reason in want.values())
+        markers = [t for st in ahead_steps for _, _, toks, _ in st for t in toks if t < 0]
+        assert markers and not [t for st in sync_steps for _, _, toks, _ in st for t in toks if t < 0]
+        # a marker names a row of the step before: the j-th of its segments that wanted logits
+        for before, st in zip(ahead_steps, ahead_steps[1:]):
+            wanting = [rid for rid, _, _, wants in before if wants]
+            for rid, start, toks, _ in st:
+                if toks[0] < 0:
+                    assert len(toks) == 1 and wanting[-toks[0] - 1] == rid
+        assert not cache.requests and cache.free_pages() == [pages]
+        cache.check()
+        if pages == 14:
+            assert a.preemptions > 0 and b.preemptions > 0
