@@ -21,7 +21,7 @@
 //
 // Requirements (else the caller uses another kernel): bfloat16, K a multiple of 8, row strides
 // multiples of 8 elements, 16-byte aligned base pointers.
-#include "tcgen05_common.cuh"
+#include "gemm_epilogue.cuh"
 
 namespace {
 
@@ -36,8 +36,7 @@ __host__ __device__ constexpr int stages_for(int bn) { return bn >= 256 ? 4 : bn
 constexpr int JLLM_TC_MAX_TILES = 65536;  // counter words at the head of the workspace of streamed products
 constexpr int THREADS = 192;           // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
 constexpr int TMEM_COLS = 512;
-constexpr int STAGING_ROW = 36;        // floats of a staged row of 32 values: 16-byte aligned, and rows fall in other banks
-constexpr int STAGING_BYTES = 4 * 32 * STAGING_ROW * 4;      // 32 rows for each of the four epilogue warps
+constexpr int STAGING_BYTES = 4 * STAGING_WARP_FLOATS * 4;   // a 32 x 32 block for each of the four epilogue warps
 __host__ __device__ constexpr size_t smem_bytes_for(int bn) {
     return (size_t)stages_for(bn) * (A_BYTES + bn * BK * 2) + 1024 /* alignment slack */ + 256 /* barriers */ +
            STAGING_BYTES;
@@ -79,35 +78,41 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __nv_bfloat
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN, tiles = tiles_m * tiles_n;
     const int k_blocks = (K + BK - 1) / BK;
     const int padded_rows = (N + 127) & ~127;       // rows of the packed weight
-    // The work of a block: whole tiles, tile = block, block + grid, ... as long as full rounds of tiles last. The
-    // tiles of a last, partly filled round are streamed instead (stream-K): their (tile, k block) pairs, in tile
-    // order, are cut into one equal run per block, so that no SM idles through that round; a tile whose k blocks
-    // lie in several blocks' runs is finished by whichever of them comes last (below). Blocks that run at the
-    // same time always work on neighbouring tiles, which share their W and A tiles in L2. All three roles walk
-    // the same units with this.
+    // The work of a block. Plain: whole tiles, tile = block, block + grid, ... Streamed (stream-K): only the full
+    // rounds of tiles go that way; the tiles of the last, partly filled round are cut up instead: their (tile, k
+    // block) pairs, in tile order, are dealt out as one equal run per block, and every block walks its run FIRST
+    // and its whole tiles after it, so that no SM idles through a round and what the cutting costs (parked partial
+    // tiles and their adding up, in the epilogue warps) lies under the main loops of the whole tiles that follow.
+    // Of the blocks that hold k blocks of one tile, the one with the tile's FIRST k blocks finishes it: that part
+    // is the last of its run, and the others' parts are the first of theirs, so they are parked by the time it
+    // asks for them and nobody who is waited for waits himself. Blocks that run at the same time always work on
+    // neighbouring tiles, which share their W and A tiles in L2. All three roles walk the same units with this.
     const int whole_tiles = stream ? tiles / (int)gridDim.x * (int)gridDim.x : tiles;
     const long long sk_kb = (long long)(tiles - whole_tiles) * k_blocks;     // streamed (tile, k block) pairs
-    const long long run_lo = sk_kb * blockIdx.x / gridDim.x, run_hi = sk_kb * (blockIdx.x + 1) / gridDim.x;
+    // (fewer pairs than blocks: the first `dealt` blocks take one each, so that no run between two others is empty)
+    const long long dealt = min((long long)gridDim.x, max(sk_kb, 1LL));
+    auto run_start = [&](long long c) { return sk_kb * min(c, dealt) / dealt; };
+    const long long run_lo = run_start(blockIdx.x), run_hi = run_start(blockIdx.x + 1);
     struct Walk {
         long long at;
         int i;
     };
     auto first_unit = [&]() { return Walk{run_lo, 0}; };
     auto next_unit = [&](Walk& w, int& tile, int& lo, int& hi) {
-        const int t = blockIdx.x + w.i * gridDim.x;
-        if (t < whole_tiles) {
-            tile = t;
-            lo = 0;
-            hi = k_blocks;
-            ++w.i;
+        if (w.at < run_hi) {
+            const int st = (int)(w.at / k_blocks);
+            tile = whole_tiles + st;
+            lo = (int)(w.at - (long long)st * k_blocks);
+            hi = (int)min((long long)k_blocks, lo + (run_hi - w.at));
+            w.at += hi - lo;
             return true;
         }
-        if (w.at >= run_hi) return false;
-        const int st = (int)(w.at / k_blocks);
-        tile = whole_tiles + st;
-        lo = (int)(w.at - (long long)st * k_blocks);
-        hi = (int)min((long long)k_blocks, lo + (run_hi - w.at));
-        w.at += hi - lo;
+        const int t = blockIdx.x + w.i * gridDim.x;
+        if (t >= whole_tiles) return false;
+        tile = t;
+        lo = 0;
+        hi = k_blocks;
+        ++w.i;
         return true;
     };
 
@@ -208,6 +213,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __nv_bfloat
     } else {
         // ---------------- epilogue: warps 2..5, TMEM lanes 32 * (warp % 4) ----------------
         const int quad = warp & 3;
+        const TileEpilogue<Tout> ep{out, ldo, M, N, accumulate, has_bias, swiglu, bias};
         uint32_t local_tile = 0;
         bool ok = true;
         Walk walk = first_unit();
@@ -217,145 +223,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __nv_bfloat
             const uint32_t buf = local_tile & 1u;
             if (!mbar_wait(acc_full_bar(buf), (local_tile >> 1) & 1u, abort_flag, spin)) { ok = false; break; }
             tcgen05_fence_after();
-            const int row = m0 + quad * 32 + lane;
             const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quad * 32) << 16);
             // bias / residual / SwiGLU and the store of 32 columns of this thread's row
-            // all 32 rows of this warp lie inside the matrix, and float32 rows can be accessed 16 bytes at a time
-            const bool rows_whole = !swiglu && m0 + quad * 32 + 32 <= M && sizeof(Tout) == 4 && (ldo & 3) == 0 &&
-                                    (((uintptr_t)out) & 15u) == 0;
-            // Through shared memory, so that a warp's accesses are whole lines: a thread holds 32 values of ONE row, and
-            // written (or added) from there a warp's instruction would touch 32 rows with 16 bytes each. The warp parks
-            // its 32 x 32 block and takes it back four rows at a time, eight threads to a row: four full 128-byte lines
-            // per instruction, and all eight loads of a residual add are on their way before the first store.
-            auto staged_rows = [&](uint32_t (&v)[32], int c0) {
-                const int n_base = n0 + c0;
-                float* mine = staging + quad * (32 * STAGING_ROW);
-                float4* srow = reinterpret_cast<float4*>(mine + lane * STAGING_ROW);
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    srow[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                          __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
-                __syncwarp();
-                const int sub = lane >> 3, c4 = (lane & 7) * 4;
-                float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (has_bias)
-                    bv = make_float4(bias[n_base + c4], bias[n_base + c4 + 1], bias[n_base + c4 + 2], bias[n_base + c4 + 3]);
-                float* d0 = reinterpret_cast<float*>(out) + (size_t)(m0 + quad * 32 + sub) * ldo + n_base + c4;
-                float4 old[8];
-                if (accumulate) {
-#pragma unroll
-                    for (int p = 0; p < 8; ++p) old[p] = *reinterpret_cast<const float4*>(d0 + (size_t)(4 * p) * ldo);
-                }
-#pragma unroll
-                for (int p = 0; p < 8; ++p) {
-                    float4 x = *reinterpret_cast<const float4*>(mine + (4 * p + sub) * STAGING_ROW + c4);
-                    x.x += bv.x; x.y += bv.y; x.z += bv.z; x.w += bv.w;
-                    if (accumulate) { x.x += old[p].x; x.y += old[p].y; x.z += old[p].z; x.w += old[p].w; }
-                    *reinterpret_cast<float4*>(d0 + (size_t)(4 * p) * ldo) = x;
-                }
-                __syncwarp();
-            };
-            auto finalize = [&](uint32_t (&v)[32], int c0) {
-                if (rows_whole && n0 + c0 + 32 <= N) {
-                    staged_rows(v, c0);
-                } else if (row < M && swiglu) {
-                    // columns come in blocks of 16: 8 gate columns, then the 8 up columns of the same hidden units
-                    const int n_base = n0 + c0;
-                    Tout* dst = out + (size_t)row * ldo + (n_base >> 1);
-                    // (the tensor-core path may use the fast exponential: its result is rounded to bfloat16 anyway)
-                    float hv[16];
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int cg = (j >> 3) * 16 + (j & 7);
-                        const float gt = __uint_as_float(v[cg]), up = __uint_as_float(v[cg + 8]);
-                        hv[j] = __fdividef(gt, 1.f + __expf(-gt)) * up;
-                    }
-                    if (sizeof(Tout) == 2 && n_base + 32 <= N && ((((uintptr_t)dst) & 15u) == 0)) {
-                        uint32_t p[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            __nv_bfloat162 b2 = __floats2bfloat162_rn(hv[2 * j], hv[2 * j + 1]);
-                            p[j] = *reinterpret_cast<uint32_t*>(&b2);
-                        }
-                        reinterpret_cast<uint4*>(dst)[0] = make_uint4(p[0], p[1], p[2], p[3]);
-                        reinterpret_cast<uint4*>(dst)[1] = make_uint4(p[4], p[5], p[6], p[7]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const int cg = (j >> 3) * 16 + (j & 7);
-                            if (n_base + cg + 8 < N) dst[j] = from_float<Tout>(hv[j]);
-                        }
-                    }
-                } else if (row < M) {
-                    const int n_base = n0 + c0;
-                    Tout* dst = out + (size_t)row * ldo + n_base;
-                    if (n_base + 32 <= N) {
-                        if constexpr (sizeof(Tout) == 4) {
-                            float4* d4 = reinterpret_cast<float4*>(dst);
-                            const bool vec = (((uintptr_t)dst) & 15u) == 0;
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                float4 r;
-                                r.x = __uint_as_float(v[4 * j + 0]);
-                                r.y = __uint_as_float(v[4 * j + 1]);
-                                r.z = __uint_as_float(v[4 * j + 2]);
-                                r.w = __uint_as_float(v[4 * j + 3]);
-                                if (has_bias) {
-                                    r.x += bias[n_base + 4 * j + 0];
-                                    r.y += bias[n_base + 4 * j + 1];
-                                    r.z += bias[n_base + 4 * j + 2];
-                                    r.w += bias[n_base + 4 * j + 3];
-                                }
-                                if (vec) {
-                                    if (accumulate) {
-                                        const float4 o = d4[j];
-                                        r.x += o.x; r.y += o.y; r.z += o.z; r.w += o.w;
-                                    }
-                                    d4[j] = r;
-                                } else {
-                                    float* d = reinterpret_cast<float*>(dst) + 4 * j;
-                                    if (accumulate) { r.x += d[0]; r.y += d[1]; r.z += d[2]; r.w += d[3]; }
-                                    d[0] = r.x; d[1] = r.y; d[2] = r.z; d[3] = r.w;
-                                }
-                            }
-                        } else {
-                            const bool vec = (((uintptr_t)dst) & 15u) == 0;
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                uint32_t p[4];
-#pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    float lo = __uint_as_float(v[8 * j + 2 * e]), hi = __uint_as_float(v[8 * j + 2 * e + 1]);
-                                    if (has_bias) { lo += bias[n_base + 8 * j + 2 * e]; hi += bias[n_base + 8 * j + 2 * e + 1]; }
-                                    if (accumulate) { lo += to_float(dst[8 * j + 2 * e]); hi += to_float(dst[8 * j + 2 * e + 1]); }
-                                    __nv_bfloat162 b2 = __floats2bfloat162_rn(lo, hi);
-                                    p[e] = *reinterpret_cast<uint32_t*>(&b2);
-                                }
-                                if (vec) {
-                                    reinterpret_cast<uint4*>(dst)[j] = make_uint4(p[0], p[1], p[2], p[3]);
-                                } else {
-#pragma unroll
-                                    for (int e = 0; e < 4; ++e) {
-                                        __nv_bfloat162 b2 = *reinterpret_cast<__nv_bfloat162*>(&p[e]);
-                                        dst[8 * j + 2 * e] = b2.x;
-                                        dst[8 * j + 2 * e + 1] = b2.y;
-                                    }
-                                }
-                            }
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if (n_base + j < N) {
-                                float r = __uint_as_float(v[j]);
-                                if (has_bias) r += bias[n_base + j];
-                                if (accumulate) r += to_float(dst[j]);
-                                dst[j] = from_float<Tout>(r);
-                            }
-                        }
-                    }
-                }
-            };
+            const int row0 = m0 + quad * 32;
+            const bool whole = ep.rows_whole(row0);
+            float* my_staging = staging + quad * STAGING_WARP_FLOATS;
+            auto finalize = [&](uint32_t (&v)[32], int c0) { ep.store(v, row0, lane, n0 + c0, whole, my_staging); };
             if (k_lo == 0 && k_hi == k_blocks) {      // the whole tile is this block's
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -369,67 +242,69 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __nv_bfloat
                 if (lane == 0) mbar_arrive(acc_empty_bar(buf));
                 continue;
             }
-            // ---- the tile's k blocks are spread over several blocks: park this part ([block][first or later unit
-            // of the block][BN columns][128 rows]: a warp's 32 rows of one column are 128 contiguous bytes); the
-            // blocks that hold parts of the tile are consecutive ----
-            auto run_start = [&](long long c) { return sk_kb * c / gridDim.x; };
-            auto block_of = [&](long long kb_index) {   // the block whose run holds this streamed (tile, k block) pair
-                return (int)(((kb_index + 1) * gridDim.x + sk_kb - 1) / sk_kb - 1);
-            };
-            const long long tile_kb0 = (long long)(tile - whole_tiles) * k_blocks;
-            const int c_first = block_of(tile_kb0), parts = block_of(tile_kb0 + k_blocks - 1) - c_first + 1;
-            auto part_of = [&](int c) {                 // where block c parked its part of this tile
-                const int slot = run_start(c) >= tile_kb0 ? 0 : 1;
-                return partials + (size_t)(2 * c + slot) * BM * BN + quad * 32 + lane;
-            };
-            float* mine = part_of(blockIdx.x);
+            // ---- the tile's k blocks are spread over several (consecutive) blocks ----
+            if (k_lo > 0) {
+                // Not the tile's first k blocks: this is the first unit of the block's run. Park the part ([block][BN
+                // columns][128 rows]: a warp's 32 rows of one column are 128 contiguous bytes) and count it in.
+                float* mine = partials + (size_t)blockIdx.x * BM * BN + quad * 32 + lane;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(taddr + c0, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) __stcg(mine + (size_t)(c0 + j) * BM, __uint_as_float(v[j]));
+                }
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+                asm volatile("bar.sync 1, 128;" ::: "memory");           // the four epilogue warps have written
+                if (warp == 2 && lane == 0) {
+                    __threadfence();
+                    atomicAdd(&counters[tile], 1);
+                }
+                continue;
+            }
+            // The tile's first k blocks, the last unit of this block's run: wait (bounded) until the blocks after this
+            // one have parked theirs, add them to the accumulator in k order (so the sum does not depend on who was
+            // when) and finish the tile. All blocks of the grid are resident, one per SM.
+            const long long tile_last_kb = (long long)(tile - whole_tiles + 1) * k_blocks - 1;
+            const int others = (int)(((tile_last_kb + 1) * dealt + sk_kb - 1) / sk_kb - 1) - (int)blockIdx.x;
+            if (warp == 2 && lane == 0) {
+                int seen = 0;
+                for (uint32_t tries = 0; seen < others && tries < spin; ++tries) {
+                    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(counters + tile) : "memory");
+                    if (seen < others) {
+                        if ((tries & 255u) == 255u && *abort_flag) break;
+                        __nanosleep(32);
+                    }
+                }
+                if (seen >= others) counters[tile] = 0;               // back to zero for the next product
+                *last_flag = seen >= others;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (!*last_flag) { ok = false; break; }
+            const float* theirs = partials + (size_t)(blockIdx.x + 1) * BM * BN + quad * 32 + lane;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t v[32];
                 tmem_ld_32x32b_x32(taddr + c0, v);
-                tmem_ld_wait();
+                float x[32];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) __stcg(mine + (size_t)(c0 + j) * BM, __uint_as_float(v[j]));
+                for (int j = 0; j < 32; ++j) x[j] = __ldcg(theirs + (size_t)(c0 + j) * BM);
+                tmem_ld_wait();
+                for (int p = 1;; ++p) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + x[j]);
+                    if (p >= others) break;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) x[j] = __ldcg(theirs + (size_t)p * BM * BN + (size_t)(c0 + j) * BM);
+                }
+                finalize(v, c0);
             }
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty_bar(buf));
-            asm volatile("bar.sync 1, 128;" ::: "memory");           // the four epilogue warps have written
-            if (warp == 2 && lane == 0) {
-                __threadfence();
-                const int seen = atomicAdd(&counters[tile], 1);
-                *last_flag = seen == parts - 1;
-                if (seen == parts - 1) {
-                    counters[tile] = 0;                               // back to zero for the next product
-                    __threadfence();
-                }
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (*last_flag == 0) continue;
-            // ---- the block that came last adds the parts in k order (deterministic) and finishes the tile ----
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                float acc[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) acc[j] = 0.f;
-                for (int s0 = 0; s0 < parts; s0 += 2) {     // two parts' loads in flight at a time, added in k order
-                    const float* p0 = part_of(c_first + s0) + (size_t)c0 * BM;
-                    const float* p1 = part_of(c_first + min(s0 + 1, parts - 1)) + (size_t)c0 * BM;
-                    float x0[32], x1[32];
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        x0[j] = __ldcg(p0 + (size_t)j * BM);
-                        x1[j] = __ldcg(p1 + (size_t)j * BM);
-                    }
-                    const bool two = s0 + 1 < parts;
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) acc[j] = two ? (acc[j] + x0[j]) + x1[j] : acc[j] + x0[j];
-                }
-                uint32_t v[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(acc[j]);
-                finalize(v, c0);
-            }
         }
         if (!ok && lane == 0) { *abort_flag = 1; atomicExch(error_word, 3); }
     }
@@ -510,9 +385,6 @@ JLLM_EXPORT int jllm_gemm_tcgen05(const void* a, int lda, const void* w, int k_b
         const long long cost = ((t + sms - 1) / sms) * (rows_per_tile + widths[i]);
         if (best < 0 || cost < best) { best = cost; BN = widths[i]; }
     }
-    // The tiles of a last, partly filled round can be streamed (stream-K, stream_mode 1). It is not done by default:
-    // on the layer shapes of an 8B model with 2,048 rows the parked partial tiles and their adding up cost what the
-    // idle SMs of the last round cost (QKV 92 us streamed, 81 us plain; gate_up 307 / 291; down 207 / 178).
     bool streamed = false;
     if (tile_width > 0) BN = tile_width;
     JLLM_REQUIRE(BN == 256 || BN == 192 || BN == 128 || BN == 64 || BN == 32, "gemm_tcgen05: tile width %d", BN);
@@ -523,20 +395,25 @@ JLLM_EXPORT int jllm_gemm_tcgen05(const void* a, int lda, const void* w, int k_b
     if (!error_word) return jllm_fail(JLLM_CUDA_ERROR, "gemm_tcgen05: no error word");
     const int tiles = tiles_m * ((N + BN - 1) / BN);
     const int k_blocks = (K + BK - 1) / BK;
-    // stream_mode: 1 = streamed, else plain. The workspace of a streamed product holds one counter per tile (zero
-    // before the first product, left zero by every product) and two parked partial tiles per block.
+    // stream_mode 1: the tiles of a last, partly filled round are streamed (stream-K), and fewer tiles than SMs are cut
+    // up too. Not the default: on the layer shapes of an 8B model with 2,048 rows the SMs that the last round leaves
+    // idle cost little (the busy ones run the faster for it: the products are bound by what the memory system and the
+    // power limit give all SMs together), and the parked partial tiles cost about as much (QKV 81 us streamed, 82
+    // plain; O 63 / 60; gate_up 318 / 289; down 184 / 191). The workspace of a streamed product holds one counter per
+    // tile (zero before the first product, left zero by every product) and one parked partial tile per block.
     int grid = tiles < sms ? tiles : sms;
-    if (stream_mode > 0) {
-        streamed = true;
+    if (stream_mode == 1) {
         const long long all_kb = (long long)tiles * k_blocks;
         grid = all_kb < sms ? (int)all_kb : sms;
     }
     if (max_blocks > 0 && grid > max_blocks) grid = max_blocks;
-    const long long need = JLLM_TC_MAX_TILES + (long long)grid * 2 * BM * BN;
-    const bool room = workspace != nullptr && workspace_floats >= need && tiles <= JLLM_TC_MAX_TILES;
-    if (streamed)
+    const long long need = JLLM_TC_MAX_TILES + (long long)grid * BM * BN;
+    if (stream_mode == 1) {
+        const bool room = workspace != nullptr && workspace_floats >= need && tiles <= JLLM_TC_MAX_TILES;
         JLLM_REQUIRE(room, "gemm_tcgen05: a streamed product of %d tiles on %d blocks needs a workspace of %lld floats "
                            "(got %lld) and at most %d tiles", tiles, grid, need, workspace_floats, JLLM_TC_MAX_TILES);
+        streamed = true;
+    }
     int* counters = reinterpret_cast<int*>(workspace);
     float* partials = workspace ? workspace + JLLM_TC_MAX_TILES : nullptr;
     const int splits = streamed ? 1 : 0;      // the kernel's `stream` argument

@@ -136,6 +136,8 @@ class _Signatures:
     jllm_gemm_plain = [P, I, I, P, I, P, I, P, I, I, I, I, I, I, P]
     jllm_gemm_small_m = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, P]
     jllm_gemm_tcgen05 = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, I, P, ctypes.c_longlong, I, I, P]
+    jllm_gemm_pair = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, I, P]
+    jllm_gemm_pair_resident = []
     jllm_gemm_stream = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, P, ctypes.c_longlong, I, P]
     jllm_gemm_tcgen05_error = []
     jllm_gemm_tcgen05_starve_next = []
@@ -256,8 +258,8 @@ SMALL_M_ROWS = int(os.environ.get("JLLM_B200_SMALL_M_ROWS", "64"))
 WIDE_ROWS = int(os.environ.get("JLLM_B200_WIDE_ROWS", "16384"))
 SWAP_MIN_BYTES = int(os.environ.get("JLLM_B200_SWAP_MIN_BYTES", str(40_000_000)))
 _workspaces = {}
-# counters of up to 65,536 tiles, then two parked 128 x 256 partial tiles for each of up to 160 blocks
-STREAM_WORKSPACE_FLOATS = 65536 + 160 * 2 * 128 * 256
+# counters of up to 65,536 tiles, then one parked 128 x 256 partial tile for each of up to 160 blocks
+STREAM_WORKSPACE_FLOATS = 65536 + 160 * 128 * 256
 SWAP_WORKSPACE_FLOATS = 2 * 65536 + 160 * 2 * 128 * 128       # gemm_stream: two counters per tile, then the parts
 
 
@@ -273,9 +275,9 @@ def gemm_workspace(key, floats: int = 8 << 20) -> torch.Tensor:
 
 
 def gemm_kernel_for(rows: int, out_features: int, in_features: int = 4096, rows_fit: bool = True,
-                    tiles_fit: bool = True) -> str:
-    """"rows", "swap", "tiles" or "" for a bfloat16 product of `rows` rows against a [out_features, in_features]
-    weight, given which kernels take its strides and alignment."""
+                    tiles_fit: bool = True, sms: int = 148, pairs: int = 74) -> str:
+    """"rows", "swap", "tiles", "pair" or "" for a bfloat16 product of `rows` rows against a [out_features, in_features]
+    weight, given which kernels take its strides and alignment, the SMs and the pairs of them the device runs at a time."""
     # 16 or more rows against a wide matrix (gate_up): 128 or more 192-wide tcgen05 tiles stream it faster than the
     # weight-row kernel, whose blocks have half their loads in flight once they hold more than two token tiles
     wide = rows >= 16 and out_features >= WIDE_ROWS and tiles_fit
@@ -283,7 +285,16 @@ def gemm_kernel_for(rows: int, out_features: int, in_features: int = 4096, rows_
         return "swap"
     if rows <= min(SMALL_M_ROWS, 64) and rows_fit and not wide:
         return "rows"
-    return "tiles" if tiles_fit else ""
+    if not tiles_fit:
+        return ""
+    # Many rows: two SMs to a 256 x 256 tile take in a third less per multiply-add than one SM with a 128 x 256 tile,
+    # which is what bounds these products. It pays where its tiles keep three quarters of the pairs busy or more and its rounds of
+    # tiles, each about a tenth shorter than a round of the one-SM kernel's, are no more than that kernel's.
+    col_tiles = -(-out_features // 256)
+    pair_tiles, single_tiles = -(-rows // 256) * col_tiles, -(-rows // 128) * col_tiles
+    if pairs > 0 and pair_tiles * 4 >= pairs * 3 and -(-pair_tiles // pairs) * 0.9 <= -(-single_tiles // sms):
+        return "pair"
+    return "tiles"
 
 
 def gemm_bf16(a, w, out, bias=None, accumulate=False, swiglu=False) -> None:
@@ -291,11 +302,15 @@ def gemm_bf16(a, w, out, bias=None, accumulate=False, swiglu=False) -> None:
     plain [out, in] matrix is packed on the spot). With `swiglu` the rows of w are blocks of 8 gate rows followed by
     their 8 up rows and out[m, j] = silu(gate_j) * up_j."""
     w = _packed(w)
-    kernel = gemm_kernel_for(a.shape[0], w.rows, w.cols, _rows_fit(a, w), _tcgen05_fits(a, w))
+    rows = a.shape[0]
+    kernel = gemm_kernel_for(rows, w.rows, w.cols, _rows_fit(a, w), _tcgen05_fits(a, w), sm_count(),
+                             resident_pairs() if rows > 128 else 0)
     if kernel == "rows":
         return gemm_small_m(a, w, out, bias, accumulate, swiglu=swiglu)
     if kernel == "swap":
         return gemm_stream(a, w, out, bias, accumulate, swiglu=swiglu)
+    if kernel == "pair":
+        return gemm_pair(a, w, out, bias, accumulate, swiglu=swiglu)
     if kernel == "tiles":
         return gemm_tcgen05(a, w, out, bias, accumulate, swiglu=swiglu)
     raise KernelError("the tensor-core matrix product is not built for this shape")
@@ -306,15 +321,37 @@ def gemm_tcgen05(a, w, out, bias=None, accumulate=False, max_blocks: int = 0, sw
     """The prefill product: tcgen05.mma tiles of 128 x `tile_width` (0: chosen from the shape, 256 for big products,
     down to 32 when the rows are few) with the accumulator in tensor memory; the activations' tiles come by TMA, the
     packed weight's by contiguous bulk copies. `stream_mode` 1: the tiles of a last, partly filled round are
-    streamed (stream-K: equal runs of (tile, k block) pairs per block, partial tiles meeting in a workspace); off by
-    default (measured slower on 8B layer shapes)."""
+    streamed (stream-K: equal runs of (tile, k block) pairs per block, walked before the block's whole tiles; partial
+    tiles meet in a workspace); not the default (it gains little where the SMs share one memory system and one power
+    limit)."""
     w = _packed(w)
     assert a.dtype == torch.bfloat16 and out.stride(-1) == 1 and a.shape[1] == w.cols
-    ws = gemm_workspace(a.device, STREAM_WORKSPACE_FLOATS) if stream_mode > 0 else None
+    ws = gemm_workspace(a.device, STREAM_WORKSPACE_FLOATS) if stream_mode == 1 else None
     _call("jllm_gemm_tcgen05", a.data_ptr(), a.stride(0), w.data.data_ptr(), w.k_blocks, _p(bias),
           _DT[bias.dtype] if bias is not None else F32, out.data_ptr(), _DT[out.dtype], out.stride(0),
           int(accumulate), a.shape[0], w.rows, w.cols, int(max_blocks), int(swiglu), _p(ws),
           ws.numel() if ws is not None else 0, int(stream_mode), int(tile_width), _stream())
+
+
+def gemm_pair(a, w, out, bias=None, accumulate=False, swiglu=False, max_pairs: int = 0) -> None:
+    """The product of a prefill with many rows: two SMs to a 256 x 256 tile (tcgen05 cta_group::2), each bringing half of
+    the tile's rows of A and of W; epilogues as `gemm_tcgen05`."""
+    w = _packed(w)
+    assert a.dtype == torch.bfloat16 and out.stride(-1) == 1 and a.shape[1] == w.cols
+    _call("jllm_gemm_pair", a.data_ptr(), a.stride(0), w.data.data_ptr(), w.k_blocks, _p(bias),
+          _DT[bias.dtype] if bias is not None else F32, out.data_ptr(), _DT[out.dtype], out.stride(0),
+          int(accumulate), a.shape[0], w.rows, w.cols, int(max_pairs), int(swiglu), _stream())
+
+
+_resident_pairs = None
+
+
+def resident_pairs() -> int:
+    """How many clusters of two blocks of the paired product the device runs at a time (0: it is not offered)."""
+    global _resident_pairs
+    if _resident_pairs is None:
+        _resident_pairs = max(0, int(library().jllm_gemm_pair_resident()))
+    return _resident_pairs
 
 
 class PackedWeight:

@@ -186,6 +186,44 @@ def test_gemm_tcgen05(ops, M, N, K):
     assert ops.gemm_tcgen05_error() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (1, 8, 8), (100, 517, 72), (300, 1000, 200), (2048, 6144, 4096),
+                                   (257, 4096, 12288), (700, 384, 136), (129, 257, 1032)])
+def test_gemm_pair(ops, M, N, K):
+    """Two SMs to a 256 x 256 tile (tcgen05 cta_group::2): the product with a bias, the residual add with few pairs (each
+    walks many tiles and both accumulators), bfloat16 into a view with columns beside it, the SwiGLU epilogue; rows and
+    columns that end inside a tile, inside a block's half of it, and a tile whose second half of W does not exist."""
+    if ops.resident_pairs() < 1:
+        pytest.skip("the device runs no pair of blocks of this kernel")
+    a, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=1, scale=0.05)
+    bias = rnd(N, dtype=torch.bfloat16, seed=2)
+    tol = 1e-4 * math.sqrt(K) * 0.05
+    out = torch.full((M, N), float("nan"), device=DEV)
+    ops.gemm_pair(a, w, out, bias)
+    assert ops.gemm_tcgen05_error() == 0
+    assert torch.allclose(out.cpu(), gemm_want(a, w, bias), rtol=1e-4, atol=tol), float((out.cpu() - gemm_want(a, w, bias)).abs().max())
+    base = rnd(M, N, seed=3)
+    for pairs in (3, 0):
+        acc = base.clone()
+        ops.gemm_pair(a, w, acc, None, accumulate=True, max_pairs=pairs)
+        assert torch.allclose(acc.cpu(), gemm_want(a, w, None, base), rtol=1e-4, atol=tol)
+    out16 = torch.zeros(M, N + 8, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_pair(a, w, out16[:, :N])
+    assert torch.allclose(out16[:, :N].float().cpu(), gemm_want(a, w), rtol=2 ** -7, atol=2e-3)
+    assert float(out16[:, N:].abs().max()) == 0
+    # the same bits as the one-SM kernel: the same products summed in the same order, k block by k block
+    single = torch.empty(M, N, device=DEV)
+    ops.gemm_tcgen05(a, w, single, bias)
+    assert torch.equal(single, out)
+    if N % 16 == 0:
+        hidden = N // 2
+        g = gemm_want(a, w.view(hidden // 8, 2, 8, K)[:, 0].reshape(hidden, K))
+        u = gemm_want(a, w.view(hidden // 8, 2, 8, K)[:, 1].reshape(hidden, K))
+        h = torch.full((M, hidden), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.gemm_pair(a, w, h, swiglu=True)
+        assert torch.allclose(h.float().cpu(), P.silu(g) * u, rtol=2 ** -7, atol=1e-3)
+    assert ops.gemm_tcgen05_error() == 0
+
+
 @pytest.mark.parametrize("width", [32, 64, 128, 192, 256])
 @pytest.mark.parametrize("M,N,K", [(64, 4096, 4096), (33, 517, 72), (200, 1000, 1032), (128, 24576, 512)])
 def test_gemm_tcgen05_tile_widths(ops, M, N, K, width):

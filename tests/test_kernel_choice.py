@@ -15,7 +15,12 @@ def test_product_kernel_by_rows_and_shape():
     assert k(64, 4096, 12288) == "swap" and k(128, 4096, 12288) == "swap" and k(129, 4096, 12288) == "tiles"
     assert k(40, 4096, 4096) == "rows" and k(41, 4096, 4096) == "swap"         # O (34 MB): from 41 rows
     assert k(64, 24576, 4096) == "tiles"                                       # gate_up: whole tiles fill the SMs
-    assert k(2048, 4096, 4096) == "tiles"
+    # many rows: two SMs to a 256 x 256 tile where such tiles keep the pairs busy in no more rounds than one-SM tiles
+    assert k(2048, 4096, 4096) == "pair" and k(2048, 6144, 4096) == "pair" and k(2048, 24576, 4096) == "pair"
+    assert k(1024, 4096, 12288) == "pair" and k(512, 24576, 4096) == "pair"
+    assert k(512, 6144, 4096) == "tiles"                   # 48 tiles for 74 pairs
+    assert k(300, 24576, 4096) == "tiles"                  # 300 rows: three 128-row tiles, not two of 256
+    assert k(2048, 4096, 4096, pairs=0) == "tiles"         # a device that runs no pairs
     assert k(16, 24576, 4096, tiles_fit=False) == "rows"
     assert k(8, 4096, 4096, rows_fit=False) == "tiles"
     assert k(8, 4096, 4096, rows_fit=False, tiles_fit=False) == ""
