@@ -282,6 +282,12 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
 
 JLLM_BOUNDS_READER(attention_decode)
 
+namespace {
+// a test's switch: the partials are added up by the combine kernels, as where the library's counters do not reach
+int g_separate_combine = 0;
+}
+JLLM_EXPORT void jllm_attention_decode_separate_combine(int on) { g_separate_combine = on; }
+
 #include "attention_decode_staged.cuh"
 
 // Floats of scratch the split path needs: (head_dim + 2) per (row, head, split).
@@ -312,13 +318,18 @@ JLLM_EXPORT int jllm_attention_decode(const void* q, int q_stride, const void* k
     const int hdc = (head_dim + 63) / 64;
     if (head_dim == 64 || head_dim == 128 || head_dim == 256) {
         // the common head sizes stream the cache through a shared-memory ring (attention_decode_staged.cuh)
+        // The last block of a (row, kv head) pair adds the pair's partials up itself where the library's counters reach,
+        // up to 8 splits: with more (few rows, long ranges) one block's adding of all of a pair's parts is slower than
+        // the combine kernel's block per head (a step of one row at 4,096 keys: 3.46 ms against 3.43 ms).
+        int* counters = splits > 1 && splits <= 8 && (long long)rows * kv_heads <= staged::PAIR_COUNTERS && !g_separate_combine
+                            ? staged::pair_counters() : nullptr;
 #define JLLM_STAGED(HD)                                                                                             \
     staged::launch<HD>(q, q_stride, k_cache, v_cache, out, out_stride, row_seg, row_pos, block_tables, table_stride, \
-                       rows, heads, kv_heads, page_size, window, scale_log2, splits, part_o, part_ml, stream)
+                       rows, heads, kv_heads, page_size, window, scale_log2, splits, part_o, part_ml, counters, stream)
         if (head_dim == 64) JLLM_STAGED(64); else if (head_dim == 128) JLLM_STAGED(128); else JLLM_STAGED(256);
 #undef JLLM_STAGED
         int rc2 = jllm_check_launch("attention_decode_staged");
-        if (rc2 != JLLM_OK || splits == 1) return rc2;
+        if (rc2 != JLLM_OK || splits == 1 || counters != nullptr) return rc2;
         jllm_launch(attention_combine_kernel, dim3(rows, heads), dim3(128), 0, stream, true, (const float*)part_o,
                     (const float*)part_ml, (__nv_bfloat16*)out, out_stride, heads, head_dim, splits);
         return jllm_check_launch("attention_combine");
@@ -371,9 +382,12 @@ JLLM_EXPORT int jllm_attention_decode_flat(const void* q, int q_stride, const vo
     float* part_o = scratch;
     float* part_ml = scratch + ((size_t)rows * kv_heads + blocks) * G * head_dim;
     const float scale_log2 = scale * LOG2E;
+    // (a run of the deal is never empty when there are at least as many key tiles as blocks: every pair has one or more)
+    int* counters = (long long)rows * kv_heads <= staged::PAIR_COUNTERS && (long long)rows * kv_heads >= blocks &&
+                            !g_separate_combine ? staged::pair_counters() : nullptr;
 #define JLLM_FLAT(HD)                                                                                                  \
     staged::launch_flat<HD>(q, q_stride, k_cache, v_cache, out, out_stride, row_seg, row_pos, block_tables, table_stride, \
-                            rows, heads, kv_heads, page_size, window, scale_log2, blocks, part_o, part_ml, stream)
+                            rows, heads, kv_heads, page_size, window, scale_log2, blocks, part_o, part_ml, counters, stream)
     if (head_dim == 64) JLLM_FLAT(64); else if (head_dim == 128) JLLM_FLAT(128); else JLLM_FLAT(256);
 #undef JLLM_FLAT
     return jllm_check_launch("attention_decode_flat");

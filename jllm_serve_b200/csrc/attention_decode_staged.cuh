@@ -261,6 +261,82 @@ __device__ __forceinline__ void attend(uint8_t* smem_raw, const __nv_bfloat16* _
     }
 }
 
+// ---- the partials of a (row, kv head) pair added up inside the attention kernel ------------------------------------
+// Every block that has written a partial of the pair counts itself in (after a fence: its partial is visible to the
+// device first); the one that finds itself last adds the partials up, in the order of the parts whoever it is, and puts
+// the counter back to zero for the next launch. Nobody waits for anybody. The counters belong to the library (zero
+// when it is loaded): launches of these kernels on one device must not overlap.
+constexpr int PAIR_COUNTERS = 1 << 16;
+__device__ int g_pair_counters[PAIR_COUNTERS];
+
+// true in all threads of the one block that is the `expected`-th to arrive; all threads of the block call it
+__device__ __forceinline__ bool last_of_pair(int* counter, int expected) {
+    __shared__ int s_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int seen = atomicAdd(counter, 1);
+        s_last = seen == expected - 1;
+        if (s_last) *counter = 0;
+    }
+    __syncthreads();
+    const bool last = s_last != 0;
+    if (last) __threadfence();
+    return last;
+}
+
+// out_pair[row * HD + d] for the G heads of the pair from `parts` partials: part p of head `row` has its sums at
+// po + p * o_part + row * o_row and (maximum, weight) at pml + p * ml_part + row * ml_row. A warp per head; the
+// arithmetic and its order are those of the combine kernels. parts <= 64.
+template <int HD>
+__device__ __forceinline__ void combine_pair(const float* __restrict__ po, size_t o_part, size_t o_row,
+                                             const float* __restrict__ pml, size_t ml_part, size_t ml_row, int parts,
+                                             int G, __nv_bfloat16* __restrict__ out_pair) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int row = warp; row < G; row += WARPS) {
+        float ms[2], ls[2], w[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int p = lane + 32 * h;
+            ms[h] = p < parts ? __ldcg(pml + p * ml_part + row * ml_row) : -INFINITY;
+            ls[h] = p < parts ? __ldcg(pml + p * ml_part + row * ml_row + 1) : 0.f;
+        }
+        float M = fmaxf(ms[0], ms[1]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        float L = 0.f;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            w[h] = ms[h] == -INFINITY ? 0.f : exp2f(ms[h] - M);
+            for (int i = 0; i < 32 && i + 32 * h < parts; ++i) L += __shfl_sync(0xffffffffu, ls[h] * w[h], i);
+        }
+        const float inv = 1.f / L;
+        float acc[HD / 32];
+#pragma unroll
+        for (int j = 0; j < HD / 32; ++j) acc[j] = 0.f;
+        for (int p0 = 0; p0 < parts; p0 += 4) {        // four parts' loads on their way at a time; added in part order
+            float x[4][HD / 32], wq[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int p = p0 + q;
+                wq[q] = __shfl_sync(0xffffffffu, p < 32 ? w[0] : w[1], p & 31);
+                if (p >= parts) wq[q] = 0.f;
+                const float* src = po + (size_t)min(p, parts - 1) * o_part + row * o_row + lane;
+#pragma unroll
+                for (int j = 0; j < HD / 32; ++j) x[q][j] = __ldcg(src + 32 * j);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                if (wq[q] == 0.f) continue;
+#pragma unroll
+                for (int j = 0; j < HD / 32; ++j) acc[j] += x[q][j] * wq[q];
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < HD / 32; ++j) out_pair[(size_t)row * HD + lane + 32 * j] = __float2bfloat16_rn(acc[j] * inv);
+    }
+}
+
 template <int HD>
 __global__ void __launch_bounds__(THREADS)
 attention_decode_staged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
@@ -268,7 +344,8 @@ attention_decode_staged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
                                __nv_bfloat16* __restrict__ out, int out_stride, const int* __restrict__ row_seg,
                                const int* __restrict__ row_pos, const int* __restrict__ block_tables, int table_stride,
                                int heads, int kv_heads, int page_size, int num_pages, int window, float scale_log2,
-                               int splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
+                               int splits, float* __restrict__ part_o, float* __restrict__ part_ml,
+                               int* __restrict__ counters) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const int r = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int G = heads / kv_heads;
@@ -285,6 +362,12 @@ attention_decode_staged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
     attend<HD>(smem_raw, q, q_stride, k_cache, v_cache, out, out_stride, table, table_stride, num_pages, heads, kv_heads,
                page_size, scale_log2, r, kvh, P, first, tile_lo, max(0, tile_hi - tile_lo), splits == 1, part_o + slot * HD,
                (size_t)splits * HD, part_ml + slot * 2, (size_t)splits * 2, true);
+    // (without counters a combine kernel follows)
+    if (splits > 1 && counters != nullptr && last_of_pair(counters + (size_t)r * kv_heads + kvh, splits)) {
+        const size_t slot0 = ((size_t)r * heads + kvh * G) * splits;
+        combine_pair<HD>(part_o + slot0 * HD, (size_t)HD, (size_t)splits * HD, part_ml + slot0 * 2, (size_t)2,
+                         (size_t)splits * 2, splits, G, out + (size_t)r * out_stride + (size_t)kvh * G * HD);
+    }
 }
 
 // ---- the same attention with the key tiles of all (row, kv head) pairs dealt out evenly ----------------------------------
@@ -325,7 +408,7 @@ attention_decode_flat_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, 
                              const int* __restrict__ row_seg, const int* __restrict__ row_pos,
                              const int* __restrict__ block_tables, int table_stride, int rows, int heads, int kv_heads,
                              int page_size, int num_pages, int window, float scale_log2, float* __restrict__ part_o,
-                             float* __restrict__ part_ml) {
+                             float* __restrict__ part_ml, int* __restrict__ counters) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ int s_cum[FLAT_MAX_ROWS + 1];
     pdl_wait();
@@ -350,11 +433,21 @@ attention_decode_flat_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, 
         const int n = (int)min((long long)(tiles_r - tile_lo), end - at);
         const int P = row_pos[r], first = window > 0 ? max(0, P + 1 - window) : 0;
         const size_t slot = (size_t)r * kv_heads + kvh + blockIdx.x;
+        // the blocks whose runs meet this pair follow one another (the host sees to it that no run is empty)
+        const long long start = at - tile_lo;
+        auto block_of = [&](long long tile) { return (int)(((tile + 1) * gridDim.x + all - 1) / all - 1); };
+        const int b_first = block_of(start), parts = block_of(start + tiles_r - 1) - b_first + 1;
+        const bool alone = counters != nullptr && parts == 1;       // this block has all of the pair: no partial
         attend<HD>(smem_raw, q, q_stride, k_cache, v_cache, out, out_stride, block_tables + (size_t)row_seg[r] * table_stride,
-                   table_stride, num_pages, heads, kv_heads, page_size, scale_log2, r, kvh, P, first, tile_lo, n, false,
+                   table_stride, num_pages, heads, kv_heads, page_size, scale_log2, r, kvh, P, first, tile_lo, n, alone,
                    part_o + slot * G * HD,
                    (size_t)HD, part_ml + slot * G * 2, (size_t)2);
         at += n;
+        if (counters != nullptr && !alone && last_of_pair(counters + (size_t)r * kv_heads + kvh, parts)) {
+            const size_t slot0 = (size_t)r * kv_heads + kvh + b_first;      // the slots of the pair's parts follow one another
+            combine_pair<HD>(part_o + slot0 * G * HD, (size_t)G * HD, (size_t)HD, part_ml + slot0 * G * 2, (size_t)G * 2,
+                             (size_t)2, parts, G, out + (size_t)r * out_stride + (size_t)kvh * G * HD);
+        }
         __syncthreads();                              // shared memory is the next stretch's
     }
 }
@@ -418,7 +511,7 @@ template <int HD>
 void launch_flat(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out, int out_stride,
                  const int* row_seg, const int* row_pos, const int* block_tables, int table_stride, int rows, int heads,
                  int kv_heads, int page_size, int window, float scale_log2, int blocks, float* part_o, float* part_ml,
-                 cudaStream_t stream) {
+                 int* counters, cudaStream_t stream) {
     const size_t stage_bytes = (size_t)STAGES * 2 * TILE * HD * 2;
     const size_t merge_bytes = ((size_t)WARPS * 16 * HD + WARPS * 16 * 2) * sizeof(float);
     const size_t smem = 16 * HD * 2 + (stage_bytes > merge_bytes ? stage_bytes : merge_bytes);
@@ -427,16 +520,18 @@ void launch_flat(const void* q, int q_stride, const void* k_cache, const void* v
     jllm_launch(kern, dim3(blocks), dim3(THREADS), smem, stream, true, (const __nv_bfloat16*)q, q_stride,
                 (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out, out_stride, row_seg,
                 row_pos, block_tables, table_stride, rows, heads, kv_heads, page_size, jllm_pool_pages(), window, scale_log2,
-                part_o, part_ml);
-    jllm_launch(attention_combine_flat_kernel, dim3(rows, heads), dim3(128), 0, stream, true, (const float*)part_o,
-                (const float*)part_ml, (__nv_bfloat16*)out, out_stride, row_pos, rows, heads, kv_heads, HD, window, blocks);
+                part_o, part_ml, counters);
+    if (counters == nullptr)
+        jllm_launch(attention_combine_flat_kernel, dim3(rows, heads), dim3(128), 0, stream, true, (const float*)part_o,
+                    (const float*)part_ml, (__nv_bfloat16*)out, out_stride, row_pos, rows, heads, kv_heads, HD, window,
+                    blocks);
 }
 
 template <int HD>
 void launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out, int out_stride,
             const int* row_seg, const int* row_pos, const int* block_tables, int table_stride, int rows, int heads,
             int kv_heads, int page_size, int window, float scale_log2, int splits, float* part_o, float* part_ml,
-            cudaStream_t stream) {
+            int* counters, cudaStream_t stream) {
     const size_t stage_bytes = (size_t)STAGES * 2 * TILE * HD * 2;
     const size_t merge_bytes = ((size_t)WARPS * 16 * HD + WARPS * 16 * 2) * sizeof(float);
     const size_t smem = 16 * HD * 2 + (stage_bytes > merge_bytes ? stage_bytes : merge_bytes);
@@ -445,7 +540,23 @@ void launch(const void* q, int q_stride, const void* k_cache, const void* v_cach
     jllm_launch(kern, dim3(rows, kv_heads, splits), dim3(THREADS), smem, stream, true,
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
         (__nv_bfloat16*)out, out_stride, row_seg, row_pos, block_tables, table_stride, heads, kv_heads, page_size,
-        jllm_pool_pages(), window, scale_log2, splits, part_o, part_ml);
+        jllm_pool_pages(), window, scale_log2, splits, part_o, part_ml, counters);
+}
+
+// The library's pair counters on the current device (nullptr: the combine kernels run instead).
+inline int* pair_counters() {
+    static int* ptrs[64] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (ptrs[dev] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_pair_counters) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        ptrs[dev] = static_cast<int*>(p);
+    }
+    return ptrs[dev];
 }
 
 }  // namespace staged

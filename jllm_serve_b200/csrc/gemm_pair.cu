@@ -36,6 +36,7 @@ constexpr int A_BYTES = BM * BK * 2, W_BYTES = 128 * BK * 2, STAGE_BYTES = A_BYT
 constexpr int STAGES = 6;
 constexpr int THREADS = 192;           // warp 0 producer, warp 1 MMA (first block), warps 2..5 epilogue
 constexpr int TMEM_COLS = 512;
+constexpr int PAIR_MAX_TILES = 65536;   // two counter words per tile at the head of the workspace of streamed products
 constexpr int STAGING_BYTES = 4 * STAGING_WARP_FLOATS * 4;
 constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */ + STAGING_BYTES;
 
@@ -89,7 +90,7 @@ template <typename Tout>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, VecRef bias,
                  int has_bias, Tout* __restrict__ out, int ldo, int accumulate, int M, int N, int K, int swiglu,
-                 int* __restrict__ error_word) {
+                 int stream, float* __restrict__ partials, int* __restrict__ counters, int* __restrict__ error_word) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzled tiles want 1024-byte alignment
     uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
@@ -102,6 +103,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     auto acc_empty_bar = [&](int b) { return bars + 8u * (2 * STAGES + 2 + b); };
     uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(aligned + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 4));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+    volatile int* parts_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 2);
     float* staging = reinterpret_cast<float*>(aligned + STAGES * STAGE_BYTES + 256);     // behind the barriers
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -110,6 +112,42 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int tiles_m = (M + PAIR_M - 1) / PAIR_M, tiles_n = (N + BN - 1) / BN, tiles = tiles_m * tiles_n;
     const int k_blocks = (K + BK - 1) / BK;
     const int packed_tiles = (N + 127) >> 7;          // 128-row tiles of the packed weight
+    // The work of a pair. Plain: whole tiles, tile = pair, pair + pairs, ... Streamed (stream-K): only the full rounds
+    // of tiles go that way; the tiles of the last, partly filled round are cut up instead: their (tile, k block)
+    // pairs, in tile order, are dealt out as one equal run per pair of blocks, and every pair walks its run FIRST and
+    // its whole tiles after it, so that no SM idles through a round and what the cutting costs (parked partial tiles
+    // and their adding up, in the epilogue warps) lies under the main loops of the whole tiles that follow. Of the
+    // pairs that hold k blocks of one tile, the one with the tile's FIRST k blocks finishes it: that part is the last
+    // of its run, and the others' parts are the first of theirs, so they are parked by the time it asks for them and
+    // nobody who is waited for waits himself. All roles walk the same units with this.
+    const int whole_tiles = stream ? tiles / pairs * pairs : tiles;
+    const long long sk_kb = (long long)(tiles - whole_tiles) * k_blocks;     // streamed (tile, k block) pairs
+    // (fewer of them than pairs of blocks: the first `dealt` take one each, so that no run between two others is empty)
+    const long long dealt = min((long long)pairs, max(sk_kb, 1LL));
+    auto run_start = [&](long long c) { return sk_kb * min(c, dealt) / dealt; };
+    const long long run_lo = run_start(pair), run_hi = run_start(pair + 1);
+    struct Walk {
+        long long at;
+        int i;
+    };
+    auto first_unit = [&]() { return Walk{run_lo, 0}; };
+    auto next_unit = [&](Walk& w, int& tile, int& lo, int& hi) {
+        if (w.at < run_hi) {
+            const int st = (int)(w.at / k_blocks);
+            tile = whole_tiles + st;
+            lo = (int)(w.at - (long long)st * k_blocks);
+            hi = (int)min((long long)k_blocks, lo + (run_hi - w.at));
+            w.at += hi - lo;
+            return true;
+        }
+        const int t = pair + w.i * pairs;
+        if (t >= whole_tiles) return false;
+        tile = t;
+        lo = 0;
+        hi = k_blocks;
+        ++w.i;
+        return true;
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -149,12 +187,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             int s = 0;
             uint32_t parity = 1, dst = base;
             bool ok = true;
-            for (int tile = pair; ok && tile < tiles; tile += pairs) {
+            Walk walk = first_unit();
+            int tile, lo, hi;
+            while (ok && next_unit(walk, tile, lo, hi)) {
                 const int m0 = (tile % tiles_m) * PAIR_M + (int)rank * BM, tn = (tile / tiles_m) * 2;
                 const bool mine = tn + (int)rank < packed_tiles;           // this block's half of the W rows exists
                 const uint32_t tx = 2 * A_BYTES + (tn + 1 < packed_tiles ? 2 : 1) * W_BYTES;     // both blocks' bytes
-                int wy = (tn + (int)rank) * k_blocks * 128;                // row of the packed weight's first k block
-                for (int kb = 0; kb < k_blocks; ++kb, wy += 128) {
+                int wy = ((tn + (int)rank) * k_blocks + lo) * 128;         // row of the packed weight's k block
+                for (int kb = lo; kb < hi; ++kb, wy += 128) {
                     if (!mbar_wait(empty_bar(s), parity, abort_flag)) { ok = false; break; }
                     const uint32_t full0 = in_block(full_bar(s), 0);
                     if (rank == 0) mbar_expect_tx(full_bar(s), tx);
@@ -172,19 +212,21 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             uint32_t local_tile = 0, parity = 0, a_addr = base;
             int s = 0;
             bool ok = true;
-            for (int tile = pair; ok && tile < tiles; tile += pairs, ++local_tile) {
+            Walk walk = first_unit();
+            int tile, lo, hi;
+            for (; ok && next_unit(walk, tile, lo, hi); ++local_tile) {
                 const uint32_t buf = local_tile & 1u;
                 if (!mbar_wait(acc_empty_bar(buf), ((local_tile >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
                 tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + buf * BN;
-                for (int kb = 0; kb < k_blocks; ++kb) {
+                for (int kb = lo; kb < hi; ++kb) {
                     if (!mbar_wait(full_bar(s), parity, abort_flag)) { ok = false; break; }
                     tcgen05_fence_after();
                     const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k)
                         mma_pair(tmem_d, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), IDESC,
-                                 (kb > 0 || k > 0) ? 1u : 0u);
+                                 (kb > lo || k > 0) ? 1u : 0u);
                     commit_pair(empty_bar(s));          // both blocks' stage is free when these MMAs have read it
                     a_addr += STAGE_BYTES;
                     if (++s == STAGES) { s = 0; parity ^= 1u; a_addr = base; }
@@ -200,23 +242,94 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         float* my_staging = staging + quad * STAGING_WARP_FLOATS;
         uint32_t local_tile = 0;
         bool ok = true;
-        for (int tile = pair; ok && tile < tiles; tile += pairs, ++local_tile) {
+        Walk walk = first_unit();
+        int tile, k_lo, k_hi;
+        for (; ok && next_unit(walk, tile, k_lo, k_hi); ++local_tile) {
             const int row0 = (tile % tiles_m) * PAIR_M + (int)rank * BM + quad * 32, n0 = (tile / tiles_m) * BN;
             const uint32_t buf = local_tile & 1u;
             if (!mbar_wait(acc_full_bar(buf), (local_tile >> 1) & 1u, abort_flag)) { ok = false; break; }
             tcgen05_fence_after();
             const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quad * 32) << 16);
             const bool whole = ep.rows_whole(row0);
+            auto release = [&]() {         // this warp has read the accumulator
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(in_block(acc_empty_bar(buf), 0));
+            };
+            if (k_lo == 0 && k_hi == k_blocks) {      // the whole tile is this pair's
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(taddr + c0, v);
+                    tmem_ld_wait();
+                    if (n0 + c0 < N) ep.store(v, row0, lane, n0 + c0, whole, my_staging);
+                }
+                release();
+                continue;
+            }
+            // ---- the tile's k blocks are spread over several (consecutive) pairs; a block works with the blocks of
+            // its own rank in them, which hold the same 128 rows ----
+            int* counter = counters + 2 * tile + (int)rank;
+            if (k_lo > 0) {
+                // Not the tile's first k blocks: this is the first unit of the pair's run. Park the part ([block][BN
+                // columns][128 rows]: a warp's 32 rows of one column are 128 contiguous bytes) and count it in.
+                float* mine = partials + (size_t)blockIdx.x * BM * BN + quad * 32 + lane;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(taddr + c0, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) __stcg(mine + (size_t)(c0 + j) * BM, __uint_as_float(v[j]));
+                }
+                release();
+                asm volatile("bar.sync 1, 128;" ::: "memory");           // the four epilogue warps have written
+                if (warp == 2 && lane == 0) {
+                    __threadfence();
+                    atomicAdd(counter, 1);
+                }
+                continue;
+            }
+            // The tile's first k blocks, the last unit of this pair's run: wait (bounded) until the pairs after this
+            // one have parked theirs, add them to the accumulator in k order (so the sum does not depend on who was
+            // when) and finish the tile. All blocks of the grid are resident.
+            const long long tile_last_kb = (long long)(tile - whole_tiles + 1) * k_blocks - 1;
+            const int others = (int)(((tile_last_kb + 1) * dealt + sk_kb - 1) / sk_kb - 1) - pair;
+            if (warp == 2 && lane == 0) {
+                int seen = 0;
+                for (uint32_t tries = 0; seen < others && tries < SPIN_LIMIT; ++tries) {
+                    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+                    if (seen < others) {
+                        if ((tries & 255u) == 255u && *abort_flag) break;
+                        __nanosleep(32);
+                    }
+                }
+                if (seen >= others) *counter = 0;                     // back to zero for the next product
+                *parts_flag = seen >= others;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (!*parts_flag) { ok = false; break; }
+            const float* theirs = partials + (size_t)(blockIdx.x + 2) * BM * BN + quad * 32 + lane;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t v[32];
                 tmem_ld_32x32b_x32(taddr + c0, v);
+                float x[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) x[j] = __ldcg(theirs + (size_t)(c0 + j) * BM);
                 tmem_ld_wait();
+                for (int p = 1;; ++p) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + x[j]);
+                    if (p >= others) break;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) x[j] = __ldcg(theirs + (size_t)(2 * p) * BM * BN + (size_t)(c0 + j) * BM);
+                }
                 if (n0 + c0 < N) ep.store(v, row0, lane, n0 + c0, whole, my_staging);
             }
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(in_block(acc_empty_bar(buf), 0));
+            release();
+            // (the next unit's wait on another flag value cannot pass a warp that has not read this one yet)
+            asm volatile("bar.sync 1, 128;" ::: "memory");
         }
         if (!ok && lane == 0) give_up(23);
     }
@@ -307,7 +420,8 @@ JLLM_EXPORT int jllm_gemm_pair_fits(const void* a, int lda, const void* w_packed
 // w: ops.pack_weight of the [N, K] weight (k_blocks_packed = ceil(K / 64) its k blocks).
 JLLM_EXPORT int jllm_gemm_pair(const void* a, int lda, const void* w, int k_blocks_packed, const void* bias, int bias_dtype,
                                void* out, int out_dtype, int ldo, int accumulate, int M, int N, int K, int max_pairs,
-                               int swiglu, cudaStream_t stream) {
+                               int swiglu, float* workspace, long long workspace_floats, int stream_mode,
+                               cudaStream_t stream) {
     JLLM_REQUIRE(jllm_gemm_pair_fits(a, lda, w, M, N, K),
                  "gemm_pair: needs K %% 8 == 0 and 16-byte aligned rows (M=%d N=%d K=%d lda=%d)", M, N, K, lda);
     JLLM_REQUIRE(k_blocks_packed == (K + BK - 1) / BK, "gemm_pair: the packed weight has %d k blocks, K=%d needs %d",
@@ -329,13 +443,31 @@ JLLM_EXPORT int jllm_gemm_pair(const void* a, int lda, const void* w, int k_bloc
     JLLM_REQUIRE(pairs >= 1, "gemm_pair: the device runs no cluster of two blocks with %zu bytes of shared memory", SMEM_BYTES);
     if (pairs > tiles) pairs = tiles;
     if (max_pairs > 0 && pairs > max_pairs) pairs = max_pairs;
+    // stream_mode 1: the tiles of a last, partly filled round are cut up over all pairs (stream-K). Not the default: what
+    // an idle pair in the last round loses, the busy ones win back (they share one memory system and one power limit).
+    // The O product of 2,048 rows (128 tiles on 74 pairs), a pair's main loops by the device's clock: plain 21.0 us for
+    // its first tile, 18.6 us for its second, which only 54 pairs have; streamed 17.5 us for 0.73 of a tile, then
+    // 20.2 us for a whole one; 50 us against 48 to 56 us in all. The workspace holds two counters per tile (zero
+    // before the first product, left zero by every product) and one parked partial tile per block.
+    const long long need = 2LL * PAIR_MAX_TILES + 2LL * pairs * BM * BN;
+    int streamed = 0;
+    if (stream_mode == 1) {
+        const bool room = workspace != nullptr && workspace_floats >= need && tiles <= PAIR_MAX_TILES;
+        JLLM_REQUIRE(room, "gemm_pair: a streamed product of %d tiles on %d pairs needs a workspace of %lld floats (got "
+                           "%lld) and at most %d tiles", tiles, pairs, need, workspace_floats, PAIR_MAX_TILES);
+        streamed = 1;
+    }
+    int* counters = reinterpret_cast<int*>(workspace);
+    float* partials = workspace ? workspace + 2 * PAIR_MAX_TILES : nullptr;
     const VecRef b{bias, bias_dtype};
     if (out_dtype == JLLM_F32) {
         jllm_launch(gemm_pair_kernel<float>, dim3(2 * pairs), dim3(THREADS), SMEM_BYTES, stream, true, map_a, map_w, b,
-                    (int)(bias != nullptr), (float*)out, ldo, accumulate, M, N, K, swiglu, error_word);
+                    (int)(bias != nullptr), (float*)out, ldo, accumulate, M, N, K, swiglu, streamed, partials, counters,
+                    error_word);
     } else {
         jllm_launch(gemm_pair_kernel<__nv_bfloat16>, dim3(2 * pairs), dim3(THREADS), SMEM_BYTES, stream, true, map_a, map_w,
-                    b, (int)(bias != nullptr), (__nv_bfloat16*)out, ldo, accumulate, M, N, K, swiglu, error_word);
+                    b, (int)(bias != nullptr), (__nv_bfloat16*)out, ldo, accumulate, M, N, K, swiglu, streamed, partials,
+                    counters, error_word);
     }
     return jllm_check_launch("gemm_pair");
 }

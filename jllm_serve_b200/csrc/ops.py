@@ -136,7 +136,7 @@ class _Signatures:
     jllm_gemm_plain = [P, I, I, P, I, P, I, P, I, I, I, I, I, I, P]
     jllm_gemm_small_m = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, P]
     jllm_gemm_tcgen05 = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, I, P, ctypes.c_longlong, I, I, P]
-    jllm_gemm_pair = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, I, P]
+    jllm_gemm_pair = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, I, P, ctypes.c_longlong, I, P]
     jllm_gemm_pair_resident = []
     jllm_gemm_stream = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, P, ctypes.c_longlong, I, P]
     jllm_gemm_tcgen05_error = []
@@ -148,6 +148,7 @@ class _Signatures:
     jllm_attention_prefill_tc = [P, I, P, P, ctypes.c_longlong, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P]
     jllm_attention_prefill_tc_error = []
     jllm_attention_prefill_pair = [P, I, P, P, ctypes.c_longlong, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P]
+    jllm_attention_decode_separate_combine = [I]
     jllm_argmax = [P, I, I, I, P, P]
     jllm_sample = [P, I, I, I, P, P, P, P, P, P, P]
 
@@ -261,6 +262,7 @@ _workspaces = {}
 # counters of up to 65,536 tiles, then one parked 128 x 256 partial tile for each of up to 160 blocks
 STREAM_WORKSPACE_FLOATS = 65536 + 160 * 128 * 256
 SWAP_WORKSPACE_FLOATS = 2 * 65536 + 160 * 2 * 128 * 128       # gemm_stream: two counters per tile, then the parts
+PAIR_WORKSPACE_FLOATS = 2 * 65536 + 160 * 128 * 256           # gemm_pair: two counters per tile, a part per block
 
 
 def gemm_workspace(key, floats: int = 8 << 20) -> torch.Tensor:
@@ -333,14 +335,18 @@ def gemm_tcgen05(a, w, out, bias=None, accumulate=False, max_blocks: int = 0, sw
           ws.numel() if ws is not None else 0, int(stream_mode), int(tile_width), _stream())
 
 
-def gemm_pair(a, w, out, bias=None, accumulate=False, swiglu=False, max_pairs: int = 0) -> None:
+def gemm_pair(a, w, out, bias=None, accumulate=False, swiglu=False, max_pairs: int = 0, stream_mode: int = 0) -> None:
     """The product of a prefill with many rows: two SMs to a 256 x 256 tile (tcgen05 cta_group::2), each bringing half of
-    the tile's rows of A and of W; epilogues as `gemm_tcgen05`."""
+    the tile's rows of A and of W; epilogues as `gemm_tcgen05`. `stream_mode` 1: the tiles of a last, partly filled
+    round are cut up over all pairs (stream-K: equal runs of (tile, k block) pairs, walked before the whole tiles; partial
+    tiles meet in a workspace); not the default (the busy pairs win back what the idle ones of a last round lose)."""
     w = _packed(w)
     assert a.dtype == torch.bfloat16 and out.stride(-1) == 1 and a.shape[1] == w.cols
+    ws = gemm_workspace((a.device, "pair"), PAIR_WORKSPACE_FLOATS) if stream_mode == 1 else None
     _call("jllm_gemm_pair", a.data_ptr(), a.stride(0), w.data.data_ptr(), w.k_blocks, _p(bias),
           _DT[bias.dtype] if bias is not None else F32, out.data_ptr(), _DT[out.dtype], out.stride(0),
-          int(accumulate), a.shape[0], w.rows, w.cols, int(max_pairs), int(swiglu), _stream())
+          int(accumulate), a.shape[0], w.rows, w.cols, int(max_pairs), int(swiglu), _p(ws),
+          ws.numel() if ws is not None else 0, int(stream_mode), _stream())
 
 
 _resident_pairs = None
@@ -468,6 +474,12 @@ def check_kernel_errors() -> None:
         if caught:
             raise KernelError("out of bounds (the accesses were skipped): " + "; ".join(
                 f"{name}: {what} {index} with limit {limit}, {n} in all" for name, (what, index, limit, n) in caught.items()))
+
+
+def attention_decode_separate_combine(on: bool) -> None:
+    """A test's switch: the partial results of split or dealt-out decode attention are added up by a combine kernel of
+    their own (as where the library's pair counters do not reach) instead of by the last block of every pair."""
+    library().jllm_attention_decode_separate_combine(int(bool(on)))
 
 
 def gemm_tcgen05_starve_next() -> None:

@@ -204,16 +204,25 @@ def test_gemm_pair(ops, M, N, K):
     base = rnd(M, N, seed=3)
     for pairs in (3, 0):
         acc = base.clone()
-        ops.gemm_pair(a, w, acc, None, accumulate=True, max_pairs=pairs)
+        ops.gemm_pair(a, w, acc, None, accumulate=True, max_pairs=pairs, stream_mode=2)
         assert torch.allclose(acc.cpu(), gemm_want(a, w, None, base), rtol=1e-4, atol=tol)
+    # streamed: the tiles of the last round are cut up over the pairs, whose parts are added in k order (the same bits twice)
+    for pairs in (3, 5, 0):
+        one, two = base.clone(), base.clone()
+        ops.gemm_pair(a, w, one, None, accumulate=True, max_pairs=pairs, stream_mode=1)
+        ops.gemm_pair(a, w, two, None, accumulate=True, max_pairs=pairs, stream_mode=1)
+        assert torch.allclose(one.cpu(), gemm_want(a, w, None, base), rtol=1e-4, atol=tol) and torch.equal(one, two)
     out16 = torch.zeros(M, N + 8, dtype=torch.bfloat16, device=DEV)
-    ops.gemm_pair(a, w, out16[:, :N])
-    assert torch.allclose(out16[:, :N].float().cpu(), gemm_want(a, w), rtol=2 ** -7, atol=2e-3)
-    assert float(out16[:, N:].abs().max()) == 0
+    for mode in (2, 1):
+        out16[:, :N].fill_(float("nan"))
+        ops.gemm_pair(a, w, out16[:, :N], stream_mode=mode, max_pairs=7 if mode == 1 else 0)
+        assert torch.allclose(out16[:, :N].float().cpu(), gemm_want(a, w), rtol=2 ** -7, atol=2e-3)
+        assert float(out16[:, N:].abs().max()) == 0
     # the same bits as the one-SM kernel: the same products summed in the same order, k block by k block
-    single = torch.empty(M, N, device=DEV)
+    single, again = torch.empty(M, N, device=DEV), torch.empty(M, N, device=DEV)
     ops.gemm_tcgen05(a, w, single, bias)
-    assert torch.equal(single, out)
+    ops.gemm_pair(a, w, again, bias, stream_mode=2)
+    assert torch.equal(single, again)
     if N % 16 == 0:
         hidden = N // 2
         g = gemm_want(a, w.view(hidden // 8, 2, 8, K)[:, 0].reshape(hidden, K))
@@ -459,6 +468,18 @@ def test_attention_decode(ops, H, Hkv, hd, page, window, splits):
         ops.attention_decode(q1, kc, vc, out1, rseg1, rpos1, tables, len(lens), H, Hkv, hd, page, window, scale, splits,
                              scratch)
         rows_close(out1, want1, f"decode splits {splits} {far}")
+        # the partials added up by the last block of every pair (head sizes 64, 128, 256) or by a kernel of their own:
+        # the same bits; and again, with the counters that the first launch must have left at zero
+        again, apart = torch.full_like(q1, float("nan")), torch.full_like(q1, float("nan"))
+        ops.attention_decode(q1, kc, vc, again, rseg1, rpos1, tables, len(lens), H, Hkv, hd, page, window, scale, splits,
+                             scratch)
+        ops.attention_decode_separate_combine(True)
+        try:
+            ops.attention_decode(q1, kc, vc, apart, rseg1, rpos1, tables, len(lens), H, Hkv, hd, page, window, scale,
+                                 splits, scratch)
+        finally:
+            ops.attention_decode_separate_combine(False)
+        assert torch.equal(out1, again) and torch.equal(out1, apart)
 
 
 @pytest.mark.parametrize("blocks", [1, 7, 40, 296])
@@ -480,6 +501,16 @@ def test_attention_decode_dealt_out_evenly(ops, H, Hkv, hd, page, window, blocks
         ops.attention_decode_flat(q1, kc, vc, out1, rseg1, rpos1, tables, len(lens), H, Hkv, hd, page, window, scale,
                                   blocks, scratch)
         rows_close(out1, want1, f"decode dealt out over {blocks} blocks {far}")
+        again, apart = torch.full_like(q1, float("nan")), torch.full_like(q1, float("nan"))
+        ops.attention_decode_flat(q1, kc, vc, again, rseg1, rpos1, tables, len(lens), H, Hkv, hd, page, window, scale,
+                                  blocks, scratch)
+        ops.attention_decode_separate_combine(True)
+        try:
+            ops.attention_decode_flat(q1, kc, vc, apart, rseg1, rpos1, tables, len(lens), H, Hkv, hd, page, window, scale,
+                                      blocks, scratch)
+        finally:
+            ops.attention_decode_separate_combine(False)
+        assert torch.equal(out1, again) and torch.equal(out1, apart)
 
 
 def test_attention_decode_dealt_out_evenly_random_shapes(ops):
