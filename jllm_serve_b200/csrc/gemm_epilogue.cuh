@@ -8,12 +8,58 @@ namespace tc {
 
 constexpr int STAGING_ROW = 36;        // floats of a staged row of 32 values: 16-byte aligned, and rows fall in other banks
 constexpr int STAGING_WARP_FLOATS = 32 * STAGING_ROW;      // shared memory a warp needs for `staged`
+constexpr int BULK_WARP_BYTES = 32 * 32 * 4;                // ... and for `bulk`: a 32 x 32 block, 1024-byte aligned
 
 template <typename Tout>
 struct TileEpilogue {
     Tout* out;
     int ldo, M, N, accumulate, has_bias, swiglu;
     VecRef bias;
+    // not null: a float32 output written (or added into) by tiled bulk copies of 32 x 32 blocks from shared memory,
+    // which the copy engine clips to [M, N]; the residual add is then done where the data lies (in L2), the SM neither
+    // loads the old values nor waits for them
+    const CUtensorMap* out_map;
+
+    // The warp's 32 x 32 block leaves through shared memory by one bulk copy: rows of 128 bytes whose 16-byte chunk c
+    // lies at chunk position c ^ (row & 7) (the 128-byte swizzle of the output's tensor map: a quarter warp's 16-byte
+    // stores fall into eight different chunks). `stage`: the warp's 4 KB of shared memory, 1024-byte aligned. The
+    // copy before this one must have read the buffer; `bulk_done` waits for the last ones to be written.
+    __device__ __forceinline__ void bulk(uint32_t (&v)[32], int row0, int lane, int n_base, uint32_t stage) const {
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        __syncwarp();
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            float4 x = make_float4(__uint_as_float(v[4 * c]), __uint_as_float(v[4 * c + 1]), __uint_as_float(v[4 * c + 2]),
+                                   __uint_as_float(v[4 * c + 3]));
+            if (has_bias) {      // (columns beyond N are clipped by the copy; the bias is not read there)
+                const int n = n_base + 4 * c;
+                if (n < N) x.x += bias[n];
+                if (n + 1 < N) x.y += bias[n + 1];
+                if (n + 2 < N) x.z += bias[n + 2];
+                if (n + 3 < N) x.w += bias[n + 3];
+            }
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(stage + lane * 128 + ((c ^ (lane & 7)) << 4)),
+                         "f"(x.x), "f"(x.y), "f"(x.z), "f"(x.w)
+                         : "memory");
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+            if (accumulate)
+                asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
+                             ::"l"(out_map), "r"(stage), "r"(n_base), "r"(row0)
+                             : "memory");
+            else
+                asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                             ::"l"(out_map), "r"(stage), "r"(n_base), "r"(row0)
+                             : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+    }
+    // before the kernel ends: this warp's bulk copies have been written
+    __device__ __forceinline__ void bulk_done(int lane) const {
+        if (out_map != nullptr && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    }
 
     // All 32 rows of the warp lie inside the matrix and float32 rows can be accessed 16 bytes at a time: the block goes
     // through shared memory (`staged`).
@@ -52,10 +98,13 @@ struct TileEpilogue {
         __syncwarp();
     }
 
-    // v: columns [n_base, n_base + 32) of row row0 + lane. `whole` = rows_whole(row0); `mine`: the warp's staging.
+    // v: columns [n_base, n_base + 32) of row row0 + lane. `whole` = rows_whole(row0); `mine`: the warp's staging
+    // (STAGING_WARP_FLOATS floats, or BULK_WARP_BYTES aligned to 1024 bytes with an output map).
     __device__ __forceinline__ void store(uint32_t (&v)[32], int row0, int lane, int n_base, bool whole, float* mine) const {
         const int row = row0 + lane;
-        if (whole && n_base + 32 <= N) {
+        if (out_map != nullptr) {
+            if (row0 < M && n_base < N) bulk(v, row0, lane, n_base, smem_u32(mine));
+        } else if (whole && n_base + 32 <= N) {
             staged(v, row0, lane, n_base, mine);
         } else if (row < M && swiglu) {
             // columns come in blocks of 16: 8 gate columns, then the 8 up columns of the same hidden units

@@ -88,23 +88,25 @@ __device__ __forceinline__ void commit_pair(uint32_t bar) {
 
 template <typename Tout>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
-gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, VecRef bias,
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                 const __grid_constant__ CUtensorMap map_out, int bulk_out, VecRef bias,
                  int has_bias, Tout* __restrict__ out, int ldo, int accumulate, int M, int N, int K, int swiglu,
                  int stream, float* __restrict__ partials, int* __restrict__ counters, int* __restrict__ error_word) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzled tiles want 1024-byte alignment
     uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t bars = base + STAGES * STAGE_BYTES;
+    // the stages, the epilogue's staging (1024-byte aligned, as the stages are), the barriers
+    const uint32_t bars = base + STAGES * STAGE_BYTES + STAGING_BYTES;
     // barriers: full[STAGES] (the first block's are used), empty[STAGES] (each block its own), acc_full[2] (each its
     // own), acc_empty[2] (the first block's); then the TMEM base and the abort flag
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
     auto acc_full_bar = [&](int b) { return bars + 8u * (2 * STAGES + b); };
     auto acc_empty_bar = [&](int b) { return bars + 8u * (2 * STAGES + 2 + b); };
-    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(aligned + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 4));
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(aligned + STAGES * STAGE_BYTES + STAGING_BYTES + 8 * (2 * STAGES + 4));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
     volatile int* parts_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 2);
-    float* staging = reinterpret_cast<float*>(aligned + STAGES * STAGE_BYTES + 256);     // behind the barriers
+    uint8_t* staging = aligned + STAGES * STAGE_BYTES;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_rank();             // 0: the pair's first block, which issues the MMAs
@@ -238,8 +240,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     } else {
         // ---------------- epilogue: warps 2..5 of both blocks, TMEM lanes 32 * (warp % 4) ----------------
         const int quad = warp & 3;
-        const TileEpilogue<Tout> ep{out, ldo, M, N, accumulate, has_bias, swiglu, bias};
-        float* my_staging = staging + quad * STAGING_WARP_FLOATS;
+        const TileEpilogue<Tout> ep{out, ldo, M, N, accumulate, has_bias, swiglu, bias, bulk_out ? &map_out : nullptr};
+        float* my_staging = reinterpret_cast<float*>(staging + quad * (bulk_out ? BULK_WARP_BYTES : STAGING_WARP_FLOATS * 4));
         uint32_t local_tile = 0;
         bool ok = true;
         Walk walk = first_unit();
@@ -331,6 +333,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             // (the next unit's wait on another flag value cannot pass a warp that has not read this one yet)
             asm volatile("bar.sync 1, 128;" ::: "memory");
         }
+        ep.bulk_done(lane);
         if (!ok && lane == 0) give_up(23);
     }
     tcgen05_fence_before();
@@ -411,6 +414,7 @@ int resident_pairs() {
 }  // namespace
 
 int* jllm_gemm_error_word();
+extern int g_plain_stores;
 
 JLLM_EXPORT int jllm_gemm_pair_fits(const void* a, int lda, const void* w_packed, int M, int N, int K) {
     return M >= 1 && N >= 1 && K >= 8 && K % 8 == 0 && lda % 8 == 0 && ((uintptr_t)a % 16) == 0 &&
@@ -436,6 +440,12 @@ JLLM_EXPORT int jllm_gemm_pair(const void* a, int lda, const void* w, int k_bloc
     if (rc != JLLM_OK) return rc;
     rc = packed_map_for(w, packed_rows, &map_w);
     if (rc != JLLM_OK) return rc;
+    CUtensorMap map_out = {};
+    const int bulk_out = out_dtype == JLLM_F32 && !swiglu && ldo % 4 == 0 && ((uintptr_t)out % 16) == 0 && !g_plain_stores;
+    if (bulk_out) {
+        rc = tensor_map_out_f32(out, M, N, ldo, &map_out);
+        if (rc != JLLM_OK) return rc;
+    }
     int* error_word = jllm_gemm_error_word();
     if (!error_word) return jllm_fail(JLLM_CUDA_ERROR, "gemm_pair: no error word");
     const int tiles = ((M + PAIR_M - 1) / PAIR_M) * ((N + BN - 1) / BN);
@@ -461,12 +471,13 @@ JLLM_EXPORT int jllm_gemm_pair(const void* a, int lda, const void* w, int k_bloc
     float* partials = workspace ? workspace + 2 * PAIR_MAX_TILES : nullptr;
     const VecRef b{bias, bias_dtype};
     if (out_dtype == JLLM_F32) {
-        jllm_launch(gemm_pair_kernel<float>, dim3(2 * pairs), dim3(THREADS), SMEM_BYTES, stream, true, map_a, map_w, b,
+        jllm_launch(gemm_pair_kernel<float>, dim3(2 * pairs), dim3(THREADS), SMEM_BYTES, stream, true, map_a, map_w, map_out,
+                    bulk_out, b,
                     (int)(bias != nullptr), (float*)out, ldo, accumulate, M, N, K, swiglu, streamed, partials, counters,
                     error_word);
     } else {
         jllm_launch(gemm_pair_kernel<__nv_bfloat16>, dim3(2 * pairs), dim3(THREADS), SMEM_BYTES, stream, true, map_a, map_w,
-                    b, (int)(bias != nullptr), (__nv_bfloat16*)out, ldo, accumulate, M, N, K, swiglu, streamed, partials,
+                    map_out, 0, b, (int)(bias != nullptr), (__nv_bfloat16*)out, ldo, accumulate, M, N, K, swiglu, streamed, partials,
                     counters, error_word);
     }
     return jllm_check_launch("gemm_pair");

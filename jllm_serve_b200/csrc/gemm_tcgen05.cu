@@ -50,7 +50,8 @@ __host__ __device__ constexpr uint32_t idesc_for(int bn) {
 
 template <typename Tout, int BN>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __nv_bfloat16* __restrict__ w_packed, VecRef bias,
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_out, int bulk_out,
+                    const __nv_bfloat16* __restrict__ w_packed, VecRef bias,
                     int has_bias, Tout* __restrict__ out, int ldo, int accumulate, int M, int N, int K, int swiglu,
                     int stream, float* __restrict__ partials, int* __restrict__ counters, int* __restrict__ error_word,
                     int starve) {
@@ -63,16 +64,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __nv_bfloat
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzled tiles want 1024-byte alignment
     uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t bars = base + STAGES * STAGE_BYTES;
+    // the stages, the epilogue's staging (1024-byte aligned, as the stages are), the barriers
+    const uint32_t bars = base + STAGES * STAGE_BYTES + STAGING_BYTES;
     // barriers: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]; then the TMEM base and the abort flag
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
     auto acc_full_bar = [&](int b) { return bars + 8u * (2 * STAGES + b); };
     auto acc_empty_bar = [&](int b) { return bars + 8u * (2 * STAGES + 2 + b); };
-    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(aligned + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 4));
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(aligned + STAGES * STAGE_BYTES + STAGING_BYTES + 8 * (2 * STAGES + 4));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
     volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 2);
-    float* staging = reinterpret_cast<float*>(aligned + STAGES * STAGE_BYTES + 256);     // behind the barriers
+    uint8_t* staging = aligned + STAGES * STAGE_BYTES;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN, tiles = tiles_m * tiles_n;
@@ -213,7 +215,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __nv_bfloat
     } else {
         // ---------------- epilogue: warps 2..5, TMEM lanes 32 * (warp % 4) ----------------
         const int quad = warp & 3;
-        const TileEpilogue<Tout> ep{out, ldo, M, N, accumulate, has_bias, swiglu, bias};
+        const TileEpilogue<Tout> ep{out, ldo, M, N, accumulate, has_bias, swiglu, bias, bulk_out ? &map_out : nullptr};
         uint32_t local_tile = 0;
         bool ok = true;
         Walk walk = first_unit();
@@ -227,7 +229,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __nv_bfloat
             // bias / residual / SwiGLU and the store of 32 columns of this thread's row
             const int row0 = m0 + quad * 32;
             const bool whole = ep.rows_whole(row0);
-            float* my_staging = staging + quad * STAGING_WARP_FLOATS;
+            float* my_staging = reinterpret_cast<float*>(staging + quad * (bulk_out ? BULK_WARP_BYTES : STAGING_WARP_FLOATS * 4));
             auto finalize = [&](uint32_t (&v)[32], int c0) { ep.store(v, row0, lane, n0 + c0, whole, my_staging); };
             if (k_lo == 0 && k_hi == k_blocks) {      // the whole tile is this block's
 #pragma unroll 1
@@ -306,6 +308,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __nv_bfloat
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty_bar(buf));
         }
+        ep.bulk_done(lane);
         if (!ok && lane == 0) { *abort_flag = 1; atomicExch(error_word, 3); }
     }
     tcgen05_fence_before();
@@ -361,6 +364,11 @@ thread_local int g_starve_next = 0;
 }
 JLLM_EXPORT void jllm_gemm_tcgen05_starve_next() { g_starve_next = 1; }
 
+// A test's switch: float32 outputs are stored (and added into) by the epilogue warps' own loads and stores, as where
+// the output's rows allow no tensor map, instead of by bulk copies. For the paired product too.
+int g_plain_stores = 0;
+JLLM_EXPORT void jllm_gemm_plain_stores(int on) { g_plain_stores = on; }
+
 // w: ops.pack_weight of the [N, K] weight (k_blocks_packed = ceil(K / 64) its k blocks).
 JLLM_EXPORT int jllm_gemm_tcgen05(const void* a, int lda, const void* w, int k_blocks_packed, const void* bias, int bias_dtype,
                                   void* out, int out_dtype, int ldo, int accumulate, int M, int N, int K, int max_blocks,
@@ -391,6 +399,13 @@ JLLM_EXPORT int jllm_gemm_tcgen05(const void* a, int lda, const void* w, int k_b
     CUtensorMap map_a;
     int rc = tensor_map_for(a, M, K, lda, BM, &map_a);
     if (rc != JLLM_OK) return rc;
+    // a float32 output leaves by tiled bulk copies (the residual add as a reduce in L2) where its rows allow a tensor map
+    CUtensorMap map_out = {};
+    const int bulk_out = out_dtype == JLLM_F32 && !swiglu && ldo % 4 == 0 && ((uintptr_t)out % 16) == 0 && !g_plain_stores;
+    if (bulk_out) {
+        rc = tensor_map_out_f32(out, M, N, ldo, &map_out);
+        if (rc != JLLM_OK) return rc;
+    }
     int* error_word = error_word_for_device();
     if (!error_word) return jllm_fail(JLLM_CUDA_ERROR, "gemm_tcgen05: no error word");
     const int tiles = tiles_m * ((N + BN - 1) / BN);
@@ -426,7 +441,8 @@ JLLM_EXPORT int jllm_gemm_tcgen05(const void* a, int lda, const void* w, int k_b
     do {                                                                                                              \
         auto kern = gemm_tcgen05_kernel<T, W>;                                                                        \
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes_for(W));             \
-        jllm_launch(kern, dim3(grid), dim3(THREADS), smem_bytes_for(W), stream, true, map_a, (const __nv_bfloat16*)w, b, \
+        jllm_launch(kern, dim3(grid), dim3(THREADS), smem_bytes_for(W), stream, true, map_a, map_out, bulk_out,        \
+                    (const __nv_bfloat16*)w, b,                                                                      \
                     (int)(bias != nullptr), (T*)out, ldo, accumulate, M, N, K, swiglu, splits, partials, counters,    \
                     error_word, starve);                                                                              \
     } while (0)

@@ -138,6 +138,7 @@ class _Signatures:
     jllm_gemm_tcgen05 = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, I, P, ctypes.c_longlong, I, I, P]
     jllm_gemm_pair = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, I, P, ctypes.c_longlong, I, P]
     jllm_gemm_pair_resident = []
+    jllm_gemm_plain_stores = [I]
     jllm_gemm_stream = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, P, ctypes.c_longlong, I, P]
     jllm_gemm_tcgen05_error = []
     jllm_gemm_tcgen05_starve_next = []
@@ -474,6 +475,12 @@ def check_kernel_errors() -> None:
         if caught:
             raise KernelError("out of bounds (the accesses were skipped): " + "; ".join(
                 f"{name}: {what} {index} with limit {limit}, {n} in all" for name, (what, index, limit, n) in caught.items()))
+
+
+def gemm_plain_stores(on: bool) -> None:
+    """A test's switch: the tcgen05 products store float32 outputs (and add into them) with the epilogue warps' own loads
+    and stores, as where the output's rows allow no tensor map, instead of by tiled bulk copies."""
+    library().jllm_gemm_plain_stores(int(bool(on)))
 
 
 def attention_decode_separate_combine(on: bool) -> None:

@@ -203,5 +203,35 @@ inline int tensor_map_for(const void* ptr, long long rows, long long cols, long 
     return JLLM_OK;
 }
 
+// A [rows, cols] float32 matrix with row stride ld, written (or added into) in boxes of 32 x 32 with the 128-byte swizzle.
+inline int tensor_map_out_f32(const void* ptr, long long rows, long long cols, long long ld, CUtensorMap* out) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    const MapKey key{ptr, rows, cols, ld, 32};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = it->second;
+        return JLLM_OK;
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return jllm_fail(JLLM_CUDA_ERROR, "gemm: the driver does not offer cuTensorMapEncodeTiled");
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+    const cuuint32_t box[2] = {32, 32};
+    const cuuint32_t elem[2] = {1, 1};
+    CUtensorMap map;
+    const CUresult r = fn(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return jllm_fail(JLLM_CUDA_ERROR, "gemm: cuTensorMapEncodeTiled failed (%d) for a float32 output [%lld, %lld] ld %lld",
+                         (int)r, rows, cols, ld);
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, map);
+    *out = map;
+    return JLLM_OK;
+}
+
 
 }  // namespace tc

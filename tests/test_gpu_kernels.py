@@ -233,6 +233,42 @@ def test_gemm_pair(ops, M, N, K):
     assert ops.gemm_tcgen05_error() == 0
 
 
+@pytest.mark.parametrize("kernel", ["tiles", "pair"])
+@pytest.mark.parametrize("M,N,K", [(300, 1000, 200), (2048, 4096, 512), (129, 260, 136), (31, 36, 64), (513, 7936, 72)])
+def test_gemm_float32_output_by_bulk_copies(ops, M, N, K, kernel):
+    """A float32 output whose rows allow a tensor map leaves the tcgen05 products by tiled bulk copies of 32 x 32 blocks
+    (the residual add as a reduce where the data lies): the same bits as the epilogue warps' own loads and stores, for
+    the product with a bias and for the add, into a view that starts 16 bytes into wider rows; what lies beside the
+    view, and beyond M and N inside the last blocks, is left alone."""
+    if kernel == "pair" and ops.resident_pairs() < 1:
+        pytest.skip("the device runs no pair of blocks of this kernel")
+    go = ops.gemm_pair if kernel == "pair" else ops.gemm_tcgen05
+    a, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=1, scale=0.05)
+    bias = rnd(N, dtype=torch.bfloat16, seed=2)
+    tol = 1e-4 * math.sqrt(K) * 0.05
+    base = rnd(M + 3, N + 12, seed=3)
+    results = {}
+    for plain in (False, True):
+        ops.gemm_plain_stores(plain)
+        try:
+            wide = base.clone()
+            view = wide[:M, 4:4 + N]
+            go(a, w, view, bias)
+            fresh = view.clone()
+            go(a, w, view, None, accumulate=True)
+            results[plain] = (fresh, view.clone(), wide)
+        finally:
+            ops.gemm_plain_stores(False)
+    fresh, added, wide = results[False]
+    assert ops.gemm_tcgen05_error() == 0
+    assert torch.allclose(fresh.cpu(), gemm_want(a, w, bias), rtol=1e-4, atol=tol)
+    assert torch.allclose(added.cpu(), gemm_want(a, w, None, fresh), rtol=1e-4, atol=tol)
+    assert torch.equal(fresh, results[True][0]) and torch.equal(added, results[True][1])
+    untouched = torch.ones_like(base, dtype=torch.bool)
+    untouched[:M, 4:4 + N] = False
+    assert torch.equal(wide[untouched], base[untouched])
+
+
 @pytest.mark.parametrize("width", [32, 64, 128, 192, 256])
 @pytest.mark.parametrize("M,N,K", [(64, 4096, 4096), (33, 517, 72), (200, 1000, 1032), (128, 24576, 512)])
 def test_gemm_tcgen05_tile_widths(ops, M, N, K, width):
