@@ -295,10 +295,12 @@ JLLM_EXPORT long long jllm_attention_decode_scratch_floats(int rows, int heads, 
     return splits <= 1 ? 0 : (long long)rows * heads * splits * (head_dim + 2);
 }
 
-JLLM_EXPORT int jllm_attention_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
-                                      int out_stride, const int* row_seg, const int* row_pos, const int* block_tables,
-                                      int table_stride, int rows, int heads, int kv_heads, int head_dim, int page_size,
-                                      int window, float scale, int splits, float* scratch, cudaStream_t stream) {
+namespace {
+
+int decode_split(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out, int out_stride,
+                 const int* row_seg, const int* row_pos, const int* block_tables, int table_stride, int rows, int heads,
+                 int kv_heads, int head_dim, int page_size, int window, float scale, int splits, float* scratch,
+                 const staged::Fresh& fresh, cudaStream_t stream) {
     JLLM_REQUIRE(rows >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && page_size > 0,
                  "attention_decode: rows=%d heads=%d kv_heads=%d page_size=%d", rows, heads, kv_heads, page_size);
     JLLM_REQUIRE(head_dim % 16 == 0 && head_dim >= 16 && head_dim <= 256,
@@ -325,7 +327,7 @@ JLLM_EXPORT int jllm_attention_decode(const void* q, int q_stride, const void* k
                             ? staged::pair_counters() : nullptr;
 #define JLLM_STAGED(HD)                                                                                             \
     staged::launch<HD>(q, q_stride, k_cache, v_cache, out, out_stride, row_seg, row_pos, block_tables, table_stride, \
-                       rows, heads, kv_heads, page_size, window, scale_log2, splits, part_o, part_ml, counters, stream)
+                       rows, heads, kv_heads, page_size, window, scale_log2, splits, part_o, part_ml, counters, fresh, stream)
         if (head_dim == 64) JLLM_STAGED(64); else if (head_dim == 128) JLLM_STAGED(128); else JLLM_STAGED(256);
 #undef JLLM_STAGED
         int rc2 = jllm_check_launch("attention_decode_staged");
@@ -334,6 +336,7 @@ JLLM_EXPORT int jllm_attention_decode(const void* q, int q_stride, const void* k
                     (const float*)part_ml, (__nv_bfloat16*)out, out_stride, heads, head_dim, splits);
         return jllm_check_launch("attention_combine");
     }
+    JLLM_REQUIRE(fresh.qkv == nullptr, "attention_decode: head_dim=%d has no kernel that norms and rotates its own row", head_dim);
 #define JLLM_LAUNCH(HDC)                                                                                            \
     {                                                                                                               \
         auto kern = attention_decode_kernel<HDC>;                                                                   \
@@ -353,6 +356,16 @@ JLLM_EXPORT int jllm_attention_decode(const void* q, int q_stride, const void* k
     return jllm_check_launch("attention_combine");
 }
 
+}  // namespace
+
+JLLM_EXPORT int jllm_attention_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
+                                      int out_stride, const int* row_seg, const int* row_pos, const int* block_tables,
+                                      int table_stride, int rows, int heads, int kv_heads, int head_dim, int page_size,
+                                      int window, float scale, int splits, float* scratch, cudaStream_t stream) {
+    return decode_split(q, q_stride, k_cache, v_cache, out, out_stride, row_seg, row_pos, block_tables, table_stride, rows,
+                        heads, kv_heads, head_dim, page_size, window, scale, splits, scratch, staged::Fresh{}, stream);
+}
+
 // Floats of scratch of the evenly dealt variant: (head_dim + 2) per head of a kv head, for every pair and every block.
 JLLM_EXPORT long long jllm_attention_decode_flat_scratch_floats(int rows, int heads, int kv_heads, int head_dim, int blocks) {
     return ((long long)rows * kv_heads + blocks) * (heads / kv_heads) * (head_dim + 2);
@@ -360,10 +373,12 @@ JLLM_EXPORT long long jllm_attention_decode_flat_scratch_floats(int rows, int he
 
 // Decode attention with the key tiles of all (row, kv head) pairs dealt out evenly over `blocks` blocks (head sizes
 // 64, 128, 256; at most 1,024 rows; at most 62 blocks per kv head, so that a pair's tiles fall to at most 64 blocks).
-JLLM_EXPORT int jllm_attention_decode_flat(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
-                                           int out_stride, const int* row_seg, const int* row_pos, const int* block_tables,
-                                           int table_stride, int rows, int heads, int kv_heads, int head_dim, int page_size,
-                                           int window, float scale, int blocks, float* scratch, cudaStream_t stream) {
+namespace {
+
+int decode_flat(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out, int out_stride,
+                const int* row_seg, const int* row_pos, const int* block_tables, int table_stride, int rows, int heads,
+                int kv_heads, int head_dim, int page_size, int window, float scale, int blocks, float* scratch,
+                const staged::Fresh& fresh, cudaStream_t stream) {
     JLLM_REQUIRE(rows >= 0 && rows <= staged::FLAT_MAX_ROWS && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 &&
                      page_size > 0 && heads / kv_heads <= 16,
                  "attention_decode_flat: rows=%d (at most %d) heads=%d kv_heads=%d page_size=%d", rows,
@@ -387,10 +402,54 @@ JLLM_EXPORT int jllm_attention_decode_flat(const void* q, int q_stride, const vo
                             !g_separate_combine ? staged::pair_counters() : nullptr;
 #define JLLM_FLAT(HD)                                                                                                  \
     staged::launch_flat<HD>(q, q_stride, k_cache, v_cache, out, out_stride, row_seg, row_pos, block_tables, table_stride, \
-                            rows, heads, kv_heads, page_size, window, scale_log2, blocks, part_o, part_ml, counters, stream)
+                            rows, heads, kv_heads, page_size, window, scale_log2, blocks, part_o, part_ml, counters, fresh, stream)
     if (head_dim == 64) JLLM_FLAT(64); else if (head_dim == 128) JLLM_FLAT(128); else JLLM_FLAT(256);
 #undef JLLM_FLAT
     return jllm_check_launch("attention_decode_flat");
+}
+
+}  // namespace
+
+JLLM_EXPORT int jllm_attention_decode_flat(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
+                                           int out_stride, const int* row_seg, const int* row_pos, const int* block_tables,
+                                           int table_stride, int rows, int heads, int kv_heads, int head_dim, int page_size,
+                                           int window, float scale, int blocks, float* scratch, cudaStream_t stream) {
+    return decode_flat(q, q_stride, k_cache, v_cache, out, out_stride, row_seg, row_pos, block_tables, table_stride, rows,
+                       heads, kv_heads, head_dim, page_size, window, scale, blocks, scratch, staged::Fresh{}, stream);
+}
+
+// Decode attention that first finishes its own row: `qkv` ([rows, stride]: query, key and value heads side by side) is as
+// the QKV product left it. Every block norms (use_norm) and rotates the queries of its kv head, and the block that holds
+// a row's newest position makes that key and value, writes them to the cache (k_cache, v_cache: written here) and uses
+// them. Head sizes 64, 128, 256, rotated over their whole width (cos_t, sin_t: [positions, head_dim / 2]). `flat` 0: `n`
+// key splits per (row, kv head); 1: the key tiles of all pairs dealt out over `n` blocks. The same bits as
+// jllm_qk_norm_rope_store followed by jllm_attention_decode(_flat).
+JLLM_EXPORT int jllm_attention_decode_fresh(const void* qkv, int qkv_stride, const void* q_gain, const void* k_gain,
+                                            int gain_dtype, int use_norm, float eps, const float* cos_t, const float* sin_t,
+                                            void* k_cache, void* v_cache, void* out, int out_stride, const int* row_seg,
+                                            const int* row_pos, const int* block_tables, int table_stride, int rows,
+                                            int heads, int kv_heads, int head_dim, int page_size, int window, float scale,
+                                            int flat, int n, float* scratch, cudaStream_t stream) {
+    JLLM_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256, "attention_decode_fresh: head_dim=%d is not 64, 128 or 256",
+                 head_dim);
+    JLLM_REQUIRE(qkv != nullptr && cos_t != nullptr && sin_t != nullptr && (!use_norm || (q_gain != nullptr && k_gain != nullptr)),
+                 "attention_decode_fresh: needs qkv, the angle tables and, with the norm, both gains");
+    staged::Fresh fresh{};
+    fresh.qkv = (const __nv_bfloat16*)qkv;
+    fresh.stride = qkv_stride;
+    fresh.use_norm = use_norm;
+    fresh.eps = eps;
+    fresh.q_gain = VecRef{q_gain, gain_dtype};
+    fresh.k_gain = VecRef{k_gain, gain_dtype};
+    fresh.cos_t = cos_t;
+    fresh.sin_t = sin_t;
+    fresh.k_out = (__nv_bfloat16*)k_cache;
+    fresh.v_out = (__nv_bfloat16*)v_cache;
+    if (flat)
+        return decode_flat(qkv, qkv_stride, k_cache, v_cache, out, out_stride, row_seg, row_pos, block_tables, table_stride,
+                           rows, heads, kv_heads, head_dim, page_size, window, scale, n, scratch, fresh, stream);
+    return decode_split(qkv, qkv_stride, k_cache, v_cache, out, out_stride, row_seg, row_pos, block_tables, table_stride,
+                        rows, heads, kv_heads, head_dim, page_size, window, scale, n, scratch, fresh, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------

@@ -10,6 +10,7 @@
 // softmax state; the four are merged at the end exactly as in the direct kernel, and the per-split
 // partials go to the same scratch layout and combine kernel.
 #pragma once
+#include "head_rotate.cuh"
 
 namespace staged {
 
@@ -45,6 +46,50 @@ __device__ __forceinline__ void wait_group() { asm volatile("cp.async.wait_group
 template <int HD>
 __device__ __forceinline__ uint32_t off(int r, int c) { return (uint32_t)((r * (HD / 8) + (c ^ (r & 7))) * 16); }
 
+// What the kernel in front of a FRESH launch left undone: the step's own queries, key and value lie in `qkv` as the QKV
+// product wrote them ([rows, stride]: query heads, key heads, value heads side by side), not yet normed, rotated or
+// written to the cache. The attention then does that work for its own row: every block norms and rotates the G
+// queries of its kv head on their way into shared memory, and the one block whose keys hold the row's newest position
+// makes that key (norm, rotation) and value, writes them to the cache and puts them into its own tile. One launch
+// and its dependent wait less per layer than with a kernel of their own. qkv == nullptr: a plain launch.
+struct Fresh {
+    const __nv_bfloat16* qkv;
+    int stride, use_norm;
+    float eps;
+    VecRef q_gain, k_gain;
+    const float* cos_t;        // [positions, HD / 2]
+    const float* sin_t;
+    __nv_bfloat16* k_out;      // the cache, to be written
+    __nv_bfloat16* v_out;
+};
+
+// a head from global memory into the registers of a warp, as head_norm_rope wants it
+template <int V>
+__device__ __forceinline__ void head_load(const __nv_bfloat16* __restrict__ src, int lane, float (&a)[V], float (&b)[V]) {
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        a[i] = __bfloat162float(src[lane * V + i]);
+        b[i] = __bfloat162float(src[32 * V + lane * V + i]);
+    }
+}
+// ... and back as bfloat16: into row `row` of a swizzled tile in shared memory, and (dst not null) to global memory
+template <int HD>
+__device__ __forceinline__ void head_store(uint8_t* tile, int row, __nv_bfloat16* __restrict__ dst, int lane,
+                                           const float (&a)[HD / 64], const float (&b)[HD / 64]) {
+    constexpr int V = HD / 64, HALF = HD / 2;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        const int e0 = lane * V + i, e1 = HALF + e0;
+        const __nv_bfloat16 v0 = __float2bfloat16_rn(a[i]), v1 = __float2bfloat16_rn(b[i]);
+        *reinterpret_cast<__nv_bfloat16*>(tile + off<HD>(row, e0 >> 3) + (e0 & 7) * 2) = v0;
+        *reinterpret_cast<__nv_bfloat16*>(tile + off<HD>(row, e1 >> 3) + (e1 & 7) * 2) = v1;
+        if (dst != nullptr) {
+            dst[e0] = v0;
+            dst[e1] = v1;
+        }
+    }
+}
+
 // The keys [first + tile_lo * 64, ...) of n_tiles tiles of one (row, kv head), for the G query heads of that kv head:
 // the result goes to `out` if these are all the row's keys (`whole`), else as a partial (sums, maximum, weight) for
 // head j of the group to part_o + j * o_stride and part_ml + j * ml_stride. All threads of the block call it.
@@ -56,7 +101,7 @@ __device__ __forceinline__ void attend(uint8_t* smem_raw, const __nv_bfloat16* _
                                        float scale_log2, int r, int kvh, int P,
                                        int first, int tile_lo, int n_tiles, bool whole, float* __restrict__ part_o,
                                        size_t o_stride, float* __restrict__ part_ml, size_t ml_stride,
-                                       bool early = false) {
+                                       const Fresh& fresh, bool early = false) {
     // `early`: the block has not yet waited for the kernel in front of it (programmatic dependent launch). That kernel
     // wrote the queries and the key and value of position P; the block tables and the positions came from the host
     // before the step, and the keys and values of earlier positions were written by earlier steps. So the rows of
@@ -71,6 +116,7 @@ __device__ __forceinline__ void attend(uint8_t* smem_raw, const __nv_bfloat16* _
     const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
 
     // Q: the G heads of this kv head as rows 0 .. G-1 of a 16-row tile (the rest zero)
+    const bool fused = fresh.qkv != nullptr;
     auto load_q = [&]() {
         for (int i = threadIdx.x; i < 16 * CHUNKS; i += THREADS) {
             const int row = i / CHUNKS, c = i % CHUNKS;
@@ -81,6 +127,7 @@ __device__ __forceinline__ void attend(uint8_t* smem_raw, const __nv_bfloat16* _
     // Where the rows of a tile lie in the cache (element offset of the key's first value, -1 past the end): looked
     // up by one thread per row a tile ahead of the copies, so that no copy waits for a page-table load.
     __shared__ long long s_row_base[2][TILE];
+    __shared__ __align__(16) __nv_bfloat16 s_fresh[2 * HD];       // the row's newest key and value (a fresh launch)
     auto find_rows = [&](int i) {
         if (i < n_tiles && threadIdx.x < TILE) {
             const int key = first + (tile_lo + i) * TILE + threadIdx.x;
@@ -124,10 +171,69 @@ __device__ __forceinline__ void attend(uint8_t* smem_raw, const __nv_bfloat16* _
         pdl_wait();
         pdl_trigger();
     }
-    load_q();
+    // A fresh launch: this row's queries, and in one block of the pair its newest key and value, are still to be made.
+    // Their raw values are asked for first, then the first tiles, and the arithmetic is done while the tiles travel.
+    constexpr int V = HD / 64;
+    const int fresh_tile = (P - first) / TILE - tile_lo;      // of this block's tiles, the one with position P (if any)
+    const bool makes_kv = fused && fresh_tile >= 0 && fresh_tile < n_tiles;
+    float qa[V], qb[V], ka[V], kb[V];
+    uint4 vv = make_uint4(0, 0, 0, 0);
+    if (fused) {
+        const __nv_bfloat16* mine = fresh.qkv + (size_t)r * fresh.stride;
+        if (warp < G) head_load<V>(mine + (size_t)(kvh * G + warp) * HD, lane, qa, qb);
+        if (makes_kv && warp == 0) head_load<V>(mine + (size_t)(heads + kvh) * HD, lane, ka, kb);
+        if (makes_kv && warp == 1 && lane < CHUNKS)
+            vv = *reinterpret_cast<const uint4*>(mine + (size_t)(heads + kv_heads + kvh) * HD + lane * 8);
+    } else {
+        load_q();
+    }
     if (!pre0) load_tile(0); else if (!pre1) load_tile(1);     // (each load_tile commits a group; Q rides in this one)
     if (!pre0 && !pre1) load_tile(1);
     if (pre0 && pre1) commit();                                 // Q alone
+    if (fused) {
+        const float* cos_row = fresh.cos_t + (size_t)P * (HD / 2);
+        const float* sin_row = fresh.sin_t + (size_t)P * (HD / 2);
+        // the queries: a warp per head, norm and rotation in registers, bfloat16 into the tile (visible to all after the
+        // barrier that the first key tile waits at); rows beyond the G heads are zero
+        for (int row = warp; row < 16; row += WARPS) {
+            if (row < G) {
+                if (row != warp) head_load<V>(fresh.qkv + (size_t)r * fresh.stride + (size_t)(kvh * G + row) * HD, lane, qa, qb);
+                head_norm_rope<V>(qa, qb, lane, fresh.use_norm, fresh.eps, fresh.q_gain, cos_row, sin_row);
+                head_store<HD>(smem_raw, row, nullptr, lane, qa, qb);
+            } else {
+                for (int c = lane; c < CHUNKS; c += 32)
+                    *reinterpret_cast<uint4*>(smem_raw + off<HD>(row, c)) = make_uint4(0, 0, 0, 0);
+            }
+        }
+        if (makes_kv) {
+            // The row's newest key and value fall to this block: warp 0 makes the key (norm, rotation), warp 1 takes the
+            // value; both write the cache and park their HD values in shared memory until the tile that holds position P
+            // has arrived (the barriers of the loop lie between).
+            const int pg = page_shift >= 0 ? P >> page_shift : P / page_size;
+            const int in_page = page_shift >= 0 ? P & (page_size - 1) : P % page_size;
+            const long long page = jllm_page_of(table, pg, table_len, num_pages);       // -1: checked build, bad entry
+            const bool writes = !kCheckBounds || page >= 0;
+            const size_t at = writes ? (size_t)page * page_stride + ((size_t)kvh * page_size + in_page) * HD : 0;
+            if (warp == 0) {
+                head_norm_rope<V>(ka, kb, lane, fresh.use_norm, fresh.eps, fresh.k_gain, cos_row, sin_row);
+                __nv_bfloat16* dst = writes ? fresh.k_out + at : nullptr;
+#pragma unroll
+                for (int i = 0; i < V; ++i) {
+                    const int e0 = lane * V + i, e1 = HD / 2 + e0;
+                    const __nv_bfloat16 v0 = __float2bfloat16_rn(ka[i]), v1 = __float2bfloat16_rn(kb[i]);
+                    s_fresh[e0] = v0;
+                    s_fresh[e1] = v1;
+                    if (dst != nullptr) {
+                        dst[e0] = v0;
+                        dst[e1] = v1;
+                    }
+                }
+            } else if (warp == 1 && lane < CHUNKS) {
+                reinterpret_cast<uint4*>(s_fresh + HD)[lane] = vv;
+                if (writes) *reinterpret_cast<uint4*>(fresh.v_out + at + lane * 8) = vv;
+            }
+        }
+    }
     __syncthreads();        // everyone has read the rows of tile 0: its slot takes those of tile 2
     find_rows(2);
 
@@ -151,6 +257,18 @@ __device__ __forceinline__ void attend(uint8_t* smem_raw, const __nv_bfloat16* _
             for (int ks = 0; ks < HD / 16; ++ks) ldsm4(qf[ks], s_q + off<HD>(lane & 15, ks * 2 + (lane >> 4)));
         }
         const uint32_t sk = s_kv + (i % STAGES) * STAGE_BYTES, sv = sk + TILE_BYTES;
+        if (fused && i == fresh_tile) {
+            // This tile holds the row's newest position (the copy brought whatever the cache held there): the key and value
+            // made at the start go into their row of the tile. (One block of a (row, kv head) pair comes here, once.)
+            uint8_t* tile_k = smem_raw + 16 * HD * 2 + (size_t)(i % STAGES) * STAGE_BYTES;
+            const int row = P - first - (tile_lo + i) * TILE;
+            if (threadIdx.x < 2 * CHUNKS) {
+                const int which = threadIdx.x / CHUNKS, c = threadIdx.x % CHUNKS;     // 0: key, 1: value
+                *reinterpret_cast<uint4*>(tile_k + which * TILE_BYTES + off<HD>(row, c)) =
+                    reinterpret_cast<const uint4*>(s_fresh)[which * CHUNKS + c];
+            }
+            __syncthreads();
+        }
         const int key0 = first + (tile_lo + i) * TILE + warp * 16;
         if (key0 > P) continue;     // this warp's 16 keys of the last tile are all past the end (warp-uniform)
         float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -345,7 +463,7 @@ attention_decode_staged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
                                const int* __restrict__ row_pos, const int* __restrict__ block_tables, int table_stride,
                                int heads, int kv_heads, int page_size, int num_pages, int window, float scale_log2,
                                int splits, float* __restrict__ part_o, float* __restrict__ part_ml,
-                               int* __restrict__ counters) {
+                               int* __restrict__ counters, const Fresh fresh) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const int r = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int G = heads / kv_heads;
@@ -361,7 +479,7 @@ attention_decode_staged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
     const size_t slot = ((size_t)r * heads + kvh * G) * splits + split;
     attend<HD>(smem_raw, q, q_stride, k_cache, v_cache, out, out_stride, table, table_stride, num_pages, heads, kv_heads,
                page_size, scale_log2, r, kvh, P, first, tile_lo, max(0, tile_hi - tile_lo), splits == 1, part_o + slot * HD,
-               (size_t)splits * HD, part_ml + slot * 2, (size_t)splits * 2, true);
+               (size_t)splits * HD, part_ml + slot * 2, (size_t)splits * 2, fresh, true);
     // (without counters a combine kernel follows)
     if (splits > 1 && counters != nullptr && last_of_pair(counters + (size_t)r * kv_heads + kvh, splits)) {
         const size_t slot0 = ((size_t)r * heads + kvh * G) * splits;
@@ -408,7 +526,7 @@ attention_decode_flat_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, 
                              const int* __restrict__ row_seg, const int* __restrict__ row_pos,
                              const int* __restrict__ block_tables, int table_stride, int rows, int heads, int kv_heads,
                              int page_size, int num_pages, int window, float scale_log2, float* __restrict__ part_o,
-                             float* __restrict__ part_ml, int* __restrict__ counters) {
+                             float* __restrict__ part_ml, int* __restrict__ counters, const Fresh fresh) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ int s_cum[FLAT_MAX_ROWS + 1];
     pdl_wait();
@@ -441,7 +559,7 @@ attention_decode_flat_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, 
         attend<HD>(smem_raw, q, q_stride, k_cache, v_cache, out, out_stride, block_tables + (size_t)row_seg[r] * table_stride,
                    table_stride, num_pages, heads, kv_heads, page_size, scale_log2, r, kvh, P, first, tile_lo, n, alone,
                    part_o + slot * G * HD,
-                   (size_t)HD, part_ml + slot * G * 2, (size_t)2);
+                   (size_t)HD, part_ml + slot * G * 2, (size_t)2, fresh);
         at += n;
         if (counters != nullptr && !alone && last_of_pair(counters + (size_t)r * kv_heads + kvh, parts)) {
             const size_t slot0 = (size_t)r * kv_heads + kvh + b_first;      // the slots of the pair's parts follow one another
@@ -511,7 +629,7 @@ template <int HD>
 void launch_flat(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out, int out_stride,
                  const int* row_seg, const int* row_pos, const int* block_tables, int table_stride, int rows, int heads,
                  int kv_heads, int page_size, int window, float scale_log2, int blocks, float* part_o, float* part_ml,
-                 int* counters, cudaStream_t stream) {
+                 int* counters, const Fresh& fresh, cudaStream_t stream) {
     const size_t stage_bytes = (size_t)STAGES * 2 * TILE * HD * 2;
     const size_t merge_bytes = ((size_t)WARPS * 16 * HD + WARPS * 16 * 2) * sizeof(float);
     const size_t smem = 16 * HD * 2 + (stage_bytes > merge_bytes ? stage_bytes : merge_bytes);
@@ -520,7 +638,7 @@ void launch_flat(const void* q, int q_stride, const void* k_cache, const void* v
     jllm_launch(kern, dim3(blocks), dim3(THREADS), smem, stream, true, (const __nv_bfloat16*)q, q_stride,
                 (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out, out_stride, row_seg,
                 row_pos, block_tables, table_stride, rows, heads, kv_heads, page_size, jllm_pool_pages(), window, scale_log2,
-                part_o, part_ml, counters);
+                part_o, part_ml, counters, fresh);
     if (counters == nullptr)
         jllm_launch(attention_combine_flat_kernel, dim3(rows, heads), dim3(128), 0, stream, true, (const float*)part_o,
                     (const float*)part_ml, (__nv_bfloat16*)out, out_stride, row_pos, rows, heads, kv_heads, HD, window,
@@ -531,7 +649,7 @@ template <int HD>
 void launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out, int out_stride,
             const int* row_seg, const int* row_pos, const int* block_tables, int table_stride, int rows, int heads,
             int kv_heads, int page_size, int window, float scale_log2, int splits, float* part_o, float* part_ml,
-            int* counters, cudaStream_t stream) {
+            int* counters, const Fresh& fresh, cudaStream_t stream) {
     const size_t stage_bytes = (size_t)STAGES * 2 * TILE * HD * 2;
     const size_t merge_bytes = ((size_t)WARPS * 16 * HD + WARPS * 16 * 2) * sizeof(float);
     const size_t smem = 16 * HD * 2 + (stage_bytes > merge_bytes ? stage_bytes : merge_bytes);
@@ -540,7 +658,7 @@ void launch(const void* q, int q_stride, const void* k_cache, const void* v_cach
     jllm_launch(kern, dim3(rows, kv_heads, splits), dim3(THREADS), smem, stream, true,
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
         (__nv_bfloat16*)out, out_stride, row_seg, row_pos, block_tables, table_stride, heads, kv_heads, page_size,
-        jllm_pool_pages(), window, scale_log2, splits, part_o, part_ml, counters);
+        jllm_pool_pages(), window, scale_log2, splits, part_o, part_ml, counters, fresh);
 }
 
 // The library's pair counters on the current device (nullptr: the combine kernels run instead).

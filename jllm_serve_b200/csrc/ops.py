@@ -150,6 +150,7 @@ class _Signatures:
     jllm_attention_prefill_tc_error = []
     jllm_attention_prefill_pair = [P, I, P, P, ctypes.c_longlong, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P]
     jllm_attention_decode_separate_combine = [I]
+    jllm_attention_decode_fresh = [P, I, P, P, I, I, F, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P]
     jllm_argmax = [P, I, I, I, P, P]
     jllm_sample = [P, I, I, I, P, P, P, P, P, P, P]
 
@@ -524,7 +525,7 @@ def attention_decode(q, k_cache, v_cache, out, row_seg, row_pos, block_tables, r
         assert scratch is not None and scratch.dtype == torch.float32 and \
             scratch.numel() >= attention_decode_scratch_floats(rows, heads, head_dim, splits)
     global launch_count
-    launch_count += 1 if splits > 1 else 0     # the combine kernel
+    launch_count += _combine_launches("split", splits, rows, kv_heads, head_dim)
     _call("jllm_attention_decode", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
           out.stride(0), row_seg.data_ptr(), row_pos.data_ptr(), block_tables.data_ptr(), block_tables.stride(0),
           rows, heads, kv_heads, head_dim, page_size, int(window), float(scale), int(splits), _p(scratch), _stream())
@@ -540,7 +541,7 @@ def attention_decode_flat(q, k_cache, v_cache, out, row_seg, row_pos, block_tabl
     assert scratch.dtype == torch.float32 and \
         scratch.numel() >= attention_decode_flat_scratch_floats(rows, heads, kv_heads, head_dim, blocks)
     global launch_count
-    launch_count += 1                          # the combine kernel
+    launch_count += _combine_launches("flat", blocks, rows, kv_heads, head_dim)
     _call("jllm_attention_decode_flat", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
           out.stride(0), row_seg.data_ptr(), row_pos.data_ptr(), block_tables.data_ptr(), block_tables.stride(0),
           rows, heads, kv_heads, head_dim, page_size, int(window), float(scale), int(blocks), scratch.data_ptr(), _stream())
@@ -579,6 +580,49 @@ def _attention_decode_rows(q, k_cache, v_cache, out, row_seg, positions, table, 
                                      page_size, window, scale, n, scratch)
     return attention_decode(q, k_cache, v_cache, out, row_seg, positions, table, rows, heads, kv_heads, head_dim, page_size,
                             window, scale, n, scratch)
+
+
+def attention_decode_fresh_fits(dtype, heads, kv_heads, head_dim, rotary_dim) -> bool:
+    """Whether the decode attention can finish its own rows (norm, rotation, cache write) instead of a kernel in front."""
+    return (FRESH_DECODE and dtype == torch.bfloat16 and head_dim in (64, 128, 256) and rotary_dim == head_dim
+            and heads % kv_heads == 0 and heads // kv_heads <= 16)
+
+
+FRESH_DECODE = int(os.environ.get("JLLM_B200_FRESH_DECODE", "1"))
+
+
+def attention_decode_fresh(qkv, q_gain, k_gain, eps, cos, sin, k_cache, v_cache, out, row_seg, positions, table, rows,
+                           heads, kv_heads, head_dim, page_size, window, scale, kv_bucket, scratch) -> bool:
+    """Decode attention over rows whose queries, key and value lie in `qkv` as the QKV product left them: the kernel norms
+    and rotates them itself and writes the key and value of every row's newest position to the cache (what
+    `qk_norm_rope_store` does in a launch of its own). Taken, and True returned, where `decode_plan` gives every (row, kv
+    head) pair blocks of its own: a step of 8 rows 4.17 ms against 4.24, of one row 3.38 against 3.43; where the key tiles
+    are dealt out over the blocks (64 rows: 10.46 against 10.44 ms) nothing is launched and the caller takes the two
+    kernels."""
+    bucket = kv_bucket if window <= 0 else max(1, min(kv_bucket, window // 256))
+    how, n = decode_plan(rows, kv_heads, bucket, heads, head_dim, scratch)
+    if how == "flat" and FRESH_DECODE != 2:
+        return False
+    use_norm = q_gain is not None
+    global launch_count
+    launch_count += _combine_launches(how, n, rows, kv_heads, head_dim)
+    _call("jllm_attention_decode_fresh", qkv.data_ptr(), qkv.stride(0), _p(q_gain), _p(k_gain),
+          _DT[q_gain.dtype] if use_norm else F32, int(use_norm), float(eps), cos.data_ptr(), sin.data_ptr(),
+          k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), out.stride(0), row_seg.data_ptr(), positions.data_ptr(),
+          table.data_ptr(), table.stride(0), rows, heads, kv_heads, head_dim, page_size, int(window), float(scale),
+          int(how == "flat"), int(n), _p(scratch), _stream())
+    return True
+
+
+PAIR_COUNTERS = 1 << 16      # the library's counters of (row, kv head) pairs: within them no combine kernel follows
+
+
+def _combine_launches(how, n, rows, kv_heads, head_dim) -> int:
+    """Kernels that a decode attention launches besides the attention itself (the count `bench.py` reports)."""
+    within = rows * kv_heads <= PAIR_COUNTERS and head_dim in (64, 128, 256)
+    if how == "flat":
+        return 0 if within and rows * kv_heads >= n else 1
+    return 0 if n == 1 or (within and n <= 8) else 1
 
 
 def attention(q, k_cache, v_cache, out, batch, group, heads, kv_heads, head_dim, page_size, window, scale,

@@ -5,7 +5,7 @@
 // alone (fixed reduction order), so it is the same in any batch.
 #include <cstdlib>
 
-#include "common.cuh"
+#include "head_rotate.cuh"
 
 // ---------------------------------------------------------------------------------------------------
 // x[r, :] = table[ids[r], :]  (float residual stream from a float or bfloat16 table)
@@ -60,10 +60,7 @@ JLLM_EXPORT int jllm_feed_tokens(int* ids, const int* sampled, int rows, int sam
 // RMSNorm: out[r] = (x[src(r)] * (1 / sqrt(mean(x^2) + eps))) * gain, src(r) = row_index ? row_index[r] : r
 // The scale is taken in double from a float mean, as the reference does.
 // ---------------------------------------------------------------------------------------------------
-__device__ __forceinline__ float rms_scale(float sum_squares, int n, float eps) {
-    const float mean = sum_squares / (float)n + eps;
-    return (float)(1.0 / sqrt((double)mean));
-}
+// (rms_scale: head_rotate.cuh)
 
 template <typename Tout>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, VecRef gain, Tout* __restrict__ out,
@@ -263,31 +260,9 @@ qk_norm_rope_store_warp_kernel(T* __restrict__ qkv, VecRef q_gain, VecRef k_gain
         a[i] = to_float(src[lane * V + i]);
         b[i] = to_float(src[HALF + lane * V + i]);
     }
-    if (is_q || is_k) {
-        if (use_norm) {
-            float ss = 0.f;
-#pragma unroll
-            for (int i = 0; i < V; ++i) ss = fmaf(a[i], a[i], ss);
-#pragma unroll
-            for (int i = 0; i < V; ++i) ss = fmaf(b[i], b[i], ss);
-            ss = warp_sum(ss);
-            const float s = rms_scale(ss, HD, eps);
-            const VecRef g = is_q ? q_gain : k_gain;
-#pragma unroll
-            for (int i = 0; i < V; ++i) {
-                a[i] = __fmul_rn(__fmul_rn(a[i], s), g[lane * V + i]);
-                b[i] = __fmul_rn(__fmul_rn(b[i], s), g[HALF + lane * V + i]);
-            }
-        }
-        const float* c = cos_t + (size_t)positions[r] * HALF + lane * V;
-        const float* sn = sin_t + (size_t)positions[r] * HALF + lane * V;
-#pragma unroll
-        for (int i = 0; i < V; ++i) {
-            const float x0 = a[i], x1 = b[i];
-            a[i] = __fsub_rn(__fmul_rn(x0, c[i]), __fmul_rn(x1, sn[i]));
-            b[i] = __fadd_rn(__fmul_rn(x1, c[i]), __fmul_rn(x0, sn[i]));
-        }
-    }
+    if (is_q || is_k)
+        head_norm_rope<V>(a, b, lane, use_norm, eps, is_q ? q_gain : k_gain, cos_t + (size_t)positions[r] * HALF,
+                          sin_t + (size_t)positions[r] * HALF);
     T* dst = src;
     if (!is_q) {
         const int kvh = is_k ? h - heads : h - heads - kv_heads;

@@ -71,13 +71,22 @@ class GqaAttention(Mixer):
                 self._q_only = self.qkv.rows(0, self.q_width)
             self._q_only.forward(xb, qkv)
         rope = self.rope
+        att = self.rt.buffer("attention_out", self.q_width)[:rows]
+        scratch = self.rt.buffer("attention_scratch", 2 << 20, torch.float32, rows=1)[0]
+        if (cache.writes and batch.decode_only and rope is not None and ops.attention_decode_fits(qkv.dtype, s.heads, s.kv_heads, s.head_dim)
+                and ops.attention_decode_fresh_fits(qkv.dtype, s.heads, s.kv_heads, s.head_dim, rope.rotary_dim)):
+            # a step of single rows: the attention kernel norms and rotates its own rows and writes their keys and values
+            # (where that pays: it says whether it ran)
+            if ops.attention_decode_fresh(qkv, self.q_gain, self.k_gain, s.qk_norm_eps, rope.cos, rope.sin, cache.keys,
+                                          cache.values, att, batch.row_seg, batch.positions,
+                                          batch.block_tables[cache.group], rows, s.heads, s.kv_heads, s.head_dim,
+                                          self.rt.page_size, s.window, s.scale, batch.kv_bucket, scratch):
+                return self.out.forward(att, x, accumulate=True)
         ops.qk_norm_rope_store(qkv, self.q_gain, self.k_gain, s.qk_norm_eps,
                                rope.cos if rope else None, rope.sin if rope else None,
                                rope.rotary_dim if rope else 0, batch.positions,
                                batch.slots[cache.group] if cache.writes else None, cache.keys, cache.values,
                                s.heads, s.kv_heads, s.head_dim, self.rt.page_size, write_kv=cache.writes)
-        att = self.rt.buffer("attention_out", self.q_width)[:rows]
-        scratch = self.rt.buffer("attention_scratch", 2 << 20, torch.float32, rows=1)[0]
         ops.attention(qkv, cache.keys, cache.values, att, batch, cache.group, s.heads, s.kv_heads, s.head_dim,
                       self.rt.page_size, s.window, s.scale, scratch)
         self.out.forward(att, x, accumulate=True)

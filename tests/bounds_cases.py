@@ -82,6 +82,54 @@ def main() -> int:
         ops.check_kernel_errors()
         print(f"ok: {name} head size {hd}")
 
+    # ---- the decode attention that makes its own rows' keys and values: a spoilt page of the newest position is neither
+    # read nor written; afterwards the same bits as the row-wise kernel followed by the attention ----------------------
+    hd, scale, eps = 128, 1.0 / math.sqrt(128), 1e-6
+    lens = [40, 300, 200, 70]
+    pool = sum(-(-n // page) for n in lens) + 3
+    ops.set_pool_pages(pool)
+    tables = torch.full((4, 20), -1, dtype=torch.int32)
+    at = 0
+    for r, n in enumerate(lens):
+        k = -(-n // page)
+        tables[r, :k] = torch.arange(at, at + k, dtype=torch.int32)
+        at += k
+    tables = tables.to(DEV)
+    kc0 = (torch.randn(pool, Hkv, page, hd, device=DEV) * 0.5).to(torch.bfloat16)
+    vc0 = torch.randn(pool, Hkv, page, hd, device=DEV).to(torch.bfloat16)
+    qkv = torch.randn(4, (H + 2 * Hkv) * hd, device=DEV).to(torch.bfloat16)
+    gain = torch.ones(hd, dtype=torch.bfloat16, device=DEV)
+    ang = torch.outer(torch.arange(301, dtype=torch.float64), 1e4 ** (-torch.arange(hd // 2, dtype=torch.float64) * 2 / hd))
+    cos, sin = ang.cos().float().to(DEV), ang.sin().float().to(DEV)
+    seg, pos = i32([0, 1, 2, 3]), i32([n - 1 for n in lens])
+    scratch = torch.empty(1 << 20, device=DEV)
+
+    def fresh(tab, kc, vc, out):
+        ops._call("jllm_attention_decode_fresh", qkv.data_ptr(), qkv.stride(0), gain.data_ptr(), gain.data_ptr(),
+                  ops._DT[gain.dtype], 1, eps, cos.data_ptr(), sin.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr(),
+                  out.stride(0), seg.data_ptr(), pos.data_ptr(), tab.data_ptr(), tab.stride(0), 4, H, Hkv, hd, page, 0,
+                  scale, 0, 3, scratch.data_ptr(), ops._stream())
+        torch.cuda.synchronize()
+
+    bad = tables.clone()
+    bad[3, (lens[3] - 1) // page] = pool + 9          # the page of request 3's newest position
+    kc, vc, out = kc0.clone(), vc0.clone(), torch.empty(4, H * hd, dtype=torch.bfloat16, device=DEV)
+    fresh(bad, kc, vc, out)
+    caught("attention_decode", "a page id")
+    rest = [r for r in range(pool) if r != int(tables[3, (lens[3] - 1) // page])]
+    slots = i32([int(tables[r, (n - 1) // page]) * page + (n - 1) % page for r, n in enumerate(lens)])
+    work, kc_a, vc_a, out_a = qkv.clone(), kc0.clone(), vc0.clone(), torch.empty_like(out)
+    ops.qk_norm_rope_store(work, gain, gain, eps, cos, sin, hd, pos, slots, kc_a, vc_a, H, Hkv, hd, page)
+    ops.attention_decode(work, kc_a, vc_a, out_a, seg, pos, tables, 4, H, Hkv, hd, page, 0, scale, 3, scratch)
+    assert torch.equal(kc[rest].view(torch.int16), kc_a[rest].view(torch.int16))      # requests 0 to 2 were written as always
+    assert torch.equal(out[:3], out_a[:3])
+    kc, vc = kc0.clone(), vc0.clone()
+    fresh(tables, kc, vc, out)
+    assert ops.bounds_errors() == {}
+    assert torch.equal(out, out_a) and torch.equal(kc.view(torch.int16), kc_a.view(torch.int16)) and \
+        torch.equal(vc.view(torch.int16), vc_a.view(torch.int16))
+    print("ok: decode attention that makes its own rows")
+
     # ---- the cache write: a slot beyond the pool is dropped, the others are written --------------------------------
     for dtype, hd in ((torch.float32, 48), (torch.bfloat16, 128)):
         R, pages = 40, 6

@@ -31,7 +31,7 @@ def test_bad_tables_slots_and_tokens_are_skipped_and_reported():
     proc = subprocess.run([sys.executable, str(ROOT / "tests" / "bounds_cases.py")], env=checked_env(),
                           capture_output=True, text=True, timeout=900)
     assert proc.returncode == 0, (proc.stdout[-3000:], proc.stderr[-3000:])
-    assert proc.stdout.count("ok:") == 9, proc.stdout
+    assert proc.stdout.count("ok:") == 10, proc.stdout
 
 
 def test_replay_traces_run_clean_under_the_checked_library():

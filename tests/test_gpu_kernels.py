@@ -518,6 +518,67 @@ def test_attention_decode(ops, H, Hkv, hd, page, window, splits):
         assert torch.equal(out1, again) and torch.equal(out1, apart)
 
 
+@pytest.mark.parametrize("how,n", [("split", 1), ("split", 3), ("split", 8), ("split", 20), ("flat", 5), ("flat", 40)])
+@pytest.mark.parametrize("H,Hkv,hd,page,window,norm", [(32, 8, 128, 16, 0, True), (16, 1, 256, 16, 0, False),
+                                                        (8, 2, 64, 8, 100, True), (6, 3, 64, 1, 0, True),
+                                                        (4, 4, 128, 4, 70, False)])
+def test_attention_decode_fresh(ops, H, Hkv, hd, page, window, norm, how, n):
+    """The decode attention that norms and rotates its own rows and writes their keys and values: the same bits, in
+    its output and in the cache, as the row-wise kernel followed by the decode attention; positions at the start, the
+    end and the middle of pages and of 64-key tiles; what the cache held at the newest position does not matter."""
+    import random
+    rng = random.Random(H * 100 + hd + n)
+    lens = [1, 17, 64, 65, 131, 300, 1000, 128, 2]
+    R, eps, scale = len(lens), 1e-6, 1.0 / math.sqrt(hd)
+    pages_of = [-(-L // page) for L in lens]
+    pool = sum(pages_of) + 7
+    order = list(range(pool))
+    rng.shuffle(order)
+    tables = torch.full((R, max(pages_of) + 1), -1, dtype=torch.int32)
+    at = 0
+    for r, npg in enumerate(pages_of):
+        tables[r, :npg] = torch.tensor(order[at:at + npg], dtype=torch.int32)
+        at += npg
+    kc = (rnd(pool, Hkv, page, hd, seed=5) * 0.5).to(torch.bfloat16)
+    vc = rnd(pool, Hkv, page, hd, seed=6).to(torch.bfloat16)
+    positions = torch.tensor([L - 1 for L in lens], dtype=torch.int32)
+    slots = torch.tensor([int(tables[r, (L - 1) // page]) * page + (L - 1) % page for r, L in enumerate(lens)], dtype=torch.int32)
+    for r in range(R):          # nothing may be read of what the cache holds at the newest position
+        kc[int(slots[r]) // page, :, int(slots[r]) % page] = float("nan")
+        vc[int(slots[r]) // page, :, int(slots[r]) % page] = float("nan")
+    qkv = rnd(R, (H + 2 * Hkv) * hd, dtype=torch.bfloat16, seed=7)
+    qg, kg = (1 + 0.1 * rnd(hd, seed=8)).to(torch.bfloat16), (1 + 0.1 * rnd(hd, seed=9)).to(torch.bfloat16)
+    cos, sin = P.rope_table(range(max(lens) + 1), hd, 50000.0)
+    cos, sin = cos.to(DEV), sin.to(DEV)
+    seg, pos, tab = torch.arange(R, dtype=torch.int32, device=DEV), positions.to(DEV), tables.to(DEV)
+    if how == "flat":
+        n = min(n, 62 * Hkv)
+        scratch = torch.full((ops.attention_decode_flat_scratch_floats(R, H, Hkv, hd, n),), float("nan"), device=DEV)
+    else:
+        scratch = torch.full((ops.attention_decode_scratch_floats(R, H, hd, n) + 1,), float("nan"), device=DEV)
+    # apart: the row-wise kernel, then the attention
+    work, kc_a, vc_a = qkv.clone(), kc.clone(), vc.clone()
+    ops.qk_norm_rope_store(work, qg if norm else None, kg if norm else None, eps, cos, sin, hd, pos, slots.to(DEV), kc_a, vc_a,
+                           H, Hkv, hd, page)
+    out_a = torch.full((R, H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    if how == "flat":
+        ops.attention_decode_flat(work, kc_a, vc_a, out_a, seg, pos, tab, R, H, Hkv, hd, page, window, scale, n, scratch)
+    else:
+        ops.attention_decode(work, kc_a, vc_a, out_a, seg, pos, tab, R, H, Hkv, hd, page, window, scale, n, scratch)
+    # in one
+    kc_b, vc_b = kc.clone(), vc.clone()
+    out_b = torch.full((R, H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops._call("jllm_attention_decode_fresh", qkv.data_ptr(), qkv.stride(0), qg.data_ptr() if norm else None,
+              kg.data_ptr() if norm else None, ops._DT[qg.dtype], int(norm), eps, cos.data_ptr(), sin.data_ptr(),
+              kc_b.data_ptr(), vc_b.data_ptr(), out_b.data_ptr(), out_b.stride(0), seg.data_ptr(), pos.data_ptr(),
+              tab.data_ptr(), tab.stride(0), R, H, Hkv, hd, page, window, scale, int(how == "flat"), n, scratch.data_ptr(),
+              ops._stream())
+    assert torch.isfinite(out_a.float()).all()
+    assert torch.equal(out_a, out_b)
+    assert torch.equal(kc_a.view(torch.int16), kc_b.view(torch.int16)) and torch.equal(vc_a.view(torch.int16), vc_b.view(torch.int16))
+    assert torch.equal(work[:, H * hd:], qkv[:, H * hd:])
+
+
 @pytest.mark.parametrize("blocks", [1, 7, 40, 296])
 @pytest.mark.parametrize("H,Hkv,hd,page,window", [(32, 8, 128, 16, 0), (16, 1, 256, 16, 0), (8, 2, 64, 16, 100),
                                                    (6, 3, 64, 8, 21), (4, 4, 128, 4, 0)])
