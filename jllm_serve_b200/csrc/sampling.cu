@@ -86,6 +86,72 @@ __global__ void __launch_bounds__(THREADS) argmax_kernel(const float* __restrict
     if (threadIdx.x == 0) out[blockIdx.x] = t;
 }
 
+// The same with a row dealt out over `parts` blocks (few rows of a long vocabulary: one block per row leaves the GPU
+// to a handful of SMs, each reading 600 KB alone). Block (row, part) scans its stretch with 16-byte loads and parks its
+// best (value, index); the block of a row that finds itself last at the row's counter (after a fence; nobody waits)
+// takes the best of the parts. "Better" is a total order (higher value, then lower index), so the result does not depend
+// on who came when. Scratch and counters belong to the library (zero when it is loaded, left at zero): launches on one
+// device must not overlap.
+constexpr int ARGMAX_MAX_ROWS = 4096, ARGMAX_MAX_PARTS = 32;
+__device__ ArgBest g_argmax_parts[ARGMAX_MAX_ROWS * ARGMAX_MAX_PARTS];
+__device__ int g_argmax_counters[ARGMAX_MAX_ROWS];
+
+__global__ void __launch_bounds__(256) argmax_parts_kernel(const float* __restrict__ logits, int ld, int vocab, int parts,
+                                                           int* __restrict__ out) {
+    __shared__ ArgBest scratch[9];
+    __shared__ int s_last;
+    pdl_wait();
+    pdl_trigger();
+    const int r = blockIdx.x, part = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float* row = logits + (size_t)r * ld;
+    // stretches of whole groups of four columns (the rows are 16-byte aligned: the host sees to it)
+    const int groups = (vocab + 3) >> 2, g_lo = (int)((long long)groups * part / parts),
+              g_hi = (int)((long long)groups * (part + 1) / parts);
+    ArgBest best{-INFINITY, 0x7fffffff};
+    for (int g = g_lo + threadIdx.x; g < g_hi; g += 256) {
+        const int i = 4 * g;
+        if (i + 3 < vocab) {
+            const float4 v = *reinterpret_cast<const float4*>(row + i);
+            best = better(best, ArgBest{v.x, i});
+            best = better(best, ArgBest{v.y, i + 1});
+            best = better(best, ArgBest{v.z, i + 2});
+            best = better(best, ArgBest{v.w, i + 3});
+        } else {
+            for (int j = i; j < vocab; ++j) best = better(best, ArgBest{row[j], j});
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ArgBest other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+        best = better(best, other);
+    }
+    if (lane == 0) scratch[warp] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w) best = better(best, scratch[w]);
+        g_argmax_parts[r * ARGMAX_MAX_PARTS + part] = best;
+        __threadfence();
+        const int seen = atomicAdd(&g_argmax_counters[r], 1);
+        s_last = seen == parts - 1;
+        if (s_last) g_argmax_counters[r] = 0;
+    }
+    __syncthreads();
+    if (s_last && warp == 0) {
+        __threadfence();
+        ArgBest t{-INFINITY, 0x7fffffff};
+        if (lane < parts) {
+            t.v = __ldcg(&g_argmax_parts[r * ARGMAX_MAX_PARTS + lane].v);
+            t.i = __ldcg(&g_argmax_parts[r * ARGMAX_MAX_PARTS + lane].i);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            ArgBest other{__shfl_xor_sync(0xffffffffu, t.v, o), __shfl_xor_sync(0xffffffffu, t.i, o)};
+            t = better(t, other);
+        }
+        if (lane == 0) out[r] = t.i == 0x7fffffff ? 0 : t.i;      // a row of NaNs: index 0
+    }
+}
+
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
@@ -226,6 +292,15 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* 
 JLLM_EXPORT int jllm_argmax(const float* logits, int ld, int rows, int vocab, int* out, cudaStream_t stream) {
     JLLM_REQUIRE(rows >= 0 && vocab > 0 && ld >= vocab, "argmax: rows=%d vocab=%d ld=%d", rows, vocab, ld);
     if (rows == 0) return JLLM_OK;
+    // few rows: as many blocks per row as give every SM about two, each with 4,096 columns or more
+    const int sms = jllm_device_sm_count() > 0 ? jllm_device_sm_count() : 1;
+    int parts = (2 * sms + rows - 1) / rows;
+    if (parts > ARGMAX_MAX_PARTS) parts = ARGMAX_MAX_PARTS;
+    if (parts > vocab / 4096) parts = vocab / 4096;
+    if (parts >= 2 && rows <= ARGMAX_MAX_ROWS && ld % 4 == 0 && ((uintptr_t)logits % 16) == 0) {
+        jllm_launch(argmax_parts_kernel, dim3(rows, parts), dim3(256), 0, stream, true, logits, ld, vocab, parts, out);
+        return jllm_check_launch("argmax");
+    }
     jllm_launch(argmax_kernel, dim3(rows), dim3(THREADS), 0, stream, true, logits, ld, vocab, out);
     return jllm_check_launch("argmax");
 }

@@ -641,6 +641,22 @@ def test_argmax_lowest_index_among_equals(ops):
     assert out.tolist() == [P.argmax_lowest(logits[0].cpu()), 70000, 0, 151935]
     ops.argmax(logits, out, vocab=151000)                    # padding rows of the head are never chosen
     assert out.tolist()[3] == P.argmax_lowest(logits[3, :151000].cpu())
+    # rows dealt out over several blocks and rows with one block each, widths that end inside a group of four columns,
+    # equal maxima in different blocks' stretches, a view with wider rows, a row of NaNs; twice (the counters are left at zero)
+    for rows, vocab, ld in ((1, 151936, 151936), (3, 50001, 50004), (40, 32003, 32004), (200, 9001, 9004), (2, 777, 780),
+                            (5, 40000, 40001)):
+        wide = rnd(rows, ld, seed=rows)
+        wide[0, 5] = wide[0, vocab - 1] = 70.0
+        if rows > 2:
+            wide[1, vocab - 2] = wide[1, vocab // 2] = 70.0
+            wide[2, :] = float("nan")
+        view = wide[:, :vocab]
+        want = [P.argmax_lowest(view[r].cpu()) if not torch.isnan(view[r]).all() else 0 for r in range(rows)]
+        got = torch.full((rows,), -1, dtype=torch.int32, device=DEV)
+        for _ in range(2):
+            got.fill_(-1)
+            ops.argmax(view, got)
+            assert got.tolist() == want, (rows, vocab, ld)
 
 
 @pytest.mark.parametrize("T,k,p,mp", [(0.8, 0, 1.0, 0.0), (1.0, 20, 0.95, 0.0), (0.6, 0, 0.9, 0.0), (1.3, 0, 1.0, 0.05),
