@@ -282,6 +282,8 @@ def main() -> int:
                "peak_tflops": pk["bf16_tflops"], "peak_source": pk["source"]}
     if "bf16_tflops_sustained" in pk:       # the same against what the GEMM library sustains under the power cap
         prefill["frac_of_sustained"] = round(flops / (pre_ms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)
+    if args.skip_prefill:
+        prefill = None
 
     # ---- decode at batch 1 and 64 --------------------------------------------------------------------------------
     points = {}
