@@ -292,12 +292,16 @@ def gemm_kernel_for(rows: int, out_features: int, in_features: int = 4096, rows_
     if not tiles_fit:
         return ""
     # Many rows: two SMs to a 256 x 256 tile take in a third less per multiply-add than one SM with a 128 x 256 tile,
-    # which is what bounds these products. It pays where its tiles keep three quarters of the pairs busy or more and its rounds of
-    # tiles, each about a tenth shorter than a round of the one-SM kernel's, are no more than that kernel's.
+    # which is what bounds these products. It pays where its tiles keep three quarters of the pairs busy or more and its
+    # rounds of tiles, each about a tenth shorter than a round of one-SM tiles of the same width, take less than the
+    # one-SM kernel's rounds at the tile width that kernel would choose (rounds x (rows + width) of a tile, as it does).
     col_tiles = -(-out_features // 256)
-    pair_tiles, single_tiles = -(-rows // 256) * col_tiles, -(-rows // 128) * col_tiles
-    if pairs > 0 and pair_tiles * 4 >= pairs * 3 and -(-pair_tiles // pairs) * 0.9 <= -(-single_tiles // sms):
-        return "pair"
+    pair_tiles = -(-rows // 256) * col_tiles
+    if pairs > 0 and pair_tiles * 4 >= pairs * 3:
+        row_tiles, tile_rows = -(-rows // 128), min(rows, 128)
+        single = min(-(-(row_tiles * -(-out_features // w)) // sms) * (tile_rows + w) for w in (256, 192, 128, 64, 32))
+        if -(-pair_tiles // pairs) * 0.9 * (128 + 256) <= single:
+            return "pair"
     return "tiles"
 
 

@@ -20,6 +20,8 @@ def test_product_kernel_by_rows_and_shape():
     assert k(1024, 4096, 12288) == "pair" and k(512, 24576, 4096) == "pair"
     assert k(512, 6144, 4096) == "tiles"                   # 48 tiles for 74 pairs
     assert k(300, 24576, 4096) == "tiles"                  # 300 rows: three 128-row tiles, not two of 256
+    assert k(1024, 6144, 4096) == "tiles"                  # the one-SM kernel would take 192-wide tiles: 2 rounds of 0.83
+    assert k(544, 5120, 5120) == "tiles" and k(544, 5120, 17408) == "tiles"     # a third pair tile an eighth full
     assert k(2048, 4096, 4096, pairs=0) == "tiles"         # a device that runs no pairs
     assert k(16, 24576, 4096, tiles_fit=False) == "rows"
     assert k(8, 4096, 4096, rows_fit=False) == "tiles"
