@@ -72,21 +72,16 @@ __device__ __forceinline__ void head_load(const __nv_bfloat16* __restrict__ src,
         b[i] = __bfloat162float(src[32 * V + lane * V + i]);
     }
 }
-// ... and back as bfloat16: into row `row` of a swizzled tile in shared memory, and (dst not null) to global memory
+// ... and back as bfloat16 into row `row` of a swizzled tile in shared memory
 template <int HD>
-__device__ __forceinline__ void head_store(uint8_t* tile, int row, __nv_bfloat16* __restrict__ dst, int lane,
-                                           const float (&a)[HD / 64], const float (&b)[HD / 64]) {
+__device__ __forceinline__ void head_store(uint8_t* tile, int row, int lane, const float (&a)[HD / 64],
+                                           const float (&b)[HD / 64]) {
     constexpr int V = HD / 64, HALF = HD / 2;
 #pragma unroll
     for (int i = 0; i < V; ++i) {
         const int e0 = lane * V + i, e1 = HALF + e0;
-        const __nv_bfloat16 v0 = __float2bfloat16_rn(a[i]), v1 = __float2bfloat16_rn(b[i]);
-        *reinterpret_cast<__nv_bfloat16*>(tile + off<HD>(row, e0 >> 3) + (e0 & 7) * 2) = v0;
-        *reinterpret_cast<__nv_bfloat16*>(tile + off<HD>(row, e1 >> 3) + (e1 & 7) * 2) = v1;
-        if (dst != nullptr) {
-            dst[e0] = v0;
-            dst[e1] = v1;
-        }
+        *reinterpret_cast<__nv_bfloat16*>(tile + off<HD>(row, e0 >> 3) + (e0 & 7) * 2) = __float2bfloat16_rn(a[i]);
+        *reinterpret_cast<__nv_bfloat16*>(tile + off<HD>(row, e1 >> 3) + (e1 & 7) * 2) = __float2bfloat16_rn(b[i]);
     }
 }
 
@@ -199,7 +194,7 @@ __device__ __forceinline__ void attend(uint8_t* smem_raw, const __nv_bfloat16* _
             if (row < G) {
                 if (row != warp) head_load<V>(fresh.qkv + (size_t)r * fresh.stride + (size_t)(kvh * G + row) * HD, lane, qa, qb);
                 head_norm_rope<V>(qa, qb, lane, fresh.use_norm, fresh.eps, fresh.q_gain, cos_row, sin_row);
-                head_store<HD>(smem_raw, row, nullptr, lane, qa, qb);
+                head_store<HD>(smem_raw, row, lane, qa, qb);
             } else {
                 for (int c = lane; c < CHUNKS; c += 32)
                     *reinterpret_cast<uint4*>(smem_raw + off<HD>(row, c)) = make_uint4(0, 0, 0, 0);

@@ -247,16 +247,19 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
                             if (!(key <= P && key >= lo)) v[c][i] = __float_as_uint(-INFINITY);
                         }
                 }
-                float mx = -INFINITY;
+                // (four chains, then their maximum: one chain of 128 dependent comparisons is pure latency for a warp
+                // that has its scheduler almost to itself)
+                float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[c][i]));
+                    for (int i = 0; i < 32; ++i) mxs[i & 3] = fmaxf(mxs[i & 3], __uint_as_float(v[c][i]));
+                const float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
                 const float m_cand = fmaxf(m, mx * scale_log2);
                 const float m_new = (m_cand - m > 8.f) ? m_cand : m;
                 const float m_use = m_new == -INFINITY ? 0.f : m_new;
                 const float corr = fast_exp2(m - m_use);
-                float sum = 0.f;
+                float sums[2] = {0.f, 0.f};
                 // P over the first 64 columns of S: two stores of 32 packed columns
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
@@ -267,24 +270,23 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
                         for (int i = 0; i < 32; i += 2) {
                             const float p0 = fast_exp2(fmaf(__uint_as_float(v[2 * half + c][i]), scale_log2, -m_use));
                             const float p1 = fast_exp2(fmaf(__uint_as_float(v[2 * half + c][i + 1]), scale_log2, -m_use));
-                            sum += p0 + p1;
+                            sums[(i >> 1) & 1] += p0 + p1;
                             __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
                             pk[(c * 32 + i) >> 1] = *reinterpret_cast<uint32_t*>(&b2);
                         }
                     tmem_st_32x32b_x32(s_addr + half * 32, pk);
                 }
                 m = m_new;
-                l = l * corr + sum;
+                l = l * corr + (sums[0] + sums[1]);
                 if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {  // the reference moved for a row of this warp
-                    uint32_t o[4][32];
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(o_addr + c * 32, o[c]);
-                    tmem_ld_wait();
-#pragma unroll
+#pragma unroll 1
                     for (int c = 0; c < 4; ++c) {
+                        uint32_t o[32];
+                        tmem_ld_32x32b_x32(o_addr + c * 32, o);
+                        tmem_ld_wait();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[c][i] = __float_as_uint(__uint_as_float(o[c][i]) * corr);
-                        tmem_st_32x32b_x32(o_addr + c * 32, o[c]);
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+                        tmem_st_32x32b_x32(o_addr + c * 32, o);
                     }
                 }
                 tmem_st_wait();

@@ -592,7 +592,7 @@ def attention_decode_fresh_fits(dtype, heads, kv_heads, head_dim, rotary_dim) ->
             and heads % kv_heads == 0 and heads // kv_heads <= 16)
 
 
-FRESH_DECODE = int(os.environ.get("JLLM_B200_FRESH_DECODE", "1"))
+FRESH_DECODE = int(os.environ.get("JLLM_B200_FRESH_DECODE", "1"))      # 0: never; 2: also where the key tiles are dealt out
 
 
 def attention_decode_fresh(qkv, q_gain, k_gain, eps, cos, sin, k_cache, v_cache, out, row_seg, positions, table, rows,
