@@ -217,7 +217,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
             for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(lane_addr + b * 128 + c * 32, v[c]);
             tmem_ld_wait();
-            float mx = -INFINITY;
             if (masked) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
@@ -227,10 +226,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                         if (!(key <= P && key >= lo)) v[c][i] = __float_as_uint(-INFINITY);
                     }
             }
+            // (four chains, then their maximum: one chain of 128 dependent comparisons is pure latency)
+            float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
             for (int c = 0; c < 4; ++c)
 #pragma unroll
-                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[c][i]));
+                for (int i = 0; i < 32; ++i) mxs[i & 3] = fmaxf(mxs[i & 3], __uint_as_float(v[c][i]));
+            const float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
             // The reference point of the exponentials only moves when the maximum grew by more than 2^8: until
             // then p stays below 256, which bfloat16 and the float32 sum hold as well, and O needs no rescaling.
             const float m_cand = fmaxf(m, mx * scale_log2);
