@@ -37,3 +37,21 @@ def test_bfloat16_follows_float32_at_8b_layer_sizes():
         assert s["argmax_agree"] >= 0.96, (name, s)
         # where the two paths choose differently, the 32-bit path holds the other choice for almost as good
         assert s["worst_choice_gap_rel"] <= 1e-2, (name, s)
+
+
+def test_bfloat16_follows_float32_with_a_prompt_of_many_rows():
+    """The same with 1,280 rows in one step and portions of 1,024: the products then run two SMs to a tile, with
+    float32 outputs by tiled bulk copies, and the attention two query tiles to a block."""
+    from jllm_serve_b200.csrc import ops
+    from jllm_serve_b200.precision_check import compare_precisions
+    for rows in (1280, 1024):
+        assert ops.gemm_kernel_for(rows, 24576, 4096, sms=ops.sm_count(), pairs=ops.resident_pairs()) == "pair"
+    got = compare_precisions(CONFIG, seed=5, prompt=1280, tail=4, portion=1024)
+    print(f"layers {CONFIG['num_hidden_layers']} of {QWEN3_8B_LAYERS}: {got}")
+    for name in ("alone", "mixed"):
+        s = got[name]
+        assert s["rows"] >= 1284
+        assert s["max_rel"] <= 1.5e-2, (name, s)
+        assert s["rms_rel"] <= 1.3e-2, (name, s)
+        assert s["argmax_agree"] >= 0.96, (name, s)
+        assert s["worst_choice_gap_rel"] <= 1e-2, (name, s)
