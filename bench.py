@@ -160,8 +160,9 @@ def main() -> int:
     if not (args.skip_check or args.prefill_only):
         # the 32-bit path against the bfloat16 path at these layer sizes, on two layers (untimed, before the model)
         from jllm_serve_b200.precision_check import compare_precisions
-        got = compare_precisions(dict(shape, num_hidden_layers=2), seed=0)["mixed"]
-        check = {"what": "bfloat16 logits against the 32-bit path, a 256+44-row prompt beside 2 decoding requests, "
+        # (a prompt of 1,280 rows in portions of 1,024, so that the products of many rows are the ones the prefill takes)
+        got = compare_precisions(dict(shape, num_hidden_layers=2), seed=0, prompt=1280, tail=16, portion=1024)["mixed"]
+        check = {"what": "bfloat16 logits against the 32-bit path, a 1024+256-row prompt beside 2 decoding requests, "
                          "then 16 tokens one by one", "layers": 2, "layers_of_config": shape["num_hidden_layers"],
                  "rows": got["rows"], "max_rel": round(got["max_rel"], 5), "rms_rel": round(got["rms_rel"], 5),
                  "argmax_agree": round(got["argmax_agree"], 4), "choice_gap_rel": round(got["worst_choice_gap_rel"], 5)}
