@@ -78,6 +78,17 @@ def main() -> int:
         case(f"decode attention ({n} splits)",
              lambda i: ops.attention_decode(q, caches[i][0], caches[i][1], out, seg, pos, tables, M, H, Hkv, hd, page, 0,
                                             1 / math.sqrt(hd), n, scratch), n_caches, M * ctx * Hkv * hd * 4)
+    if how != "flat":
+        # the same with the rows' own norm, rotation and cache write done by the attention (what a decode step takes)
+        ang_d = torch.outer(torch.arange(ctx + 1, dtype=torch.float64),
+                            1e6 ** (-torch.arange(hd // 2, dtype=torch.float64) * 2 / hd))
+        cos_d, sin_d = ang_d.cos().float().to(dev), ang_d.sin().float().to(dev)
+        gains = torch.ones(hd, device=dev, dtype=bf)
+        qkv_raw = torch.randn(M, (H + 2 * Hkv) * hd, device=dev).to(bf)
+        case(f"decode attention, finishing its own rows ({n} splits)",
+             lambda i: ops.attention_decode_fresh(qkv_raw, gains, gains, 1e-6, cos_d, sin_d, caches[i][0], caches[i][1], out, seg,
+                                                  pos, tables, M, H, Hkv, hd, page, 0, 1 / math.sqrt(hd), max(1, ctx // 256),
+                                                  scratch), n_caches, M * ctx * Hkv * hd * 4)
     ctx_pad = max(ctx, T) + page
     ang = torch.outer(torch.arange(ctx_pad, dtype=torch.float64), 1e6 ** (-torch.arange(hd // 2, dtype=torch.float64) * 2 / hd))
     cos_t, sin_t = ang.cos().float().to(dev), ang.sin().float().to(dev)
