@@ -35,6 +35,7 @@ DEFAULTS: Dict[str, Tuple[str, str]] = {
     "engine.min-chunk": ("16", "a portion is trimmed to the room left only down to this many rows"),
     "engine.max-running": ("64", "most requests generating at a time"),
     "engine.cuda-graphs": ("true", "replay captured decode steps"),
+    "engine.overlap": ("true", "plan and launch a step while the one before still runs (its tokens are read a step later)"),
     "sampling.temperature": ("0.6", "0 means greedy"),
     "sampling.top-k": ("20", "0 disables"),
     "sampling.top-p": ("0.95", "1 disables"),
@@ -57,7 +58,7 @@ ALIASES = {
     "max-tokens": "sampling.max-tokens", "ignore-eos": "sampling.ignore-eos",
 }
 CLI_ONLY = {"tokens", "random-prompt", "config", "prompt-seed"}
-BOOLEAN_KEYS = {"sampling.ignore-eos", "engine.cuda-graphs"}
+BOOLEAN_KEYS = {"sampling.ignore-eos", "engine.cuda-graphs", "engine.overlap"}
 
 
 class SettingsError(ValueError):
@@ -159,6 +160,7 @@ class Settings:
         self.integer("bench.rounds", 1)
         self.integer("bench.prompt-tokens", 1)
         self.boolean("engine.cuda-graphs")
+        self.boolean("engine.overlap")
         self.sampling()
         return self
 
@@ -200,7 +202,8 @@ def build_engine(s: Settings):
               page_size=s.integer("backend.kv-block"), kv_share=s.number("backend.kv-share"),
               num_pages="auto" if s.get("backend.num-pages") == "auto" else (s.integer("backend.num-pages") or None),
               max_batch_tokens=budget, chunk=batch, min_chunk=s.integer("engine.min-chunk"),
-              max_running=s.integer("engine.max-running"), cuda_graphs=s.boolean("engine.cuda-graphs"))
+              max_running=s.integer("engine.max-running"), cuda_graphs=s.boolean("engine.cuda-graphs"),
+              overlap=s.boolean("engine.overlap"))
     if s.get("model.random-weights"):
         if not s.get("model.config"):
             raise SettingsError("--random-weights needs --model-config <config.json>")
