@@ -233,6 +233,38 @@ def test_gemm_pair(ops, M, N, K):
     assert ops.gemm_tcgen05_error() == 0
 
 
+def test_gemm_pair_random_shapes(ops):
+    """Random shapes of the paired product (rows, columns and k that end anywhere inside tiles, few pairs or all): the
+    one-SM product's bits and the plain float32 product's values; with the last round's tiles cut up over the pairs
+    (their parts are added in another grouping) the values, and the same bits when run again."""
+    import random
+    if ops.resident_pairs() < 1:
+        pytest.skip("the device runs no pair of blocks of this kernel")
+    rng = random.Random(11)
+    for trial in range(14):
+        M = rng.choice([rng.randint(1, 300), rng.randint(300, 1500)])
+        N = rng.choice([rng.randint(1, 600), 8 * rng.randint(1, 400)])
+        K = 8 * rng.randint(1, 160)
+        a, w = rnd(M, K, dtype=torch.bfloat16, seed=trial), rnd(N, K, dtype=torch.bfloat16, seed=100 + trial, scale=0.05)
+        bias = rnd(N, dtype=torch.bfloat16, seed=200 + trial)
+        ld = N + rng.choice([0, 4, 5])
+        base = rnd(M, ld, seed=300 + trial)
+        got, ref = base.clone(), base.clone()
+        pairs, mode = rng.choice([0, 1, 3, 9]), rng.choice([1, 2])
+        ops.gemm_pair(a, w, got[:, :N], bias, accumulate=True, max_pairs=pairs, stream_mode=mode)
+        ops.gemm_tcgen05(a, w, ref[:, :N], bias, accumulate=True)
+        what = f"trial {trial}: M={M} N={N} K={K} ld={ld} pairs={pairs} mode={mode}"
+        assert ops.gemm_tcgen05_error() == 0, what
+        if mode == 2:
+            assert torch.equal(got, ref), what
+        else:
+            again = base.clone()
+            ops.gemm_pair(a, w, again[:, :N], bias, accumulate=True, max_pairs=pairs, stream_mode=mode)
+            assert torch.equal(got, again) and torch.equal(got[:, N:], base[:, N:]), what
+        tol = 1e-4 * math.sqrt(K) * 0.05
+        assert torch.allclose(got[:, :N].cpu(), gemm_want(a, w, bias, base[:, :N]), rtol=1e-4, atol=tol), what
+
+
 @pytest.mark.parametrize("kernel", ["tiles", "pair"])
 @pytest.mark.parametrize("M,N,K", [(300, 1000, 200), (2048, 4096, 512), (129, 260, 136), (31, 36, 64), (513, 7936, 72)])
 def test_gemm_float32_output_by_bulk_copies(ops, M, N, K, kernel):
@@ -577,6 +609,55 @@ def test_attention_decode_fresh(ops, H, Hkv, hd, page, window, norm, how, n):
     assert torch.equal(out_a, out_b)
     assert torch.equal(kc_a.view(torch.int16), kc_b.view(torch.int16)) and torch.equal(vc_a.view(torch.int16), vc_b.view(torch.int16))
     assert torch.equal(work[:, H * hd:], qkv[:, H * hd:])
+
+
+def test_attention_decode_fresh_random_shapes(ops):
+    """Random rows, lengths, splits and page sizes: the attention that finishes its own rows against the row-wise kernel
+    followed by the attention (bits of the output and of the cache)."""
+    import random
+    rng = random.Random(23)
+    for trial in range(10):
+        H, Hkv, hd = rng.choice([(8, 2, 128), (4, 4, 64), (16, 2, 128), (4, 1, 256)])
+        page = rng.choice([1, 4, 16, 32])
+        lens = [rng.choice([1, 2, 63, 64, 65, 128, rng.randint(1, 700)]) for _ in range(rng.randint(1, 9))]
+        R, eps, scale = len(lens), 1e-6, 1.0 / math.sqrt(hd)
+        norm, splits = rng.random() < 0.7, rng.choice([1, 2, 5, 8, 13])
+        pages_of = [-(-L // page) for L in lens]
+        pool = sum(pages_of) + 3
+        order = list(range(pool))
+        rng.shuffle(order)
+        tables = torch.full((R, max(pages_of) + 1), -1, dtype=torch.int32)
+        at = 0
+        for r, npg in enumerate(pages_of):
+            tables[r, :npg] = torch.tensor(order[at:at + npg], dtype=torch.int32)
+            at += npg
+        kc = (rnd(pool, Hkv, page, hd, seed=trial) * 0.5).to(torch.bfloat16)
+        vc = rnd(pool, Hkv, page, hd, seed=50 + trial).to(torch.bfloat16)
+        positions = torch.tensor([L - 1 for L in lens], dtype=torch.int32)
+        slots = torch.tensor([int(tables[r, (L - 1) // page]) * page + (L - 1) % page for r, L in enumerate(lens)],
+                             dtype=torch.int32)
+        qkv = rnd(R, (H + 2 * Hkv) * hd, dtype=torch.bfloat16, seed=70 + trial)
+        qg, kg = (1 + 0.1 * rnd(hd, seed=8)).to(torch.bfloat16), (1 + 0.1 * rnd(hd, seed=9)).to(torch.bfloat16)
+        cos, sin = P.rope_table(range(max(lens) + 1), hd, 10000.0)
+        cos, sin = cos.to(DEV), sin.to(DEV)
+        seg, pos, tab = torch.arange(R, dtype=torch.int32, device=DEV), positions.to(DEV), tables.to(DEV)
+        scratch = torch.full((ops.attention_decode_scratch_floats(R, H, hd, splits) + 1,), float("nan"), device=DEV)
+        work, kc_a, vc_a = qkv.clone(), kc.clone(), vc.clone()
+        ops.qk_norm_rope_store(work, qg if norm else None, kg if norm else None, eps, cos, sin, hd, pos, slots.to(DEV), kc_a,
+                               vc_a, H, Hkv, hd, page)
+        out_a = torch.full((R, H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.attention_decode(work, kc_a, vc_a, out_a, seg, pos, tab, R, H, Hkv, hd, page, 0, scale, splits, scratch)
+        kc_b, vc_b = kc.clone(), vc.clone()
+        out_b = torch.full((R, H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops._call("jllm_attention_decode_fresh", qkv.data_ptr(), qkv.stride(0), qg.data_ptr() if norm else None,
+                  kg.data_ptr() if norm else None, ops._DT[qg.dtype], int(norm), eps, cos.data_ptr(), sin.data_ptr(),
+                  kc_b.data_ptr(), vc_b.data_ptr(), out_b.data_ptr(), out_b.stride(0), seg.data_ptr(), pos.data_ptr(),
+                  tab.data_ptr(), tab.stride(0), R, H, Hkv, hd, page, 0, scale, 0, splits, scratch.data_ptr(), ops._stream())
+        what = f"trial {trial}: heads {H}/{Hkv} of {hd}, page {page}, lens {lens}, {splits} splits, norm {norm}"
+        assert torch.isfinite(out_a.float()).all(), what
+        assert torch.equal(out_a, out_b), what
+        assert torch.equal(kc_a.view(torch.int16), kc_b.view(torch.int16)), what
+        assert torch.equal(vc_a.view(torch.int16), vc_b.view(torch.int16)), what
 
 
 @pytest.mark.parametrize("blocks", [1, 7, 40, 296])
