@@ -25,6 +25,12 @@ CONFIG = dict(model_type="qwen3", architectures=["Qwen3ForCausalLM"], hidden_siz
               attention_bias=False, use_sliding_window=False, max_position_embeddings=40960, hidden_act="silu")
 
 
+# the layer sizes of the other two configurations that are benchmarked (Qwen3-14B, Qwen3-32B: 5,120 wide, 40 or 64 query
+# heads, 17,408 or 25,600 hidden units: 272 and 400 k blocks for the down product)
+OTHER_SIZES = {"14b": dict(CONFIG, hidden_size=5120, num_attention_heads=40, intermediate_size=17408),
+               "32b": dict(CONFIG, hidden_size=5120, num_attention_heads=64, intermediate_size=25600)}
+
+
 def test_bfloat16_follows_float32_at_8b_layer_sizes():
     from jllm_serve_b200.precision_check import compare_precisions
     got = compare_precisions(CONFIG, seed=3)
@@ -55,3 +61,20 @@ def test_bfloat16_follows_float32_with_a_prompt_of_many_rows():
         assert s["rms_rel"] <= 1.3e-2, (name, s)
         assert s["argmax_agree"] >= 0.96, (name, s)
         assert s["worst_choice_gap_rel"] <= 1e-2, (name, s)
+
+
+@pytest.mark.parametrize("size", ["14b", "32b"])
+def test_bfloat16_follows_float32_at_other_layer_sizes(size):
+    """The same at the layer sizes of Qwen3-14B and Qwen3-32B, with a short prompt (128-row tiles, the weight-stream
+    products) and with one of 1,280 rows (two SMs to a tile)."""
+    from jllm_serve_b200.precision_check import compare_precisions
+    for kw in (dict(prompt=300, tail=16, portion=256), dict(prompt=1280, tail=4, portion=1024)):
+        got = compare_precisions(OTHER_SIZES[size], seed=1, **kw)
+        print(f"{size}, two layers, {kw}: {got}")
+        for name in ("alone", "mixed"):
+            s = got[name]
+            assert s["rows"] >= kw["prompt"] + kw["tail"]
+            assert s["max_rel"] <= 1.5e-2, (size, name, s)
+            assert s["rms_rel"] <= 1.3e-2, (size, name, s)
+            assert s["argmax_agree"] >= 0.96, (size, name, s)
+            assert s["worst_choice_gap_rel"] <= 1e-2, (size, name, s)
