@@ -12,7 +12,9 @@ the back of the prefill line, so prompts alternate (docs/25:133-134).
 
 Admission is first come, first served (the reference's classes, aging and sessions,
 engine/Admission.java:217-285, are not built): a waiting request starts when fewer than
-`max_running` run and the pages of its first portion are free.
+`max_running` run and there are free pages for all the tokens it has (prompt and, after a preemption, what it had
+generated) and one more, and a page to spare for every request that runs already; with nothing else running it
+starts if its first portion fits.
 
 When pages run out. A step's pages are reserved before it runs. If the pool cannot cover
 a step, the most recently admitted running request is preempted: its pages go back, it
@@ -192,13 +194,22 @@ class Scheduler:
         while self.waiting and len(self.running) < self.max_running:
             r = self.waiting[0]
             first = min(r.remaining, self.chunk, self.budget)
+            # Room for everything it has so far (its prompt, and what it had generated when it was preempted) and one
+            # token more, not only for its first portion: a request that starts on less is preempted as soon as it has
+            # grown, and one that was preempted would come back into the room it has just given up, again and again.
+            # ... beside what the running requests still lack for the tokens THEY have (one that was admitted a moment
+            # ago holds nothing yet), and a page of growth for each of them.
+            if self.running:
+                page = self.cache.page_size
+                owed = sum(max(0, -(-(len(q.prompt) + len(q.output) + 1) // page) - -(-q.launched // page))
+                           for q in self.running)
+                if not self._fits_now(r, r.remaining + 1, spare_pages=owed + len(self.running)):
+                    break
             if not self._fits_now(r, first + 1):
-                if not self.running:
-                    # alone in an empty pool and still no room: it can never run
-                    self.waiting.pop(0)
-                    self._finish(r, "kv_exhausted")
-                    continue
-                break
+                # alone in an empty pool and still no room for its first portion: it can never run
+                self.waiting.pop(0)
+                self._finish(r, "kv_exhausted")
+                continue
             self.waiting.pop(0)
             r.state, r.admitted = RUNNING, next(self._admissions)
             self.running.append(r)
@@ -206,12 +217,12 @@ class Scheduler:
             if r.remaining > 1:
                 self.prefill_line.append(r)
 
-    def _fits_now(self, r: Request, rows: int) -> bool:
+    def _fits_now(self, r: Request, rows: int, spare_pages: int = 0) -> bool:
         rows = min(rows, self.ctx - r.launched)
         if self.cache.is_open(r.id):
             return self.cache.can_reserve(r.id, r.launched, rows)
         missing = -(-(r.launched + rows) // self.cache.page_size)
-        return all(missing <= free for free in self.cache.free_pages())
+        return all(missing + spare_pages <= free for free in self.cache.free_pages())
 
     def plan(self, inflight: Optional[Sequence["PlannedSegment"]] = None) -> Optional[List[PlannedSegment]]:
         """Admits, picks the step's segments and reserves their pages (preempting if the pool is short). With

@@ -86,9 +86,9 @@ def test_the_steps_generate_forms_replayed_with_every_row_wanted(name, dtype):
     from jllm_serve_b200.engine import Engine, ModelRunner, Segment
     from jllm_serve_b200.sampling import SamplingParams
     vocab = CONFIGS[name]["vocab_size"]
-    lengths = (300, 150, 420, 280, 510, 200, 345, 180)
+    lengths = (300, 150, 420, 280, 510, 200, 345, 180, 390, 260, 470, 330)
     prompts = [random_tokens(n, vocab, 90 + i) for i, n in enumerate(lengths)]
-    engine = Engine(model_folder(name), dtype=dtype, page_size=16, max_tokens_cached=1536, max_batch_tokens=300,
+    engine = Engine(model_folder(name), dtype=dtype, page_size=16, max_tokens_cached=1280, max_batch_tokens=300,
                     chunk=260, min_chunk=16, max_running=6, ctx=1024)
     log = []
     step, close = engine.runner.step, engine.runner.cache.close

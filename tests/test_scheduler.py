@@ -156,17 +156,67 @@ def test_max_running_and_first_come_first_served():
 
 
 def test_preempts_the_newest_when_pages_run_out_and_recomputes():
-    # 6 pages of 4 positions: two requests of 8 + up to 8 new tokens cannot both stay
-    s, cache = make(pages=6, page_size=4, budget=32, chunk=16, max_running=2)
-    s.add(Request("old", list(range(8)), SamplingParams.greedy_params(8)))
-    s.add(Request("new", list(range(8)), SamplingParams.greedy_params(8)))
+    # 8 pages of 4 positions: two requests of 8 tokens both start (3 pages each with the token to come, and one to
+    # spare), but with up to 12 new tokens each (5 pages in the end) they cannot both stay
+    s, cache = make(pages=8, page_size=4, budget=32, chunk=16, max_running=2)
+    s.add(Request("old", list(range(8)), SamplingParams.greedy_params(12)))
+    s.add(Request("new", list(range(8)), SamplingParams.greedy_params(12)))
     steps = drive(s, cache)
     assert s.preemptions >= 1 and s.finished["new"].preemptions >= 1 and s.finished["old"].preemptions == 0
-    assert len(s.finished["old"].output) == 8 and len(s.finished["new"].output) == 8
+    assert len(s.finished["old"].output) == 12 and len(s.finished["new"].output) == 12
     # after its preemption `new` is prefilled again from position 0 with what it had generated so far
     restarts = [x for st in steps for x in st if x[0] == "new" and x[1] == 0]
     assert len(restarts) >= 2 and restarts[-1][2] > 8
-    assert cache.free_pages() == [6]
+    assert cache.free_pages() == [8]
+
+
+def test_a_waiting_request_starts_when_all_it_has_fits_not_only_its_first_portion():
+    # 10 pages of 4 positions. `a` (8 tokens, 20 more to come) runs; `b` has 28 tokens: 8 pages with the token to come,
+    # beside the pages `a` still lacks for its own tokens and a page to spare for it: more than there are. Its first
+    # portion (16 rows) would fit at once, and started on that it would be preempted when `a` has grown. It waits for
+    # `a` to end instead; nothing is preempted.
+    s, cache = make(pages=10, page_size=4, budget=32, chunk=16, max_running=2)
+    s.add(Request("a", list(range(8)), SamplingParams.greedy_params(20)))
+    s.add(Request("b", list(range(28)), SamplingParams.greedy_params(4)))
+    steps = drive(s, cache)
+    assert s.preemptions == 0
+    last_a = max(i for i, st in enumerate(steps) if any(x[0] == "a" for x in st))
+    first_b = min(i for i, st in enumerate(steps) if any(x[0] == "b" for x in st))
+    assert first_b > last_a
+    assert len(s.finished["a"].output) == 20 and len(s.finished["b"].output) == 4
+    # with 23 tokens (6 pages, beside the 3 that `a` still lacks and the one to spare) it starts beside `a` at once
+    s, cache = make(pages=10, page_size=4, budget=32, chunk=16, max_running=2)
+    s.add(Request("a", list(range(8)), SamplingParams.greedy_params(4)))
+    s.add(Request("b", list(range(23)), SamplingParams.greedy_params(1)))
+    steps = drive(s, cache)
+    assert any(x[0] == "b" for x in steps[1]) and s.preemptions == 0
+    # alone in the pool a request starts on its first portion even if all of it will never fit (it ends when the pool does)
+    s, cache = make(pages=4, page_size=4, budget=32, chunk=8, max_running=2)
+    s.add(Request("long", list(range(15)), SamplingParams.greedy_params(9)))
+    drive(s, cache)
+    assert s.finished["long"].finish_reason == "kv_exhausted" and len(s.finished["long"].output) == 2
+
+
+def test_a_preempted_request_does_not_come_back_into_the_room_it_gave_up():
+    """Many growing requests in a pool that holds a third of them: a request that was preempted waits until all it has
+    fits again, so preemptions stay few (started on its first portion alone it came back at once, was preempted again as
+    soon as it had grown, and every time its prompt was computed anew)."""
+    rng = random.Random(5)
+    s, cache = make(pages=60, page_size=4, budget=48, chunk=32, max_running=12, ctx=256)
+    want = {}
+    for i in range(30):
+        n, m = rng.randrange(8, 60), rng.randrange(10, 40)
+        s.add(Request(f"r{i}", [rng.randrange(50) for _ in range(n)], SamplingParams.greedy_params(m)))
+        want[f"r{i}"] = (n, m)
+    steps = drive(s, cache, token_of=lambda r: len(r.output))
+    assert set(s.finished) == set(want)
+    for rid, (n, m) in want.items():
+        assert s.finished[rid].output == list(range(m))
+    computed = sum(rows for st in steps for _, _, rows, _ in st)
+    needed = sum(n + m - 1 for n, m in want.values())
+    print(f"preemptions {s.preemptions}, rows computed {computed} for {needed} needed")
+    assert s.preemptions <= len(want) and computed <= 1.5 * needed
+    assert cache.free_pages() == [60]
 
 
 def test_request_that_can_never_fit_ends_with_kv_exhausted():
@@ -294,7 +344,7 @@ def test_planning_one_step_ahead_gives_the_same_outputs():
             s.add(Request(f"q{i}", [(i + t) % 50 for t in range(n)], SamplingParams.greedy_params(new)))
         return s, cache
 
-    for pages in (64, 14):           # roomy, and so tight that requests are preempted and recomputed
+    for pages in (64, 11):           # roomy, and so tight that a request is preempted and recomputed
         a, _ = make(pages)
         want, sync_steps = drive_ahead(a, token_of, ahead=False)
         b, cache = make(pages)
@@ -311,5 +361,5 @@ def test_planning_one_step_ahead_gives_the_same_outputs():
                     assert len(toks) == 1 and wanting[-toks[0] - 1] == rid
         assert not cache.requests and cache.free_pages() == [pages]
         cache.check()
-        if pages == 14:
+        if pages == 11:
             assert a.preemptions > 0 and b.preemptions > 0
