@@ -36,6 +36,7 @@ DEFAULTS: Dict[str, Tuple[str, str]] = {
     "engine.max-running": ("64", "most requests generating at a time"),
     "engine.cuda-graphs": ("true", "replay captured decode steps"),
     "engine.overlap": ("true", "plan and launch a step while the one before still runs (its tokens are read a step later)"),
+    "engine.fill-portions": ("true", "a step with room left takes the next prompts' portions too (false: one portion a step)"),
     "sampling.temperature": ("0.6", "0 means greedy"),
     "sampling.top-k": ("20", "0 disables"),
     "sampling.top-p": ("0.95", "1 disables"),
@@ -58,7 +59,7 @@ ALIASES = {
     "max-tokens": "sampling.max-tokens", "ignore-eos": "sampling.ignore-eos",
 }
 CLI_ONLY = {"tokens", "random-prompt", "config", "prompt-seed"}
-BOOLEAN_KEYS = {"sampling.ignore-eos", "engine.cuda-graphs", "engine.overlap"}
+BOOLEAN_KEYS = {"sampling.ignore-eos", "engine.cuda-graphs", "engine.overlap", "engine.fill-portions"}
 
 
 class SettingsError(ValueError):
@@ -161,6 +162,7 @@ class Settings:
         self.integer("bench.prompt-tokens", 1)
         self.boolean("engine.cuda-graphs")
         self.boolean("engine.overlap")
+        self.boolean("engine.fill-portions")
         self.sampling()
         return self
 
@@ -203,7 +205,7 @@ def build_engine(s: Settings):
               num_pages="auto" if s.get("backend.num-pages") == "auto" else (s.integer("backend.num-pages") or None),
               max_batch_tokens=budget, chunk=batch, min_chunk=s.integer("engine.min-chunk"),
               max_running=s.integer("engine.max-running"), cuda_graphs=s.boolean("engine.cuda-graphs"),
-              overlap=s.boolean("engine.overlap"))
+              overlap=s.boolean("engine.overlap"), fill_portions=s.boolean("engine.fill-portions"))
     if s.get("model.random-weights"):
         if not s.get("model.config"):
             raise SettingsError("--random-weights needs --model-config <config.json>")

@@ -56,12 +56,14 @@ class Engine:
                  num_pages=None, max_tokens_cached: Optional[int] = None,
                  max_batch_tokens: int = 2048, chunk: int = 512, min_chunk: int = 16, max_running: int = 64,
                  sample_vocab: Optional[int] = None, cuda_graphs: bool = True, kv_share: float = 0.6,
-                 overlap: bool = True):
+                 overlap: bool = True, fill_portions: bool = True):
         """`num_pages`: pages of the cache pool, or "auto" for the share `kv_share` of the device memory that is
         free once the weights are loaded; without it the pool holds `max_tokens_cached` tokens (default: four
         full contexts). `overlap`: a step is planned and launched while the step before it still runs, its sampled
         tokens going from one step into the next on the device; the host reads them one step later (what `step_once`
-        returns lags by a step; `run_until_done` and `generate` do not care)."""
+        returns lags by a step; `run_until_done` and `generate` do not care). `fill_portions`: a step whose first prompt
+        portion left room in `max_batch_tokens` takes the portions of the next waiting prompts too (False: one portion
+        to a step, as the reference plans its passes)."""
         self.runner = ModelRunner(model_dir, config=config, seed=seed, dtype=dtype, device=device,
                                   page_size=page_size, num_pages=num_pages, max_tokens=max_tokens_cached,
                                   max_batch_tokens=max_batch_tokens, max_requests=max_running, ctx=ctx,
@@ -69,7 +71,8 @@ class Engine:
         core = self.runner.spec.core
         self.scheduler = Scheduler(self.runner.cache, self.runner.ctx, max_batch_tokens, chunk, min_chunk, max_running,
                                    eos_ids=core.eos, commits=False,       # the runner commits every step it ran
-                                   row_quantum=ops.TILE_ROWS if self.runner.dtype == torch.bfloat16 else 0)
+                                   row_quantum=ops.TILE_ROWS if self.runner.dtype == torch.bfloat16 else 0,
+                                   fill_portions=fill_portions)
         self.sampler = Sampler(self.runner.device, max_running, core.vocab, sample_vocab)
         self._rngs = {}
         self._times = {}

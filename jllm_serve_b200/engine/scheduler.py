@@ -8,7 +8,9 @@ rides along with its one token, in order of arrival, while it fits the budget; t
 prompt portion, the head of the prefill line, takes what is left, trimmed to the room, but
 only if that is at least `min_chunk` rows (or all the portion needs); if nothing fits, the
 oldest item goes alone, so a pass is never empty. A prompt that has run a portion goes to
-the back of the prefill line, so prompts alternate (docs/25:133-134).
+the back of the prefill line, so prompts alternate (docs/25:133-134). Beyond that rule, a pass whose head portion
+left room takes the portions of the next prompts in the line too (`_more_portions`; `fill_portions=False` is the
+reference's one portion to a pass).
 
 Admission is first come, first served (the reference's classes, aging and sessions,
 engine/Admission.java:217-285, are not built): a waiting request starts when fewer than
@@ -152,10 +154,13 @@ class PlannedSegment:
 
 class Scheduler:
     def __init__(self, cache, ctx: int, max_batch_tokens: int, chunk: int = 512, min_chunk: int = 16,
-                 max_running: int = 64, eos_ids: Sequence[int] = (), commits: bool = True, row_quantum: int = 0):
+                 max_running: int = 64, eos_ids: Sequence[int] = (), commits: bool = True, row_quantum: int = 0,
+                 fill_portions: bool = True):
         """`commits`: whether `plan` records the new lengths in the cache when it hands a step out (False when whoever
-        runs the steps does that itself, as the model runner does at launch). `row_quantum`: see `plan_pass`."""
+        runs the steps does that itself, as the model runner does at launch). `row_quantum`: see `plan_pass`.
+        `fill_portions`: see `_more_portions`."""
         self.cache, self.ctx, self.commits, self.row_quantum = cache, ctx, commits, row_quantum
+        self.fill_portions = fill_portions
         self.budget, self.chunk, self.min_chunk, self.max_running = max_batch_tokens, chunk, min_chunk, max_running
         self.eos = set(eos_ids)
         self.waiting: List[Request] = []
@@ -244,6 +249,8 @@ class Scheduler:
             if not items:
                 return []
             picks = plan_pass(items, self.budget, self.min_chunk, self.row_quantum)
+            if self.fill_portions:
+                picks = self._more_portions(picks, items)
             try:      # pages for every pick, or for none
                 self.cache.reserve_all([p.ref.id for p in picks], [p.ref.launched for p in picks],
                                        [p.rows for p in picks])
@@ -280,6 +287,29 @@ class Scheduler:
                 if self.commits:       # as the model runner does when it launches a step: the rows count as written
                     self.cache.commit(seg.request.id, seg.request.launched)
             return segments
+
+    def _more_portions(self, picks: List[Pick], items: Sequence[Item]) -> List[Pick]:
+        """Beyond the reference's rule (one prompt portion to a pass): if the head of the prefill line got all the rows it
+        asked for and the budget has room left, the portions of the prompts behind it are taken too, in the line's order,
+        each whole or cut to the room as the head would be. The reference's passes are sized for a GPU that a portion of
+        512 rows fills; here a step streams every weight once whatever its rows, and thirty prompts of fifty tokens that
+        arrive together should cost two steps, not thirty. The portions stay in front of the single rows."""
+        chunks = [i for i in items if i.kind == "chunk"]
+        if not picks or picks[0].kind != "chunk" or len(chunks) < 2 or picks[0].rows < chunks[0].rows:
+            return picks
+        used, more, q = sum(p.rows for p in picks), [], self.row_quantum
+        for it in chunks[1:]:
+            rows = min(it.rows, self.budget - used)
+            over = (used + rows) % q if q > 1 else 0
+            if over and used + rows > q and (it.more or rows < it.rows) and rows - over >= max(self.min_chunk, 1):
+                rows -= over
+            if rows < 1 or rows < min(self.min_chunk, it.rows):
+                break
+            more.append(Pick(it.ref, "chunk", rows))
+            used += rows
+            if rows < it.rows:
+                break
+        return picks[:1] + more + picks[1:]
 
     def _full(self, r: Request) -> bool:
         """With the tokens it has and those on their way the request has all it may have."""

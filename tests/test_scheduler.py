@@ -70,10 +70,11 @@ def test_a_chunk_that_is_cut_anyway_is_cut_at_a_whole_number_of_tiles():
 
 # ---- the scheduler over a real cache manager, with a fake model -------------------------------------------
 
-def make(pages=64, page_size=4, budget=32, chunk=16, max_running=4, ctx=256, eos=(), row_quantum=0):
+def make(pages=64, page_size=4, budget=32, chunk=16, max_running=4, ctx=256, eos=(), row_quantum=0, fill_portions=False):
+    """(`fill_portions` off: the reference's one prompt portion to a pass, which most of these tests pin.)"""
     cache = CacheManager([PagedKeysValues(1, 8)], page_size, pages, max_running)
     return Scheduler(cache, ctx, budget, chunk, min_chunk=4, max_running=max_running, eos_ids=eos,
-                     row_quantum=row_quantum), cache
+                     row_quantum=row_quantum, fill_portions=fill_portions), cache
 
 
 def drive(s, cache, token_of=lambda r: 7, limit=10000):
@@ -117,6 +118,49 @@ def test_prompt_is_cut_into_portions_and_decoding_rides_along():
     assert s.finished["a"].output == [7, 7, 7] and s.finished["a"].finish_reason == "length"
     assert len(s.finished["b"].output) == 6
     assert cache.free_pages() == [64] and not cache.requests
+
+
+def test_a_pass_with_room_takes_the_next_prompts_portions_too():
+    """Beyond the reference's rule: when the head of the prefill line got all it asked for, the prompts behind it are
+    taken into the same pass while the budget lasts, the last one cut to the room (never below the smallest portion,
+    and with a row quantum to a whole number of tiles); portions stay in front of the single rows."""
+    s, cache = make(budget=32, chunk=16, fill_portions=True)
+    s.add(Request("a", list(range(40)), SamplingParams.greedy_params(3)))
+    s.add(Request("b", list(range(5)), SamplingParams.greedy_params(6)))
+    s.add(Request("c", list(range(30)), SamplingParams.greedy_params(2)))
+    steps = drive(s, cache)
+    assert steps[0] == [("a", 0, 16, False), ("b", 0, 5, True), ("c", 0, 11, False)]      # 16 + 5 + 11 = the budget
+    assert steps[1] == [("a", 16, 16, False), ("c", 11, 15, False), ("b", 5, 1, True)]     # c asked for 16: cut to the room
+    assert all(sum(x[2] for x in st) <= 32 for st in steps)
+    for st in steps:                                             # portions first, then the single rows of decoding requests
+        kinds = [rows > 1 or not wants for _, _, rows, wants in st]
+        assert kinds == sorted(kinds, reverse=True), st
+    assert [len(s.finished[r].output) for r in "abc"] == [3, 6, 2] and cache.free_pages() == [64]
+    # thirty short prompts that arrive together: a few passes, not thirty
+    s, cache = make(pages=400, budget=64, chunk=16, max_running=30, fill_portions=True)
+    for i in range(30):
+        s.add(Request(f"p{i}", list(range(6)), SamplingParams.greedy_params(2)))
+    steps = drive(s, cache)
+    assert len(steps) <= 5 and sum(rows for _, _, rows, _ in steps[0]) == 64        # ten whole prompts and four rows of the next
+    one, cache1 = make(pages=400, budget=64, chunk=16, max_running=30)
+    for i in range(30):
+        one.add(Request(f"p{i}", list(range(6)), SamplingParams.greedy_params(2)))
+    assert len(drive(one, cache1)) >= 30
+    # a head that the budget cut leaves no room: nothing is added; a portion that would fall below the smallest waits
+    s, cache = make(budget=20, chunk=16, fill_portions=True)
+    s.add(Request("a", list(range(16)), SamplingParams.greedy_params(2)))
+    s.add(Request("b", list(range(30)), SamplingParams.greedy_params(2)))
+    steps = drive(s, cache)
+    assert steps[0] == [("a", 0, 16, True), ("b", 0, 4, False)]          # 4 rows: the smallest portion
+    s, cache = make(budget=19, chunk=16, fill_portions=True)
+    s.add(Request("a", list(range(16)), SamplingParams.greedy_params(2)))
+    s.add(Request("b", list(range(30)), SamplingParams.greedy_params(2)))
+    assert drive(s, cache)[0] == [("a", 0, 16, True)]                    # 3 rows of room: below it
+    # with a row quantum the last portion is cut so that the pass is a whole number of tiles
+    s, cache = make(pages=200, budget=64, chunk=30, row_quantum=8, fill_portions=True)
+    s.add(Request("a", list(range(30)), SamplingParams.greedy_params(2)))
+    s.add(Request("b", list(range(100)), SamplingParams.greedy_params(2)))
+    assert drive(s, cache)[0] == [("a", 0, 30, True), ("b", 0, 26, False)]        # 30 + 30 would be 60: cut to 56
 
 
 def test_stop_token_ends_without_being_emitted():
