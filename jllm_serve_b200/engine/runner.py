@@ -8,6 +8,7 @@ trace replay, the benchmark and the tests all go through this one function.
 """
 from __future__ import annotations
 
+import gc
 import json
 from pathlib import Path
 from typing import Hashable, List, Optional, Sequence
@@ -248,8 +249,18 @@ class ModelRunner:
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count
-            with torch.cuda.graph(graph):
-                self.model.forward(batch, self.cache, self._static_logits)
+            # Nothing may destroy another CUDA graph while this one is captured (the driver forbids it and the capture
+            # is lost): the garbage collector could, if it found an abandoned runner's graphs just now. It runs before
+            # the capture and is held off during it.
+            gc.collect()
+            collecting = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph):
+                    self.model.forward(batch, self.cache, self._static_logits)
+            finally:
+                if collecting:
+                    gc.enable()
             if len(self._graphs) >= self.max_graphs:       # the shape that was captured first makes room
                 oldest = next(iter(self._graphs))
                 del self._graphs[oldest], self._graph_kernels[oldest]

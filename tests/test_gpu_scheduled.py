@@ -113,7 +113,7 @@ def test_the_steps_generate_forms_replayed_with_every_row_wanted(name, dtype):
     runner = ModelRunner(model_folder(name), dtype=dtype, page_size=16, num_pages=96, max_batch_tokens=300,
                          max_requests=6, ctx=1024, poison_freed_pages=True)
     checker = RowChecker(model_folder(name), sequences, dtype, what=f"{name} generate's steps")
-    shaped = 0
+    shaped = several = 0
     for kind, what in log:
         if kind == "end":
             runner.finish(what)
@@ -128,6 +128,7 @@ def test_the_steps_generate_forms_replayed_with_every_row_wanted(name, dtype):
         rows = runner.step(segs).float().cpu()
         b = runner.last_batch
         shaped += b.multi_segments > 0 and b.multi_rows > 128 and b.rows > b.multi_rows
+        several += b.multi_segments > 1          # a step with room took a second prompt's portion too
         r = 0
         for rid, toks, start in what:
             for k in range(len(toks)):
@@ -139,3 +140,4 @@ def test_the_steps_generate_forms_replayed_with_every_row_wanted(name, dtype):
         checker.seen.add((rid, len(toks) - 1))
     checker.finish()
     assert shaped >= 10, f"only {shaped} steps had a portion of more than 128 rows before single rows"
+    assert several >= 3, f"only {several} steps held portions of more than one prompt"
