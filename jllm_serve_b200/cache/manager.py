@@ -195,6 +195,11 @@ class CacheManager:
             for g in self.fixed:
                 g.storage = allocate((len(g.runs), max_requests) + tuple(g.need.shape), g.need.dtype)
 
+    def release_storage(self) -> None:
+        """Lets go of the groups' device storage now (the books stay): for a runner that is being closed."""
+        for g in list(self.paged) + list(self.fixed):
+            g.storage = None
+
     def __del__(self):
         try:
             if getattr(self, "_ptr", None):

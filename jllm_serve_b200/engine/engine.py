@@ -159,6 +159,20 @@ class Engine:
         ops.check_kernel_errors()          # a kernel that gave up on a bounded wait must not pass for a result
         return finished
 
+    def close(self) -> None:
+        """The engine's device memory (weights, cache, captured steps) is let go now; the engine cannot step afterwards.
+        Also at the end of a `with Engine(...) as engine:` block."""
+        self._inflight = None
+        self.runner.close()
+        self.sampler = None
+        self.scheduler = None
+
+    def __enter__(self) -> "Engine":
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self.close()
+
     def result_of(self, rid: Hashable) -> Result:
         r = self.scheduler.finished[rid]
         t = self._times[rid]

@@ -275,6 +275,23 @@ class ModelRunner:
             return logits_out[:batch.num_wanted]
         return out
 
+    def close(self) -> None:
+        """Lets go of what the runner holds on the device (captured graphs, the model, the cache), now and not when the
+        garbage collector gets to it: a program that builds one runner after another need not hold two at a time. The
+        runner cannot step afterwards."""
+        torch.cuda.synchronize(self.device)
+        self._graphs.clear()
+        self._graph_kernels.clear()
+        self._graph_seen.clear()
+        self._static_logits = None
+        self.model = None
+        if self.cache is not None:
+            self.cache.release_storage()       # (the manager and its books are a cycle: the collector's, later)
+        self.cache = None
+        self.builder = None
+        self.last_batch = None
+        self.runtime._buffers.clear()
+
     def finish(self, request: Hashable) -> None:
         """The request is over: everything it holds is given back."""
         if not self.cache.is_open(request):

@@ -103,6 +103,7 @@ def compare_precisions(config: dict, seed: int = 0, prompt: int = 300, tail: int
 
     exact = ModelRunner(dtype="float32", **kw)
     want = _rows_of(exact, alone + whole_sides)
+    exact.close()
     del exact
     torch.cuda.empty_cache()
     fast = ModelRunner(dtype="bfloat16", **kw)
@@ -117,6 +118,7 @@ def compare_precisions(config: dict, seed: int = 0, prompt: int = 300, tail: int
             st.add(row, want[key])
         out[name] = st.summary()
     out["mixed"]["largest_step_rows"] = portion + len(others)
+    fast.close()
     del fast
     torch.cuda.empty_cache()
     return out

@@ -168,3 +168,32 @@ def test_seeded_sampling_is_the_same_with_and_without_planning_ahead():
     a = engine_for("B", "float32", overlap=False).generate(prompts, params)
     b = engine_for("B", "float32", overlap=True).generate(prompts, params)
     assert [r.tokens for r in a] == [r.tokens for r in b]
+
+
+def test_a_closed_engine_gives_its_device_memory_back_at_once(tmp_path):
+    """`with Engine(...)`: at the end of the block the weights, the cache and the captured steps are let go without
+    waiting for the garbage collector, so the next engine finds the memory (and no graph dies in mid-capture later)."""
+    import gc
+
+    import torch
+    from jllm_serve_b200.engine import Engine
+    from jllm_serve_b200.sampling import SamplingParams
+    folder = model_folder("B")
+    gc.collect()
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    before = torch.cuda.memory_allocated()
+    gc.disable()
+    try:
+        with Engine(folder, dtype="bfloat16", page_size=8, max_tokens_cached=4096, max_batch_tokens=64, chunk=32,
+                    max_running=4, ctx=256) as engine:
+            out = engine.generate([[1, 2, 3], [4, 5, 6, 7]], SamplingParams.greedy_params(12, ignore_eos=True))
+            assert len(out[0].tokens) == 12 and engine.runner._graphs          # decode steps were captured
+            held = torch.cuda.memory_allocated() - before
+            assert held > 1 << 20
+        left = torch.cuda.memory_allocated() - before
+    finally:
+        gc.enable()
+    assert left <= held // 20, f"{left} of {held} bytes are still held after close()"
+    with pytest.raises(Exception):
+        engine.generate([[1, 2]], SamplingParams.greedy_params(2))
