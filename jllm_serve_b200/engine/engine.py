@@ -95,6 +95,17 @@ class Engine:
         self._times[rid] = {"start": time.perf_counter(), "first": None, "end": None}
         return rid
 
+    def cancel(self, request_id: Hashable) -> bool:
+        """Ends the request now (finish reason "cancelled"; `result_of` gives what it had generated). Its pages go back
+        at once; a step in flight that still carries a row of it runs on, and the row is ignored. False if there is no
+        such request or it has ended already."""
+        r = self.scheduler.cancel(request_id)
+        if r is None:
+            return False
+        self._times[request_id]["end"] = time.perf_counter()
+        self._rngs.pop(request_id, None)
+        return True
+
     def step_once(self) -> List[Request]:
         """One scheduler step: plan, launch, and read the tokens of the step before (without `overlap`: of this
         step). Returns the requests that finished, those included that the scheduler ended while planning because

@@ -185,6 +185,20 @@ class Scheduler:
         request.state = WAITING
         self.waiting.append(request)
 
+    def cancel(self, request_id: Hashable) -> Optional[Request]:
+        """Ends a waiting or running request now, with the reason "cancelled" (the reference: engine/Engine.java:668-671):
+        what it holds is given back, what it has generated so far stays its output. Rows of it that a step in flight
+        still carries are passed over when that step is completed, as those of a request that a stop token ended. None if
+        there is no such request, or it has ended already."""
+        for r in self.waiting + self.running:
+            if r.id == request_id:
+                if r in self.waiting:
+                    self.waiting.remove(r)
+                self._release(r)
+                self._finish(r, "cancelled")
+                return r
+        return None
+
     def has_work(self) -> bool:
         return bool(self.waiting or self.running)
 

@@ -197,3 +197,34 @@ def test_a_closed_engine_gives_its_device_memory_back_at_once(tmp_path):
     assert left <= held // 20, f"{left} of {held} bytes are still held after close()"
     with pytest.raises(Exception):
         engine.generate([[1, 2]], SamplingParams.greedy_params(2))
+
+
+@pytest.mark.parametrize("overlap", [False, True])
+def test_cancel_in_the_middle_leaves_the_others_as_they_are_alone(overlap):
+    """Three requests step by step through the entry point's own loop; one is cancelled while it decodes (with planning
+    ahead: while a step that carries its row is in flight), one while it still waits. The cancelled ones end with
+    "cancelled" and the tokens they had; the third's tokens are those it generates alone; a request added afterwards
+    takes the pages that came back and is right too; nothing is left in the cache."""
+    from jllm_serve_b200.sampling import SamplingParams
+    name = "B"
+    cfg, w = P.load_plain(model_folder(name))
+    prompts = prompts_for(name, (21, 40, 9, 30), seed=77)
+    params = SamplingParams.greedy_params(20, ignore_eos=True)
+    with engine_for(name, "float32", overlap=overlap, max_running=2, max_tokens_cached=160) as eng:
+        a, b, c = (eng.add_request(p, params) for p in prompts[:3])      # two may run: c waits
+        for _ in range(9):
+            eng.step_once()
+        running = {r.id for r in eng.scheduler.running}
+        assert running == {a, b} and [r.id for r in eng.scheduler.waiting] == [c]
+        assert eng.cancel(c) and eng.cancel(a) and not eng.cancel(a)
+        d = eng.add_request(prompts[3], params)
+        eng.run_until_done()
+        ra, rb, rc, rd = (eng.result_of(i) for i in (a, b, c, d))
+        assert rc.finish_reason == "cancelled" and rc.tokens == []
+        want_a = P.greedy_generate(cfg, w, prompts[0], 20)
+        assert ra.finish_reason == "cancelled" and 1 <= len(ra.tokens) < 20 and ra.tokens == want_a[:len(ra.tokens)]
+        assert rb.finish_reason == "length" and rb.tokens == P.greedy_generate(cfg, w, prompts[1], 20)
+        assert rd.finish_reason == "length" and rd.tokens == P.greedy_generate(cfg, w, prompts[3], 20)
+        assert not eng.runner.cache.requests and eng._inflight is None
+        eng.runner.cache.check()
+        assert eng.runner.cache.free_pages() == [20]

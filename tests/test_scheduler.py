@@ -407,3 +407,36 @@ def test_planning_one_step_ahead_gives_the_same_outputs():
         cache.check()
         if pages == 11:
             assert a.preemptions > 0 and b.preemptions > 0
+
+
+def test_cancel_ends_a_waiting_or_running_request_and_frees_its_pages():
+    """`cancel` ends a request where it stands: one that waits never starts; one that runs gives its pages back at
+    once and keeps what it had generated; a row of it in a step that is still in flight is passed over when the step
+    completes, and the others in that step are untouched. A second cancel, or one of an unknown request, is None."""
+    s, cache = make(pages=16, max_running=2)
+    for name, n in (("a", 6), ("b", 5), ("c", 7)):
+        s.add(Request(name, list(range(1, n + 1)), SamplingParams.greedy_params(8)))
+    for _ in range(4):                                                  # a and b decode; c waits (two may run)
+        plan = s.plan()
+        s.complete(plan, [7 for p in plan if p.wants_logits])
+    assert {r.id for r in s.running} == {"a", "b"} and [r.id for r in s.waiting] == ["c"]
+    assert s.cancel("c").finish_reason == "cancelled" and not s.waiting and s.finished["c"].output == []
+    held = cache.free_pages()[0]
+    inflight = s.plan()                                                 # a step with a row of a and a row of b ...
+    assert sorted(p.request.id for p in inflight) == ["a", "b"]
+    had = list(next(r for r in s.running if r.id == "a").output)
+    gone = s.cancel("a")                                                # ... and a is cancelled before it is read
+    assert gone.finish_reason == "cancelled" and gone.output == had and len(had) >= 1
+    assert cache.free_pages()[0] > held and not cache.is_open("a")
+    cache.check()
+    after = s.plan(inflight=inflight)                                   # planned ahead: b alone, a's row is gone
+    assert [p.request.id for p in after] == ["b"]
+    b_before = len(next(r for r in s.running if r.id == "b").output)
+    done = s.complete(inflight, [9, 9])
+    assert done == [] and gone.output == had                            # a's token of that step is dropped
+    assert len(next(r for r in s.running if r.id == "b").output) == b_before + 1
+    assert s.cancel("a") is None and s.cancel("nobody") is None
+    s.complete(after, [7])
+    drive(s, cache)
+    assert s.finished["b"].finish_reason == "length" and len(s.finished["b"].output) == 8
+    assert cache.free_pages() == [16] and not cache.requests
