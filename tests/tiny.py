@@ -50,3 +50,31 @@ def make_model_folder(config: dict, seed: int, where=None, vector_dtype=None) ->
 def random_tokens(n: int, vocab: int, seed: int) -> list:
     g = torch.Generator().manual_seed(seed)
     return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+
+def random_config(seed: int) -> dict:
+    """A configuration drawn from everything the architecture's keys allow at tiny sizes: head sizes in steps of 16 up
+    to 256, any number of heads and groups (also odd ones), widths and vocabularies that are no powers of two, with and
+    without window, biases, tied head, linear or yarn scaling, partial rotary."""
+    import random
+    rng = random.Random(seed)
+    kv_heads = rng.choice([1, 2, 3, 4, 5])
+    layers = rng.randint(1, 4)
+    cfg = dict(model_type="qwen3", architectures=["Qwen3ForCausalLM"], hidden_size=8 * rng.randint(4, 40),
+               num_hidden_layers=layers, num_attention_heads=kv_heads * rng.choice([1, 2, 3, 4, 5, 7, 8]),
+               num_key_value_heads=kv_heads, head_dim=rng.choice([16, 32, 48, 64, 80, 96, 112, 128, 128, 160, 256]),
+               intermediate_size=8 * rng.randint(5, 60), vocab_size=rng.randint(50, 1500),
+               rope_theta=float(rng.choice([1e4, 5e4, 1e6])), rms_norm_eps=rng.choice([1e-6, 1e-5, 3e-6]),
+               tie_word_embeddings=rng.random() < 0.5, attention_bias=rng.random() < 0.4, use_sliding_window=False,
+               max_position_embeddings=1024, hidden_act="silu")
+    if rng.random() < 0.5:
+        cfg.update(use_sliding_window=True, sliding_window=rng.randint(5, 200), max_window_layers=rng.randint(0, layers))
+    scaling = rng.random()
+    if scaling < 0.2:
+        cfg["rope_scaling"] = {"rope_type": "linear", "factor": rng.choice([2.0, 4.0])}
+    elif scaling < 0.4:
+        cfg["rope_scaling"] = {"rope_type": "yarn", "factor": rng.choice([2.0, 4.0]),
+                               "original_max_position_embeddings": 256}
+    if rng.random() < 0.25:
+        cfg["partial_rotary_factor"] = rng.choice([0.25, 0.5])
+    return cfg
