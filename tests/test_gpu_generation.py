@@ -228,3 +228,50 @@ def test_cancel_in_the_middle_leaves_the_others_as_they_are_alone(overlap):
         assert not eng.runner.cache.requests and eng._inflight is None
         eng.runner.cache.check()
         assert eng.runner.cache.free_pages() == [20]
+
+
+@pytest.mark.parametrize("name,seed", [("B", 0), ("E", 1), ("C", 2), ("B", 3)])
+def test_random_arrivals_cancels_and_a_tight_pool(name, seed):
+    """Sixty requests (greedy and seeded sampling) arrive a few at a time, some are cancelled where they stand, the pool
+    holds three or four of them, so that requests are preempted and recomputed; with and without planning ahead and
+    further prompts' portions in a step. In float32 every request that ran to its end has the very tokens it generates
+    alone, every cancelled one a beginning of them, and the cache ends empty with its books in order."""
+    from jllm_serve_b200.csrc import ops
+    from jllm_serve_b200.sampling import SamplingParams
+    rng = random.Random(seed)
+    vocab = CONFIGS[name]["vocab_size"]
+    specs = []
+    for i in range(60):
+        n, out = rng.randint(1, 150), rng.randint(1, 40)
+        params = (SamplingParams.greedy_params(out, ignore_eos=True) if rng.random() < 0.6 else
+                  SamplingParams(temperature=0.9, top_k=30, top_p=0.9, seed=1000 * seed + i, max_tokens=out, ignore_eos=True))
+        specs.append((random_tokens(n, vocab, 7919 * seed + i), params))
+    kw = dict(max_batch_tokens=96, chunk=64, max_running=5, ctx=256)
+    with engine_for(name, "float32", max_tokens_cached=640, **kw) as roomy:
+        alone = [roomy.generate([p], sp)[0].tokens for p, sp in specs]
+    with engine_for(name, "float32", max_tokens_cached=384, overlap=seed % 2 == 0, fill_portions=seed % 3 != 0, **kw) as eng:
+        pending, ids, cancelled, steps = list(range(60)), {}, set(), 0
+        while pending or eng.scheduler.has_work() or eng._inflight is not None:
+            for _ in range(min(len(pending), rng.randint(0, 3))):
+                i = pending.pop(0)
+                ids[eng.add_request(*specs[i])] = i
+            live = [r.id for r in eng.scheduler.running + eng.scheduler.waiting]
+            if live and rng.random() < 0.08:
+                rid = rng.choice(live)
+                assert eng.cancel(rid)
+                cancelled.add(rid)
+            eng.step_once()
+            steps += 1
+            assert steps < 20000
+        ops.check_kernel_errors()
+        eng.runner.cache.check()
+        assert not eng.runner.cache.requests and set(eng.runner.cache.free_pages()) == {48}
+        assert cancelled, "the load cancelled nothing"
+        # (C's layers but the first look back 40 tokens only and give their pages back as they go: its pool is never short)
+        assert name == "C" or eng.scheduler.preemptions > 0, "the pool was large enough: nothing was preempted"
+        for rid, i in ids.items():
+            r = eng.result_of(rid)
+            if rid in cancelled:
+                assert r.finish_reason == "cancelled" and r.tokens == alone[i][:len(r.tokens)], f"cancelled request {i}"
+            else:
+                assert r.finish_reason == "length" and r.tokens == alone[i], f"request {i}"
