@@ -193,6 +193,17 @@ class Engine:
                       Stats(len(r.prompt), 0, len(r.output), (first - t["start"]) * 1e3, (end - first) * 1e3,
                             r.preemptions))
 
+    def take_result(self, rid: Hashable) -> Result:
+        """`result_of` for a request that has ended, after which the engine forgets the request: whoever drives
+        `add_request` and `step_once` for a long time takes every result this way, or the finished requests pile up."""
+        if rid not in self.scheduler.finished:
+            raise KeyError(f"request {rid!r} has not ended (or its result was taken already)")
+        out = self.result_of(rid)
+        self.scheduler.finished.pop(rid)
+        self._rngs.pop(rid, None)
+        self._times.pop(rid, None)
+        return out
+
     def generate(self, prompts: Sequence[Sequence[int]],
                  params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> List[Result]:
         """Generates for every prompt (token ids); one SamplingParams for all, or one per prompt."""
@@ -202,12 +213,7 @@ class Engine:
             raise ValueError(f"{len(prompts)} prompts but {len(params)} sampling parameters")
         ids = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
         self.run_until_done()
-        out = [self.result_of(i) for i in ids]
-        for i in ids:
-            self.scheduler.finished.pop(i, None)
-            self._rngs.pop(i, None)
-            self._times.pop(i, None)
-        return out
+        return [self.take_result(i) for i in ids]
 
     def step(self, segments: Sequence[Segment]) -> torch.Tensor:
         """The raw step function: logits [wanted places, vocab] for a batch of (request, its next tokens)."""

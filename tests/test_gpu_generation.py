@@ -219,7 +219,10 @@ def test_cancel_in_the_middle_leaves_the_others_as_they_are_alone(overlap):
         assert eng.cancel(c) and eng.cancel(a) and not eng.cancel(a)
         d = eng.add_request(prompts[3], params)
         eng.run_until_done()
-        ra, rb, rc, rd = (eng.result_of(i) for i in (a, b, c, d))
+        ra, rb, rc, rd = (eng.take_result(i) for i in (a, b, c, d))
+        assert not eng.scheduler.finished and not eng._times and not eng._rngs       # taken: nothing is kept
+        with pytest.raises(KeyError):
+            eng.take_result(a)
         assert rc.finish_reason == "cancelled" and rc.tokens == []
         want_a = P.greedy_generate(cfg, w, prompts[0], 20)
         assert ra.finish_reason == "cancelled" and 1 <= len(ra.tokens) < 20 and ra.tokens == want_a[:len(ra.tokens)]
