@@ -616,12 +616,16 @@ def test_attention_decode_fresh_random_shapes(ops):
     followed by the attention (bits of the output and of the cache)."""
     import random
     rng = random.Random(23)
-    for trial in range(10):
+    for trial in range(14):
         H, Hkv, hd = rng.choice([(8, 2, 128), (4, 4, 64), (16, 2, 128), (4, 1, 256)])
         page = rng.choice([1, 4, 16, 32])
         lens = [rng.choice([1, 2, 63, 64, 65, 128, rng.randint(1, 700)]) for _ in range(rng.randint(1, 9))]
         R, eps, scale = len(lens), 1e-6, 1.0 / math.sqrt(hd)
         norm, splits = rng.random() < 0.7, rng.choice([1, 2, 5, 8, 13])
+        if trial >= 10:                 # the last trials: thousands of keys, many splits
+            page, splits = rng.choice([16, 64]), rng.choice([4, 13, 32])
+            lens = [rng.randint(3000, 40000) for _ in range(rng.randint(1, 5))] + [rng.randint(1, 100)]
+            R = len(lens)
         pages_of = [-(-L // page) for L in lens]
         pool = sum(pages_of) + 3
         order = list(range(pool))
