@@ -26,19 +26,24 @@ def _tokens(n: int, vocab: int, seed: int) -> List[int]:
 
 
 def _rows_of(runner, trace) -> Dict[tuple, torch.Tensor]:
-    """Runs [(entries, ends)] with entries [(request, tokens, want all?)]; {(request, position): logits row}."""
+    """Runs [(entries, ends)] with entries [(request, tokens, want)], want = True (every row's logits), False (none) or
+    a number (those of the last so many rows); {(request, position): logits row}."""
     from .engine import Segment
+
+    def wanted(toks, want):
+        n = len(toks)
+        return list(range(n)) if want is True else list(range(max(0, n - int(want)), n))
+
     fed, out = {}, {}
     for entries, ends in trace:
-        segs = [Segment(rid, toks, fed.get(rid, 0), list(range(len(toks))) if want else []) for rid, toks, want in entries]
+        segs = [Segment(rid, toks, fed.get(rid, 0), wanted(toks, want)) for rid, toks, want in entries]
         rows = runner.step(segs).clone()
         r = 0
         for rid, toks, want in entries:
             base = fed.get(rid, 0)
-            if want:
-                for k in range(len(toks)):
-                    out[(rid, base + k)] = rows[r]
-                    r += 1
+            for k in wanted(toks, want):
+                out[(rid, base + k)] = rows[r]
+                r += 1
             fed[rid] = base + len(toks)
         for rid in ends:
             runner.finish(rid)
@@ -69,24 +74,29 @@ class _Stats:
 
 
 def compare_precisions(config: dict, seed: int = 0, prompt: int = 300, tail: int = 16, portion: int = 256,
-                       others: Sequence[int] = (40, 90), page_size: int = 16, device: str = "cuda:0") -> dict:
+                       others: Sequence[int] = (40, 90), page_size: int = 16, device: str = "cuda:0",
+                       want_last: int = 0) -> dict:
     """Logits of the bfloat16 path against the 32-bit path of the same random model. Returns, for the request
     alone ("alone") and for the same request in portions beside two decoding requests ("mixed", all three
     requests' rows): rows compared, the largest difference as a share of the largest |logit|, the rms error as a
     share of the rms logit, the share of rows with the same best token, and the largest gap (same unit as the
-    first) between the 32-bit path's best logit and its logit of the bfloat16 path's choice."""
+    first) between the 32-bit path's best logit and its logit of the bfloat16 path's choice.
+    `want_last` > 0 (long prompts: the logits of thousands of rows would fill the device): only the last so many
+    rows of every portion are compared, and the 32-bit path runs the very same steps."""
     from .engine import ModelRunner
     vocab = config["vocab_size"]
     main = _tokens(prompt + tail, vocab, seed + 1)
-    side = {f"side{i}": _tokens(n + 2 + tail, vocab, seed + 2 + i) for i, n in enumerate(others)}
-    ctx = 64 * (-(-(prompt + tail + max(others) + 2) // 64))
+    steps_beside = max(2, -(-prompt // portion))
+    side = {f"side{i}": _tokens(n + steps_beside + tail, vocab, seed + 2 + i) for i, n in enumerate(others)}
+    ctx = 64 * (-(-(prompt + tail + max(others) + steps_beside) // 64))
     kw = dict(config=config, seed=seed, device=device, page_size=page_size, max_batch_tokens=prompt + tail + len(others),
               max_requests=len(others) + 1, ctx=ctx, num_pages=(len(others) + 1) * (ctx // page_size + 1))
 
-    alone = [([("main", main[:prompt], True)], [])]
+    every = want_last if want_last > 0 else True
+    alone = [([("main", main[:prompt], every)], [])]
     alone += [([("main", main[p:p + 1], True)], ["main"] if p == prompt + tail - 1 else []) for p in range(prompt, prompt + tail)]
     whole_sides = [([(rid, toks, True)], [rid]) for rid, toks in side.items()]
-    mixed = [([(rid, toks[:n], True)], []) for (rid, toks), n in zip(side.items(), others)]
+    mixed = [([(rid, toks[:n], every)], []) for (rid, toks), n in zip(side.items(), others)]
     at = {rid: n for rid, n in zip(side, others)}
 
     def beside(entry):
@@ -95,14 +105,14 @@ def compare_precisions(config: dict, seed: int = 0, prompt: int = 300, tail: int
             at[rid] += 1
         return rows
 
-    mixed.append((beside(("main", main[:portion], True)), []))
-    mixed.append((beside(("main", main[portion:prompt], True)), []))
+    for lo in range(0, prompt, portion):
+        mixed.append((beside(("main", main[lo:min(prompt, lo + portion)], every)), []))
     for p in range(prompt, prompt + tail):
         mixed.append((beside(("main", main[p:p + 1], True)), []))
     mixed[-1] = (mixed[-1][0], ["main"] + list(side))
 
     exact = ModelRunner(dtype="float32", **kw)
-    want = _rows_of(exact, alone + whole_sides)
+    want = _rows_of(exact, alone + whole_sides) if want_last <= 0 else {**_rows_of(exact, alone), **_rows_of(exact, mixed)}
     exact.close()
     del exact
     torch.cuda.empty_cache()

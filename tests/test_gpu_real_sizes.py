@@ -78,3 +78,19 @@ def test_bfloat16_follows_float32_at_other_layer_sizes(size):
             assert s["rms_rel"] <= 1.3e-2, (size, name, s)
             assert s["argmax_agree"] >= 0.96, (size, name, s)
             assert s["worst_choice_gap_rel"] <= 1e-2, (size, name, s)
+
+
+def test_bfloat16_follows_float32_far_into_a_long_prompt():
+    """A prompt of 9,000 tokens, whole and in portions of 2,048 beside two requests that decode at 5,000 and 3,000
+    tokens of context: the last rows of every portion and every decoded row. The flash attention then runs portions
+    whose keys begin thousands of positions back, the decode attention many splits, the products two SMs to a tile."""
+    from jllm_serve_b200.precision_check import compare_precisions
+    got = compare_precisions(CONFIG, seed=7, prompt=9000, tail=6, portion=2048, others=(5000, 3000), want_last=4)
+    print(f"layers {CONFIG['num_hidden_layers']} of {QWEN3_8B_LAYERS}: {got}")
+    assert got["alone"]["rows"] == 10 and got["mixed"]["rows"] == 8 + 5 * 6 + 6 * 3
+    for name in ("alone", "mixed"):
+        s = got[name]
+        assert s["max_rel"] <= 1.5e-2, (name, s)
+        assert s["rms_rel"] <= 1.3e-2, (name, s)
+        assert s["argmax_agree"] >= 0.85, (name, s)          # (ten rows: one other choice is a tenth)
+        assert s["worst_choice_gap_rel"] <= 1e-2, (name, s)
