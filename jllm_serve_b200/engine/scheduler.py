@@ -180,6 +180,9 @@ class Scheduler:
             raise ValueError(f"request {request.id!r}: the prompt is empty")
         if n >= self.ctx:
             raise ValueError(f"request {request.id!r}: a prompt of {n} tokens does not fit the context of {self.ctx}")
+        if request.id in self.finished or any(r.id == request.id for r in self.waiting + self.running):
+            raise ValueError(f"request {request.id!r}: there is a request of this name already "
+                             f"({'ended, its result not taken' if request.id in self.finished else 'not ended'})")
         request.arrival = next(self._clock)
         request.max_new = min(request.params.max_tokens, self.ctx - n)
         request.state = WAITING

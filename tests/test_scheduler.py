@@ -440,3 +440,17 @@ def test_cancel_ends_a_waiting_or_running_request_and_frees_its_pages():
     drive(s, cache)
     assert s.finished["b"].finish_reason == "length" and len(s.finished["b"].output) == 8
     assert cache.free_pages() == [16] and not cache.requests
+
+
+def test_a_request_name_is_taken_until_its_result_is():
+    s, cache = make()
+    s.add(Request("a", [1, 2, 3], SamplingParams.greedy_params(2)))
+    with pytest.raises(ValueError, match="already"):
+        s.add(Request("a", [4, 5], SamplingParams.greedy_params(2)))
+    drive(s, cache)
+    with pytest.raises(ValueError, match="result not taken"):
+        s.add(Request("a", [4, 5], SamplingParams.greedy_params(2)))
+    s.finished.pop("a")
+    s.add(Request("a", [4, 5], SamplingParams.greedy_params(2)))
+    drive(s, cache)
+    assert len(s.finished["a"].output) == 2
