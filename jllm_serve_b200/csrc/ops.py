@@ -575,9 +575,35 @@ def decode_plan(rows, kv_heads, kv_bucket, heads, head_dim, scratch, places: int
     return "flat", blocks
 
 
+KV_BUCKET_MAX = 32
+# the buckets a decode step is planned for: a step's bucket is rounded down to one of them, so that a context that grows
+# asks for a new plan (and a newly captured step) sixteen times in its life and not every 256 tokens
+KV_BUCKET_LEVELS = (1, 2, 3, 4, 5, 6, 7, 8, 10, 12, 14, 16, 20, 24, 28, 32)
+
+
+def bucket_level(kv_bucket: int) -> int:
+    """`kv_bucket` rounded down to the nearest of KV_BUCKET_LEVELS (a plan for fewer keys is always a valid one)."""
+    return max(l for l in KV_BUCKET_LEVELS if l <= max(1, kv_bucket))
+
+
+def _windowed_bucket(kv_bucket: int, window: int) -> int:
+    return kv_bucket if window <= 0 else max(1, min(kv_bucket, window // 256))
+
+
+def decode_bucket_cap(rows, kv_heads, heads, head_dim, window, scratch, places: int = 0) -> int:
+    """The smallest bucket from which on `decode_plan` says the same for every larger one: with so many keys the split is
+    bounded by the places for blocks, not by the keys, and a step's launches no longer change as its context grows."""
+    def plan(b):
+        return decode_plan(rows, kv_heads, _windowed_bucket(b, window), heads, head_dim, scratch, places)
+    cap, top = KV_BUCKET_MAX, plan(KV_BUCKET_MAX)
+    while cap > 1 and plan(cap - 1) == top:
+        cap -= 1
+    return cap
+
+
 def _attention_decode_rows(q, k_cache, v_cache, out, row_seg, positions, table, rows, heads, kv_heads, head_dim, page_size,
                            window, scale, kv_bucket, scratch):
-    bucket = kv_bucket if window <= 0 else max(1, min(kv_bucket, window // 256))
+    bucket = _windowed_bucket(kv_bucket, window)
     how, n = decode_plan(rows, kv_heads, bucket, heads, head_dim, scratch)
     if how == "flat":
         return attention_decode_flat(q, k_cache, v_cache, out, row_seg, positions, table, rows, heads, kv_heads, head_dim,
@@ -603,7 +629,7 @@ def attention_decode_fresh(qkv, q_gain, k_gain, eps, cos, sin, k_cache, v_cache,
     head) pair blocks of its own: a step of 8 rows 4.17 ms against 4.24, of one row 3.38 against 3.43; where the key tiles
     are dealt out over the blocks (64 rows: 10.46 against 10.44 ms) nothing is launched and the caller takes the two
     kernels."""
-    bucket = kv_bucket if window <= 0 else max(1, min(kv_bucket, window // 256))
+    bucket = _windowed_bucket(kv_bucket, window)
     how, n = decode_plan(rows, kv_heads, bucket, heads, head_dim, scratch)
     if how == "flat" and FRESH_DECODE != 2:
         return False

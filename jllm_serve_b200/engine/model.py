@@ -61,6 +61,10 @@ class DecoderModel:
         """Whether a decode step of this model may be captured once and replayed: every part says so of itself."""
         return all(b.graph_safe for b in self.blocks) and all(pe.graph_safe for pe in self.position_encodings)
 
+    def decode_bucket_cap(self, rows: int) -> int:
+        """The bucket from which on a decode step of `rows` rows no longer changes its launches: the largest the parts name."""
+        return max([getattr(b, "decode_bucket_cap", lambda _: 32)(rows) for b in self.blocks] or [1])
+
     def cache_needs(self) -> List[Optional[object]]:
         """One entry per scheduled run: what it keeps between steps (None if it reads another run's cache; a
         tuple if the mixer keeps several things, say paged keys and values and a state of fixed size)."""

@@ -105,6 +105,7 @@ class ModelRunner:
         self.use_graphs = bool(cuda_graphs)
         self.graph_safe = bool(getattr(self.model, "graph_safe", False))    # a model that does not say is not replayed
         self._graphs, self._graph_seen, self._static_logits, self._graph_kernels = {}, set(), None, {}
+        self._bucket_caps = {}         # rows of a decode step -> the bucket from which on its launches stay the same
         self.max_graphs = 256          # captured decode shapes kept (rows x wanted rows x key-range bucket)
 
     def _allocate(self, shape, kind):
@@ -235,6 +236,13 @@ class ModelRunner:
         the launches bake in: rows, wanted rows and the split of the attention's key range. All device
         addresses a step uses are fixed (batch tables, scratch buffers, the cache), so replaying is exact.
         The returned logits live in a buffer that the next replay overwrites."""
+        if batch.decode_only:
+            # the bucket that the parts plan their launches by: clamped to where it stops mattering, and rounded down to
+            # one of a few levels, so that a growing context seldom asks for a new plan (and a new capture)
+            cap = self._bucket_caps.get(batch.rows)
+            if cap is None:
+                cap = self._bucket_caps[batch.rows] = self.model.decode_bucket_cap(batch.rows)
+            batch.kv_bucket = ops.bucket_level(min(batch.kv_bucket, cap))
         if not (self.use_graphs and self.graph_safe and batch.decode_only):
             return self.model.forward(batch, self.cache, logits_out)
         key = (batch.rows, batch.num_wanted, batch.kv_bucket)
@@ -250,9 +258,9 @@ class ModelRunner:
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count
             # Nothing may destroy another CUDA graph while this one is captured (the driver forbids it and the capture
-            # is lost): the garbage collector could, if it found an abandoned runner's graphs just now. It runs before
-            # the capture and is held off during it.
-            gc.collect()
+            # is lost): the garbage collector could, if it found an abandoned runner's graphs just now. It is held off
+            # during the capture. (A full collection beforehand costs 30 ms and more with a model's objects alive, as
+            # much as eight decode steps; `close()` is how a runner's graphs go at a chosen time.)
             collecting = gc.isenabled()
             gc.disable()
             try:

@@ -60,6 +60,13 @@ class GqaAttention(Mixer):
     def cache_need(cls, spec):
         return PagedKeysValues(spec.kv_heads, spec.head_dim, spec.window)
 
+    def decode_bucket_cap(self, rows: int) -> int:
+        s = self.spec
+        if not ops.attention_decode_fits(self.rt.dtype, s.heads, s.kv_heads, s.head_dim):
+            return 1                   # the plain attention's launches do not depend on the context
+        scratch = self.rt.buffer("attention_scratch", 2 << 20, torch.float32, rows=1)[0]
+        return ops.decode_bucket_cap(rows, s.kv_heads, s.heads, s.head_dim, s.window, scratch)
+
     def forward(self, xb, x, batch, cache) -> None:
         s, rows = self.spec, xb.shape[0]
         if cache.writes:

@@ -83,6 +83,14 @@ class Mixer(Part):
         """A `cache.CacheNeed` (or None): what a run of this mixer keeps between steps."""
         return None
 
+    def decode_bucket_cap(self, rows: int) -> int:
+        """The smallest `batch.kv_bucket` (the longest request's keys in units of 256, at most 32) from which on a step of
+        `rows` single rows launches the same kernels in the same shapes however long the context is; 32: the launches
+        may change up to the largest bucket (the safe answer, and the default). The step function clamps a decode
+        step's bucket to the largest cap among the model's parts: a context that grows then asks for a newly captured
+        step a few times in its life and not every 256 tokens."""
+        return 32
+
     def forward(self, xb, x, batch, cache) -> None:
         raise NotImplementedError
 
@@ -98,6 +106,10 @@ class Block(Part):
     # an arrangement says itself whether its step can be captured and replayed (usually: whether all its parts
     # can); one that does not say is run launch by launch
     graph_safe = False
+
+    def decode_bucket_cap(self, rows: int) -> int:
+        """See `Mixer.decode_bucket_cap`: the largest cap among the arrangement's parts."""
+        return 32
 
     def forward(self, x, batch, cache) -> None:
         raise NotImplementedError

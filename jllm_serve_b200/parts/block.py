@@ -28,6 +28,10 @@ class PreNormBlock(Block):
     def graph_safe(self) -> bool:
         return all(getattr(p, "graph_safe", False) for p in (self.mixer_norm, self.ffn_norm, self.mixer, self.feed_forward))
 
+    def decode_bucket_cap(self, rows: int) -> int:
+        # (norms and feed-forwards do not look at the bucket; a mixer that does not say gets the safe answer)
+        return getattr(self.mixer, "decode_bucket_cap", lambda _: 32)(rows)
+
     @classmethod
     def wants(cls, spec, dim: int, prefix: str) -> dict:
         names = spec.names

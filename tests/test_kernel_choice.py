@@ -50,3 +50,30 @@ def test_decode_attention_is_dealt_out_evenly_only_where_that_pays():
     assert how == "flat" and blocks == 62 * 3
     assert ops.decode_plan(64, 8, 16, 32, 80, scratch, places=296)[0] == "split"            # a head size the flat kernel lacks
     assert ops.decode_plan(64, 8, 16, 32, 128, torch.empty(1000), places=296)[0] == "split"  # no room for its partial results
+
+
+def test_a_decode_steps_bucket_is_clamped_where_it_stops_mattering():
+    """`decode_bucket_cap`: from that bucket on the plan of a decode step is the same for every longer context, so the
+    step function may clamp the bucket there (and a growing context does not ask for a new captured step every 256
+    tokens); below it the bucket is rounded down to one of sixteen levels, each a valid plan for fewer keys."""
+    import torch
+    from jllm_serve_b200.csrc import ops
+    scratch = torch.empty(2 << 20)
+    for rows, heads, kv_heads, hd, window in [(1, 32, 8, 128, 0), (8, 32, 8, 128, 0), (64, 32, 8, 128, 0), (3, 40, 8, 128, 0),
+                                              (8, 64, 8, 128, 0), (200, 6, 3, 64, 0), (2, 16, 1, 256, 0), (8, 32, 8, 128, 700),
+                                              (1, 4, 4, 64, 5000), (37, 8, 2, 64, 0)]:
+        cap = ops.decode_bucket_cap(rows, kv_heads, heads, hd, window, scratch, places=296)
+        assert 1 <= cap <= ops.KV_BUCKET_MAX
+
+        def plan(b):
+            return ops.decode_plan(rows, kv_heads, ops._windowed_bucket(b, window), heads, hd, scratch, 296)
+        for b in range(1, ops.KV_BUCKET_MAX + 1):
+            assert plan(min(b, cap)) == plan(b), (rows, heads, kv_heads, hd, window, b, cap)
+        assert cap == 1 or plan(cap - 1) != plan(cap)
+    assert ops.decode_bucket_cap(8, 8, 32, 128, 0, scratch, places=296) == 2       # four splits from 512 keys on
+    assert ops.decode_bucket_cap(1, 8, 32, 128, 0, scratch, places=296) == 16      # 32 splits from 4,096 keys on
+    levels = [ops.bucket_level(b) for b in range(0, 40)]
+    assert levels[:9] == [1, 1, 2, 3, 4, 5, 6, 7, 8] and levels[32:] == [32] * 8
+    assert all(l <= max(1, b) and l in ops.KV_BUCKET_LEVELS for b, l in enumerate(levels))
+    assert all(4 * b <= 5 * l + 4 for b, l in enumerate(levels[:33]))                # never more than a quarter below
+    assert len(set(levels)) == 16
