@@ -365,7 +365,7 @@ def end_to_end(engine, batch: int, steps: int, warmup: int, vocab: int):
               file=sys.stderr, flush=True)
     engine.run_until_done()
     for i in ids:
-        engine.scheduler.finished.pop(i, None)
+        engine.take_result(i)
     return {"value": round(done / dt, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * engine.sampler.max_rows,
             "ms_per_step": round(dt / steps * 1e3, 4), "tokens_per_step": round(done / steps, 2),
             "preemptions": sched.preemptions}
