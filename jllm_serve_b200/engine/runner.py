@@ -237,12 +237,12 @@ class ModelRunner:
         addresses a step uses are fixed (batch tables, scratch buffers, the cache), so replaying is exact.
         The returned logits live in a buffer that the next replay overwrites."""
         if batch.decode_only:
-            # the bucket that the parts plan their launches by: clamped to where it stops mattering, and rounded down to
-            # one of a few levels, so that a growing context seldom asks for a new plan (and a new capture)
+            # the bucket that the parts plan their launches by: clamped to where it stops mattering, and below that rounded
+            # down to one of a few levels, so that a growing context seldom asks for a new plan (and a new capture)
             cap = self._bucket_caps.get(batch.rows)
             if cap is None:
                 cap = self._bucket_caps[batch.rows] = self.model.decode_bucket_cap(batch.rows)
-            batch.kv_bucket = ops.bucket_level(min(batch.kv_bucket, cap))
+            batch.kv_bucket = cap if batch.kv_bucket >= cap else ops.bucket_level(batch.kv_bucket)
         if not (self.use_graphs and self.graph_safe and batch.decode_only):
             return self.model.forward(batch, self.cache, logits_out)
         key = (batch.rows, batch.num_wanted, batch.kv_bucket)
