@@ -1,4 +1,4 @@
-// out[m, n] (+)= sum_k a[m, k] * w[n, k] (+ bias[n]) for FEW rows m (a decode step, at most 128): a stream of the
+// out[m, n] (+)= sum_k a[m, k] * w[n, k] (+ bias[n]) for FEW rows m (a decode step, at most 256): a stream of the
 // weights through the 5th-generation tensor cores with the operands swapped.
 //
 // With few rows the product is nothing but reading W once, so everything is shaped for that read:
@@ -29,7 +29,7 @@ using namespace tc;
 constexpr int WM = 128, BK = 64;
 constexpr int W_TILE_BYTES = WM * BK * 2;       // 16 KB
 constexpr int THREADS = 192;
-constexpr int MAX_TOKENS = 128;
+constexpr int MAX_TOKENS = 256;                  // the N side of one tcgen05.mma; two accumulators of 256 columns are all of tensor memory
 constexpr int MAX_TILES = 65536;                 // counter words at the head of the workspace
 
 __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {

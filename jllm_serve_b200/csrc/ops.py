@@ -253,9 +253,11 @@ def gemm_bf16_fits(a, w, out) -> bool:
 #            and for small matrices up to 64 rows;
 #   "swap"   gemm_stream: tcgen05 with the weight rows as the M side, one 16 KB bulk copy per tile, the k blocks dealt
 #            out evenly over the SMs; from 17 to 128 rows for matrices of 40 MB or more (QKV, down), from 41 rows for
-#            smaller ones (O), where the row kernel's time grows with the rows; not for very wide matrices (gate_up),
-#            which whole tiles of the tiles kernel fill the SMs with;
+#            smaller ones (O), where the row kernel's time grows with the rows; up to 160 rows for all of these and up to
+#            256 for matrices much longer than high (down); not for very wide matrices (gate_up), which whole tiles of
+#            the tiles kernel fill the SMs with;
 #   "tiles"  gemm_tcgen05: tokens as the M side, 128 x BN tiles; above that, and from 16 rows for very wide matrices.
+SWAP_MAX_ROWS = 256      # gemm_stream: the tokens are the N side of one tcgen05.mma
 TILE_ROWS = 128          # rows of a tcgen05 product tile (BM in gemm_tcgen05.cu): a step of 129 rows pays for 256
 SMALL_M_ROWS = int(os.environ.get("JLLM_B200_SMALL_M_ROWS", "64"))
 WIDE_ROWS = int(os.environ.get("JLLM_B200_WIDE_ROWS", "16384"))
@@ -263,7 +265,7 @@ SWAP_MIN_BYTES = int(os.environ.get("JLLM_B200_SWAP_MIN_BYTES", str(40_000_000))
 _workspaces = {}
 # counters of up to 65,536 tiles, then one parked 128 x 256 partial tile for each of up to 160 blocks
 STREAM_WORKSPACE_FLOATS = 65536 + 160 * 128 * 256
-SWAP_WORKSPACE_FLOATS = 2 * 65536 + 160 * 2 * 128 * 128       # gemm_stream: two counters per tile, then the parts
+SWAP_WORKSPACE_FLOATS = 2 * 65536 + 160 * 2 * 256 * 128       # gemm_stream: two counters per tile, then the parts
 PAIR_WORKSPACE_FLOATS = 2 * 65536 + 160 * 128 * 256           # gemm_pair: two counters per tile, a part per block
 
 
@@ -286,6 +288,11 @@ def gemm_kernel_for(rows: int, out_features: int, in_features: int = 4096, rows_
     # weight-row kernel, whose blocks have half their loads in flight once they hold more than two token tiles
     wide = rows >= 16 and out_features >= WIDE_ROWS and tiles_fit
     if tiles_fit and not wide and 16 < rows <= 128 and (out_features * in_features * 2 >= SWAP_MIN_BYTES or rows > 40):
+        return "swap"
+    # 129 to 256 rows (the tokens are still one tcgen05 N side): the parked parts grow with the rows, so it keeps only
+    # what the tiles kernel is worst at, matrices much longer than high (down: 12,288 k for 4,096 rows; 31 to 41 us
+    # against 58), and everything up to 160 rows (QKV 20 to 22 us against 23, O 19 to 20 against 22)
+    if tiles_fit and not wide and 128 < rows <= SWAP_MAX_ROWS and (rows <= 160 or in_features >= 2 * out_features):
         return "swap"
     if rows <= min(SMALL_M_ROWS, 64) and rows_fit and not wide:
         return "rows"
@@ -417,12 +424,12 @@ def pack_weight(w: torch.Tensor) -> PackedWeight:
 
 def gemm_stream_fits(a, packed: PackedWeight) -> bool:
     M, K = a.shape
-    return (1 <= M <= 128 and K == packed.cols and K >= 8 and K % 8 == 0 and a.stride(0) % 8 == 0 and a.stride(1) == 1
+    return (1 <= M <= SWAP_MAX_ROWS and K == packed.cols and K >= 8 and K % 8 == 0 and a.stride(0) % 8 == 0 and a.stride(1) == 1
             and a.data_ptr() % 16 == 0)
 
 
 def gemm_stream(a, packed: PackedWeight, out, bias=None, accumulate=False, swiglu=False, max_blocks: int = 0) -> None:
-    """out (+)= a @ W^T (+ bias) for at most 128 rows: the packed weight streamed once through tcgen05.mma with the
+    """out (+)= a @ W^T (+ bias) for at most 256 rows: the packed weight streamed once through tcgen05.mma with the
     weight rows as the M side (see gemm_stream.cu). With `swiglu` the rows of W are blocks of 8 gate rows followed by
     their 8 up rows and out[m, j] = silu(gate_j) * up_j. A tile's parts (its k blocks may fall to several blocks) are
     added in k order: two runs give the same bits."""

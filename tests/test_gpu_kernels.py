@@ -113,7 +113,7 @@ def test_gemm_small_m(ops, M, N, K):
     assert torch.allclose(out16.float().cpu(), gemm_want(a, w), rtol=2 ** -7, atol=2e-3)
 
 
-@pytest.mark.parametrize("M", [1, 5, 8, 16, 17, 33, 64, 100, 128])
+@pytest.mark.parametrize("M", [1, 5, 8, 16, 17, 33, 64, 100, 128, 129, 200, 256])
 @pytest.mark.parametrize("N,K", [(40, 64), (517, 72), (6144, 4096), (4096, 12288), (4736, 1000), (128, 8)])
 def test_gemm_stream(ops, M, N, K):
     """The weight-stream product over a packed weight: whole tiles and tiles whose k blocks fall to several blocks,
@@ -141,7 +141,7 @@ def test_gemm_stream(ops, M, N, K):
     assert float(out16[:, N:].abs().max()) == 0 and ops.gemm_tcgen05_error() == 0
 
 
-@pytest.mark.parametrize("M", [1, 8, 20, 64, 128])
+@pytest.mark.parametrize("M", [1, 8, 20, 64, 128, 250])
 @pytest.mark.parametrize("hidden,K", [(8, 8), (200, 72), (12288, 4096), (1000, 136)])
 def test_gemm_stream_with_swiglu_epilogue(ops, M, hidden, K):
     a = rnd(M, K, dtype=torch.bfloat16)

@@ -94,3 +94,21 @@ def test_bfloat16_follows_float32_far_into_a_long_prompt():
         assert s["rms_rel"] <= 1.3e-2, (name, s)
         assert s["argmax_agree"] >= 0.85, (name, s)          # (ten rows: one other choice is a tenth)
         assert s["worst_choice_gap_rel"] <= 1e-2, (name, s)
+
+
+def test_bfloat16_follows_float32_with_portions_of_some_two_hundred_rows():
+    """Steps of 129 to 256 rows (portions of 150 and 220 rows beside two decoding requests): the tokens are still one
+    N side of the weight-stream product, which takes the down product there, and up to 160 rows the others too."""
+    from jllm_serve_b200.csrc import ops
+    from jllm_serve_b200.precision_check import compare_precisions
+    assert ops.gemm_kernel_for(222, 4096, 12288) == "swap" and ops.gemm_kernel_for(152, 6144, 4096) == "swap"
+    for portion in (150, 220):
+        got = compare_precisions(CONFIG, seed=9, prompt=2 * portion, tail=4, portion=portion)
+        print(f"portions of {portion}, layers {CONFIG['num_hidden_layers']} of {QWEN3_8B_LAYERS}: {got}")
+        for name in ("alone", "mixed"):
+            s = got[name]
+            assert s["rows"] >= 2 * portion + 4
+            assert s["max_rel"] <= 1.5e-2, (name, s)
+            assert s["rms_rel"] <= 1.3e-2, (name, s)
+            assert s["argmax_agree"] >= 0.96, (name, s)
+            assert s["worst_choice_gap_rel"] <= 1e-2, (name, s)

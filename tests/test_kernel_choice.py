@@ -11,8 +11,11 @@ def test_product_kernel_by_rows_and_shape():
     assert k(16, 24576, 4096) == "tiles"                   # 16 rows against gate_up: tcgen05 tiles
     assert k(16, 6144, 4096) == "rows"
     assert k(17, 6144, 4096) == "swap"                     # QKV (50 MB) from 17 rows: weight rows as the MMA's M side
-    assert k(64, 6144, 4096) == "swap" and k(128, 6144, 4096) == "swap" and k(129, 6144, 4096) == "tiles"
-    assert k(64, 4096, 12288) == "swap" and k(128, 4096, 12288) == "swap" and k(129, 4096, 12288) == "tiles"
+    assert k(64, 6144, 4096) == "swap" and k(128, 6144, 4096) == "swap" and k(160, 6144, 4096) == "swap"
+    assert k(161, 6144, 4096) == "tiles" and k(161, 4096, 4096) == "tiles"      # above 160 rows its parked parts cost too much
+    # ... except against matrices much longer than high (down), up to the 256 tokens of one tcgen05 N side
+    assert k(64, 4096, 12288) == "swap" and k(128, 4096, 12288) == "swap" and k(256, 4096, 12288) == "swap"
+    assert k(257, 4096, 12288) == "tiles" and k(256, 5120, 17408) == "swap" and k(200, 24576, 4096) == "tiles"
     assert k(40, 4096, 4096) == "rows" and k(41, 4096, 4096) == "swap"         # O (34 MB): from 41 rows
     assert k(64, 24576, 4096) == "tiles"                                       # gate_up: whole tiles fill the SMs
     # many rows: two SMs to a 256 x 256 tile where such tiles keep the pairs busy in no more rounds than one-SM tiles
