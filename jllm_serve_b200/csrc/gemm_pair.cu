@@ -451,7 +451,9 @@ JLLM_EXPORT int jllm_gemm_pair(const void* a, int lda, const void* w, int k_bloc
     const int tiles = ((M + PAIR_M - 1) / PAIR_M) * ((N + BN - 1) / BN);
     int pairs = out_dtype == JLLM_F32 ? resident_pairs<float>() : resident_pairs<__nv_bfloat16>();
     JLLM_REQUIRE(pairs >= 1, "gemm_pair: the device runs no cluster of two blocks with %zu bytes of shared memory", SMEM_BYTES);
-    if (pairs > tiles) pairs = tiles;
+    // (a streamed product of fewer tiles than pairs still runs on all pairs: every tile is cut up then)
+    const long long units = stream_mode == 1 ? (long long)tiles * k_blocks_packed : (long long)tiles;
+    if (pairs > units) pairs = (int)units;
     if (max_pairs > 0 && pairs > max_pairs) pairs = max_pairs;
     // stream_mode 1: the tiles of a last, partly filled round are cut up over all pairs (stream-K). Not the default: what
     // an idle pair in the last round loses, the busy ones win back (they share one memory system and one power limit).

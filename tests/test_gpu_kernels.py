@@ -265,6 +265,28 @@ def test_gemm_pair_random_shapes(ops):
         assert torch.allclose(got[:, :N].cpu(), gemm_want(a, w, bias, base[:, :N]), rtol=1e-4, atol=tol), what
 
 
+@pytest.mark.parametrize("M,N,K", [(512, 4096, 12288), (300, 6144, 4096), (256, 1000, 520)])
+def test_gemm_pair_streamed_with_fewer_tiles_than_pairs(ops, M, N, K):
+    """Fewer 256 x 256 tiles than the device runs pairs: streamed, every tile's k blocks are cut up over ALL pairs (a
+    tile then has two to four parts, one of which finishes it): the plain product's values, and the same bits twice."""
+    if ops.resident_pairs() < 1:
+        pytest.skip("the device runs no pair of blocks of this kernel")
+    assert -(-M // 256) * -(-N // 256) < ops.resident_pairs()
+    a, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=1, scale=0.05)
+    bias, base = rnd(N, dtype=torch.bfloat16, seed=2), rnd(M, N, seed=3)
+    want = gemm_want(a, w, bias, base)
+    tol = 1e-4 * math.sqrt(K) * 0.05
+    got, again = base.clone(), base.clone()
+    ops.gemm_pair(a, w, got, bias, accumulate=True, stream_mode=1)
+    ops.gemm_pair(a, w, again, bias, accumulate=True, stream_mode=1)
+    assert ops.gemm_tcgen05_error() == 0
+    assert torch.allclose(got.cpu(), want, rtol=1e-4, atol=tol), float((got.cpu() - want).abs().max())
+    assert torch.equal(got, again)
+    out16 = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_pair(a, w, out16, stream_mode=1)
+    assert torch.allclose(out16.float().cpu(), gemm_want(a, w), rtol=2 ** -7, atol=2e-3) and ops.gemm_tcgen05_error() == 0
+
+
 @pytest.mark.parametrize("kernel", ["tiles", "pair"])
 @pytest.mark.parametrize("M,N,K", [(300, 1000, 200), (2048, 4096, 512), (129, 260, 136), (31, 36, 64), (513, 7936, 72)])
 def test_gemm_float32_output_by_bulk_copies(ops, M, N, K, kernel):
