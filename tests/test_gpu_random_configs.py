@@ -40,3 +40,39 @@ def test_a_random_configuration_under_every_cut(seed, tmp_path):
                 checker.row(rid, position, row)
             checker.finish()
             runner.close()
+
+
+EDGE = dict(model_type="qwen3", architectures=["Qwen3ForCausalLM"], hidden_size=64, num_hidden_layers=2,
+            num_attention_heads=4, num_key_value_heads=2, head_dim=16, intermediate_size=128, vocab_size=256,
+            rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=True, attention_bias=False,
+            use_sliding_window=False, max_position_embeddings=512, hidden_act="silu")
+
+
+@pytest.mark.parametrize("what,change", [
+    ("24 query heads to a kv head, head size 128", dict(num_attention_heads=24, num_key_value_heads=1, head_dim=128)),
+    ("17 query heads to a kv head", dict(num_attention_heads=17, num_key_value_heads=1, head_dim=32)),
+    ("a width that is no multiple of 4", dict(hidden_size=50, intermediate_size=70)),
+    ("widths that are multiples of 4, not of 8", dict(hidden_size=100, intermediate_size=36)),
+    ("a vocabulary of 7", dict(vocab_size=7)),
+    ("a prime vocabulary", dict(vocab_size=100003)),
+    ("head size 24 (no multiple of 16)", dict(head_dim=24)),
+    ("head size 272 (beyond the tensor-core attention kernels)", dict(head_dim=272)),
+    ("eight hidden units", dict(intermediate_size=8))])
+def test_sizes_at_the_edge_of_what_the_kernels_take(what, change, tmp_path):
+    """Sizes that the fast kernels do not take fall to the plain ones (or are taken after all): never a wrong result.
+    Whole, mixed with pages used again, and a tail decoded one by one, in both precisions, against the plain model."""
+    from jllm_serve_b200.engine import ModelRunner
+    cfg = dict(EDGE, **change)
+    folder = make_model_folder(cfg, 5, tmp_path / "model")
+    reqs = {f"r{j}": random_tokens(n, cfg["vocab_size"], 50 + j) for j, n in enumerate((3, 70, 150, 33))}
+    for dtype in ("float32", "bfloat16"):
+        for cut, steps in (("whole", traces.whole(reqs)), ("mixed", traces.mixed(reqs, max_live=3)),
+                           ("decode tail", traces.prompt_then_decode(reqs, 20))):
+            runner = ModelRunner(folder, dtype=dtype, page_size=16, num_pages=traces.peak_tokens(steps, 64) // 16 + 2,
+                                 max_batch_tokens=512, max_requests=8, ctx=256, poison_freed_pages=True)
+            got = replay(runner, steps)
+            checker = RowChecker(folder, reqs, dtype, None, f"{what}, {cut}")
+            for (rid, position), row in got.items():
+                checker.row(rid, position, row)
+            checker.finish()
+            runner.close()
