@@ -241,7 +241,7 @@ class ModelRunner:
             # down to one of a few levels, so that a growing context seldom asks for a new plan (and a new capture)
             cap = self._bucket_caps.get(batch.rows)
             if cap is None:
-                cap = self._bucket_caps[batch.rows] = self.model.decode_bucket_cap(batch.rows)
+                cap = self._bucket_caps[batch.rows] = getattr(self.model, "decode_bucket_cap", lambda _: 32)(batch.rows)
             batch.kv_bucket = cap if batch.kv_bucket >= cap else ops.bucket_level(batch.kv_bucket)
         if not (self.use_graphs and self.graph_safe and batch.decode_only):
             return self.model.forward(batch, self.cache, logits_out)
