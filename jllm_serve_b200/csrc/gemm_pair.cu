@@ -106,6 +106,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(aligned + STAGES * STAGE_BYTES + STAGING_BYTES + 8 * (2 * STAGES + 4));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
     volatile int* parts_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 2);
+    const uint32_t fix_bar = bars + 8u * (2 * STAGES + 4) + 16u;   // parked parts arriving by bulk copy (behind the three words)
     uint8_t* staging = aligned + STAGES * STAGE_BYTES;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -160,6 +161,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             mbar_init(acc_full_bar(b), 1);
             mbar_init(acc_empty_bar(b), 8);   // one arrival per epilogue warp of both blocks
         }
+        mbar_init(fix_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -242,7 +244,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const int quad = warp & 3;
         const TileEpilogue<Tout> ep{out, ldo, M, N, accumulate, has_bias, swiglu, bias, bulk_out ? &map_out : nullptr};
         float* my_staging = reinterpret_cast<float*>(staging + quad * (bulk_out ? BULK_WARP_BYTES : STAGING_WARP_FLOATS * 4));
-        uint32_t local_tile = 0;
+        uint32_t local_tile = 0, fix_parity = 0;
         bool ok = true;
         Walk walk = first_unit();
         int tile, k_lo, k_hi;
@@ -311,6 +313,53 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (!*parts_flag) { ok = false; break; }
+            // Nothing follows this unit in this pair's work (always so when the product has fewer tiles than pairs): every
+            // product of the pair is done, so the ring of stages is idle, and the parked parts come into it by bulk copies,
+            // a stage's worth (64 columns of one part) each, as many pieces at a time as the ring holds with all their
+            // parts: 192 KB on their way instead of one load per thread and column, the adding in the same order.
+            const bool ring_idle = walk.at >= run_hi && (long long)pair + (long long)walk.i * pairs >= whole_tiles;
+            if (ring_idle && others <= STAGES) {
+                constexpr int PIECE = 64;
+                static_assert(PIECE * BM * 4 == STAGE_BYTES, "a piece of a parked part fills one stage");
+                const int per_round = STAGES / others;
+                for (int p0 = 0; ok && p0 < BN / PIECE; p0 += per_round) {
+                    const int p1 = min(BN / PIECE, p0 + per_round);
+                    if (warp == 2 && lane == 0) {
+                        // the parts were written by other blocks' ordinary stores (seen through the counter) and the ring
+                        // was read by this block's ordinary loads: both before the copies of the asynchronous proxy
+                        asm volatile("fence.proxy.async;" ::: "memory");
+                        mbar_expect_tx(fix_bar, (uint32_t)((p1 - p0) * others) * STAGE_BYTES);
+                        for (int pc = p0; pc < p1; ++pc)
+                            for (int q = 0; q < others; ++q)
+                                bulk_copy(base + (uint32_t)((pc - p0) * others + q) * STAGE_BYTES,
+                                          partials + (size_t)(blockIdx.x + 2 * (q + 1)) * BM * BN + (size_t)pc * PIECE * BM,
+                                          STAGE_BYTES, fix_bar);
+                    }
+                    if (!mbar_wait(fix_bar, fix_parity, abort_flag)) { ok = false; break; }
+                    fix_parity ^= 1u;
+#pragma unroll 1
+                    for (int pc = p0; pc < p1; ++pc)
+#pragma unroll 1
+                        for (int h = 0; h < PIECE; h += 32) {
+                            const int c0 = pc * PIECE + h;
+                            uint32_t v[32];
+                            tmem_ld_32x32b_x32(taddr + c0, v);
+                            tmem_ld_wait();
+                            for (int q = 0; q < others; ++q) {
+                                const float* src = reinterpret_cast<const float*>(aligned + (size_t)((pc - p0) * others + q) * STAGE_BYTES) +
+                                                   (size_t)h * BM + quad * 32 + lane;
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + src[(size_t)j * BM]);
+                            }
+                            if (n0 + c0 < N) ep.store(v, row0, lane, n0 + c0, whole, my_staging);
+                        }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");      // all have read the ring: the next round may overwrite it
+                }
+                if (!ok) break;
+                release();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                continue;
+            }
             const float* theirs = partials + (size_t)(blockIdx.x + 2) * BM * BN + quad * 32 + lane;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {

@@ -282,7 +282,7 @@ def gemm_workspace(key, floats: int = 8 << 20) -> torch.Tensor:
 
 def gemm_kernel_for(rows: int, out_features: int, in_features: int = 4096, rows_fit: bool = True,
                     tiles_fit: bool = True, sms: int = 148, pairs: int = 74) -> str:
-    """"rows", "swap", "tiles", "pair" or "" for a bfloat16 product of `rows` rows against a [out_features, in_features]
+    """"rows", "swap", "tiles", "pair", "pair-streamed" or "" for a bfloat16 product of `rows` rows against a [out_features, in_features]
     weight, given which kernels take its strides and alignment, the SMs and the pairs of them the device runs at a time."""
     # 16 or more rows against a wide matrix (gate_up): 128 or more 192-wide tcgen05 tiles stream it faster than the
     # weight-row kernel, whose blocks have half their loads in flight once they hold more than two token tiles
@@ -298,6 +298,11 @@ def gemm_kernel_for(rows: int, out_features: int, in_features: int = 4096, rows_
         return "rows"
     if not tiles_fit:
         return ""
+    # 257 to 512 rows against a matrix much longer than high (down): its few 256 x 256 tiles cut up over ALL pairs, the
+    # parts of a tile meeting in a workspace (8B shape, 384 rows: 49 us against 59 on one-SM tiles; 512 rows: 52 against
+    # 67; the shorter matrices lose that way, and above 512 rows the whole tiles are enough)
+    if pairs > 0 and tiles_fit and 256 < rows <= 512 and in_features >= 2 * out_features:
+        return "pair-streamed"
     # Many rows: two SMs to a 256 x 256 tile take in a third less per multiply-add than one SM with a 128 x 256 tile,
     # which is what bounds these products. It pays where its tiles keep three quarters of the pairs busy or more and its
     # rounds of tiles, each about a tenth shorter than a round of one-SM tiles of the same width, take less than the
@@ -326,6 +331,8 @@ def gemm_bf16(a, w, out, bias=None, accumulate=False, swiglu=False) -> None:
         return gemm_stream(a, w, out, bias, accumulate, swiglu=swiglu)
     if kernel == "pair":
         return gemm_pair(a, w, out, bias, accumulate, swiglu=swiglu)
+    if kernel == "pair-streamed":
+        return gemm_pair(a, w, out, bias, accumulate, swiglu=swiglu, stream_mode=1)
     if kernel == "tiles":
         return gemm_tcgen05(a, w, out, bias, accumulate, swiglu=swiglu)
     raise KernelError("the tensor-core matrix product is not built for this shape")

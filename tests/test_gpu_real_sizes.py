@@ -96,13 +96,16 @@ def test_bfloat16_follows_float32_far_into_a_long_prompt():
         assert s["worst_choice_gap_rel"] <= 1e-2, (name, s)
 
 
-def test_bfloat16_follows_float32_with_portions_of_some_two_hundred_rows():
-    """Steps of 129 to 256 rows (portions of 150 and 220 rows beside two decoding requests): the tokens are still one
-    N side of the weight-stream product, which takes the down product there, and up to 160 rows the others too."""
+def test_bfloat16_follows_float32_with_portions_of_some_hundred_rows():
+    """Steps of 129 to 512 rows (portions of 150, 220 and 440 rows beside two decoding requests). Up to 256 rows the
+    tokens are still one N side of the weight-stream product, which takes the down product there, and up to 160 rows
+    the others too; from 257 to 512 rows the down product's 256 x 256 tiles are cut up over all pairs of SMs."""
     from jllm_serve_b200.csrc import ops
     from jllm_serve_b200.precision_check import compare_precisions
     assert ops.gemm_kernel_for(222, 4096, 12288) == "swap" and ops.gemm_kernel_for(152, 6144, 4096) == "swap"
-    for portion in (150, 220):
+    if ops.resident_pairs() > 0:       # 442 rows: the down product's tiles cut up over all pairs
+        assert ops.gemm_kernel_for(442, 4096, 12288, pairs=ops.resident_pairs()) == "pair-streamed"
+    for portion in (150, 220, 440):
         got = compare_precisions(CONFIG, seed=9, prompt=2 * portion, tail=4, portion=portion)
         print(f"portions of {portion}, layers {CONFIG['num_hidden_layers']} of {QWEN3_8B_LAYERS}: {got}")
         for name in ("alone", "mixed"):

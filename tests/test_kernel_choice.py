@@ -15,7 +15,10 @@ def test_product_kernel_by_rows_and_shape():
     assert k(161, 6144, 4096) == "tiles" and k(161, 4096, 4096) == "tiles"      # above 160 rows its parked parts cost too much
     # ... except against matrices much longer than high (down), up to the 256 tokens of one tcgen05 N side
     assert k(64, 4096, 12288) == "swap" and k(128, 4096, 12288) == "swap" and k(256, 4096, 12288) == "swap"
-    assert k(257, 4096, 12288) == "tiles" and k(256, 5120, 17408) == "swap" and k(200, 24576, 4096) == "tiles"
+    assert k(256, 5120, 17408) == "swap" and k(200, 24576, 4096) == "tiles"
+    # 257 to 512 rows against such a matrix: its few 256 x 256 tiles cut up over all pairs
+    assert k(257, 4096, 12288) == "pair-streamed" and k(512, 5120, 17408) == "pair-streamed"
+    assert k(513, 4096, 12288) == "tiles" and k(400, 6144, 4096) == "tiles" and k(400, 4096, 12288, pairs=0) == "tiles"
     assert k(40, 4096, 4096) == "rows" and k(41, 4096, 4096) == "swap"         # O (34 MB): from 41 rows
     assert k(64, 24576, 4096) == "tiles"                                       # gate_up: whole tiles fill the SMs
     # many rows: two SMs to a 256 x 256 tile where such tiles keep the pairs busy in no more rounds than one-SM tiles
