@@ -294,6 +294,59 @@ def test_random_load_always_finishes(seed, row_quantum):
     assert cache.free_pages() == [24]
 
 
+@pytest.mark.parametrize("ahead", [False, True])
+@pytest.mark.parametrize("seed", range(6))
+def test_random_arrivals_and_cancels_keep_the_books(seed, ahead):
+    """Requests arrive while others run, some are cancelled where they stand (waiting, in the middle of their prompt,
+    decoding, with a row in a step that is in flight), the pool is tight; with and without planning a step ahead. After
+    every step the cache's books are in order; at the end every request has ended once, the cancelled ones with a
+    beginning of what they would have produced, the others with all of it, and every page is back."""
+    rng = random.Random(100 + seed)
+    s, cache = make(pages=20, page_size=4, budget=24, chunk=12, max_running=4, ctx=128, fill_portions=seed % 2 == 0)
+    plans = [(rng.randrange(1, 40), rng.randrange(1, 20)) for _ in range(30)]
+    pending, cancelled, inflight, steps = list(range(30)), set(), None, 0
+
+    def complete(plan):
+        # the fake model's token is the request's output length at the time its row is read
+        s.complete(plan, [len(p.request.output) for p in plan if p.wants_logits])
+
+    while pending or s.has_work() or inflight is not None:
+        for _ in range(min(len(pending), rng.randrange(0, 3))):
+            i = pending.pop(0)
+            s.add(Request(f"r{i}", [rng.randrange(50) for _ in range(plans[i][0])], SamplingParams.greedy_params(plans[i][1])))
+        live = [r.id for r in s.running + s.waiting]
+        if live and rng.random() < 0.15:
+            rid = rng.choice(live)
+            assert s.cancel(rid).finish_reason == "cancelled"
+            cancelled.add(rid)
+        plan = None
+        if inflight is not None and ahead:
+            plan = s.plan(inflight=inflight)
+        if plan is None:
+            if inflight is not None:
+                complete(inflight)
+                inflight = None
+            plan = s.plan()
+        s.take_ended()
+        if inflight is not None:
+            complete(inflight)
+        inflight = plan or None
+        if not ahead and inflight is not None:
+            complete(inflight)
+            inflight = None
+        cache.check()
+        steps += 1
+        assert steps < 5000
+    assert set(s.finished) == {f"r{i}" for i in range(30)} and cancelled
+    for i, (_, m) in enumerate(plans):
+        r = s.finished[f"r{i}"]
+        if r.id in cancelled:
+            assert r.finish_reason == "cancelled" and r.output == list(range(len(r.output))) and len(r.output) <= m
+        else:
+            assert r.finish_reason == "length" and r.output == list(range(m))
+    assert cache.free_pages() == [20] and not cache.requests
+
+
 # ---- settings and command line ------------------------------------------------------------------------------
 
 def test_settings_layers_aliases_and_errors(tmp_path):
