@@ -151,8 +151,9 @@ class Engine:
         sampled = self.sampler.fetch(ticket)
         now = time.perf_counter()
         for p in plan:
-            if p.wants_logits and self._times[p.request.id]["first"] is None:
-                self._times[p.request.id]["first"] = now
+            times = self._times.get(p.request.id)       # (None: cancelled while the step ran, its result taken already)
+            if p.wants_logits and times is not None and times["first"] is None:
+                times["first"] = now
         done = self.scheduler.complete(plan, sampled)
         for r in done:
             self._times[r.id]["end"] = now
