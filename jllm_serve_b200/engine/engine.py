@@ -20,7 +20,7 @@ from ..csrc import ops
 from ..sampling import RequestRng, Sampler, SamplingParams
 from .batch import Segment
 from .runner import ModelRunner
-from .scheduler import Request, Scheduler
+from .scheduler import FINISHED, Request, Scheduler
 
 
 @dataclass
@@ -151,7 +151,9 @@ class Engine:
         sampled = self.sampler.fetch(ticket)
         now = time.perf_counter()
         for p in plan:
-            times = self._times.get(p.request.id)       # (None: cancelled while the step ran, its result taken already)
+            if p.request.state == FINISHED:             # cancelled while the step ran (its result may be taken already)
+                continue
+            times = self._times.get(p.request.id)
             if p.wants_logits and times is not None and times["first"] is None:
                 times["first"] = now
         done = self.scheduler.complete(plan, sampled)
