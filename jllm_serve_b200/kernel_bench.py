@@ -26,6 +26,9 @@ def main() -> int:
     ap.add_argument("--repeat", type=int, default=20)
     ap.add_argument("--only", default="", help="run only the kernels whose name contains this")
     ap.add_argument("--eager", action="store_true", help="launch from the host call by call instead of replaying a graph")
+    ap.add_argument("--all-kernels", action="store_true",
+                    help="the products of the prefill step also on every product kernel that takes their shape, not only "
+                         "on the one the dispatch chooses")
     args = ap.parse_args()
 
     from .csrc import ops
@@ -69,7 +72,7 @@ def main() -> int:
     seg = torch.arange(M, dtype=torch.int32, device=dev)
     pos = torch.full((M,), ctx - 1, dtype=torch.int32, device=dev)
     scratch = torch.empty(2 << 20, device=dev)
-    how, n = ops.decode_plan(M, Hkv, max(1, min(32, ctx // 256, -(-296 // M))), H, hd, scratch)
+    how, n = ops.decode_plan(M, Hkv, max(1, min(32, ctx // 256, -(-ops.resident_blocks() // M))), H, hd, scratch)
     if how == "flat":
         case(f"decode attention (dealt out over {n} blocks)",
              lambda i: ops.attention_decode_flat(q, caches[i][0], caches[i][1], out, seg, pos, tables, M, H, Hkv, hd, page, 0,
@@ -106,11 +109,30 @@ def main() -> int:
     h_p = torch.empty(T, F, device=dev, dtype=bf)
     qkv_p = torch.empty(T, (H + 2 * Hkv) * hd, device=dev, dtype=bf)
     x_p = torch.randn(T, D, device=dev)
-    case("prefill gemm qkv", lambda i: ops.gemm_bf16(a_p, w_qkv[i], qkv_p), len(w_qkv), flops=2 * T * D * qkv_p.shape[1])
-    case("prefill gemm gate_up + swiglu", lambda i: ops.gemm_bf16(a_p, w_gu[i], h_p, swiglu=True), len(w_gu),
-         flops=2 * T * D * 2 * F)
-    case("prefill gemm down (+= residual)", lambda i: ops.gemm_bf16(h_p, w_down[i], x_p, None, True), len(w_down),
-         flops=2 * T * D * F)
+    products = [("qkv", a_p, w_qkv, qkv_p, False, False, 2 * T * D * qkv_p.shape[1]),
+                ("o (+= residual)", a_p, w_o, x_p, True, False, 2 * T * D * D),
+                ("gate_up + swiglu", a_p, w_gu, h_p, False, True, 2 * T * D * 2 * F),
+                ("down (+= residual)", h_p, w_down, x_p, True, False, 2 * T * D * F)]
+    pairs = ops.resident_pairs() if T > 128 else 0
+    for what, a_, ws_, out_, acc_, glu_, flops_ in products:
+        chosen = ops.gemm_kernel_for(T, ws_[0].rows, ws_[0].cols, T <= 64, True, ops.sm_count(), pairs)
+        case(f"prefill gemm {what} [{chosen}]",
+             lambda i, a_=a_, ws_=ws_, out_=out_, acc_=acc_, glu_=glu_: ops.gemm_bf16(a_, ws_[i], out_, None, acc_, glu_),
+             len(ws_), flops=flops_)
+        if not args.all_kernels:
+            continue
+        # every product kernel that takes this shape, side by side on the same packed weights
+        kernels = {"tiles": lambda i, a_=a_, ws_=ws_, out_=out_, acc_=acc_, glu_=glu_: ops.gemm_tcgen05(a_, ws_[i], out_, None, acc_, swiglu=glu_)}
+        if pairs > 0:
+            kernels["pair"] = lambda i, a_=a_, ws_=ws_, out_=out_, acc_=acc_, glu_=glu_: ops.gemm_pair(a_, ws_[i], out_, None, acc_, swiglu=glu_)
+            kernels["pair-streamed"] = lambda i, a_=a_, ws_=ws_, out_=out_, acc_=acc_, glu_=glu_: ops.gemm_pair(a_, ws_[i], out_, None, acc_, swiglu=glu_, stream_mode=1)
+        if T <= ops.SWAP_MAX_ROWS:
+            kernels["swap"] = lambda i, a_=a_, ws_=ws_, out_=out_, acc_=acc_, glu_=glu_: ops.gemm_stream(a_, ws_[i], out_, None, acc_, swiglu=glu_)
+        if T <= 64:
+            kernels["rows"] = lambda i, a_=a_, ws_=ws_, out_=out_, acc_=acc_, glu_=glu_: ops.gemm_small_m(a_, ws_[i], out_, None, acc_, swiglu=glu_)
+        for kernel, fn in kernels.items():
+            if kernel != chosen:
+                case(f"prefill gemm {what} on {kernel}", fn, len(ws_), flops=flops_)
     pp = T // page + 1
     kc, vc = torch.randn(pp, Hkv, page, hd, device=dev).to(bf), torch.randn(pp, Hkv, page, hd, device=dev).to(bf)
     tp = torch.arange(pp, dtype=torch.int32, device=dev).reshape(1, -1).contiguous()
